@@ -1,0 +1,363 @@
+#!/usr/bin/env python
+"""Benchmark of the causal linear-attention hot path: causal_dot_product forward+backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 2] [--mode fp32|mma]
+    python bench.py --impl reference ...      # the reference's CPU kernel on the host cores
+
+One "step" is one forward + backward of ``causal_dot_product`` over the (batch, head)
+units one GPU holds.  The default workload is configuration 2 (B8 H8 L4096 D=M=64, fp32,
+Q,K = elu(x)+1, V,G ~ N(0,1), seeded synthetic data).  With N > 1 every rank holds its own
+B=8 slice of a global batch of 8N (the (batch, head) units are independent, so there is no
+data-path collective): weak scaling.  Metric: Mtokens/s, tokens = batch * sequence length.
+
+Printed by rank 0: ONE JSON line.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "causal linear-attn fwd+bwd Mtokens/s"
+UNIT = "Mtokens/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 4, 5])
+    ap.add_argument("--mode", default=None, choices=["fp32", "mma"])
+    ap.add_argument("--L", type=int, default=None, help="override the sequence length")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def workload_name(cfg, shape):
+    return "config%d causal_dot_product fwd+bwd N%d H%d L%d D%d M%d %s" % (
+        cfg, shape["N"], shape["H"], shape["L"], shape["D"], shape["M"],
+        str(shape["dtype"]).replace("torch.", ""))
+
+
+# ------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arm (the reference's own OpenMP kernel, or the C port when it is not built)
+# ------------------------------------------------------------------------------------------
+def cpu_arm(Q, K, V, G, budget_s, min_steps=2, max_steps=1000, warmup=1):
+    """fwd+bwd of the CPU implementation on the host cores; returns (seconds per step,
+    kind, cores, steps timed)."""
+    from oracle import causal_oracle as orc
+    kind = "reference" if orc.reference_ext() is not None else "port"
+    Q, K, V, G = (t.float().contiguous() for t in (Q, K, V, G))
+    if kind == "reference":
+        def step():
+            orc.reference_forward(Q, K, V)
+            orc.reference_backward(Q, K, V, G)
+    else:
+        def step():
+            orc.c_forward(Q, K, V)
+            orc.c_backward(Q, K, V, G)
+    for _ in range(warmup):
+        step()
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < max_steps and (len(times) < min_steps or time.perf_counter() < t_end):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    cores = int(os.environ.get("OMP_NUM_THREADS", 0)) or os.cpu_count()
+    return statistics.median(times), kind, cores, len(times)
+
+
+def run_reference(args, shape, inputs, name):
+    Q, K, V, G = inputs
+    tokens = shape["N"] * shape["L"]
+    from oracle import causal_oracle as orc
+    kind = "reference" if orc.reference_ext() is not None else "port"
+    Qf, Kf, Vf, Gf = (t.float().contiguous() for t in (Q, K, V, G))
+
+    def step():
+        if kind == "reference":
+            orc.reference_forward(Qf, Kf, Vf)
+            orc.reference_backward(Qf, Kf, Vf, Gf)
+        else:
+            orc.c_forward(Qf, Kf, Vf)
+            orc.c_backward(Qf, Kf, Vf, Gf)
+
+    for _ in range(max(1, min(args.warmup, 3))):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    cores = int(os.environ.get("OMP_NUM_THREADS", 0)) or os.cpu_count()
+    value = tokens / dt / 1e6
+    sample = "%d steps of the full workload (%s), fp32, all (batch, head) units" % (args.steps, name)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
+        "config": {"workload": name, "device": "host CPU",
+                   "parallel_units": shape["N"] * shape["H"]},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+
+    from fast_transformers_b200 import workloads
+    shape = dict(workloads.SHAPES[args.config])
+    if args.L:
+        shape["L"] = args.L
+    name = workload_name(args.config, shape)
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        inputs = workloads.make_inputs(args.config, scale_L=args.L)
+        run_reference(args, shape, inputs, name)
+        return 0
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path")
+    import fast_transformers_b200 as ftb
+    from fast_transformers_b200 import _native
+    from fast_transformers_b200.causal_product import causal_dot_product
+    lib = _native.lib()   # raises if the native library is missing
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    mode = args.mode or ftb.get_mode()
+    # every rank draws its own slice of the global batch (trial = rank)
+    Q, K, V, G = workloads.make_inputs(args.config, trial=rank, scale_L=args.L)
+    pinned = [t.pin_memory() for t in (Q, K, V, G)]
+    Qd, Kd, Vd, Gd = (t.to(dev) for t in (Q, K, V, G))
+    Qd.requires_grad_(True), Kd.requires_grad_(True), Vd.requires_grad_(True)
+    tokens = shape["N"] * shape["L"]
+    token_heads = tokens * shape["H"]
+    esize = Qd.element_size()
+
+    def step():
+        Qd.grad = Kd.grad = Vd.grad = None
+        with ftb.mode(mode):
+            out = causal_dot_product(Qd, Kd, Vd)
+            out.backward(Gd)
+        return out
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = lib.ftb_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    launches = lib.ftb_launch_count() - launches0
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    value = world * tokens / (ms_step * 1e-3) / 1e6
+
+    # ---- per-kernel device time (instrumented pass, after the timed region) --------------
+    lib.ftb_timing_enable(1)
+    for _ in range(args.steps):
+        # the backward pass runs on an autograd thread; call the native functions directly
+        # so every launch is made (and recorded) by this thread
+        from fast_transformers_b200.causal_product import (causal_dot_backward_cuda,
+                                                           causal_dot_product_cuda)
+        o = torch.empty(shape["N"], shape["H"], shape["L"], shape["M"], device=dev, dtype=Qd.dtype)
+        gq, gk, gv = torch.empty_like(Qd), torch.empty_like(Kd), torch.empty_like(Vd)
+        causal_dot_product_cuda(Qd.data, Kd.data, Vd.data, o, mode)
+        causal_dot_backward_cuda(Qd.data, Kd.data, Vd.data, Gd, gq, gk, gv, mode)
+    kinds = _native.timing_read()
+    lib.ftb_timing_enable(0)
+    peaks = {}
+    ppath = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(ppath):
+        peaks = json.load(open(ppath))
+    peak_gbs = peaks.get("hbm_gbs", 6650.0)
+    peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+    total_kernel_ms = sum(v[0] for v in kinds.values()) or 1.0
+    top = max(kinds.items(), key=lambda kv: kv[1][0]) if kinds else ("none", (0.0, 0))
+    top_name, (top_ms, top_n) = top
+    # algorithmic bytes one launch of the dominant kernel moves: every launch of a scan
+    # kernel reads three operand tensors and writes one (forward: Q,K,V -> out, and the three
+    # gradient scans likewise); the fused tensor-core kernels move the whole pass.
+    D, M = shape["D"], shape["M"]
+    per_launch_elems = {
+        "simt_scan": (2 * D + 2 * M),               # averaged over the four role permutations
+        "mma_fwd": (2 * D + 2 * M),
+        "mma_bwd": (4 * D + 3 * M),
+        "state_sum": (D + M),
+        "mma_state": (D + M),
+    }.get(top_name, 0)
+    alg_bytes_launch = per_launch_elems * esize * token_heads
+    avg_ms = top_ms / top_n if top_n else 0.0
+    achieved = alg_bytes_launch / (avg_ms * 1e-3) / 1e9 if avg_ms else 0.0
+    step_alg_bytes = workloads.algorithmic_bytes(D, M, esize) * token_heads
+    roofline = {
+        "bound": "hbm", "kernel": top_name, "achieved": achieved, "peak": peak_gbs,
+        "unit": "GB/s", "frac": achieved / peak_gbs if peak_gbs else None,
+        "peak_source": peak_src, "traffic": None,
+        "avg_launch_ms": avg_ms, "share_of_kernel_time": top_ms / total_kernel_ms,
+        "kernels": {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
+                    for k, v in kinds.items()},
+        "whole_step": {"algorithmic_bytes": step_alg_bytes,
+                       "achieved_GBps": step_alg_bytes / (ms_step * 1e-3) / 1e9,
+                       "frac_of_hbm_peak": step_alg_bytes / (ms_step * 1e-3) / 1e9 / peak_gbs,
+                       "achieved_TFLOPs": workloads.algorithmic_flops(D, M) * token_heads /
+                       (ms_step * 1e-3) / 1e12},
+    }
+
+    # ---- end to end through the public API with host buffers ------------------------------
+    e2e = None
+    if not args.no_e2e:
+        host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (V, Q, K, V)]
+        dq = [torch.empty_like(t, device=dev) for t in (Q, K, V, G)]
+
+        def e2e_step():
+            for d, h in zip(dq, pinned):
+                d.copy_(h, non_blocking=True)
+            q, k, v = (d.detach().requires_grad_(True) for d in dq[:3])
+            with ftb.mode(mode):
+                out = causal_dot_product(q, k, v)
+                out.backward(dq[3])
+            for h, d in zip(host_out, (out.detach(), q.grad, k.grad, v.grad)):
+                h.copy_(d, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        e0.record()
+        n_e2e = max(3, min(args.steps, 10))
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item() / n_e2e
+        nbytes = sum(x.numel() * x.element_size() for x in pinned)
+        e2e = {"value": world * tokens / (e2e_ms * 1e-3) / 1e6, "unit": UNIT,
+               "h2d_bytes_per_step": nbytes,
+               "d2h_bytes_per_step": sum(h.numel() * h.element_size() for h in host_out),
+               "ms_per_step": e2e_ms, "steps": n_e2e,
+               "api": "fast_transformers_b200.causal_product.causal_dot_product (autograd) with "
+                      "pinned host tensors copied in and all four results copied out"}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sec, kind, cores, nst = cpu_arm(Q, K, V, G, budget_s=12.0)
+        cpu_baseline = {"value": tokens / sec / 1e6, "unit": UNIT, "cores": cores, "kind": kind,
+                        "sample": "%d timed steps of the full workload (%s) after 1 warm-up, "
+                                  "median" % (nst, name), "ms_per_step": sec * 1e3}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": {"fp32": "f32", "mma": "tf32" if esize == 4 else "bf16"}[mode],
+            "data": "synthetic (seeded)",
+            "config": {"workload": name, "mode": mode, "io_dtype": str(Qd.dtype).replace("torch.", ""),
+                       "global_batch": shape["N"] * world, "sharding": "(batch, head) units per rank, no collective",
+                       "l2": "inputs+outputs per step (%.0f MB) exceed the 126 MB L2; no flush" %
+                             (step_alg_bytes / 1e6)},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "gpu_launches": int(launches), "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

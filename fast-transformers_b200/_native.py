@@ -1,0 +1,95 @@
+"""ctypes binding of ``libftb200.so`` (the C ABI declared in ``include/ftb200.h``).
+
+The library is looked up next to this file.  It is never rebuilt or replaced silently at
+call time: if it is missing, ``lib()`` raises ``RuntimeError`` telling how to build it
+(``python fast-transformers_b200/build.py``).  There is no other implementation to fall
+back to.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libftb200.so")
+
+OK, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE, ERR_CUDA, ERR_TIMEOUT, ERR_INVALID = range(7)
+F32, BF16 = 0, 1
+MODE_FP32_SIMT, MODE_MMA = 0, 1
+MODE_IDS = {"fp32": MODE_FP32_SIMT, "mma": MODE_MMA}
+
+# every symbol include/ftb200.h declares
+EXPORTS = (
+    "ftb_version", "ftb_status_string", "ftb_last_cuda_error", "ftb_causal_workspace_bytes",
+    "ftb_causal_dot_product", "ftb_causal_dot_backward", "ftb_causal_state_sum",
+    "ftb_launch_count", "ftb_timing_enable", "ftb_timing_read",
+)
+KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
+                "reserved6", "reserved7")
+
+_lib = None
+_i64, _vp, _int, _sz = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+_i64p = ctypes.POINTER(ctypes.c_int64)
+
+
+class NativeError(RuntimeError):
+    """A non-zero status returned by the native library."""
+
+    def __init__(self, status, message):
+        super().__init__(message)
+        self.status = status
+
+
+def lib():
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            "native library %s not found; build it with `python fast-transformers_b200/build.py` "
+            "(needs nvcc 12.9). There is no fallback implementation." % LIB_PATH)
+    L = ctypes.CDLL(LIB_PATH)
+    L.ftb_version.restype = _int
+    L.ftb_status_string.restype = ctypes.c_char_p
+    L.ftb_status_string.argtypes = [_int]
+    L.ftb_last_cuda_error.restype = _int
+    L.ftb_causal_workspace_bytes.restype = _sz
+    L.ftb_causal_workspace_bytes.argtypes = [_i64] * 5 + [_int] * 4
+    L.ftb_causal_dot_product.restype = _int
+    L.ftb_causal_dot_product.argtypes = (
+        [_vp] * 4 + [_i64] * 5 + [_i64p] * 4 + [_int, _int, _vp, _vp, _vp, _sz, _vp])
+    L.ftb_causal_dot_backward.restype = _int
+    L.ftb_causal_dot_backward.argtypes = (
+        [_vp] * 7 + [_i64] * 5 + [_i64p] * 7 + [_int, _int, _vp, _vp, _vp, _sz, _vp])
+    L.ftb_causal_state_sum.restype = _int
+    L.ftb_causal_state_sum.argtypes = (
+        [_vp] * 3 + [_i64] * 5 + [_i64p] * 2 + [_int, _int, _vp, _sz, _vp])
+    L.ftb_launch_count.restype = ctypes.c_uint64
+    L.ftb_timing_enable.restype = None
+    L.ftb_timing_enable.argtypes = [_int]
+    L.ftb_timing_read.restype = _int
+    L.ftb_timing_read.argtypes = [ctypes.POINTER(ctypes.c_float), ctypes.POINTER(_int), _int]
+    _lib = L
+    return L
+
+
+def timing_read():
+    """{kernel kind: (milliseconds, launches)} recorded since ``ftb_timing_enable(1)``."""
+    n = len(KERNEL_KINDS)
+    ms = (ctypes.c_float * n)()
+    cnt = (_int * n)()
+    check(lib().ftb_timing_read(ms, cnt, n), "ftb_timing_read")
+    return {KERNEL_KINDS[i]: (ms[i], cnt[i]) for i in range(n) if cnt[i]}
+
+
+def strides3(t):
+    s = t.stride()
+    return (ctypes.c_int64 * 3)(s[0], s[1], s[2])
+
+
+def check(status, what):
+    if status == OK:
+        return
+    L = lib()
+    msg = L.ftb_status_string(status).decode()
+    if status == ERR_CUDA:
+        msg += " (cudaError %d)" % L.ftb_last_cuda_error()
+    raise NativeError(status, "%s failed: %s" % (what, msg))

@@ -1,0 +1,96 @@
+"""Causally masked linear attention, O(L D M) per head.
+
+Mirror of ``fast_transformers/attention/causal_linear_attention.py``: ``causal_linear``
+(:19-24), ``CausalLinearAttention`` (:27-104) and its ``"causal-linear"`` registry entry
+with the same parameter tuple (:109-116).
+
+    Q = phi(queries); K = phi(keys) * key_length_mask
+    Z_i = 1 / (Q_i . sum_{j<=i} K_j + eps)
+    out_i = Z_i * Q_i . sum_{j<=i} K_j^T V_j
+
+What differs from the reference is data movement only: the kernels take (N, L, H, dim)
+storage through strides, so the four permute+contiguous copies of ``causal_linear`` are
+views here, and the normaliser comes out of the same kernel launch as the product (V is
+extended by a column of ones, whose output column is Q_i . cumsum(K)_i).
+"""
+import torch
+from torch.nn import Module
+
+from ..attention_registry import (AttentionRegistry, Callable, EventDispatcherInstance, Int,
+                                  Optional)
+from ..causal_product import causal_dot_product
+from ..events import EventDispatcher
+from ..feature_maps import elu_feature_map
+
+
+def causal_linear(Q, K, V):
+    """(N, L, H, dim) in, (N, L, H, M) out.  The permutes are views: the kernels read and
+    write the (N, L, H, dim) storage directly through strides."""
+    out = causal_dot_product(Q.permute(0, 2, 1, 3), K.permute(0, 2, 1, 3), V.permute(0, 2, 1, 3))
+    return out.permute(0, 2, 1, 3)
+
+
+class CausalLinearAttention(Module):
+    """Arguments (unchanged from the reference)
+    ---------
+        query_dimensions: int, the dimensionality of queries and keys per head
+        feature_map: callable, a FACTORY called with ``query_dimensions`` that returns the
+                     feature map (default: elu(x)+1)
+        eps: float, added to the denominator (default: 1e-6)
+        event_dispatcher: str or EventDispatcher instance (default: the global dispatcher)
+    """
+
+    def __init__(self, query_dimensions, feature_map=None, eps=1e-6, event_dispatcher=""):
+        super().__init__()
+        self.feature_map = (feature_map(query_dimensions) if feature_map
+                            else elu_feature_map(query_dimensions))
+        self.eps = eps
+        self.event_dispatcher = EventDispatcher.get(event_dispatcher)
+
+    def _make_sizes_compatible(self, Q, K):
+        """Slice K to L rows, or pad it with zero rows, when L != S (:57-69)."""
+        N, L, H, E = Q.shape
+        S = K.shape[1]
+        if L == S:
+            return Q, K
+        if L < S:
+            return Q, K[:, :L, :, :]
+        return Q, torch.cat([K, K.new_zeros(N, L - S, H, E)], dim=1)
+
+    def forward(self, queries, keys, values, attn_mask, query_lengths, key_lengths):
+        self.feature_map.new_feature_map(queries.device)
+        Q = self.feature_map.forward_queries(queries)
+        K = self.feature_map.forward_keys(keys)
+
+        if not attn_mask.lower_triangular:
+            raise RuntimeError("CausalLinearAttention only supports full lower triangular masks")
+        K = K * key_lengths.float_matrix[:, :, None, None]
+        Q, K = self._make_sizes_compatible(Q, K)
+
+        # Bring V to L rows as well.  The reference leaves V as it is (for L > S its kernel
+        # then reads past the S rows of V, multiplied by zero keys); explicit rows give the
+        # same result without touching memory that is not V's.
+        N, L, H, _ = Q.shape
+        S = values.shape[1]
+        if S > L:
+            values = values[:, :L]
+        elif S < L:
+            values = torch.cat([values, values.new_zeros(N, L - S, H, values.shape[3])], dim=1)
+
+        # One extra value column of ones: its output column is Q_i . sum_{j<=i} K_j, the
+        # denominator, so product and normaliser share one pass over Q and K.
+        M = values.shape[3]
+        Vx = torch.cat([values, values.new_ones(N, L, H, 1)], dim=-1)
+        out = causal_linear(Q, K, Vx)
+        Z = 1 / (out[..., M] + self.eps)
+        return (out[..., :M] * Z[..., None]).contiguous()
+
+
+AttentionRegistry.register(
+    "causal-linear", CausalLinearAttention,
+    [
+        ("query_dimensions", Int),
+        ("feature_map", Optional(Callable)),
+        ("event_dispatcher", Optional(EventDispatcherInstance, ""))
+    ]
+)

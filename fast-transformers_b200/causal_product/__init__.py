@@ -1,0 +1,208 @@
+"""Causal dot product ``V'_i = Q_i . sum_{j<=i} K_j^T V_j`` on B200.
+
+Mirror of ``fast_transformers/causal_product/__init__.py``: the same autograd Function
+(``CausalDotProduct`` with class-level per-device tables ``dot`` / ``dot_backward``, :20-30),
+the same alias ``causal_dot_product = CausalDotProduct.apply`` (:78) and native functions
+with the reference's in-place signatures (``causal_product_cuda.cu:1471-1483``):
+
+    causal_dot_product_cuda(queries, keys, values, product) -> None
+    causal_dot_backward_cuda(queries, keys, values, grad_out, grad_q, grad_k, grad_v) -> None
+
+Differences, all deliberate: there is no CPU entry (``dot["cpu"]`` is None and CPU tensors
+raise -- this package has no CPU path); kernels run on torch's current stream instead of
+the legacy default stream; outputs need not be zero on entry; bf16 tensors are accepted in
+addition to fp32 (bf16 in, bf16 out, fp32 state).
+"""
+import ctypes
+
+import torch
+
+from .. import _native
+from ..settings import get_mode
+
+_DTYPES = {torch.float32: _native.F32, torch.bfloat16: _native.BF16}
+
+
+def _dtype_id(t):
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        # the reference raises the same kind of error from accessor<float>
+        raise RuntimeError("expected scalar type Float (or BFloat16) but found %s" % t.dtype)
+
+
+def _check_cuda(*ts):
+    dev = ts[0].device
+    for t in ts:
+        if t.device.type != "cuda":
+            raise RuntimeError(
+                "fast_transformers_b200 runs on CUDA (sm_100a) only; got a %s tensor. "
+                "There is no CPU implementation." % t.device.type)
+        if t.device != dev:
+            raise RuntimeError("all tensors must be on the same device")
+        if t.dim() != 4:
+            raise RuntimeError("expected 4-dimensional (N, H, L, dim) tensors")
+    return dev
+
+
+def _rowmajor(t):
+    """The kernels need a contiguous last dimension (the reference asserts stride(3)==1)."""
+    return t if (t.shape[3] <= 1 or t.stride(3) == 1) else t.contiguous()
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _workspace(nbytes, device):
+    if nbytes == 0:
+        return None, 0
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    return ws, nbytes
+
+
+def _mode_id(mode):
+    return _native.MODE_IDS[mode or get_mode()]
+
+
+def _state_ok(s, N, H, D, M, dev, name):
+    if s is None:
+        return None
+    if s.dtype != torch.float32 or s.shape != (N, H, D, M) or s.device != dev:
+        raise RuntimeError("%s must be a float32 (N, H, D, M) tensor on the inputs' device" % name)
+    return s.contiguous()
+
+
+def causal_dot_product_cuda(queries, keys, values, product, mode=None, initial_state=None,
+                            final_state=None):
+    """Fill ``product`` (N, H, L, M) in place -- the reference's native forward signature
+    (``causal_product_cuda.cu:1273-1276``), plus optional fp32 states (N, H, D, M)."""
+    dev = _check_cuda(queries, keys, values, product)
+    dt = _dtype_id(queries)
+    for t in (keys, values, product):
+        if t.dtype != queries.dtype:
+            raise RuntimeError("expected scalar type %s but found %s" % (queries.dtype, t.dtype))
+    N, H, L, D = queries.shape
+    M = values.shape[3]
+    if keys.shape != (N, H, L, D) or values.shape[:3] != (N, H, L) or \
+            product.shape != (N, H, L, M):
+        raise RuntimeError("shape mismatch between queries, keys, values and product")
+    if product.shape[3] > 1 and product.stride(3) != 1:
+        raise RuntimeError("product must have a contiguous last dimension")
+    q, k, v = _rowmajor(queries), _rowmajor(keys), _rowmajor(values)
+    initial_state = _state_ok(initial_state, N, H, D, M, dev, "initial_state")
+    if final_state is not None and (final_state.dtype != torch.float32 or
+                                    final_state.shape != (N, H, D, M) or
+                                    not final_state.is_contiguous()):
+        raise RuntimeError("final_state must be a contiguous float32 (N, H, D, M) tensor")
+    L_ = _native.lib()
+    m = _mode_id(mode)
+    with torch.cuda.device(dev):
+        nbytes = L_.ftb_causal_workspace_bytes(N, H, L, D, M, dt, m, 0, int(final_state is not None))
+        ws, nbytes = _workspace(nbytes, dev)
+        st = L_.ftb_causal_dot_product(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(product), N, H, L, D, M,
+            _native.strides3(q), _native.strides3(k), _native.strides3(v),
+            _native.strides3(product), dt, m, _ptr(initial_state), _ptr(final_state),
+            _ptr(ws), nbytes, ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    _native.check(st, "ftb_causal_dot_product")
+
+
+def causal_dot_backward_cuda(queries, keys, values, grad_out, grad_queries, grad_keys,
+                             grad_values, mode=None, initial_state=None,
+                             initial_grad_state=None):
+    """Fill the three gradients in place -- the reference's native backward signature
+    (``causal_product_cuda.cu:1438-1444``).  ``grad_out`` may be any view (expanded,
+    permuted); it is made row-contiguous only if its last stride is not 1."""
+    dev = _check_cuda(queries, keys, values, grad_out, grad_queries, grad_keys, grad_values)
+    dt = _dtype_id(queries)
+    N, H, L, D = queries.shape
+    M = values.shape[3]
+    if grad_out.dtype != queries.dtype:
+        grad_out = grad_out.to(queries.dtype)
+    if grad_out.shape != (N, H, L, M):
+        raise RuntimeError("grad_out has the wrong shape")
+    q, k, v, g = (_rowmajor(t) for t in (queries, keys, values, grad_out))
+    for t in (grad_queries, grad_keys, grad_values):
+        if t.dtype != queries.dtype or (t.shape[3] > 1 and t.stride(3) != 1):
+            raise RuntimeError("gradient buffers must match the input dtype and be row-contiguous")
+    initial_state = _state_ok(initial_state, N, H, D, M, dev, "initial_state")
+    initial_grad_state = _state_ok(initial_grad_state, N, H, D, M, dev, "initial_grad_state")
+    L_ = _native.lib()
+    m = _mode_id(mode)
+    with torch.cuda.device(dev):
+        nbytes = L_.ftb_causal_workspace_bytes(N, H, L, D, M, dt, m, 1, 0)
+        ws, nbytes = _workspace(nbytes, dev)
+        st = L_.ftb_causal_dot_backward(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(grad_queries), _ptr(grad_keys),
+            _ptr(grad_values), N, H, L, D, M,
+            _native.strides3(q), _native.strides3(k), _native.strides3(v), _native.strides3(g),
+            _native.strides3(grad_queries), _native.strides3(grad_keys),
+            _native.strides3(grad_values), dt, m, _ptr(initial_state),
+            _ptr(initial_grad_state), _ptr(ws), nbytes,
+            ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    _native.check(st, "ftb_causal_dot_backward")
+
+
+def causal_state_sum(x, y, mode=None):
+    """``sum_l x[n,h,l,:] (x) y[n,h,l,:]`` as a float32 (N, H, D, M) tensor: the state a
+    range of positions contributes to the ranges after it (x=K, y=V) or before it
+    (x=Q, y=grad_out)."""
+    dev = _check_cuda(x, y)
+    dt = _dtype_id(x)
+    if y.dtype != x.dtype:
+        raise RuntimeError("expected scalar type %s but found %s" % (x.dtype, y.dtype))
+    N, H, L, D = x.shape
+    M = y.shape[3]
+    x, y = _rowmajor(x), _rowmajor(y)
+    state = torch.empty(N, H, D, M, dtype=torch.float32, device=dev)
+    L_ = _native.lib()
+    m = _mode_id(mode)
+    with torch.cuda.device(dev):
+        nbytes = L_.ftb_causal_workspace_bytes(N, H, L, D, M, dt, m, 0, 1)
+        ws, nbytes = _workspace(nbytes, dev)
+        st = L_.ftb_causal_state_sum(
+            _ptr(x), _ptr(y), _ptr(state), N, H, L, D, M, _native.strides3(x),
+            _native.strides3(y), dt, m, _ptr(ws), nbytes,
+            ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    _native.check(st, "ftb_causal_state_sum")
+    return state
+
+
+def _no_cpu(*args, **kwargs):
+    raise RuntimeError("fast_transformers_b200 has no CPU implementation of causal_dot_product; "
+                       "move the tensors to a CUDA (B200) device")
+
+
+class CausalDotProduct(torch.autograd.Function):
+    """Compute the weighted sum of values but attending only to previous values.
+
+    Same contract as ``fast_transformers.causal_product.CausalDotProduct`` (:20-74): saves
+    only Q, K, V; allocates the outputs here and lets the native function fill them."""
+    dot = {"cpu": _no_cpu, "cuda": causal_dot_product_cuda}
+    dot_backward = {"cpu": _no_cpu, "cuda": causal_dot_backward_cuda}
+
+    @staticmethod
+    def forward(ctx, Q, K, V):
+        ctx.save_for_backward(Q, K, V)
+        ctx.mode = get_mode()
+        N, H, L, _ = Q.shape
+        M = V.shape[3]
+        # the reference allocates zeros (its fallback kernels accumulate); ours overwrite
+        product = torch.empty((N, H, L, M), device=Q.device, dtype=Q.dtype)
+        CausalDotProduct.dot[Q.device.type](Q.data, K.data, V.data, product, ctx.mode)
+        return product
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        Q, K, V = ctx.saved_tensors
+        grad_Q = torch.empty(Q.shape, device=Q.device, dtype=Q.dtype)
+        grad_K = torch.empty(K.shape, device=K.device, dtype=K.dtype)
+        grad_V = torch.empty(V.shape, device=V.device, dtype=V.dtype)
+        CausalDotProduct.dot_backward[Q.device.type](
+            Q.data, K.data, V.data, grad_out, grad_Q, grad_K, grad_V, ctx.mode)
+        return grad_Q, grad_K, grad_V
+
+
+# Alias the autograd functions to python style snake case naming
+causal_dot_product = CausalDotProduct.apply

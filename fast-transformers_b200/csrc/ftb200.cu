@@ -1,0 +1,377 @@
+// C ABI of the B200 causal linear-attention kernels (see include/ftb200.h for the contract
+// and for the reference functions each entry point replaces).
+#include "ftb200.h"
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <vector>
+
+#include "simt_scan.cuh"
+
+namespace ftb {
+
+static thread_local int g_last_cuda_error = 0;
+
+static inline int cuda_fail(cudaError_t e) {
+    g_last_cuda_error = (int)e;
+    return FTB_ERR_CUDA;
+}
+#define FTB_CUDA(call)                                   \
+    do {                                                 \
+        cudaError_t e__ = (call);                        \
+        if (e__ != cudaSuccess) return cuda_fail(e__);   \
+    } while (0)
+
+// ---- launch accounting --------------------------------------------------------------------
+// A process-wide count of kernel launches, and an optional per-thread recorder that brackets
+// every launch with CUDA events on the launching stream so a caller can attribute device
+// time to kernel kinds (FTB_KERNEL_*).  Off by default; it changes nothing else.
+static std::atomic<uint64_t> g_launches{0};
+
+struct TimedSpan {
+    int kind;
+    cudaEvent_t beg, end;
+};
+static thread_local bool g_timing = false;
+static thread_local std::vector<TimedSpan> g_spans;
+
+struct LaunchScope {
+    cudaStream_t st;
+    cudaEvent_t end = nullptr;
+    LaunchScope(int kind, cudaStream_t s) : st(s) {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if (!g_timing) return;
+        TimedSpan sp;
+        sp.kind = kind;
+        if (cudaEventCreate(&sp.beg) != cudaSuccess) return;
+        if (cudaEventCreate(&sp.end) != cudaSuccess) {
+            cudaEventDestroy(sp.beg);
+            return;
+        }
+        cudaEventRecord(sp.beg, st);
+        end = sp.end;
+        g_spans.push_back(sp);
+    }
+    ~LaunchScope() {
+        if (end) cudaEventRecord(end, st);
+    }
+};
+
+// ---- segment plan (pure function of the shape, so the workspace query needs no device) --
+struct Plan {
+    int64_t seg_len;
+    int nseg;
+};
+
+constexpr int64_t kTargetCtas = 148 * 4;
+constexpr int64_t kMinSegRows = 4 * CH;
+constexpr int kSimtMaxDim = 512;
+
+static Plan simt_plan(int64_t BH, int64_t L) {
+    Plan p;
+    if (L <= 0 || BH <= 0) {
+        p.seg_len = kMinSegRows;
+        p.nseg = 1;
+        return p;
+    }
+    int64_t want = (kTargetCtas + BH - 1) / BH;
+    if (want < 1) want = 1;
+    int64_t len = (L + want - 1) / want;
+    len = (len + CH - 1) / CH * CH;
+    if (len < kMinSegRows) len = kMinSegRows;
+    p.seg_len = len;
+    p.nseg = (int)((L + len - 1) / len);
+    return p;
+}
+
+static inline Strides3 S3(const int64_t *s) { return Strides3{s[0], s[1], s[2]}; }
+
+static inline bool vec_ok(const void *ptr, const int64_t *s, int dtype) {
+    uintptr_t a = (uintptr_t)ptr;
+    size_t bytes = dtype == FTB_F32 ? 16 : 8;
+    return (a % bytes == 0) && (s[0] % 4 == 0) && (s[1] % 4 == 0) && (s[2] % 4 == 0);
+}
+
+// ---- launches ---------------------------------------------------------------------------
+static int launch_state_sum(const void *x, const void *y, const int64_t *xs, const int64_t *ys,
+                            int64_t N, int64_t H, int64_t L, int D, int M, int dtype, Plan pl,
+                            float *states, cudaStream_t st) {
+    StateSumArgs a;
+    a.x = x; a.y = y; a.sx = S3(xs); a.sy = S3(ys);
+    a.H = (int)H; a.L = L; a.D = D; a.M = M;
+    a.seg_len = pl.seg_len; a.nseg = pl.nseg; a.states = states;
+    a.vx = vec_ok(x, xs, dtype); a.vy = vec_ok(y, ys, dtype);
+    int64_t blocks = N * H * pl.nseg * ((D + KT - 1) / KT) * ((M + NC - 1) / NC);
+    if (blocks <= 0) return FTB_OK;
+    if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
+    LaunchScope scope(FTB_KERNEL_STATE_SUM, st);
+    if (dtype == FTB_F32)
+        simt_state_sum_kernel<float><<<(unsigned)blocks, NTHR, 0, st>>>(a);
+    else
+        simt_state_sum_kernel<__nv_bfloat16><<<(unsigned)blocks, NTHR, 0, st>>>(a);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+
+static int launch_prefix(float *states, const float *init, float *total, int64_t BH, int nseg,
+                         int64_t DM, int reverse, cudaStream_t st) {
+    int64_t n = BH * DM;
+    if (n <= 0) return FTB_OK;
+    int64_t blocks = (n + 255) / 256;
+    LaunchScope scope(FTB_KERNEL_STATE_PREFIX, st);
+    state_prefix_kernel<<<(unsigned)blocks, 256, 0, st>>>(states, init, total, BH, nseg, DM, reverse);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+
+template <typename TI, typename TO>
+static int launch_scan_t(const ScanArgs &a, int64_t blocks, size_t smem, cudaStream_t st) {
+    if (smem > 48 * 1024)
+        FTB_CUDA(cudaFuncSetAttribute(simt_scan_kernel<TI, TO>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LaunchScope scope(FTB_KERNEL_SIMT_SCAN, st);
+    simt_scan_kernel<TI, TO><<<(unsigned)blocks, NTHR, smem, st>>>(a);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+
+static int launch_scan(const void *a, const void *b, const void *c, void *out, const int64_t *as,
+                       const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N,
+                       int64_t H, int64_t L, int Da, int Dc, int dtype, Plan pl,
+                       const float *states, int nseg_states, int canon_is_DaDc, int reverse,
+                       cudaStream_t st) {
+    ScanArgs p;
+    p.a = a; p.b = b; p.c = c; p.out = out;
+    p.sa = S3(as); p.sb = S3(bs); p.sc = S3(cs); p.so = S3(os);
+    p.H = (int)H; p.L = L; p.Da = Da; p.Dc = Dc;
+    p.seg_len = pl.seg_len; p.nseg = pl.nseg;
+    p.states = states; p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse;
+    p.va = vec_ok(a, as, dtype); p.vb = vec_ok(b, bs, dtype);
+    p.vc = vec_ok(c, cs, dtype); p.vo = vec_ok(out, os, dtype);
+    (void)nseg_states;
+    int64_t blocks = N * H * pl.nseg * ((Dc + NC - 1) / NC);
+    if (blocks <= 0) return FTB_OK;
+    if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
+    size_t smem = scan_smem_bytes(Da);
+    if (dtype == FTB_F32) return launch_scan_t<float, float>(p, blocks, smem, st);
+    return launch_scan_t<__nv_bfloat16, __nv_bfloat16>(p, blocks, smem, st);
+}
+
+static int check_common(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M, int dtype, int mode) {
+    if (N < 0 || H < 0 || L < 0 || D < 0 || M < 0) return FTB_ERR_INVALID;
+    if (dtype != FTB_F32 && dtype != FTB_BF16) return FTB_ERR_INVALID;
+    if (mode != FTB_MODE_FP32_SIMT && mode != FTB_MODE_MMA) return FTB_ERR_INVALID;
+    if (mode == FTB_MODE_FP32_SIMT && (D > kSimtMaxDim || M > kSimtMaxDim)) return FTB_ERR_UNSUPPORTED;
+    if (mode == FTB_MODE_MMA) return FTB_ERR_UNSUPPORTED;
+    return FTB_OK;
+}
+
+static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+}  // namespace ftb
+
+using namespace ftb;
+
+extern "C" {
+
+int ftb_version(void) { return 1000; }
+
+const char *ftb_status_string(int s) {
+    switch (s) {
+        case FTB_OK: return "ok";
+        case FTB_ERR_UNSUPPORTED: return "unsupported shape, dtype or mode";
+        case FTB_ERR_ALIGNMENT: return "pointer or stride alignment not met";
+        case FTB_ERR_WORKSPACE: return "workspace missing or too small";
+        case FTB_ERR_CUDA: return "CUDA runtime error";
+        case FTB_ERR_TIMEOUT: return "device-side wait timed out";
+        case FTB_ERR_INVALID: return "invalid argument";
+        default: return "unknown status";
+    }
+}
+
+int ftb_last_cuda_error(void) { return g_last_cuda_error; }
+
+uint64_t ftb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+void ftb_timing_enable(int enable) {
+    if (!enable) {
+        for (auto &sp : g_spans) {
+            cudaEventDestroy(sp.beg);
+            cudaEventDestroy(sp.end);
+        }
+        g_spans.clear();
+    }
+    g_timing = enable != 0;
+}
+
+int ftb_timing_read(float *ms_by_kind, int *launches_by_kind, int nkinds) {
+    if (!ms_by_kind || !launches_by_kind || nkinds <= 0) return FTB_ERR_INVALID;
+    for (int i = 0; i < nkinds; ++i) {
+        ms_by_kind[i] = 0.f;
+        launches_by_kind[i] = 0;
+    }
+    int rc = FTB_OK;
+    for (auto &sp : g_spans) {
+        float ms = 0.f;
+        cudaError_t e = cudaEventSynchronize(sp.end);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, sp.beg, sp.end);
+        if (e != cudaSuccess) rc = cuda_fail(e);
+        if (sp.kind >= 0 && sp.kind < nkinds && e == cudaSuccess) {
+            ms_by_kind[sp.kind] += ms;
+            launches_by_kind[sp.kind] += 1;
+        }
+        cudaEventDestroy(sp.beg);
+        cudaEventDestroy(sp.end);
+    }
+    g_spans.clear();
+    return rc;
+}
+
+size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M,
+                                  int dtype, int mode, int backward, int want_state) {
+    (void)dtype;
+    if (N <= 0 || H <= 0 || L <= 0 || D <= 0 || M <= 0) return 0;
+    if (mode == FTB_MODE_FP32_SIMT) {
+        Plan pl = simt_plan(N * H, L);
+        size_t one = align256((size_t)N * H * pl.nseg * D * M * sizeof(float));
+        if (backward) return 2 * one;
+        return (pl.nseg > 1 || want_state) ? one : 0;
+    }
+    return 0;
+}
+
+int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *out, int64_t N,
+                           int64_t H, int64_t L, int64_t D, int64_t M, const int64_t *qs,
+                           const int64_t *ks, const int64_t *vs, const int64_t *os, int dtype,
+                           int mode, const float *initial_state, float *final_state,
+                           void *workspace, size_t workspace_bytes, void *stream) {
+    int rc = check_common(N, H, L, D, M, dtype, mode);
+    if (rc != FTB_OK) return rc;
+    if (!qs || !ks || !vs || !os) return FTB_ERR_INVALID;
+    const bool empty = (N == 0 || H == 0 || L == 0 || M == 0);
+    if (!empty && (!q || !k || !v || !out) && D > 0) return FTB_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (N == 0 || H == 0) return FTB_OK;
+    if (D == 0 || M == 0 || L == 0) {
+        // out has no columns, or is all zeros (D == 0); states are unchanged.
+        if (L > 0 && M > 0 && D == 0) {
+            for (int64_t n = 0; n < N; ++n)
+                for (int64_t h = 0; h < H; ++h)
+                    FTB_CUDA(cudaMemset2DAsync(
+                        (char *)out + (n * os[0] + h * os[1]) * (dtype == FTB_F32 ? 4 : 2),
+                        os[2] * (dtype == FTB_F32 ? 4 : 2), 0, M * (dtype == FTB_F32 ? 4 : 2), L, st));
+        }
+        if (final_state && D > 0 && M > 0) {
+            if (initial_state)
+                FTB_CUDA(cudaMemcpyAsync(final_state, initial_state, (size_t)N * H * D * M * 4,
+                                         cudaMemcpyDeviceToDevice, st));
+            else
+                FTB_CUDA(cudaMemsetAsync(final_state, 0, (size_t)N * H * D * M * 4, st));
+        }
+        return FTB_OK;
+    }
+
+    Plan pl = simt_plan(N * H, L);
+    const float *states = initial_state;   // nseg == 1: the initial state is the segment state
+    if (pl.nseg > 1 || final_state) {
+        size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, final_state != nullptr);
+        if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
+        float *ws = (float *)workspace;
+        rc = launch_state_sum(k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, ws, st);
+        if (rc) return rc;
+        rc = launch_prefix(ws, initial_state, final_state, N * H, pl.nseg, D * M, 0, st);
+        if (rc) return rc;
+        states = ws;
+    }
+    return launch_scan(q, k, v, out, qs, ks, vs, os, N, H, L, (int)D, (int)M, dtype, pl, states,
+                       pl.nseg, /*canon_is_DaDc=*/1, /*reverse=*/0, st);
+}
+
+int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const void *g, void *gq,
+                            void *gk, void *gv, int64_t N, int64_t H, int64_t L, int64_t D,
+                            int64_t M, const int64_t *qs, const int64_t *ks, const int64_t *vs,
+                            const int64_t *gs, const int64_t *gqs, const int64_t *gks,
+                            const int64_t *gvs, int dtype, int mode, const float *initial_state,
+                            const float *initial_grad_state, void *workspace,
+                            size_t workspace_bytes, void *stream) {
+    int rc = check_common(N, H, L, D, M, dtype, mode);
+    if (rc != FTB_OK) return rc;
+    if (!qs || !ks || !vs || !gs || !gqs || !gks || !gvs) return FTB_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (N == 0 || H == 0 || L == 0) return FTB_OK;
+    const size_t es = dtype == FTB_F32 ? 4 : 2;
+    if (D == 0 || M == 0) {
+        // one operand has no features: every gradient that has columns is zero
+        for (int64_t n = 0; n < N; ++n)
+            for (int64_t h = 0; h < H; ++h) {
+                if (D > 0) {
+                    FTB_CUDA(cudaMemset2DAsync((char *)gq + (n * gqs[0] + h * gqs[1]) * es,
+                                               gqs[2] * es, 0, D * es, L, st));
+                    FTB_CUDA(cudaMemset2DAsync((char *)gk + (n * gks[0] + h * gks[1]) * es,
+                                               gks[2] * es, 0, D * es, L, st));
+                }
+                if (M > 0)
+                    FTB_CUDA(cudaMemset2DAsync((char *)gv + (n * gvs[0] + h * gvs[1]) * es,
+                                               gvs[2] * es, 0, M * es, L, st));
+            }
+        return FTB_OK;
+    }
+    if (!q || !k || !v || !g || !gq || !gk || !gv) return FTB_ERR_INVALID;
+
+    Plan pl = simt_plan(N * H, L);
+    size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 1, 0);
+    if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
+    float *wsS = (float *)workspace;
+    float *wsR = (float *)((char *)workspace + need / 2);
+
+    rc = launch_state_sum(k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, wsS, st);
+    if (rc) return rc;
+    rc = launch_prefix(wsS, initial_state, nullptr, N * H, pl.nseg, D * M, 0, st);
+    if (rc) return rc;
+    rc = launch_state_sum(q, g, qs, gs, N, H, L, (int)D, (int)M, dtype, pl, wsR, st);
+    if (rc) return rc;
+    rc = launch_prefix(wsR, initial_grad_state, nullptr, N * H, pl.nseg, D * M, 1, st);
+    if (rc) return rc;
+
+    // grad_Q_i = sum_{j<=i} (g_i . v_j) k_j + S_init g_i        state viewed as [M][D]
+    rc = launch_scan(g, v, k, gq, gs, vs, ks, gqs, N, H, L, (int)M, (int)D, dtype, pl, wsS,
+                     pl.nseg, 0, 0, st);
+    if (rc) return rc;
+    // grad_K_j = sum_{i>=j} (v_j . g_i) q_i + R_init v_j        state viewed as [M][D]
+    rc = launch_scan(v, g, q, gk, vs, gs, qs, gks, N, H, L, (int)M, (int)D, dtype, pl, wsR,
+                     pl.nseg, 0, 1, st);
+    if (rc) return rc;
+    // grad_V_j = sum_{i>=j} (k_j . q_i) g_i + R_init^T k_j      state viewed as [D][M]
+    return launch_scan(k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl, wsR,
+                       pl.nseg, 1, 1, st);
+}
+
+int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, int64_t H,
+                         int64_t L, int64_t D, int64_t M, const int64_t *xs, const int64_t *ys,
+                         int dtype, int mode, void *workspace, size_t workspace_bytes,
+                         void *stream) {
+    int rc = check_common(N, H, L, D, M, dtype, mode);
+    if (rc != FTB_OK) return rc;
+    if (!xs || !ys) return FTB_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (N == 0 || H == 0 || D == 0 || M == 0) return FTB_OK;
+    if (!state) return FTB_ERR_INVALID;
+    if (L == 0) {
+        FTB_CUDA(cudaMemsetAsync(state, 0, (size_t)N * H * D * M * 4, st));
+        return FTB_OK;
+    }
+    if (!x || !y) return FTB_ERR_INVALID;
+    Plan pl = simt_plan(N * H, L);
+    if (pl.nseg == 1) {
+        return launch_state_sum(x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, state, st);
+    }
+    size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, 1);
+    if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
+    float *ws = (float *)workspace;
+    rc = launch_state_sum(x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, ws, st);
+    if (rc) return rc;
+    return launch_prefix(ws, nullptr, state, N * H, pl.nseg, D * M, 0, st);
+}
+
+}  // extern "C"

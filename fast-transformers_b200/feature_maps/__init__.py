@@ -1,0 +1,147 @@
+"""Feature maps phi applied to queries and keys before the causal product.
+
+Mirror of ``fast_transformers/feature_maps``: the ``FeatureMap`` interface and
+``elu_feature_map`` (``base.py:19-73``), and the positive orthogonal random features
+``Favor`` with its base ``RandomFourierFeatures`` (``fourier_features.py:19-113,165-243``).
+An attention layer receives a FACTORY: a callable taking the query dimensionality and
+returning the map instance (``base.py:44-54``).
+"""
+from math import log, sqrt
+import warnings
+
+import torch
+from torch.nn import Module
+
+
+class FeatureMap(Module):
+    def __init__(self, query_dims):
+        super().__init__()
+        self.query_dims = query_dims
+
+    def new_feature_map(self, device):
+        """Resample the parameters of a random map (no-op for deterministic maps)."""
+        raise NotImplementedError()
+
+    def forward_queries(self, x):
+        return self(x)
+
+    def forward_keys(self, x):
+        return self(x)
+
+    def forward(self, x):
+        raise NotImplementedError()
+
+    @classmethod
+    def factory(cls, *args, **kwargs):
+        def inner(query_dims):
+            return cls(query_dims, *args, **kwargs)
+        return inner
+
+
+class ActivationFunctionFeatureMap(FeatureMap):
+    """phi(x) = f(x) element-wise."""
+
+    def __init__(self, query_dims, activation_function):
+        super().__init__(query_dims)
+        self.activation_function = activation_function
+
+    def new_feature_map(self, device):
+        return
+
+    def forward(self, x):
+        return self.activation_function(x)
+
+
+def _elu_plus_one(x):
+    return torch.nn.functional.elu(x) + 1
+
+
+elu_feature_map = ActivationFunctionFeatureMap.factory(_elu_plus_one)
+# marker the fused layer kernel keys on: this activation can be applied on load
+_elu_plus_one.fused_id = "elu+1"
+
+
+def orthogonal_random_matrix_(w):
+    """Fill ``w`` (rows x columns) in place with blocks of ``rows`` orthogonal columns whose
+    norms follow the chi distribution with ``rows`` degrees of freedom
+    (``fourier_features.py:19-41``): QR of a Gaussian block, columns rescaled by the norms
+    of the block's rows."""
+    rows, columns = w.shape
+    for start in range(0, columns, rows):
+        end = min(start + rows, columns)
+        block = torch.randn(rows, rows, device=w.device)
+        norms = block.pow(2).sum(dim=1).sqrt()
+        Q, _ = torch.linalg.qr(block)
+        w[:, start:end] = Q[:, :end - start] * norms[None, :end - start]
+
+
+class RandomFourierFeatures(FeatureMap):
+    """[cos(x w), sin(x w)] * sqrt(2 / n_dims) with x scaled by softmax_temp^(1/2)
+    (``fourier_features.py:44-113``).  Holds the buffer ``omega`` (query_dims x n_dims/2),
+    resampled by ``new_feature_map`` every ``redraw`` calls, never in eval mode when
+    ``deterministic_eval``."""
+
+    def __init__(self, query_dimensions, n_dims=None, softmax_temp=None, orthogonal=False,
+                 redraw=1, deterministic_eval=False):
+        super().__init__(query_dimensions)
+        self.n_dims = n_dims or query_dimensions
+        self.query_dimensions = query_dimensions
+        self.orthogonal = orthogonal
+        self.softmax_temp = 1 / sqrt(query_dimensions) if softmax_temp is None else softmax_temp
+        self.redraw = redraw
+        self.deterministic_eval = deterministic_eval
+        self.register_buffer("omega", torch.zeros(self.query_dimensions, self.n_dims // 2))
+        self._calls = -1
+
+    def new_feature_map(self, device):
+        if self.deterministic_eval and not self.training:
+            return
+        self._calls += 1
+        if (self._calls % self.redraw) != 0:
+            return
+        omega = torch.zeros(self.query_dimensions, self.n_dims // 2, device=device)
+        if self.orthogonal:
+            orthogonal_random_matrix_(omega)
+        else:
+            omega.normal_()
+        self.register_buffer("omega", omega)
+
+    def forward(self, x):
+        x = x * sqrt(self.softmax_temp)
+        u = x.unsqueeze(-2).matmul(self.omega).squeeze(-2)
+        phi = torch.cat([torch.cos(u), torch.sin(u)], dim=-1)
+        return phi * sqrt(2 / self.n_dims)
+
+
+class Favor(RandomFourierFeatures):
+    """Positive random features approximating the softmax kernel
+    (``fourier_features.py:165-243``): with x <- x * softmax_temp^(1/2), u = x omega and
+    offset = |x|^2 / 2 + log(n_dims) / 2 (plus, when ``stabilize``, the maximum of |x|^2 over
+    the sequence axis), phi(x) = [exp(u - offset), exp(-u - offset)]."""
+
+    def __init__(self, query_dimensions, n_dims=None, softmax_temp=None, orthogonal=True,
+                 stabilize=False, redraw=1, deterministic_eval=False):
+        super().__init__(query_dimensions, n_dims=n_dims, softmax_temp=softmax_temp,
+                         orthogonal=orthogonal, redraw=redraw,
+                         deterministic_eval=deterministic_eval)
+        self.stabilize = stabilize
+
+    def _check_sequence_length(self, x):
+        if len(x.shape) != 4:
+            warnings.warn("Favor.stabilize is set to True but the input feature does not have "
+                          "the shape (N, L, H, D) which may result in unexpected behaviour")
+        if x.shape[1] < x.shape[2]:
+            warnings.warn("Favor.stabilize is set to True but the 2nd dimension of the input is "
+                          "smaller than the 3rd which could indicate that the sequence length "
+                          "and the heads are flipped. The shape of the input is "
+                          "{!r}.".format(x.shape))
+
+    def forward(self, x):
+        x = x * sqrt(self.softmax_temp)
+        norm_x_squared = torch.einsum("...d,...d->...", x, x).unsqueeze(-1)
+        u = x.unsqueeze(-2).matmul(self.omega).squeeze(-2)
+        offset = norm_x_squared * 0.5 + 0.5 * log(self.n_dims)
+        if self.stabilize:
+            self._check_sequence_length(norm_x_squared)
+            offset = offset + norm_x_squared.max(1, keepdim=True)[0]
+        return torch.cat([torch.exp(u - offset), torch.exp(-u - offset)], dim=-1)

@@ -1,0 +1,150 @@
+/*
+ * ftb200 -- C ABI of the B200 (sm_100a) causal linear-attention kernels.
+ *
+ * This is the drop-in boundary for the native functions of the reference package
+ * fast_transformers.causal_product:
+ *
+ *   causal_dot_product(queries, keys, values, product)                     -> void
+ *       fast_transformers/causal_product/causal_product_cuda.cu:1273-1285  (CUDA)
+ *       fast_transformers/causal_product/causal_product_cpu.cpp:82-124     (CPU)
+ *   causal_dot_backward(queries, keys, values, grad_out, gq, gk, gv)       -> void
+ *       fast_transformers/causal_product/causal_product_cuda.cu:1438-1467  (CUDA)
+ *       fast_transformers/causal_product/causal_product_cpu.cpp:133-209    (CPU)
+ *
+ * which the autograd Function reaches through its per-device tables
+ * (fast_transformers/causal_product/__init__.py:23-30, 44-49, 64-72).
+ *
+ * Conventions shared by every entry point
+ *   - All data pointers are DEVICE pointers on the current CUDA device of the calling
+ *     thread.  The caller allocates every output; the library fills it in place and keeps
+ *     no reference (the reference's ownership rule, __init__.py:41,59-61).  Outputs do not
+ *     need to be zeroed.
+ *   - Tensors are 4-D (N, H, L, dim) with the last dimension contiguous (the reference
+ *     asserts stride(3)==1, causal_product_cuda.cu:774-777).  `*_strides` points at three
+ *     64-bit ELEMENT strides {batch, head, position}; they may describe permuted views such
+ *     as (N, L, H, dim) storage.
+ *   - `dtype` is the element type of Q, K, V, grad_out and of the outputs: FTB_F32 or
+ *     FTB_BF16.  States are always fp32, stored as (N, H, D, M) contiguous.
+ *   - `mode` selects the arithmetic: FTB_MODE_FP32_SIMT (fp32 FMA on CUDA cores, any D, M
+ *     up to 512) or FTB_MODE_MMA (tcgen05 tensor cores: TF32 operands for fp32 I/O, bf16
+ *     operands for bf16 I/O, fp32 accumulation and fp32 running state).
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued, not synchronised.
+ *   - `workspace` is caller-provided scratch of at least ftb_causal_workspace_bytes(...)
+ *     bytes, 256-byte aligned; it may be NULL when that function returns 0.
+ *   - Return value: FTB_OK or one of the error codes below.  Nothing is enqueued when an
+ *     error is returned.  The library is re-entrant and holds no mutable global state, so
+ *     forward (caller thread) and backward (autograd thread) may run concurrently.
+ */
+#ifndef FTB200_H
+#define FTB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FTB_OK 0
+#define FTB_ERR_UNSUPPORTED 1 /* no kernel for this shape / dtype / mode            */
+#define FTB_ERR_ALIGNMENT 2   /* pointer or stride alignment required by the mode    */
+#define FTB_ERR_WORKSPACE 3   /* workspace missing or too small                      */
+#define FTB_ERR_CUDA 4        /* a CUDA runtime call failed (see ftb_last_cuda_error)*/
+#define FTB_ERR_TIMEOUT 5     /* a bounded device-side wait expired                  */
+#define FTB_ERR_INVALID 6     /* NULL pointer, negative size, unknown enum           */
+
+#define FTB_F32 0
+#define FTB_BF16 1
+
+#define FTB_MODE_FP32_SIMT 0
+#define FTB_MODE_MMA 1
+
+/* Library / ABI version (major*1000 + minor). */
+int ftb_version(void);
+
+/* Static description of a status code. */
+const char *ftb_status_string(int status);
+
+/* cudaError_t of the most recent failed runtime call made by this thread (0 if none). */
+int ftb_last_cuda_error(void);
+
+/*
+ * Launch accounting (no counterpart in the reference; used by the benchmark).
+ * ftb_launch_count: kernels launched by this library in this process so far.
+ * ftb_timing_enable(1): from now on every launch made by THIS thread is bracketed by CUDA
+ *   events on its stream.  ftb_timing_read synchronises those events, adds the elapsed
+ *   milliseconds and launch counts per kernel kind into the two arrays (length nkinds),
+ *   and forgets the recorded launches.  ftb_timing_enable(0) stops recording.
+ */
+#define FTB_KERNEL_STATE_SUM 0    /* per-segment totals  sum x (x) y                 */
+#define FTB_KERNEL_STATE_PREFIX 1 /* exclusive prefix/suffix of the segment totals   */
+#define FTB_KERNEL_SIMT_SCAN 2    /* fp32 CUDA-core segment scan                     */
+#define FTB_KERNEL_MMA_FWD 3      /* tcgen05 forward                                 */
+#define FTB_KERNEL_MMA_BWD 4      /* tcgen05 backward                                */
+#define FTB_KERNEL_MMA_STATE 5    /* tcgen05 per-segment totals                      */
+#define FTB_KERNEL_KINDS 8
+uint64_t ftb_launch_count(void);
+void ftb_timing_enable(int enable);
+int ftb_timing_read(float *ms_by_kind, int *launches_by_kind, int nkinds);
+
+/*
+ * Scratch bytes needed by ftb_causal_dot_product (backward == 0) or
+ * ftb_causal_dot_backward (backward != 0) for this problem.  `want_state` is non-zero when
+ * the call will pass a non-NULL final_state / state outputs.
+ */
+size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M,
+                                  int dtype, int mode, int backward, int want_state);
+
+/*
+ * Forward:  out[n,h,i,:] = q_i . (S_init + sum_{j<=i} k_j (x) v_j)
+ * Replaces causal_dot_product(queries, keys, values, product)
+ * (causal_product_cuda.cu:1273-1285 / causal_product_cpu.cpp:82-124).
+ *
+ * initial_state : optional (N,H,D,M) fp32 state added before position 0 (NULL = zeros);
+ *                 used when a sequence is split across devices or continued.
+ * final_state   : optional (N,H,D,M) fp32 output, S_init + sum over all L positions.
+ */
+int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *out,
+                           int64_t N, int64_t H, int64_t L, int64_t D, int64_t M,
+                           const int64_t *q_strides, const int64_t *k_strides,
+                           const int64_t *v_strides, const int64_t *out_strides,
+                           int dtype, int mode, const float *initial_state,
+                           float *final_state, void *workspace, size_t workspace_bytes,
+                           void *stream);
+
+/*
+ * Backward: gq_i = S_i g_i ; gk_i = R_i v_i ; gv_i = R_i^T k_i with
+ *           S_i = S_init + sum_{j<=i} k_j (x) v_j   and   R_i = R_init + sum_{j>=i} q_j (x) g_j.
+ * Replaces causal_dot_backward(queries, keys, values, grad_out, grad_queries, grad_keys,
+ * grad_values) (causal_product_cuda.cu:1438-1467 / causal_product_cpu.cpp:133-209).
+ *
+ * initial_state      : optional (N,H,D,M) fp32, the same S_init the forward used.
+ * initial_grad_state : optional (N,H,D,M) fp32, R contributed by positions AFTER this
+ *                      range (sequence split across devices); NULL = zeros.
+ */
+int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const void *grad_out,
+                            void *grad_q, void *grad_k, void *grad_v, int64_t N, int64_t H,
+                            int64_t L, int64_t D, int64_t M, const int64_t *q_strides,
+                            const int64_t *k_strides, const int64_t *v_strides,
+                            const int64_t *go_strides, const int64_t *gq_strides,
+                            const int64_t *gk_strides, const int64_t *gv_strides, int dtype,
+                            int mode, const float *initial_state,
+                            const float *initial_grad_state, void *workspace,
+                            size_t workspace_bytes, void *stream);
+
+/*
+ * Whole-range state  state[n,h,:,:] = sum_l x[n,h,l,:] (x) y[n,h,l,:]   ((N,H,D,M) fp32).
+ * With (x, y) = (K, V) it is what a sequence shard contributes to the forward state of
+ * the shards after it; with (x, y) = (Q, grad_out) what it contributes to the backward
+ * state of the shards before it.  The reference has no such entry point (it is single
+ * device); the sum is the one accumulated by causal_product_cpu.cpp:107-113,186-192.
+ */
+int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, int64_t H,
+                         int64_t L, int64_t D, int64_t M, const int64_t *x_strides,
+                         const int64_t *y_strides, int dtype, int mode, void *workspace,
+                         size_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FTB200_H */

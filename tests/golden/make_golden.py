@@ -1,0 +1,153 @@
+"""Generate the golden fixtures in this directory from the UNMODIFIED reference.
+
+Run in a container that has the reference checkout (default ``/root/reference``):
+
+    python oracle/build_ref.py            # compiles the reference CPU extension in place
+    python tests/golden/make_golden.py    # writes tests/golden/*.npz
+
+The reference's Python modules for this path are imported from the checkout as they are.
+Its top-level ``fast_transformers/attention/__init__.py`` imports every attention flavour
+(and through them compiled extensions that are not part of this path), so the two package
+objects ``fast_transformers`` and ``fast_transformers.attention`` are created empty with
+their ``__path__`` pointing into the checkout, and the compiled
+``causal_product_cpu`` module built by ``oracle/build_ref.py`` is registered under its
+package-qualified name.  Everything else (``causal_product/__init__.py``,
+``attention/causal_linear_attention.py``, ``attention/attention_layer.py``,
+``feature_maps``, ``masking.py``, ``attention_registry``, ``events``, ``transformers.py``)
+executes unmodified.
+
+All inputs come from seeded CPU generators; the fixtures store inputs and outputs (or, for
+the benchmark-sized config 1, only a strided sample of the outputs -- the inputs are
+regenerated from the seed by ``fast_transformers_b200.workloads``).
+"""
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from oracle import build_ref, causal_oracle  # noqa: E402
+
+
+def import_reference():
+    root = build_ref.reference_root()
+    if root is None:
+        raise SystemExit("reference checkout not found")
+    build_ref.build_reference_ext()
+    ext = causal_oracle.reference_ext()
+    pkg_dir = os.path.join(root, "fast_transformers")
+    ft = types.ModuleType("fast_transformers")
+    ft.__path__ = [pkg_dir]
+    sys.modules["fast_transformers"] = ft
+    att = types.ModuleType("fast_transformers.attention")
+    att.__path__ = [os.path.join(pkg_dir, "attention")]
+    sys.modules["fast_transformers.attention"] = att
+    sys.modules["fast_transformers.causal_product.causal_product_cpu"] = ext
+    import fast_transformers.causal_product as cp
+    import fast_transformers.attention.causal_linear_attention as cla
+    import fast_transformers.attention.attention_layer as al
+    import fast_transformers.feature_maps as fm
+    import fast_transformers.masking as masking
+    import fast_transformers.transformers as tr
+    return cp, cla, al, fm, masking, tr
+
+
+def np_(t):
+    return t.detach().cpu().numpy()
+
+
+def main():
+    cp, cla, al, fm, masking, tr = import_reference()
+    torch.set_num_threads(1)
+
+    # ---- 1. raw product, odd sizes, U[0,1) inputs (the reference tests' distribution) ----
+    g = torch.Generator().manual_seed(101)
+    N, H, L, D, M = 2, 3, 70, 19, 33
+    Q, K, V, G = (torch.rand(N, H, L, d, generator=g) for d in (D, D, M, M))
+    Qr, Kr, Vr = (t.clone().requires_grad_(True) for t in (Q, K, V))
+    out = cp.causal_dot_product(Qr, Kr, Vr)
+    out.backward(G)
+    np.savez_compressed(os.path.join(HERE, "product_small.npz"), Q=np_(Q), K=np_(K), V=np_(V),
+                        G=np_(G), out=np_(out), gQ=np_(Qr.grad), gK=np_(Kr.grad),
+                        gV=np_(Vr.grad))
+
+    # ---- 2. config 1 (B2 H4 L1024 D=M=64), strided sample of the reference outputs --------
+    from fast_transformers_b200 import workloads
+    Q, K, V, G = workloads.make_inputs(1)
+    Qr, Kr, Vr = (t.clone().requires_grad_(True) for t in (Q, K, V))
+    out = cp.causal_dot_product(Qr, Kr, Vr)
+    out.backward(G)
+    rows = torch.arange(7, 1024, 16)
+    np.savez_compressed(os.path.join(HERE, "product_config1_sample.npz"), rows=np_(rows),
+                        out=np_(out[:, :, rows]), gQ=np_(Qr.grad[:, :, rows]),
+                        gK=np_(Kr.grad[:, :, rows]), gV=np_(Vr.grad[:, :, rows]),
+                        checksum=np.array([out.double().sum().item(),
+                                           Qr.grad.double().sum().item(),
+                                           Kr.grad.double().sum().item(),
+                                           Vr.grad.double().sum().item()]))
+
+    # ---- 3. the layer: L == S, L < S, L > S, with key lengths ------------------------------
+    layer = {}
+    for name, (L, S) in {"eq": (24, 24), "lt": (16, 24), "gt": (24, 16)}.items():
+        g = torch.Generator().manual_seed(300 + L + 7 * S)
+        N, H, E, Mv = 3, 2, 8, 12
+        q = torch.randn(N, L, H, E, generator=g).requires_grad_(True)
+        k = torch.randn(N, S, H, E, generator=g).requires_grad_(True)
+        v = torch.randn(N, S, H, Mv, generator=g).requires_grad_(True)
+        w = torch.randn(N, L, H, Mv, generator=g)
+        klen = torch.tensor([S, max(1, S - 5), max(1, S // 2)])
+        att = cla.CausalLinearAttention(E)
+        y = att(q, k, v, masking.TriangularCausalMask(L), masking.LengthMask(torch.full((N,), L)),
+                masking.LengthMask(klen, max_len=S))
+        assert y.is_contiguous() and torch.isfinite(y).all()
+        vals = dict(q=q, k=k, v=v, w=w, klen=klen, y=y)
+        if L <= S:
+            # For L > S the reference passes V with S rows to a kernel that walks L rows
+            # (causal_linear_attention.py:68-69,98-102): its backward then writes grad_V rows
+            # S..L-1 past the end of the buffer.  Only the forward is recorded for that case.
+            (y * w).sum().backward()
+            vals.update(gq=q.grad, gk=k.grad, gv=v.grad)
+        for key, val in vals.items():
+            layer[name + "_" + key] = np_(val)
+    np.savez_compressed(os.path.join(HERE, "layer.npz"), **layer)
+
+    # ---- 4. Favor feature map with a fixed omega -------------------------------------------
+    g = torch.Generator().manual_seed(404)
+    E, n_dims = 16, 64
+    f = fm.Favor(E, n_dims=n_dims)
+    omega = workloads.favor_omega(E, n_dims, g)
+    f.omega.copy_(omega)
+    x = torch.randn(2, 10, 3, E, generator=g) * 0.5
+    np.savez_compressed(os.path.join(HERE, "favor.npz"), omega=np_(omega), x=np_(x),
+                        phi=np_(f(x)), elu=np_(fm.elu_feature_map(E)(x)))
+
+    # ---- 5. a two-layer causal-linear encoder built from the reference's own classes -------
+    torch.manual_seed(505)
+    d_model, heads, dq, dff, nl = 32, 4, 8, 64, 2
+    enc = tr.TransformerEncoder(
+        [tr.TransformerEncoderLayer(
+            al.AttentionLayer(cla.CausalLinearAttention(dq), d_model, heads, d_keys=dq, d_values=dq),
+            d_model, dff, 0.0, "relu") for _ in range(nl)],
+        torch.nn.LayerNorm(d_model))
+    g = torch.Generator().manual_seed(506)
+    x = torch.rand(2, 40, d_model, generator=g).requires_grad_(True)
+    w = torch.randn(2, 40, d_model, generator=g)
+    y = enc(x, attn_mask=masking.TriangularCausalMask(40))
+    (y * w).sum().backward()
+    blob = {"sd__" + k: np_(v) for k, v in enc.state_dict().items()}
+    blob.update(x=np_(x), w=np_(w), y=np_(y), gx=np_(x.grad))
+    blob.update({"gp__" + k: np_(p.grad) for k, p in enc.named_parameters()})
+    np.savez_compressed(os.path.join(HERE, "encoder.npz"), **blob)
+
+    for f_ in sorted(os.listdir(HERE)):
+        if f_.endswith(".npz"):
+            print(f_, os.path.getsize(os.path.join(HERE, f_)), "bytes")
+
+
+if __name__ == "__main__":
+    main()

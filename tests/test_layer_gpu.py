@@ -1,0 +1,77 @@
+"""CausalLinearAttention, AttentionLayer and the encoder on the GPU against the
+reference's outputs (golden fixtures) and the dense fp64 oracle."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import causal_oracle as orc  # noqa: E402
+from fast_transformers_b200.attention import CausalLinearAttention  # noqa: E402
+from fast_transformers_b200.builders import TransformerEncoderBuilder  # noqa: E402
+from fast_transformers_b200.feature_maps import Favor  # noqa: E402
+from fast_transformers_b200.masking import LengthMask, TriangularCausalMask  # noqa: E402
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _lib(native_lib):
+    assert torch.cuda.is_available()
+    return native_lib
+
+
+def T(a):
+    return torch.from_numpy(np.asarray(a))
+
+
+@pytest.mark.parametrize("case", ["eq", "lt", "gt"])
+def test_layer_matches_reference(golden, case):
+    g = golden("layer")
+    q, k, v, w = (T(g[case + "_" + n]).cuda() for n in "qkvw")
+    klen = T(g[case + "_klen"]).cuda()
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    N, L = q.shape[:2]
+    S = k.shape[1]
+    att = CausalLinearAttention(q.shape[3])
+    y = att(q, k, v, TriangularCausalMask(L, device="cuda"),
+            LengthMask(torch.full((N,), L, device="cuda")), LengthMask(klen, max_len=S))
+    assert y.is_contiguous() and y.shape == (N, L, q.shape[2], v.shape[3])
+    # the reference's own bound for the normalised product (test_causal_product.py:54-62)
+    assert (y.cpu() - T(g[case + "_y"])).abs().max() < 5e-4
+    assert orc.rel_err(y, orc.layer_forward(q, k, v, key_lengths=klen)) < 1e-5
+    (y * w).sum().backward()
+    if case != "gt":
+        for n, t in (("gq", q), ("gk", k), ("gv", v)):
+            assert (t.grad.cpu() - T(g[case + "_" + n])).abs().max() < 5e-4, n
+    else:
+        assert v.grad.shape == v.shape and torch.isfinite(v.grad).all()
+
+
+def test_layer_with_favor_map():
+    torch.manual_seed(3)
+    N, L, H, E, M = 2, 50, 3, 16, 8
+    q, k, v = (torch.randn(N, L, H, d, device="cuda") * 0.5 for d in (E, E, M))
+    att = CausalLinearAttention(E, feature_map=Favor.factory(n_dims=64, redraw=10 ** 9)).cuda()
+    lm = LengthMask(torch.full((N,), L, device="cuda"))
+    y = att(q, k, v, TriangularCausalMask(L, device="cuda"), lm, lm)
+    omega = att.feature_map.omega.double().cpu()
+    want = orc.layer_forward(q, k, v, feature=lambda x: orc.favor_features(x, omega))
+    assert orc.rel_err(y, want) < 1e-5
+
+
+def test_encoder_matches_reference(golden):
+    g = golden("encoder")
+    model = TransformerEncoderBuilder.from_kwargs(
+        n_layers=2, n_heads=4, query_dimensions=8, value_dimensions=8,
+        feed_forward_dimensions=64, attention_type="causal-linear", dropout=0.0).get()
+    model.load_state_dict({k[4:]: T(g[k]) for k in g.files if k.startswith("sd__")})
+    model = model.cuda()
+    x = T(g["x"]).cuda().requires_grad_(True)
+    with pytest.raises(RuntimeError):
+        model(x)  # the default full mask is rejected, as in the reference
+    y = model(x, attn_mask=TriangularCausalMask(40, device="cuda"))
+    assert (y.cpu() - T(g["y"])).abs().max() < 1e-4
+    (y * T(g["w"]).cuda()).sum().backward()
+    assert orc.rel_err(x.grad, T(g["gx"])) < 1e-3
+    for name, p in model.named_parameters():
+        ref = T(g["gp__" + name])
+        assert (p.grad.cpu() - ref).abs().max() <= 1e-3 * max(1.0, ref.abs().max().item()), name
