@@ -20,7 +20,7 @@ MODE_IDS = {"fp32": MODE_FP32_SIMT, "mma": MODE_MMA}
 EXPORTS = (
     "ftb_version", "ftb_status_string", "ftb_last_cuda_error", "ftb_causal_workspace_bytes",
     "ftb_causal_dot_product", "ftb_causal_dot_backward", "ftb_causal_state_sum",
-    "ftb_launch_count", "ftb_timing_enable", "ftb_timing_read",
+    "ftb_launch_count", "ftb_timing_enable", "ftb_timing_read", "ftb_device_status",
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
                 "reserved6", "reserved7")
@@ -63,6 +63,8 @@ def lib():
     L.ftb_causal_state_sum.argtypes = (
         [_vp] * 3 + [_i64] * 5 + [_i64p] * 2 + [_int, _int, _vp, _sz, _vp])
     L.ftb_launch_count.restype = ctypes.c_uint64
+    L.ftb_device_status.restype = _int
+    L.ftb_device_status.argtypes = [_int]
     L.ftb_timing_enable.restype = None
     L.ftb_timing_enable.argtypes = [_int]
     L.ftb_timing_read.restype = _int

@@ -7,6 +7,7 @@
 #include <atomic>
 #include <vector>
 
+#include "mma_host.cuh"
 #include "simt_scan.cuh"
 
 namespace ftb {
@@ -94,7 +95,7 @@ static inline bool vec_ok(const void *ptr, const int64_t *s, int dtype) {
 }
 
 // ---- launches ---------------------------------------------------------------------------
-static int launch_state_sum(const void *x, const void *y, const int64_t *xs, const int64_t *ys,
+static int simt_launch_state_sum(const void *x, const void *y, const int64_t *xs, const int64_t *ys,
                             int64_t N, int64_t H, int64_t L, int D, int M, int dtype, Plan pl,
                             float *states, cudaStream_t st) {
     StateSumArgs a;
@@ -136,7 +137,7 @@ static int launch_scan_t(const ScanArgs &a, int64_t blocks, size_t smem, cudaStr
     return FTB_OK;
 }
 
-static int launch_scan(const void *a, const void *b, const void *c, void *out, const int64_t *as,
+static int simt_launch_scan(const void *a, const void *b, const void *c, void *out, const int64_t *as,
                        const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N,
                        int64_t H, int64_t L, int Da, int Dc, int dtype, Plan pl,
                        const float *states, int nseg_states, int canon_is_DaDc, int reverse,
@@ -158,12 +159,91 @@ static int launch_scan(const void *a, const void *b, const void *c, void *out, c
     return launch_scan_t<__nv_bfloat16, __nv_bfloat16>(p, blocks, smem, st);
 }
 
+// ---- tensor-core launches -------------------------------------------------------------------
+static int mma_launch(const void *a, const void *b, const void *c, void *out, const int64_t *as,
+                      const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H,
+                      int64_t L, int Da, int Dc, int dtype, Plan pl, const float *states,
+                      float *state_out, int canon_is_DaDc, int reverse, cudaStream_t st) {
+    const bool state_only = (a == nullptr);
+    const int DCT = dtype == FTB_F32 ? 64 : 128;
+    // fp32 (TF32) operands read MN-major need the 32-byte-atom swizzle; bf16 uses one image
+    const bool atom32 = dtype == FTB_F32;
+    CUtensorMap ma, mb, mbmn, mc;
+    mma::ScanParams p;
+    int rc = mma::make_map(&mb, p.pos_b, b, N, H, L, Da, bs, dtype, false);
+    if (rc) return rc;
+    rc = mma::make_map(&mbmn, p.pos_b, b, N, H, L, Da, bs, dtype, atom32);
+    if (rc) return rc;
+    rc = mma::make_map(&mc, p.pos_c, c, N, H, L, Dc, cs, dtype, atom32);
+    if (rc) return rc;
+    if (state_only) {
+        ma = mb;
+        for (int i = 0; i < 3; ++i) p.pos_a[i] = p.pos_b[i];
+    } else {
+        rc = mma::make_map(&ma, p.pos_a, a, N, H, L, Da, as, dtype);
+        if (rc) return rc;
+        const int64_t es = dtype == FTB_F32 ? 4 : 2;
+        if (((uintptr_t)out & 15) || (os[0] * es) % 16 || (os[1] * es) % 16 || (os[2] * es) % 16)
+            return FTB_ERR_ALIGNMENT;
+    }
+    p.out = out;
+    p.so = state_only ? Strides3{0, 0, 0} : S3(os);
+    p.H = (int)H; p.L = L; p.Dc = Dc;
+    p.seg_len = pl.seg_len; p.nseg = pl.nseg;
+    p.states = states; p.state_out = state_out;
+    p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = state_only ? 1 : 0;
+    static const char *env = std::getenv("FTB200_MMA_TERMS");
+    p.terms = env ? std::atoi(env) : 7;
+    int64_t blocks = N * H * pl.nseg * (Dc / DCT);
+    if (blocks <= 0) return FTB_OK;
+    if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
+    LaunchScope scope(state_only ? FTB_KERNEL_MMA_STATE : (reverse ? FTB_KERNEL_MMA_BWD : FTB_KERNEL_MMA_FWD), st);
+    cudaError_t e;
+    if (dtype == FTB_F32)
+        e = mma::launch_t<float, 64, 64>(ma, mb, mbmn, mc, p, blocks, st);
+    else
+        e = mma::launch_t<__nv_bfloat16, 128, 128>(ma, mb, mbmn, mc, p, blocks, st);
+    if (e != cudaSuccess) return cuda_fail(e);
+    return FTB_OK;
+}
+
+static Plan choose_plan(int mode, int64_t BH, int64_t L) {
+    if (mode == FTB_MODE_MMA) {
+        mma::Plan m = mma::plan(BH, L, 1);
+        return Plan{m.seg_len, m.nseg};
+    }
+    return simt_plan(BH, L);
+}
+
+static int launch_state_sum(int mode, const void *x, const void *y, const int64_t *xs,
+                            const int64_t *ys, int64_t N, int64_t H, int64_t L, int D, int M,
+                            int dtype, Plan pl, float *states, cudaStream_t st) {
+    if (mode == FTB_MODE_MMA)
+        return mma_launch(nullptr, x, y, nullptr, nullptr, xs, ys, nullptr, N, H, L, D, M, dtype, pl,
+                          nullptr, states, 1, 0, st);
+    return simt_launch_state_sum(x, y, xs, ys, N, H, L, D, M, dtype, pl, states, st);
+}
+
+static int launch_scan(int mode, const void *a, const void *b, const void *c, void *out,
+                       const int64_t *as, const int64_t *bs, const int64_t *cs, const int64_t *os,
+                       int64_t N, int64_t H, int64_t L, int Da, int Dc, int dtype, Plan pl,
+                       const float *states, int nseg_states, int canon_is_DaDc, int reverse,
+                       cudaStream_t st) {
+    if (mode == FTB_MODE_MMA)
+        return mma_launch(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, states, nullptr,
+                          canon_is_DaDc, reverse, st);
+    return simt_launch_scan(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, states,
+                            nseg_states, canon_is_DaDc, reverse, st);
+}
+
 static int check_common(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M, int dtype, int mode) {
     if (N < 0 || H < 0 || L < 0 || D < 0 || M < 0) return FTB_ERR_INVALID;
     if (dtype != FTB_F32 && dtype != FTB_BF16) return FTB_ERR_INVALID;
     if (mode != FTB_MODE_FP32_SIMT && mode != FTB_MODE_MMA) return FTB_ERR_INVALID;
     if (mode == FTB_MODE_FP32_SIMT && (D > kSimtMaxDim || M > kSimtMaxDim)) return FTB_ERR_UNSUPPORTED;
-    if (mode == FTB_MODE_MMA) return FTB_ERR_UNSUPPORTED;
+    if (mode == FTB_MODE_MMA && D > 0 && M > 0 &&
+        !(mma::supported(dtype, D, M) && mma::supported(dtype, M, D)))
+        return FTB_ERR_UNSUPPORTED;
     return FTB_OK;
 }
 
@@ -191,6 +271,16 @@ const char *ftb_status_string(int s) {
 }
 
 int ftb_last_cuda_error(void) { return g_last_cuda_error; }
+
+int ftb_device_status(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, mma::g_device_status, sizeof(int)) != cudaSuccess) return FTB_ERR_CUDA;
+    if (reset && v) {
+        int z = 0;
+        cudaMemcpyToSymbol(mma::g_device_status, &z, sizeof(int));
+    }
+    return v;
+}
 
 uint64_t ftb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
@@ -232,8 +322,8 @@ size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, in
                                   int dtype, int mode, int backward, int want_state) {
     (void)dtype;
     if (N <= 0 || H <= 0 || L <= 0 || D <= 0 || M <= 0) return 0;
-    if (mode == FTB_MODE_FP32_SIMT) {
-        Plan pl = simt_plan(N * H, L);
+    {
+        Plan pl = choose_plan(mode, N * H, L);
         size_t one = align256((size_t)N * H * pl.nseg * D * M * sizeof(float));
         if (backward) return 2 * one;
         return (pl.nseg > 1 || want_state) ? one : 0;
@@ -272,19 +362,19 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
         return FTB_OK;
     }
 
-    Plan pl = simt_plan(N * H, L);
+    Plan pl = choose_plan(mode, N * H, L);
     const float *states = initial_state;   // nseg == 1: the initial state is the segment state
     if (pl.nseg > 1 || final_state) {
         size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, final_state != nullptr);
         if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
         float *ws = (float *)workspace;
-        rc = launch_state_sum(k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, ws, st);
+        rc = launch_state_sum(mode, k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, ws, st);
         if (rc) return rc;
         rc = launch_prefix(ws, initial_state, final_state, N * H, pl.nseg, D * M, 0, st);
         if (rc) return rc;
         states = ws;
     }
-    return launch_scan(q, k, v, out, qs, ks, vs, os, N, H, L, (int)D, (int)M, dtype, pl, states,
+    return launch_scan(mode, q, k, v, out, qs, ks, vs, os, N, H, L, (int)D, (int)M, dtype, pl, states,
                        pl.nseg, /*canon_is_DaDc=*/1, /*reverse=*/0, st);
 }
 
@@ -319,31 +409,31 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
     }
     if (!q || !k || !v || !g || !gq || !gk || !gv) return FTB_ERR_INVALID;
 
-    Plan pl = simt_plan(N * H, L);
+    Plan pl = choose_plan(mode, N * H, L);
     size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 1, 0);
     if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
     float *wsS = (float *)workspace;
     float *wsR = (float *)((char *)workspace + need / 2);
 
-    rc = launch_state_sum(k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, wsS, st);
+    rc = launch_state_sum(mode, k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, wsS, st);
     if (rc) return rc;
     rc = launch_prefix(wsS, initial_state, nullptr, N * H, pl.nseg, D * M, 0, st);
     if (rc) return rc;
-    rc = launch_state_sum(q, g, qs, gs, N, H, L, (int)D, (int)M, dtype, pl, wsR, st);
+    rc = launch_state_sum(mode, q, g, qs, gs, N, H, L, (int)D, (int)M, dtype, pl, wsR, st);
     if (rc) return rc;
     rc = launch_prefix(wsR, initial_grad_state, nullptr, N * H, pl.nseg, D * M, 1, st);
     if (rc) return rc;
 
     // grad_Q_i = sum_{j<=i} (g_i . v_j) k_j + S_init g_i        state viewed as [M][D]
-    rc = launch_scan(g, v, k, gq, gs, vs, ks, gqs, N, H, L, (int)M, (int)D, dtype, pl, wsS,
+    rc = launch_scan(mode, g, v, k, gq, gs, vs, ks, gqs, N, H, L, (int)M, (int)D, dtype, pl, wsS,
                      pl.nseg, 0, 0, st);
     if (rc) return rc;
     // grad_K_j = sum_{i>=j} (v_j . g_i) q_i + R_init v_j        state viewed as [M][D]
-    rc = launch_scan(v, g, q, gk, vs, gs, qs, gks, N, H, L, (int)M, (int)D, dtype, pl, wsR,
+    rc = launch_scan(mode, v, g, q, gk, vs, gs, qs, gks, N, H, L, (int)M, (int)D, dtype, pl, wsR,
                      pl.nseg, 0, 1, st);
     if (rc) return rc;
     // grad_V_j = sum_{i>=j} (k_j . q_i) g_i + R_init^T k_j      state viewed as [D][M]
-    return launch_scan(k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl, wsR,
+    return launch_scan(mode, k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl, wsR,
                        pl.nseg, 1, 1, st);
 }
 
@@ -362,14 +452,14 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
         return FTB_OK;
     }
     if (!x || !y) return FTB_ERR_INVALID;
-    Plan pl = simt_plan(N * H, L);
+    Plan pl = choose_plan(mode, N * H, L);
     if (pl.nseg == 1) {
-        return launch_state_sum(x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, state, st);
+        return launch_state_sum(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, state, st);
     }
     size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, 1);
     if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
     float *ws = (float *)workspace;
-    rc = launch_state_sum(x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, ws, st);
+    rc = launch_state_sum(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, ws, st);
     if (rc) return rc;
     return launch_prefix(ws, nullptr, state, N * H, pl.nseg, D * M, 0, st);
 }

@@ -1,0 +1,130 @@
+// Host-side launch logic of the tensor-core mode: TMA descriptors, segment plan, launches.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <utility>
+
+#include "mma_scan.cuh"
+
+namespace ftb {
+namespace mma {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up through the runtime, so the library carries no link
+// dependency on libcuda and still loads on a machine without a driver.
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = (EncodeTiledFn)p;
+    return fn;
+}
+
+// Tensor map over a (N, H, L, dim) view with element strides {n, h, l}.  The innermost
+// dimension is the row; the other three are ordered by ascending stride (a permuted view such
+// as (N, L, H, dim) storage has the head stride below the position stride), and `pos` receives
+// the slot (1..3) of the position, head and batch coordinates.  One box is {128 bytes of the
+// row, C positions}.  Returns FTB_OK, FTB_ERR_ALIGNMENT (TMA needs a 16-byte aligned base and
+// strides that are positive multiples of 16 bytes) or FTB_ERR_CUDA.
+static int make_map(CUtensorMap *map, int *pos, const void *base, int64_t N, int64_t H, int64_t L,
+                    int64_t dim, const int64_t *s, int dtype, bool atom32 = false) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return FTB_ERR_CUDA;
+    const int64_t es = dtype == FTB_F32 ? 4 : 2;
+    if (((uintptr_t)base & 15) != 0) return FTB_ERR_ALIGNMENT;
+    // extent, stride and role (0 = position, 1 = head, 2 = batch) of the three outer dimensions;
+    // a dimension of extent 1 may carry any stride: give it one larger than everything else
+    int64_t ext[3] = {L, H, N}, str[3] = {s[2], s[1], s[0]};
+    int role[3] = {0, 1, 2};
+    int64_t big = dim;
+    for (int i = 0; i < 3; ++i)
+        if (ext[i] > 1 && str[i] * ext[i] > big) big = str[i] * ext[i];
+    big = (big + 7) / 8 * 8;
+    for (int i = 0; i < 3; ++i) {
+        if (ext[i] <= 1) str[i] = big * (i + 1);
+        if (str[i] <= 0 || (str[i] * es) % 16) return FTB_ERR_ALIGNMENT;
+    }
+    for (int i = 0; i < 3; ++i)
+        for (int j = i + 1; j < 3; ++j)
+            if (str[j] < str[i]) {
+                std::swap(str[i], str[j]);
+                std::swap(ext[i], ext[j]);
+                std::swap(role[i], role[j]);
+            }
+    cuuint64_t gdim[4] = {(cuuint64_t)dim, (cuuint64_t)ext[0], (cuuint64_t)ext[1], (cuuint64_t)ext[2]};
+    cuuint64_t gstr[3] = {(cuuint64_t)(str[0] * es), (cuuint64_t)(str[1] * es), (cuuint64_t)(str[2] * es)};
+    cuuint32_t box[4] = {(cuuint32_t)(128 / es), 1, 1, 1};
+    for (int i = 0; i < 3; ++i) {
+        pos[role[i]] = i;
+        if (role[i] == 0) box[1 + i] = (cuuint32_t)C;
+    }
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, dtype == FTB_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                     4, const_cast<void *>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? FTB_OK : FTB_ERR_ALIGNMENT;
+}
+
+struct Plan {
+    int64_t seg_len;
+    int nseg;
+};
+
+// Segments are whole chunks.  The target is about two CTAs' worth of segments per SM over the
+// grid, bounded below by two chunks per segment so the per-segment state traffic stays small
+// next to the rows it covers.  FTB200_MMA_SEGS=<n> forces the number of segments (tuning).
+static Plan plan(int64_t BH, int64_t L, int ntile) {
+    Plan p;
+    const int64_t chunks = (L + C - 1) / C;
+    int64_t nseg = 1;
+    static const char *env = std::getenv("FTB200_MMA_SEGS");
+    if (env && std::atoi(env) > 0) {
+        nseg = std::atoi(env);
+    } else {
+        const int64_t target = 148 * 2;
+        nseg = (target + BH * ntile - 1) / (BH * ntile);
+        const int64_t max_seg = (chunks + 1) / 2;   // at least two chunks per segment
+        if (nseg > max_seg) nseg = max_seg;
+    }
+    if (nseg < 1) nseg = 1;
+    if (nseg > chunks) nseg = chunks > 0 ? chunks : 1;
+    int64_t cps = (chunks + nseg - 1) / nseg;
+    if (cps < 1) cps = 1;
+    p.seg_len = cps * C;
+    p.nseg = (int)((L + p.seg_len - 1) / p.seg_len);
+    if (p.nseg < 1) p.nseg = 1;
+    return p;
+}
+
+// Which (dtype, Da, Dc) combinations have a tensor-core kernel.
+static bool supported(int dtype, int64_t Da, int64_t Dc) {
+    if (dtype == FTB_F32) return Da == 64 && Dc % 64 == 0 && Dc >= 64;
+    return Da == 128 && Dc % 128 == 0 && Dc >= 128;
+}
+
+template <typename T, int DA, int DCT>
+static cudaError_t launch_t(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mbmn,
+                            const CUtensorMap &mc, const ScanParams &p, int64_t blocks,
+                            cudaStream_t st) {
+    using K = Cfg<T, DA, DCT>;
+    auto kern = mma_scan_kernel<T, DA, DCT>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)K::SMEM);
+    if (e != cudaSuccess) return e;
+    kern<<<(unsigned)blocks, NTHREADS, K::SMEM, st>>>(ma, mb, mbmn, mc, p);
+    return cudaGetLastError();
+}
+
+}  // namespace mma
+}  // namespace ftb

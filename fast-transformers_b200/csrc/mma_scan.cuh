@@ -1,0 +1,696 @@
+// Tensor-core (tcgen05 / TMEM / TMA) segment scan of the causal linear-attention product.
+//
+// One CTA walks one segment of one (batch, head) pair in chunks of C = 128 rows.  With the
+// role triple (a, b, c) = (Q, K, V) -- and (G, V, K), (V, G, Q), (K, Q, G) for the three
+// gradients, the last two with rows walked downwards and the mask flipped -- a chunk is
+//
+//   P   = a_c b_c^T                      tcgen05.mma  128 x 128, K = DA     (smem x smem)
+//   O   = a_c S                          tcgen05.mma  128 x DCT, K = DA     (smem x smem)
+//   O  += mask(P) c_c                    tcgen05.mma  128 x DCT, K = 128    (TMEM x smem)
+//   S  += b_c^T c_c                      tcgen05.mma  DA  x DCT, K = 128    (smem x smem)
+//
+// P, O and the fp32 running state S live in tensor memory.  a_c, b_c, c_c arrive by TMA
+// (128-byte swizzle) in a two-stage mbarrier ring; one tile layout serves as K-major operand
+// (P, a S) and as MN-major operand (mask(P) c, b^T c).  Four worker warps own one TMEM lane
+// (= one row) each: they apply the causal mask to P in place (only the diagonal 32x32 blocks
+// need arithmetic), write O rows to global memory, and copy the updated state to shared
+// memory where the next chunk's "a_c S" product reads it as an operand (TF32 reads the fp32
+// bits; the bf16 variant rounds this operand copy only -- the accumulated state stays fp32).
+//
+// Warp roles: warp 0 = TMA producer (+ TMEM allocation), warp 1 = MMA issuer, warps 2-5 =
+// workers.  Every wait is bounded: on expiry the CTA records FTB_ERR_TIMEOUT in a device
+// status word, stops issuing work, releases its tensor memory and returns.
+//
+// Maths: fast_transformers/causal_product/causal_product_cpu.cpp:106-121, :165-206 in blocks.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "simt_scan.cuh"
+
+namespace ftb {
+namespace mma {
+
+constexpr int C = 128;          // rows per chunk
+constexpr int NTHREADS = 192;   // 6 warps
+constexpr int STAGES = 2;
+
+__device__ int g_device_status = 0;   // 0 ok, else FTB_ERR_* recorded by a kernel
+
+struct ScanParams {
+    void *out;            // output tensor (scan) or nullptr (state only)
+    Strides3 so;
+    int H;
+    int64_t L;
+    int Dc;               // full width of c / out rows
+    int64_t seg_len;      // multiple of C
+    int nseg;
+    const float *states;  // initial state per (bh, seg): canonical [D][M] blocks, or nullptr
+    float *state_out;     // state-only mode: per (bh, seg) totals, canonical [DA][Dc]
+    int canon_is_DaDc;    // canonical block is [DA][Dc] (1) or [Dc][DA] (0)
+    int reverse;
+    int state_only;
+    int terms;            // bit0: a S term, bit1: mask(P) c term, bit2: state update
+    int pos_a[3], pos_b[3], pos_c[3];   // TMA coordinate slot of {position, head, batch}
+};
+
+// ---- small PTX wrappers -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait.  Returns false after ~2 s of polling or when another role has given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > 4000000000LL) {
+                *abort_flag = 1;
+                atomicExch(&g_device_status, 5 /* FTB_ERR_TIMEOUT */);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int c0, const int *pos, int row, int head, int batch) {
+    int crd[3];
+    crd[pos[0]] = row;
+    crd[pos[1]] = head;
+    crd[pos[2]] = batch;
+    const int c1 = crd[0], c2 = crd[1], c3 = crd[2];
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+template <bool F16>
+__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    if constexpr (F16) {
+        asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n" ::"r"(d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+template <bool F16>
+__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    if constexpr (F16) {
+        asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d),
+            "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d),
+            "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+        "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// ---- descriptors ----------------------------------------------------------------------------
+// Shared-memory matrix descriptor (descriptor version 1).  layout 2 = 128-byte swizzle with
+// 16-byte atoms (K-major operands, and MN-major 16-bit operands); layout 1 = 128-byte swizzle
+// with 32-byte atoms, the only layout MN-major 32-bit (TF32) operands may use.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout = 2) {
+    uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)layout << 61;
+    return d;
+}
+// Instruction descriptor: fp32 accumulate; fmt 1 = bf16, 2 = tf32; *_mn = 1 for MN-major.
+__host__ __device__ constexpr uint32_t instr_desc(int fmt, int a_mn, int b_mn, int M, int N) {
+    return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)a_mn << 15) |
+           ((uint32_t)b_mn << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+template <typename T, int DA, int DCT>
+struct Cfg {
+    static constexpr bool F16 = sizeof(T) == 2;
+    static constexpr int EPB = 128 / sizeof(T);           // elements per 128-byte block
+    static constexpr int KROWS = 32 / sizeof(T);          // K extent of one instruction
+    static constexpr int A_BLKS = DA / EPB;               // 128-byte blocks per a/b row
+    static constexpr int C_BLKS = DCT / EPB;
+    static constexpr int BLK_BYTES = C * 128;             // one [C rows][128 B] block
+    static constexpr int A_BYTES = A_BLKS * BLK_BYTES;
+    static constexpr int C_BYTES = C_BLKS * BLK_BYTES;
+    static constexpr int STAGE_BYTES = 2 * A_BYTES + C_BYTES;
+    static constexpr int SM_BLK_BYTES = DA * 128;          // state operand: [DA rows][128 B]
+    static constexpr int SM_BYTES = C_BLKS * SM_BLK_BYTES;
+    static constexpr int NOBUF = (256 + 2 * DCT + DCT <= 512) ? 2 : 1;
+    static constexpr int TM_P = 0;                         // two score buffers, 128 columns each
+    static constexpr int TM_O = 256;
+    static constexpr int TM_S = 256 + NOBUF * DCT;
+    static constexpr int FMT = F16 ? 1 : 2;
+    // MN-major operands: 16-bit types share the K-major tile image (layout 2, 8-row atoms);
+    // TF32 needs the 32-byte-atom swizzle (layout 1, 4-row atoms), so the b tile -- read
+    // K-major by the score product and MN-major by the state update -- is fetched twice into
+    // the same slot, the second time once the score product has consumed the first image.
+    static constexpr bool RELOAD_B = !F16;
+    static constexpr uint32_t MN_LAYOUT = F16 ? 2 : 1;
+    static constexpr uint32_t MN_SBO = F16 ? 1024 : 512;
+    static constexpr size_t SMEM = 1024 /* alignment slack */ + STAGES * STAGE_BYTES + SM_BYTES + 256;
+    static_assert(DA % EPB == 0 && DCT % EPB == 0, "rows must be whole 128-byte blocks");
+    static_assert(DA == 64 || DA == 128, "state rows map to 64 or 128 TMEM lanes");
+    static_assert(TM_S + DCT <= 512, "tensor memory budget");
+};
+
+template <typename T, int DA, int DCT>
+__global__ void __launch_bounds__(NTHREADS, 1)
+mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_bmn, const __grid_constant__ CUtensorMap map_c,
+                const ScanParams p) {
+    using K = Cfg<T, DA, DCT>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t stage0 = smem_base;
+    const uint32_t sm_state = smem_base + STAGES * K::STAGE_BYTES;
+    uint8_t *sm_state_gen = smem_gen + STAGES * K::STAGE_BYTES;
+    const uint32_t bars = sm_state + K::SM_BYTES;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(sm_state_gen + K::SM_BYTES + 192);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm_state_gen + K::SM_BYTES + 200);
+    // barrier addresses (8 bytes each)
+    const uint32_t bar_full = bars, bar_empty = bars + 16, bar_pfull = bars + 32,
+                   bar_pready = bars + 48, bar_ofull = bars + 64, bar_ofree = bars + 80,
+                   bar_sfull = bars + 96, bar_smready = bars + 104, bar_fullc = bars + 112,
+                   bar_bkfree = bars + 128;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- work item ---------------------------------------------------------------------------
+    const int ntile = p.Dc / DCT;
+    int64_t bid = blockIdx.x;
+    const int tile = (int)(bid % ntile);
+    bid /= ntile;
+    const int seg = (int)(bid % p.nseg);
+    const int64_t bh = bid / p.nseg;
+    const int bn = (int)(bh / p.H), bhh = (int)(bh % p.H);
+    const int n0 = tile * DCT;
+    const int64_t seg_begin = (int64_t)seg * p.seg_len;
+    const int64_t seg_end = min(p.L, seg_begin + p.seg_len);
+    const int nchunk = (int)((seg_end - seg_begin + C - 1) / C);
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+            mbar_init(bar_pfull + 8 * s, 1);
+            mbar_init(bar_pready + 8 * s, 128);
+            mbar_init(bar_ofull + 8 * s, 1);
+            mbar_init(bar_ofree + 8 * s, 128);
+            mbar_init(bar_fullc + 8 * s, K::RELOAD_B ? 2 : 1);
+            mbar_init(bar_bkfree + 8 * s, 1);
+        }
+        mbar_init(bar_sfull, 1);
+        mbar_init(bar_smready, 128);
+        fence_barrier_init();
+    }
+    if (warp == 0) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (nchunk > 0) {
+        if (warp == 0) {
+            // ================= TMA producer =====================================================
+            // bar_full[s]  : a and the K-major image of b have landed (score product, a S)
+            // bar_fullc[s] : c and the MN-major image of b have landed (mask(P) c, state update)
+            if (lane == 0) {
+                auto load_b_mn = [&](int ci) {
+                    const int c = p.reverse ? nchunk - 1 - ci : ci;
+                    const int s = ci & 1;
+                    const int row = (int)(seg_begin + (int64_t)c * C);
+                    const uint32_t st = stage0 + s * K::STAGE_BYTES;
+                    mbar_expect_tx(bar_fullc + 8 * s, K::A_BYTES);
+#pragma unroll
+                    for (int b = 0; b < K::A_BLKS; ++b)
+                        tma_load_4d(st + K::A_BYTES + b * K::BLK_BYTES, &map_bmn, bar_fullc + 8 * s,
+                                    b * K::EPB, p.pos_b, row, bhh, bn);
+                };
+                bool ok = true;
+                for (int ci = 0; ci < nchunk && ok; ++ci) {
+                    const int c = p.reverse ? nchunk - 1 - ci : ci;
+                    const int s = ci & 1, use = ci >> 1;
+                    ok = mbar_wait(bar_empty + 8 * s, (use & 1) ^ 1, abort_flag);
+                    if (!ok) break;
+                    const int row = (int)(seg_begin + (int64_t)c * C);
+                    const uint32_t st = stage0 + s * K::STAGE_BYTES;
+                    if (!p.state_only) {
+                        mbar_expect_tx(bar_full + 8 * s, 2 * K::A_BYTES);
+#pragma unroll
+                        for (int b = 0; b < K::A_BLKS; ++b)
+                            tma_load_4d(st + b * K::BLK_BYTES, &map_a, bar_full + 8 * s, b * K::EPB,
+                                        p.pos_a, row, bhh, bn);
+#pragma unroll
+                        for (int b = 0; b < K::A_BLKS; ++b)
+                            tma_load_4d(st + K::A_BYTES + b * K::BLK_BYTES, &map_b, bar_full + 8 * s,
+                                        b * K::EPB, p.pos_b, row, bhh, bn);
+                    }
+                    const bool b_with_c = p.state_only && !K::RELOAD_B;
+                    mbar_expect_tx(bar_fullc + 8 * s, K::C_BYTES + (b_with_c ? K::A_BYTES : 0));
+#pragma unroll
+                    for (int b = 0; b < K::C_BLKS; ++b)
+                        tma_load_4d(st + 2 * K::A_BYTES + b * K::BLK_BYTES, &map_c, bar_fullc + 8 * s,
+                                    n0 + b * K::EPB, p.pos_c, row, bhh, bn);
+                    if (b_with_c) {
+#pragma unroll
+                        for (int b = 0; b < K::A_BLKS; ++b)
+                            tma_load_4d(st + K::A_BYTES + b * K::BLK_BYTES, &map_bmn, bar_fullc + 8 * s,
+                                        b * K::EPB, p.pos_b, row, bhh, bn);
+                    }
+                    if constexpr (K::RELOAD_B) {
+                        if (p.state_only) {
+                            load_b_mn(ci);
+                        } else if (ci >= 1) {
+                            // the score product of chunk ci-1 has consumed the K-major image
+                            ok = mbar_wait(bar_bkfree + 8 * ((ci - 1) & 1), ((ci - 1) >> 1) & 1, abort_flag);
+                            if (ok) load_b_mn(ci - 1);
+                        }
+                    }
+                }
+                if constexpr (K::RELOAD_B) {
+                    if (ok && !p.state_only) {
+                        ok = mbar_wait(bar_bkfree + 8 * ((nchunk - 1) & 1), ((nchunk - 1) >> 1) & 1, abort_flag);
+                        if (ok) load_b_mn(nchunk - 1);
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            // ================= MMA issuer =======================================================
+            if (lane == 0) {
+                constexpr uint32_t ID_P = instr_desc(K::FMT, 0, 0, 128, 128);
+                constexpr uint32_t ID_AS = instr_desc(K::FMT, 0, 1, 128, DCT);
+                constexpr uint32_t ID_PC = instr_desc(K::FMT, 0, 1, 128, DCT);
+                constexpr uint32_t ID_ST = instr_desc(K::FMT, 1, 1, DA, DCT);
+                constexpr int KSTEP_BYTES = K::KROWS * 128;   // MN-major advance along K
+                const uint32_t tS = tmem + K::TM_S;
+                bool ok = true;
+
+                auto issue_scores = [&](int ci) {
+                    const int s = ci & 1;
+                    const uint32_t st = stage0 + s * K::STAGE_BYTES;
+                    const uint32_t tP = tmem + K::TM_P + 128 * (ci & 1);
+#pragma unroll
+                    for (int b = 0; b < K::A_BLKS; ++b)
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            uint64_t ad = smem_desc(st + b * K::BLK_BYTES + k * 32, 16, 1024);
+                            uint64_t bd = smem_desc(st + K::A_BYTES + b * K::BLK_BYTES + k * 32, 16, 1024);
+                            mma_ss<K::F16>(tP, ad, bd, ID_P, (b | k) ? 1u : 0u);
+                        }
+                    tc_commit(bar_pfull + 8 * (ci & 1));
+                    if constexpr (K::RELOAD_B) tc_commit(bar_bkfree + 8 * (ci & 1));
+                };
+
+                if (p.state_only) {
+                    for (int ci = 0; ci < nchunk && ok; ++ci) {
+                        const int s = ci & 1, use = ci >> 1;
+                        ok = mbar_wait(bar_fullc + 8 * s, use & 1, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t st = stage0 + s * K::STAGE_BYTES;
+#pragma unroll
+                        for (int k = 0; k < C / K::KROWS; ++k) {
+                            uint64_t ad = smem_desc(st + K::A_BYTES + k * KSTEP_BYTES, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
+                            uint64_t bd = smem_desc(st + 2 * K::A_BYTES + k * KSTEP_BYTES, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
+                            mma_ss<K::F16>(tS, ad, bd, ID_ST, (ci | k) ? 1u : 0u);
+                        }
+                        tc_commit(bar_empty + 8 * s);
+                    }
+                    tc_commit(bar_sfull);
+                } else {
+                    ok = mbar_wait(bar_full, 0, abort_flag);
+                    if (ok) {
+                        tc_fence_after();
+                        issue_scores(0);
+                    }
+                    for (int ci = 0; ci < nchunk && ok; ++ci) {
+                        const int s = ci & 1;
+                        const uint32_t st = stage0 + s * K::STAGE_BYTES;
+                        const int ob = ci % K::NOBUF, ouse = ci / K::NOBUF;
+                        const uint32_t tO = tmem + K::TM_O + ob * DCT;
+                        const uint32_t tP = tmem + K::TM_P + 128 * (ci & 1);
+                        // O = a S   (needs the operand copy of the previous state and a free O)
+                        ok = mbar_wait(bar_smready, ci & 1, abort_flag) &&
+                             mbar_wait(bar_ofree + 8 * ob, (ouse & 1) ^ 1, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                        uint32_t acc = 0;
+                        if (p.terms & 1) {
+#pragma unroll
+                            for (int b = 0; b < K::A_BLKS; ++b)
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    const int krow = (b * K::EPB + k * K::KROWS);   // first state row
+                                    uint64_t ad = smem_desc(st + b * K::BLK_BYTES + k * 32, 16, 1024);
+                                    uint64_t bd = smem_desc(sm_state + krow * 128, K::SM_BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
+                                    mma_ss<K::F16>(tO, ad, bd, ID_AS, acc);
+                                    acc = 1;
+                                }
+                        }
+                        // O += mask(P) c
+                        ok = mbar_wait(bar_pready + 8 * (ci & 1), (ci >> 1) & 1, abort_flag) &&
+                             mbar_wait(bar_fullc + 8 * s, (ci >> 1) & 1, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                        if (p.terms & 2) {
+#pragma unroll
+                            for (int k = 0; k < C / K::KROWS; ++k) {
+                                uint64_t bd = smem_desc(st + 2 * K::A_BYTES + k * KSTEP_BYTES, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
+                                mma_ts<K::F16>(tO, tP + k * 8, bd, ID_PC, acc);
+                                acc = 1;
+                            }
+                        }
+                        tc_commit(bar_ofull + 8 * ob);
+                        // S += b^T c
+                        if (p.terms & 4) {
+#pragma unroll
+                            for (int k = 0; k < C / K::KROWS; ++k) {
+                                uint64_t ad = smem_desc(st + K::A_BYTES + k * KSTEP_BYTES, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
+                                uint64_t bd = smem_desc(st + 2 * K::A_BYTES + k * KSTEP_BYTES, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
+                                mma_ss<K::F16>(tS, ad, bd, ID_ST, 1u);
+                            }
+                        }
+                        tc_commit(bar_sfull);
+                        tc_commit(bar_empty + 8 * s);
+                        if (ci + 1 < nchunk) {
+                            ok = mbar_wait(bar_full + 8 * ((ci + 1) & 1), ((ci + 1) >> 1) & 1, abort_flag);
+                            if (!ok) break;
+                            tc_fence_after();
+                            issue_scores(ci + 1);
+                        }
+                    }
+                }
+            }
+        } else {
+            // ================= workers: one TMEM lane (row) per thread ===========================
+            const int q = warp & 3;
+            const int i = 32 * q + lane;                       // row inside the chunk / lane
+            const uint32_t tlane = tmem + ((uint32_t)(32 * q) << 16);
+            // state row handled by this thread (DA == 64: 16 lanes per sub-partition hold rows)
+            const bool srow_ok = (DA == 128) || (lane < 16);
+            const int srow = (DA == 128) ? i : (16 * q + (lane & 15));
+            uint32_t r[32];
+            bool ok = true;
+
+            auto store_state_operand = [&](int cb) {
+                // r[] holds state row `srow`, columns 32*cb .. 32*cb+31 (fp32 bits)
+                if (!srow_ok) return;
+                if constexpr (K::F16) {
+                    uint8_t *rowp = sm_state_gen + (cb >> 1) * K::SM_BLK_BYTES + srow * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        uint4 v;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * ch + 0]), __uint_as_float(r[8 * ch + 1]));
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * ch + 2]), __uint_as_float(r[8 * ch + 3]));
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * ch + 4]), __uint_as_float(r[8 * ch + 5]));
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * ch + 6]), __uint_as_float(r[8 * ch + 7]));
+                        v.x = *reinterpret_cast<uint32_t *>(&h0);
+                        v.y = *reinterpret_cast<uint32_t *>(&h1);
+                        v.z = *reinterpret_cast<uint32_t *>(&h2);
+                        v.w = *reinterpret_cast<uint32_t *>(&h3);
+                        const int chunk16 = ((cb & 1) * 4 + ch) ^ (srow & 7);
+                        *reinterpret_cast<uint4 *>(rowp + chunk16 * 16) = v;
+                    }
+                } else {
+                    uint8_t *rowp = sm_state_gen + cb * K::SM_BLK_BYTES + srow * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) {
+                        uint4 v = make_uint4(r[4 * ch], r[4 * ch + 1], r[4 * ch + 2], r[4 * ch + 3]);
+                        *reinterpret_cast<uint4 *>(rowp + (((ch >> 1) ^ (srow & 3)) * 32) + (ch & 1) * 16) = v;
+                    }
+                }
+            };
+
+            if (p.state_only) {
+                ok = mbar_wait(bar_sfull, 0, abort_flag);
+                if (ok) {
+                    tc_fence_after();
+                    float *dst = p.state_out + ((int64_t)bh * p.nseg + seg) * ((int64_t)DA * p.Dc);
+#pragma unroll
+                    for (int cb = 0; cb < DCT / 32; ++cb) {
+                        tmem_ld32(tlane + K::TM_S + 32 * cb, r);
+                        if (srow_ok) {
+                            float4 *d4 = reinterpret_cast<float4 *>(dst + (int64_t)srow * p.Dc + n0 + 32 * cb);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                d4[e] = make_float4(__uint_as_float(r[4 * e]), __uint_as_float(r[4 * e + 1]),
+                                                    __uint_as_float(r[4 * e + 2]), __uint_as_float(r[4 * e + 3]));
+                        }
+                    }
+                }
+            } else {
+                // ---- initial state -> TMEM accumulator and shared-memory operand ---------------
+                {
+                    const float *src = p.states
+                        ? p.states + ((int64_t)bh * p.nseg + seg) * ((int64_t)DA * p.Dc) : nullptr;
+#pragma unroll
+                    for (int cb = 0; cb < DCT / 32; ++cb) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            float v = 0.f;
+                            if (src && srow_ok) {
+                                const int dc = n0 + 32 * cb + e;
+                                v = p.canon_is_DaDc ? src[(int64_t)srow * p.Dc + dc]
+                                                    : src[(int64_t)dc * DA + srow];
+                            }
+                            r[e] = __float_as_uint(v);
+                        }
+                        tmem_st32(tlane + K::TM_S + 32 * cb, r);
+                        store_state_operand(cb);
+                    }
+                    tmem_wait_st();
+                    fence_proxy_async_smem();
+                    tc_fence_before();
+                    mbar_arrive(bar_smready);
+                }
+
+                T *O = reinterpret_cast<T *>(p.out) + (int64_t)bn * p.so.n + (int64_t)bhh * p.so.h;
+                for (int ci = 0; ci < nchunk && ok; ++ci) {
+                    const int c = p.reverse ? nchunk - 1 - ci : ci;
+                    const int64_t row0 = seg_begin + (int64_t)c * C;
+                    // ---- causal mask on the scores, in place ------------------------------------
+                    ok = mbar_wait(bar_pfull + 8 * (ci & 1), (ci >> 1) & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    {
+                        const uint32_t tP = tlane + K::TM_P + 128 * (ci & 1);
+#pragma unroll
+                        for (int cb = 0; cb < 4; ++cb) {
+                            // rows of this warp are 32q..32q+31, columns of the block 32cb..32cb+31
+                            const bool all_keep = p.reverse ? (cb > q) : (cb < q);
+                            const bool all_drop = p.reverse ? (cb < q) : (cb > q);
+                            if constexpr (!K::F16) {
+                                if (all_keep) continue;
+                                if (all_drop) {
+#pragma unroll
+                                    for (int e = 0; e < 32; ++e) r[e] = 0u;
+                                } else {
+                                    tmem_ld32(tP + 32 * cb, r);
+#pragma unroll
+                                    for (int e = 0; e < 32; ++e) {
+                                        const bool keep = p.reverse ? (e >= lane) : (e <= lane);
+                                        r[e] = keep ? r[e] : 0u;
+                                    }
+                                }
+                                tmem_st32(tP + 32 * cb, r);
+                            } else {
+                                uint32_t h[16];
+                                if (all_drop) {
+#pragma unroll
+                                    for (int e = 0; e < 16; ++e) h[e] = 0u;
+                                } else {
+                                    tmem_ld32(tP + 32 * cb, r);
+#pragma unroll
+                                    for (int e = 0; e < 16; ++e) {
+                                        float x0 = __uint_as_float(r[2 * e]), x1 = __uint_as_float(r[2 * e + 1]);
+                                        if (!all_keep) {
+                                            const bool k0 = p.reverse ? (2 * e >= lane) : (2 * e <= lane);
+                                            const bool k1 = p.reverse ? (2 * e + 1 >= lane) : (2 * e + 1 <= lane);
+                                            x0 = k0 ? x0 : 0.f;
+                                            x1 = k1 ? x1 : 0.f;
+                                        }
+                                        __nv_bfloat162 hh = __floats2bfloat162_rn(x0, x1);
+                                        h[e] = *reinterpret_cast<uint32_t *>(&hh);
+                                    }
+                                }
+                                tmem_st16(tP + 16 * cb, h);
+                            }
+                        }
+                        tmem_wait_st();
+                        tc_fence_before();
+                        mbar_arrive(bar_pready + 8 * (ci & 1));
+                    }
+                    // ---- updated state -> shared-memory operand of the next chunk ---------------
+                    ok = mbar_wait(bar_sfull, ci & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (ci + 1 < nchunk) {
+#pragma unroll
+                        for (int cb = 0; cb < DCT / 32; ++cb) {
+                            tmem_ld32(tlane + K::TM_S + 32 * cb, r);
+                            store_state_operand(cb);
+                        }
+                        fence_proxy_async_smem();
+                        tc_fence_before();
+                        mbar_arrive(bar_smready);
+                    }
+                    // ---- output rows ------------------------------------------------------------
+                    const int ob = ci % K::NOBUF, ouse = ci / K::NOBUF;
+                    ok = mbar_wait(bar_ofull + 8 * ob, ouse & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    {
+                        const int64_t row = row0 + i;
+                        T *dst = O + row * p.so.l + n0;
+#pragma unroll
+                        for (int cb = 0; cb < DCT / 32; ++cb) {
+                            tmem_ld32(tlane + K::TM_O + ob * DCT + 32 * cb, r);
+                            if (row < seg_end) {
+                                if constexpr (K::F16) {
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) {
+                                        uint4 v;
+                                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * e + 0]), __uint_as_float(r[8 * e + 1]));
+                                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * e + 2]), __uint_as_float(r[8 * e + 3]));
+                                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * e + 4]), __uint_as_float(r[8 * e + 5]));
+                                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * e + 6]), __uint_as_float(r[8 * e + 7]));
+                                        v.x = *reinterpret_cast<uint32_t *>(&h0);
+                                        v.y = *reinterpret_cast<uint32_t *>(&h1);
+                                        v.z = *reinterpret_cast<uint32_t *>(&h2);
+                                        v.w = *reinterpret_cast<uint32_t *>(&h3);
+                                        *reinterpret_cast<uint4 *>(dst + 32 * cb + 8 * e) = v;
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e)
+                                        *reinterpret_cast<uint4 *>(dst + 32 * cb + 4 * e) =
+                                            make_uint4(r[4 * e], r[4 * e + 1], r[4 * e + 2], r[4 * e + 3]);
+                                }
+                            }
+                        }
+                        tc_fence_before();
+                        mbar_arrive(bar_ofree + 8 * ob);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- teardown: everyone meets here, tensor memory is returned ------------------------------
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace mma
+}  // namespace ftb

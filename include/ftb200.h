@@ -84,6 +84,12 @@ int ftb_last_cuda_error(void);
 #define FTB_KERNEL_MMA_STATE 5    /* tcgen05 per-segment totals                      */
 #define FTB_KERNEL_KINDS 8
 uint64_t ftb_launch_count(void);
+/*
+ * Device-side status word of the current device: 0, or the FTB_ERR_* code recorded by a kernel
+ * whose bounded wait expired (FTB_ERR_TIMEOUT).  Synchronises the device.  reset != 0 clears it.
+ * The reference has no counterpart (its kernels contain no waits).
+ */
+int ftb_device_status(int reset);
 void ftb_timing_enable(int enable);
 int ftb_timing_read(float *ms_by_kind, int *launches_by_kind, int nkinds);
 
