@@ -273,7 +273,7 @@ def main():
     per_launch_elems = {
         "simt_scan": (2 * D + 2 * M),               # averaged over the four role permutations
         "mma_fwd": (2 * D + 2 * M),
-        "mma_bwd": (4 * D + 3 * M),
+        "mma_bwd": (2 * D + 2 * M),
         "state_sum": (D + M),
         "mma_state": (D + M),
     }.get(top_name, 0)

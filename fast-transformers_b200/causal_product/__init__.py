@@ -74,7 +74,7 @@ def _state_ok(s, N, H, D, M, dev, name):
 
 
 def causal_dot_product_cuda(queries, keys, values, product, mode=None, initial_state=None,
-                            final_state=None):
+                            final_state=None, keep_workspace=None):
     """Fill ``product`` (N, H, L, M) in place -- the reference's native forward signature
     (``causal_product_cuda.cu:1273-1276``), plus optional fp32 states (N, H, D, M)."""
     dev = _check_cuda(queries, keys, values, product)
@@ -106,11 +106,14 @@ def causal_dot_product_cuda(queries, keys, values, product, mode=None, initial_s
             _native.strides3(product), dt, m, _ptr(initial_state), _ptr(final_state),
             _ptr(ws), nbytes, ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     _native.check(st, "ftb_causal_dot_product")
+    if keep_workspace is not None:
+        # the per-segment forward states; the backward pass reuses them if handed back
+        keep_workspace.append(ws)
 
 
 def causal_dot_backward_cuda(queries, keys, values, grad_out, grad_queries, grad_keys,
                              grad_values, mode=None, initial_state=None,
-                             initial_grad_state=None):
+                             initial_grad_state=None, forward_workspace=None):
     """Fill the three gradients in place -- the reference's native backward signature
     (``causal_product_cuda.cu:1438-1444``).  ``grad_out`` may be any view (expanded,
     permuted); it is made row-contiguous only if its last stride is not 1."""
@@ -139,7 +142,7 @@ def causal_dot_backward_cuda(queries, keys, values, grad_out, grad_queries, grad
             _native.strides3(q), _native.strides3(k), _native.strides3(v), _native.strides3(g),
             _native.strides3(grad_queries), _native.strides3(grad_keys),
             _native.strides3(grad_values), dt, m, _ptr(initial_state),
-            _ptr(initial_grad_state), _ptr(ws), nbytes,
+            _ptr(initial_grad_state), _ptr(forward_workspace), _ptr(ws), nbytes,
             ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     _native.check(st, "ftb_causal_dot_backward")
 
@@ -190,7 +193,13 @@ class CausalDotProduct(torch.autograd.Function):
         M = V.shape[3]
         # the reference allocates zeros (its fallback kernels accumulate); ours overwrite
         product = torch.empty((N, H, L, M), device=Q.device, dtype=Q.dtype)
-        CausalDotProduct.dot[Q.device.type](Q.data, K.data, V.data, product, ctx.mode)
+        kept = []
+        fwd = CausalDotProduct.dot[Q.device.type]
+        if fwd is causal_dot_product_cuda:
+            fwd(Q.data, K.data, V.data, product, ctx.mode, keep_workspace=kept)
+        else:   # a replacement installed with the reference's four-argument signature
+            fwd(Q.data, K.data, V.data, product)
+        ctx.forward_workspace = kept[0] if kept else None
         return product
 
     @staticmethod
@@ -199,8 +208,12 @@ class CausalDotProduct(torch.autograd.Function):
         grad_Q = torch.empty(Q.shape, device=Q.device, dtype=Q.dtype)
         grad_K = torch.empty(K.shape, device=K.device, dtype=K.dtype)
         grad_V = torch.empty(V.shape, device=V.device, dtype=V.dtype)
-        CausalDotProduct.dot_backward[Q.device.type](
-            Q.data, K.data, V.data, grad_out, grad_Q, grad_K, grad_V, ctx.mode)
+        bwd = CausalDotProduct.dot_backward[Q.device.type]
+        if bwd is causal_dot_backward_cuda:
+            bwd(Q.data, K.data, V.data, grad_out, grad_Q, grad_K, grad_V, ctx.mode,
+                forward_workspace=ctx.forward_workspace)
+        else:
+            bwd(Q.data, K.data, V.data, grad_out, grad_Q, grad_K, grad_V)
         return grad_Q, grad_K, grad_V
 
 

@@ -163,7 +163,8 @@ static int simt_launch_scan(const void *a, const void *b, const void *c, void *o
 static int mma_launch(const void *a, const void *b, const void *c, void *out, const int64_t *as,
                       const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H,
                       int64_t L, int Da, int Dc, int dtype, Plan pl, const float *states,
-                      float *state_out, int canon_is_DaDc, int reverse, cudaStream_t st) {
+                      const float *init, int sum_mode, float *state_out, int skip_seg,
+                      int canon_is_DaDc, int reverse, cudaStream_t st) {
     const bool state_only = (a == nullptr);
     const int DCT = dtype == FTB_F32 ? 64 : 128;
     // fp32 (TF32) operands read MN-major need the 32-byte-atom swizzle; bf16 uses one image
@@ -191,6 +192,7 @@ static int mma_launch(const void *a, const void *b, const void *c, void *out, co
     p.H = (int)H; p.L = L; p.Dc = Dc;
     p.seg_len = pl.seg_len; p.nseg = pl.nseg;
     p.states = states; p.state_out = state_out;
+    p.init = init; p.sum_mode = sum_mode; p.skip_seg = skip_seg;
     p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = state_only ? 1 : 0;
     static const char *env = std::getenv("FTB200_MMA_TERMS");
     p.terms = env ? std::atoi(env) : 7;
@@ -217,23 +219,67 @@ static Plan choose_plan(int mode, int64_t BH, int64_t L) {
 
 static int launch_state_sum(int mode, const void *x, const void *y, const int64_t *xs,
                             const int64_t *ys, int64_t N, int64_t H, int64_t L, int D, int M,
-                            int dtype, Plan pl, float *states, cudaStream_t st) {
+                            int dtype, Plan pl, float *states, int skip_seg, cudaStream_t st) {
     if (mode == FTB_MODE_MMA)
         return mma_launch(nullptr, x, y, nullptr, nullptr, xs, ys, nullptr, N, H, L, D, M, dtype, pl,
-                          nullptr, states, 1, 0, st);
+                          nullptr, nullptr, 0, states, skip_seg, 1, 0, st);
     return simt_launch_state_sum(x, y, xs, ys, N, H, L, D, M, dtype, pl, states, st);
 }
+
+// Where a scan finds the state each of its segments starts from.
+struct SegStates {
+    const float *states;  // per (bh, seg) blocks, or nullptr
+    const float *init;    // per bh block added on top, or nullptr
+    int sum_mode;         // 1: `states` are raw totals the kernel adds up itself
+};
 
 static int launch_scan(int mode, const void *a, const void *b, const void *c, void *out,
                        const int64_t *as, const int64_t *bs, const int64_t *cs, const int64_t *os,
                        int64_t N, int64_t H, int64_t L, int Da, int Dc, int dtype, Plan pl,
-                       const float *states, int nseg_states, int canon_is_DaDc, int reverse,
-                       cudaStream_t st) {
+                       SegStates ss, int canon_is_DaDc, int reverse, cudaStream_t st) {
     if (mode == FTB_MODE_MMA)
-        return mma_launch(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, states, nullptr,
-                          canon_is_DaDc, reverse, st);
-    return simt_launch_scan(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, states,
-                            nseg_states, canon_is_DaDc, reverse, st);
+        return mma_launch(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, ss.states, ss.init,
+                          ss.sum_mode, nullptr, -1, canon_is_DaDc, reverse, st);
+    return simt_launch_scan(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl,
+                            ss.states ? ss.states : ss.init, pl.nseg, canon_is_DaDc, reverse, st);
+}
+
+static inline bool sums_in_kernel(int mode, Plan pl) {
+    return mode == FTB_MODE_MMA && pl.nseg <= mma::kSumInKernelMaxSegs;
+}
+
+// Describe segment-start states that already sit in `ws` (written by prepare_states).
+static SegStates describe_states(int mode, Plan pl, const float *ws, const float *init) {
+    if (pl.nseg == 1) return SegStates{nullptr, init, 0};
+    if (sums_in_kernel(mode, pl)) return SegStates{ws, init, 1};
+    return SegStates{ws, nullptr, 0};   // exclusive prefixes with `init` folded in
+}
+
+// Per-segment totals of sum x (x) y into `ws`, turned into what the scans read; optionally the
+// grand total (init + all segments) into `total`.
+static int prepare_states(int mode, const void *x, const void *y, const int64_t *xs, const int64_t *ys,
+                          int64_t N, int64_t H, int64_t L, int D, int M, int dtype, Plan pl, float *ws,
+                          const float *init, float *total, int reverse, cudaStream_t st,
+                          SegStates *out) {
+    *out = describe_states(mode, pl, ws, init);
+    if (pl.nseg == 1 && !total) return FTB_OK;
+    int rc;
+    if (sums_in_kernel(mode, pl)) {
+        const int skip = total ? -1 : (reverse ? 0 : pl.nseg - 1);
+        rc = launch_state_sum(mode, x, y, xs, ys, N, H, L, D, M, dtype, pl, ws, skip, st);
+        if (rc || !total) return rc;
+        int64_t n = N * H * (int64_t)D * M;
+        LaunchScope scope(FTB_KERNEL_STATE_PREFIX, st);
+        state_total_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ws, init, total, N * H, pl.nseg,
+                                                                       (int64_t)D * M);
+        FTB_CUDA(cudaGetLastError());
+        return FTB_OK;
+    }
+    rc = launch_state_sum(mode, x, y, xs, ys, N, H, L, D, M, dtype, pl, ws, -1, st);
+    if (rc) return rc;
+    rc = launch_prefix(ws, init, total, N * H, pl.nseg, (int64_t)D * M, reverse, st);
+    if (pl.nseg == 1) *out = SegStates{ws, nullptr, 0};
+    return rc;
 }
 
 static int check_common(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M, int dtype, int mode) {
@@ -363,19 +409,17 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
     }
 
     Plan pl = choose_plan(mode, N * H, L);
-    const float *states = initial_state;   // nseg == 1: the initial state is the segment state
+    float *ws = (float *)workspace;
     if (pl.nseg > 1 || final_state) {
         size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, final_state != nullptr);
         if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
-        float *ws = (float *)workspace;
-        rc = launch_state_sum(mode, k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, ws, st);
-        if (rc) return rc;
-        rc = launch_prefix(ws, initial_state, final_state, N * H, pl.nseg, D * M, 0, st);
-        if (rc) return rc;
-        states = ws;
     }
-    return launch_scan(mode, q, k, v, out, qs, ks, vs, os, N, H, L, (int)D, (int)M, dtype, pl, states,
-                       pl.nseg, /*canon_is_DaDc=*/1, /*reverse=*/0, st);
+    SegStates ss;
+    rc = prepare_states(mode, k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, ws, initial_state,
+                        final_state, 0, st, &ss);
+    if (rc) return rc;
+    return launch_scan(mode, q, k, v, out, qs, ks, vs, os, N, H, L, (int)D, (int)M, dtype, pl, ss,
+                       /*canon_is_DaDc=*/1, /*reverse=*/0, st);
 }
 
 int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const void *g, void *gq,
@@ -383,8 +427,8 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
                             int64_t M, const int64_t *qs, const int64_t *ks, const int64_t *vs,
                             const int64_t *gs, const int64_t *gqs, const int64_t *gks,
                             const int64_t *gvs, int dtype, int mode, const float *initial_state,
-                            const float *initial_grad_state, void *workspace,
-                            size_t workspace_bytes, void *stream) {
+                            const float *initial_grad_state, const void *forward_workspace,
+                            void *workspace, size_t workspace_bytes, void *stream) {
     int rc = check_common(N, H, L, D, M, dtype, mode);
     if (rc != FTB_OK) return rc;
     if (!qs || !ks || !vs || !gs || !gqs || !gks || !gvs) return FTB_ERR_INVALID;
@@ -411,30 +455,31 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
 
     Plan pl = choose_plan(mode, N * H, L);
     size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 1, 0);
-    if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
+    if (need && (!workspace || workspace_bytes < need)) return FTB_ERR_WORKSPACE;
     float *wsS = (float *)workspace;
     float *wsR = (float *)((char *)workspace + need / 2);
 
-    rc = launch_state_sum(mode, k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, wsS, st);
-    if (rc) return rc;
-    rc = launch_prefix(wsS, initial_state, nullptr, N * H, pl.nseg, D * M, 0, st);
-    if (rc) return rc;
-    rc = launch_state_sum(mode, q, g, qs, gs, N, H, L, (int)D, (int)M, dtype, pl, wsR, st);
-    if (rc) return rc;
-    rc = launch_prefix(wsR, initial_grad_state, nullptr, N * H, pl.nseg, D * M, 1, st);
+    // forward states: taken from the forward call's workspace when the caller kept it
+    SegStates sS, sR;
+    if (forward_workspace && pl.nseg > 1) {
+        sS = describe_states(mode, pl, (const float *)forward_workspace, initial_state);
+    } else {
+        rc = prepare_states(mode, k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, wsS, initial_state,
+                            nullptr, 0, st, &sS);
+        if (rc) return rc;
+    }
+    rc = prepare_states(mode, q, g, qs, gs, N, H, L, (int)D, (int)M, dtype, pl, wsR, initial_grad_state,
+                        nullptr, 1, st, &sR);
     if (rc) return rc;
 
     // grad_Q_i = sum_{j<=i} (g_i . v_j) k_j + S_init g_i        state viewed as [M][D]
-    rc = launch_scan(mode, g, v, k, gq, gs, vs, ks, gqs, N, H, L, (int)M, (int)D, dtype, pl, wsS,
-                     pl.nseg, 0, 0, st);
+    rc = launch_scan(mode, g, v, k, gq, gs, vs, ks, gqs, N, H, L, (int)M, (int)D, dtype, pl, sS, 0, 0, st);
     if (rc) return rc;
     // grad_K_j = sum_{i>=j} (v_j . g_i) q_i + R_init v_j        state viewed as [M][D]
-    rc = launch_scan(mode, v, g, q, gk, vs, gs, qs, gks, N, H, L, (int)M, (int)D, dtype, pl, wsR,
-                     pl.nseg, 0, 1, st);
+    rc = launch_scan(mode, v, g, q, gk, vs, gs, qs, gks, N, H, L, (int)M, (int)D, dtype, pl, sR, 0, 1, st);
     if (rc) return rc;
     // grad_V_j = sum_{i>=j} (k_j . q_i) g_i + R_init^T k_j      state viewed as [D][M]
-    return launch_scan(mode, k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl, wsR,
-                       pl.nseg, 1, 1, st);
+    return launch_scan(mode, k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl, sR, 1, 1, st);
 }
 
 int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, int64_t H,
@@ -453,15 +498,13 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
     }
     if (!x || !y) return FTB_ERR_INVALID;
     Plan pl = choose_plan(mode, N * H, L);
-    if (pl.nseg == 1) {
-        return launch_state_sum(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, state, st);
-    }
+    if (pl.nseg == 1)
+        return launch_state_sum(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, state, -1, st);
     size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, 1);
     if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
-    float *ws = (float *)workspace;
-    rc = launch_state_sum(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, ws, st);
-    if (rc) return rc;
-    return launch_prefix(ws, nullptr, state, N * H, pl.nseg, D * M, 0, st);
+    SegStates ss;
+    return prepare_states(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, (float *)workspace,
+                          nullptr, state, 0, st, &ss);
 }
 
 }  // extern "C"

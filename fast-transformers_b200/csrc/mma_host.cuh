@@ -82,25 +82,35 @@ struct Plan {
     int nseg;
 };
 
-// Segments are whole chunks.  The target is about two CTAs' worth of segments per SM over the
-// grid, bounded below by two chunks per segment so the per-segment state traffic stays small
-// next to the rows it covers.  FTB200_MMA_SEGS=<n> forces the number of segments (tuning).
+// Segments are whole chunks; one CTA walks one segment.  The count is chosen to minimise
+// waves x (chunks per segment + a fixed per-CTA cost) over the 148 SMs, with a small charge
+// per segment for its state traffic.  FTB200_MMA_SEGS=<n> forces the count (tuning only).
+constexpr int kSumInKernelMaxSegs = 8;   // up to here the scan kernel adds up raw totals itself
+
 static Plan plan(int64_t BH, int64_t L, int ntile) {
     Plan p;
     const int64_t chunks = (L + C - 1) / C;
-    int64_t nseg = 1;
+    int64_t best = 1;
     static const char *env = std::getenv("FTB200_MMA_SEGS");
     if (env && std::atoi(env) > 0) {
-        nseg = std::atoi(env);
-    } else {
-        const int64_t target = 148 * 2;
-        nseg = (target + BH * ntile - 1) / (BH * ntile);
-        const int64_t max_seg = (chunks + 1) / 2;   // at least two chunks per segment
-        if (nseg > max_seg) nseg = max_seg;
+        best = std::atoi(env);
+    } else if (chunks > 1 && BH > 0) {
+        double best_cost = 1e30;
+        for (int64_t t = 1; t <= chunks && t <= 64; ++t) {
+            const int64_t cps = (chunks + t - 1) / t;
+            const int64_t n = (chunks + cps - 1) / cps;
+            const int64_t ctas = BH * n * ntile;
+            const int64_t waves = (ctas + 147) / 148;
+            const double cost = (double)waves * ((double)cps + 1.0) + 0.3 * (double)n;
+            if (cost < best_cost - 1e-9) {
+                best_cost = cost;
+                best = n;
+            }
+        }
     }
-    if (nseg < 1) nseg = 1;
-    if (nseg > chunks) nseg = chunks > 0 ? chunks : 1;
-    int64_t cps = (chunks + nseg - 1) / nseg;
+    if (best < 1) best = 1;
+    if (best > chunks) best = chunks > 0 ? chunks : 1;
+    int64_t cps = (chunks + best - 1) / best;
     if (cps < 1) cps = 1;
     p.seg_len = cps * C;
     p.nseg = (int)((L + p.seg_len - 1) / p.seg_len);

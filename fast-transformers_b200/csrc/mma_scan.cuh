@@ -47,7 +47,12 @@ struct ScanParams {
     int Dc;               // full width of c / out rows
     int64_t seg_len;      // multiple of C
     int nseg;
-    const float *states;  // initial state per (bh, seg): canonical [D][M] blocks, or nullptr
+    const float *states;  // per (bh, seg) canonical [D][M] blocks, or nullptr (see sum_mode)
+    const float *init;    // per bh state added to every segment's start, or nullptr
+    int sum_mode;         // 0: states[bh][seg] is the state the segment starts from;
+                          // 1: states holds raw per-segment totals: the start state is their sum
+                          //    over the segments before (reverse: after) this one
+    int skip_seg;         // state-only mode: segment whose total nobody reads (-1: none)
     float *state_out;     // state-only mode: per (bh, seg) totals, canonical [DA][Dc]
     int canon_is_DaDc;    // canonical block is [DA][Dc] (1) or [Dc][DA] (0)
     int reverse;
@@ -294,7 +299,8 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int n0 = tile * DCT;
     const int64_t seg_begin = (int64_t)seg * p.seg_len;
     const int64_t seg_end = min(p.L, seg_begin + p.seg_len);
-    const int nchunk = (int)((seg_end - seg_begin + C - 1) / C);
+    int nchunk = (int)((seg_end - seg_begin + C - 1) / C);
+    if (p.state_only && seg == p.skip_seg) nchunk = 0;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -550,20 +556,46 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             } else {
                 // ---- initial state -> TMEM accumulator and shared-memory operand ---------------
                 {
-                    const float *src = p.states
-                        ? p.states + ((int64_t)bh * p.nseg + seg) * ((int64_t)DA * p.Dc) : nullptr;
+                    const int64_t blk = (int64_t)DA * p.Dc;
+                    // blocks to add up: the per-bh initial state and either this segment's own
+                    // block or the raw totals of every segment before (after) it
+                    int s_lo = seg, s_hi = seg + 1;
+                    if (p.sum_mode) {
+                        s_lo = p.reverse ? seg + 1 : 0;
+                        s_hi = p.reverse ? p.nseg : seg;
+                    }
+                    if (!p.states) s_hi = s_lo;
 #pragma unroll
                     for (int cb = 0; cb < DCT / 32; ++cb) {
+                        float acc[32];
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            float v = 0.f;
-                            if (src && srow_ok) {
-                                const int dc = n0 + 32 * cb + e;
-                                v = p.canon_is_DaDc ? src[(int64_t)srow * p.Dc + dc]
-                                                    : src[(int64_t)dc * DA + srow];
+                        for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+                        if (srow_ok) {
+                            for (int sb = s_lo - 1; sb < s_hi; ++sb) {
+                                const float *src;
+                                if (sb < s_lo) {
+                                    if (!p.init) continue;
+                                    src = p.init + (int64_t)bh * blk;
+                                } else {
+                                    src = p.states + ((int64_t)bh * p.nseg + sb) * blk;
+                                }
+                                const int dc0 = n0 + 32 * cb;
+                                if (p.canon_is_DaDc) {
+                                    const float4 *s4 = reinterpret_cast<const float4 *>(src + (int64_t)srow * p.Dc + dc0);
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e) {
+                                        float4 v = s4[e];
+                                        acc[4 * e] += v.x; acc[4 * e + 1] += v.y;
+                                        acc[4 * e + 2] += v.z; acc[4 * e + 3] += v.w;
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int e = 0; e < 32; ++e) acc[e] += src[(int64_t)(dc0 + e) * DA + srow];
+                                }
                             }
-                            r[e] = __float_as_uint(v);
                         }
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(acc[e]);
                         tmem_st32(tlane + K::TM_S + 32 * cb, r);
                         store_state_operand(cb);
                     }

@@ -391,4 +391,16 @@ __global__ void state_prefix_kernel(float *states, const float *init, float *tot
     if (total) total[idx] = run;
 }
 
+// total[bh] = init[bh] + sum over all segments of the raw per-segment totals
+__global__ void state_total_kernel(const float *states, const float *init, float *total,
+                                   int64_t BH, int nseg, int64_t DM) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= BH * DM) return;
+    int64_t bh = idx / DM, e = idx % DM;
+    float run = init ? init[idx] : 0.f;
+    const float *base = states + bh * nseg * DM + e;
+    for (int s = 0; s < nseg; ++s) run += base[(int64_t)s * DM];
+    total[idx] = run;
+}
+
 }  // namespace ftb

@@ -127,6 +127,11 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
  * initial_state      : optional (N,H,D,M) fp32, the same S_init the forward used.
  * initial_grad_state : optional (N,H,D,M) fp32, R contributed by positions AFTER this
  *                      range (sequence split across devices); NULL = zeros.
+ * forward_workspace  : optional; the workspace buffer the forward call on the same
+ *                      q, k, v, shape, dtype, mode and initial_state used, if its contents are
+ *                      still intact.  It holds the per-segment forward states, which the
+ *                      backward then does not recompute (one pass over K and V saved).
+ *                      NULL = recompute.  The reference keeps nothing but Q, K, V either.
  */
 int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const void *grad_out,
                             void *grad_q, void *grad_k, void *grad_v, int64_t N, int64_t H,
@@ -135,8 +140,8 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
                             const int64_t *go_strides, const int64_t *gq_strides,
                             const int64_t *gk_strides, const int64_t *gv_strides, int dtype,
                             int mode, const float *initial_state,
-                            const float *initial_grad_state, void *workspace,
-                            size_t workspace_bytes, void *stream);
+                            const float *initial_grad_state, const void *forward_workspace,
+                            void *workspace, size_t workspace_bytes, void *stream);
 
 /*
  * Whole-range state  state[n,h,:,:] = sum_l x[n,h,l,:] (x) y[n,h,l,:]   ((N,H,D,M) fp32).

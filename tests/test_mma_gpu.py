@@ -1,0 +1,179 @@
+"""Parity of the tensor-core ("mma") mode -- tcgen05 MMAs with TF32 operands for fp32
+tensors and bf16 operands for bf16 tensors, fp32 accumulation and state -- against the fp64
+oracle.  Tolerance: 2e-2 on max|x - x64| / max|x64| (fp32-mode tests use 1e-5)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import causal_oracle as orc  # noqa: E402
+from fast_transformers_b200 import _native, workloads  # noqa: E402
+import fast_transformers_b200 as ftb  # noqa: E402
+from fast_transformers_b200.causal_product import (  # noqa: E402
+    causal_dot_backward_cuda, causal_dot_product, causal_dot_product_cuda, causal_state_sum)
+
+TOL = 2e-2
+NAMES = ("out", "gQ", "gK", "gV")
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _lib(native_lib):
+    assert torch.cuda.is_available()
+    yield native_lib
+    torch.cuda.synchronize()
+    assert native_lib.ftb_device_status(1) == 0, "a kernel recorded a device-side error"
+
+
+def fwd_bwd(Q, K, V, G):
+    q, k, v = (t.cuda().requires_grad_(True) for t in (Q, K, V))
+    with ftb.mode("mma"):
+        out = causal_dot_product(q, k, v)
+        out.backward(G.cuda())
+    torch.cuda.synchronize()
+    return out.detach(), q.grad, k.grad, v.grad
+
+
+def oracle(Q, K, V, G):
+    Q, K, V, G = (t.float() for t in (Q, K, V, G))
+    return (orc.chunked_forward(Q, K, V),) + tuple(orc.chunked_backward(Q, K, V, G))
+
+
+def check(Q, K, V, G, tol=TOL):
+    got, want = fwd_bwd(Q, K, V, G), oracle(Q, K, V, G)
+    errs = {}
+    for name, a, b in zip(NAMES, got, want):
+        assert a.dtype == Q.dtype and a.shape == b.shape
+        errs[name] = orc.rel_err(a, b)
+        assert errs[name] < tol, "%s: rel err %.3e" % (name, errs[name])
+    return got, errs
+
+
+def test_config1_tf32(golden):
+    Q, K, V, G = workloads.make_inputs(1)
+    got, errs = check(Q, K, V, G)
+    g = golden("product_config1_sample")
+    rows = torch.from_numpy(g["rows"])
+    for name, a in zip(NAMES, got):
+        assert orc.rel_err(a.cpu()[:, :, rows], torch.from_numpy(g[name])) < TOL, name
+    # TF32 keeps 10 mantissa bits: the error should sit well inside the bound
+    assert max(errs.values()) < 5e-3
+
+
+@pytest.mark.parametrize("L", [1, 100, 128, 129, 1000, 2304])
+def test_ragged_lengths_tf32(L):
+    g = torch.Generator().manual_seed(L)
+    Q, K, V, G = (torch.randn(2, 3, L, 64, generator=g) for _ in range(4))
+    check(Q, K, V, G)
+
+
+def test_many_heads_and_segments_tf32():
+    Q, K, V, G = workloads.make_inputs(2, scale_N=2, scale_L=2048)
+    check(Q, K, V, G)
+
+
+def test_config4_recipe_bf16_reduced():
+    """bf16 I/O, D = M = 128, fp32 state: config 4's recipe at H4, L8192."""
+    Q, K, V, G = workloads.make_inputs(4, scale_L=8192, scale_H=4)
+    assert Q.dtype == torch.bfloat16
+    check(Q, K, V, G)
+
+
+@pytest.mark.parametrize("L", [77, 640])
+def test_bf16_ragged(L):
+    g = torch.Generator().manual_seed(L)
+    Q, K, V, G = (torch.randn(1, 2, L, 128, generator=g).to(torch.bfloat16) for _ in range(4))
+    check(Q, K, V, G)
+
+
+def test_nlhd_storage_views_tf32():
+    """(N, L, H, D) storage viewed as (N, H, L, D): the head stride is below the row stride."""
+    g = torch.Generator().manual_seed(21)
+    N, L, H, D = 2, 700, 3, 64
+    Qs, Ks, Vs, Gs = (torch.randn(N, L, H, D, generator=g) for _ in range(4))
+    q, k, v = (t.cuda().permute(0, 2, 1, 3).requires_grad_(True) for t in (Qs, Ks, Vs))
+    assert not q.is_contiguous()
+    with ftb.mode("mma"):
+        out = causal_dot_product(q, k, v)
+        out.backward(Gs.cuda().permute(0, 2, 1, 3))
+    want = oracle(*(t.permute(0, 2, 1, 3) for t in (Qs, Ks, Vs, Gs)))
+    for name, a, b in zip(NAMES, (out, q.grad, k.grad, v.grad), want):
+        assert orc.rel_err(a, b) < TOL, name
+
+
+def test_states_split_sequence_tf32():
+    g = torch.Generator().manual_seed(22)
+    N, H, L, D = 1, 2, 1536, 64
+    Q, K, V, G = (torch.rand(N, H, L, D, generator=g) for _ in range(4))
+    Qd, Kd, Vd, Gd = (t.cuda() for t in (Q, K, V, G))
+    h = 640
+    want_o = orc.chunked_forward(Q, K, V)
+    want_g = orc.chunked_backward(Q, K, V, G)
+    S0 = causal_state_sum(Kd[:, :, :h], Vd[:, :, :h], mode="mma")
+    assert orc.rel_err(S0, orc.local_states(None, K[:, :, :h], V[:, :, :h])) < TOL
+    o1 = torch.empty(N, H, h, D, device="cuda")
+    o2 = torch.empty(N, H, L - h, D, device="cuda")
+    fin = torch.empty(N, H, D, D, device="cuda")
+    causal_dot_product_cuda(Qd[:, :, :h], Kd[:, :, :h], Vd[:, :, :h], o1, "mma", final_state=fin)
+    assert orc.rel_err(fin, S0) < 1e-5
+    causal_dot_product_cuda(Qd[:, :, h:], Kd[:, :, h:], Vd[:, :, h:], o2, "mma", initial_state=fin)
+    assert orc.rel_err(torch.cat([o1, o2], 2), want_o) < TOL
+    R1 = causal_state_sum(Qd[:, :, h:], Gd[:, :, h:], mode="mma")
+    g1 = [torch.empty(N, H, h, D, device="cuda") for _ in range(3)]
+    g2 = [torch.empty(N, H, L - h, D, device="cuda") for _ in range(3)]
+    causal_dot_backward_cuda(Qd[:, :, :h], Kd[:, :, :h], Vd[:, :, :h], Gd[:, :, :h], *g1, "mma",
+                             initial_grad_state=R1)
+    causal_dot_backward_cuda(Qd[:, :, h:], Kd[:, :, h:], Vd[:, :, h:], Gd[:, :, h:], *g2, "mma",
+                             initial_state=fin)
+    for a, b, c in zip(g1, g2, want_g):
+        assert orc.rel_err(torch.cat([a, b], 2), c) < TOL
+
+
+def test_forward_workspace_reuse_is_bitwise_equal_to_recompute():
+    Q, K, V, G = workloads.make_inputs(1)
+    Qd, Kd, Vd, Gd = (t.cuda() for t in (Q, K, V, G))
+    out = torch.empty_like(Vd)
+    kept = []
+    causal_dot_product_cuda(Qd, Kd, Vd, out, "mma", keep_workspace=kept)
+    a = [torch.empty_like(t) for t in (Qd, Kd, Vd)]
+    b = [torch.empty_like(t) for t in (Qd, Kd, Vd)]
+    causal_dot_backward_cuda(Qd, Kd, Vd, Gd, *a, "mma", forward_workspace=kept[0])
+    causal_dot_backward_cuda(Qd, Kd, Vd, Gd, *b, "mma")
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+def test_determinism_tf32():
+    Q, K, V, G = workloads.make_inputs(1)
+    a, b = fwd_bwd(Q, K, V, G), fwd_bwd(Q, K, V, G)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+def test_unsupported_shape_and_alignment_errors():
+    x = torch.rand(1, 1, 256, 32, device="cuda")
+    out = torch.empty_like(x)
+    with pytest.raises(_native.NativeError) as e:
+        causal_dot_product_cuda(x, x, x, out, "mma")
+    assert e.value.status == _native.ERR_UNSUPPORTED
+    # a view that starts 4 bytes into a row: TMA needs 16-byte aligned bases
+    big = torch.rand(1, 1, 256, 80, device="cuda")
+    mis = big[..., 1:65]
+    out = torch.empty(1, 1, 256, 64, device="cuda")
+    with pytest.raises(_native.NativeError) as e:
+        causal_dot_product_cuda(mis, mis, mis, out, "mma")
+    assert e.value.status == _native.ERR_ALIGNMENT
+
+
+def test_linearity_config2_full_size_tf32():
+    """Full-size config 2: out is linear in V (exactly, scaling by 2 is exact in TF32), the
+    first row is (q_0 . k_0) v_0 and the last row is q_L . K^T V."""
+    Q, K, V, _ = workloads.make_inputs(2)
+    Qd, Kd, Vd = (t.cuda() for t in (Q, K, V))
+    with ftb.mode("mma"):
+        o1 = causal_dot_product(Qd, Kd, Vd)
+        o2 = causal_dot_product(Qd, Kd, 2.0 * Vd)
+    assert torch.equal(o2, 2.0 * o1)
+    S = K.double().transpose(-1, -2) @ V.double()
+    assert orc.rel_err(o1[:, :, -1:], Q[:, :, -1:].double() @ S) < TOL
+    first = (Q[:, :, :1].double() * K[:, :, :1].double()).sum(-1, keepdim=True) * V[:, :, :1].double()
+    assert orc.rel_err(o1[:, :, :1], first) < TOL
