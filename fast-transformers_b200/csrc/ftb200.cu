@@ -184,8 +184,12 @@ static int mma_launch(const void *a, const void *b, const void *c, void *out, co
         rc = mma::make_map(&ma, p.pos_a, a, N, H, L, Da, as, dtype);
         if (rc) return rc;
         const int64_t es = dtype == FTB_F32 ? 4 : 2;
-        if (((uintptr_t)out & 15) || (os[0] * es) % 16 || (os[1] * es) % 16 || (os[2] * es) % 16)
+        if (((uintptr_t)out & 15) || (os[0] * es) % 16 || (os[1] * es) % 16 || (os[2] * es) % 16) {
+            if (std::getenv("FTB200_DEBUG"))
+                fprintf(stderr, "[ftb200] output alignment: %p strides %lld %lld %lld\n", out,
+                        (long long)os[0], (long long)os[1], (long long)os[2]);
             return FTB_ERR_ALIGNMENT;
+        }
     }
     p.out = out;
     p.so = state_only ? Strides3{0, 0, 0} : S3(os);

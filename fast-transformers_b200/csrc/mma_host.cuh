@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <utility>
 
@@ -69,11 +70,23 @@ static int make_map(CUtensorMap *map, int *pos, const void *base, int64_t N, int
         if (role[i] == 0) box[1 + i] = (cuuint32_t)C;
     }
     cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = enc(map, dtype == FTB_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                     4, const_cast<void *>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = CUDA_SUCCESS;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        r = enc(map, dtype == FTB_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                4, const_cast<void *>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_ERROR_INVALID_CONTEXT) break;
+        // A thread that has made no runtime call yet (an autograd worker) has no context bound:
+        // bind the device's primary context and try once more.
+        cudaFree(nullptr);
+    }
+    if (r != CUDA_SUCCESS && std::getenv("FTB200_DEBUG"))
+        fprintf(stderr, "[ftb200] cuTensorMapEncodeTiled failed: %d base=%p dim=%lld ext=(%lld,%lld,%lld) "
+                        "stride_bytes=(%llu,%llu,%llu) box=(%u,%u,%u,%u)\n",
+                (int)r, base, (long long)dim, (long long)ext[0], (long long)ext[1], (long long)ext[2],
+                (unsigned long long)gstr[0], (unsigned long long)gstr[1], (unsigned long long)gstr[2],
+                box[0], box[1], box[2], box[3]);
     return r == CUDA_SUCCESS ? FTB_OK : FTB_ERR_ALIGNMENT;
 }
 

@@ -18,7 +18,8 @@
 // bits; the bf16 variant rounds this operand copy only -- the accumulated state stays fp32).
 //
 // Warp roles: warp 0 = TMA producer (+ TMEM allocation), warp 1 = MMA issuer, warps 2-5 =
-// workers.  Every wait is bounded: on expiry the CTA records FTB_ERR_TIMEOUT in a device
+// state-copy workers (the loop-carried chain: state update -> operand copy -> next a S),
+// warps 6-9 = mask and output workers.  Every wait is bounded: on expiry the CTA records FTB_ERR_TIMEOUT in a device
 // status word, stops issuing work, releases its tensor memory and returns.
 //
 // Maths: fast_transformers/causal_product/causal_product_cpu.cpp:106-121, :165-206 in blocks.
@@ -34,7 +35,7 @@ namespace ftb {
 namespace mma {
 
 constexpr int C = 128;          // rows per chunk
-constexpr int NTHREADS = 192;   // 6 warps
+constexpr int NTHREADS = 320;   // 10 warps: TMA, MMA, 4 mask/state workers, 4 output workers
 constexpr int STAGES = 2;
 
 __device__ int g_device_status = 0;   // 0 ok, else FTB_ERR_* recorded by a kernel
@@ -284,7 +285,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t bar_full = bars, bar_empty = bars + 16, bar_pfull = bars + 32,
                    bar_pready = bars + 48, bar_ofull = bars + 64, bar_ofree = bars + 80,
                    bar_sfull = bars + 96, bar_smready = bars + 104, bar_fullc = bars + 112,
-                   bar_bkfree = bars + 128;
+                   bar_bkfree = bars + 128, bar_fullbmn = bars + 144;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -311,8 +312,9 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             mbar_init(bar_pready + 8 * s, 128);
             mbar_init(bar_ofull + 8 * s, 1);
             mbar_init(bar_ofree + 8 * s, 128);
-            mbar_init(bar_fullc + 8 * s, K::RELOAD_B ? 2 : 1);
+            mbar_init(bar_fullc + 8 * s, 1);
             mbar_init(bar_bkfree + 8 * s, 1);
+            mbar_init(bar_fullbmn + 8 * s, 1);
         }
         mbar_init(bar_sfull, 1);
         mbar_init(bar_smready, 128);
@@ -328,17 +330,19 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (warp == 0) {
             // ================= TMA producer =====================================================
             // bar_full[s]  : a and the K-major image of b have landed (score product, a S)
-            // bar_fullc[s] : c and the MN-major image of b have landed (mask(P) c, state update)
+            // bar_fullc[s] : c has landed (mask(P) c, state update)
+            // bar_fullbmn[s]: the MN-major image of b has landed in b's slot (state update); it is
+            //                requested as soon as the score product has consumed the K-major image
             if (lane == 0) {
                 auto load_b_mn = [&](int ci) {
                     const int c = p.reverse ? nchunk - 1 - ci : ci;
                     const int s = ci & 1;
                     const int row = (int)(seg_begin + (int64_t)c * C);
                     const uint32_t st = stage0 + s * K::STAGE_BYTES;
-                    mbar_expect_tx(bar_fullc + 8 * s, K::A_BYTES);
+                    mbar_expect_tx(bar_fullbmn + 8 * s, K::A_BYTES);
 #pragma unroll
                     for (int b = 0; b < K::A_BLKS; ++b)
-                        tma_load_4d(st + K::A_BYTES + b * K::BLK_BYTES, &map_bmn, bar_fullc + 8 * s,
+                        tma_load_4d(st + K::A_BYTES + b * K::BLK_BYTES, &map_bmn, bar_fullbmn + 8 * s,
                                     b * K::EPB, p.pos_b, row, bhh, bn);
                 };
                 bool ok = true;
@@ -376,7 +380,8 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (p.state_only) {
                             load_b_mn(ci);
                         } else if (ci >= 1) {
-                            // the score product of chunk ci-1 has consumed the K-major image
+                            // the score product of chunk ci-1 (issued right after the state update
+                            // that freed this stage) has consumed the K-major image of b
                             ok = mbar_wait(bar_bkfree + 8 * ((ci - 1) & 1), ((ci - 1) >> 1) & 1, abort_flag);
                             if (ok) load_b_mn(ci - 1);
                         }
@@ -420,6 +425,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     for (int ci = 0; ci < nchunk && ok; ++ci) {
                         const int s = ci & 1, use = ci >> 1;
                         ok = mbar_wait(bar_fullc + 8 * s, use & 1, abort_flag);
+                        if (K::RELOAD_B && ok) ok = mbar_wait(bar_fullbmn + 8 * s, use & 1, abort_flag);
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t st = stage0 + s * K::STAGE_BYTES;
@@ -477,6 +483,11 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         }
                         tc_commit(bar_ofull + 8 * ob);
                         // S += b^T c
+                        if constexpr (K::RELOAD_B) {
+                            ok = mbar_wait(bar_fullbmn + 8 * s, (ci >> 1) & 1, abort_flag);
+                            if (!ok) break;
+                            tc_fence_after();
+                        }
                         if (p.terms & 4) {
 #pragma unroll
                             for (int k = 0; k < C / K::KROWS; ++k) {
@@ -487,6 +498,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         }
                         tc_commit(bar_sfull);
                         tc_commit(bar_empty + 8 * s);
+                        // scores of the next chunk: masked while the state copy runs
                         if (ci + 1 < nchunk) {
                             ok = mbar_wait(bar_full + 8 * ((ci + 1) & 1), ((ci + 1) >> 1) & 1, abort_flag);
                             if (!ok) break;
@@ -496,8 +508,113 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                 }
             }
+        } else if (warp >= 6) {
+            // ================= output workers: O rows -> global memory ==========================
+            if (!p.state_only) {
+                const int q = warp & 3;
+                const int i = 32 * q + lane;
+                const uint32_t tlane = tmem + ((uint32_t)(32 * q) << 16);
+                uint32_t r[32];
+                bool ok = true;
+                // causal mask on the scores of chunk ci, in place
+                auto mask_scores = [&](int ci) -> bool {
+                    if (!mbar_wait(bar_pfull + 8 * (ci & 1), (ci >> 1) & 1, abort_flag)) return false;
+                    tc_fence_after();
+                    const uint32_t tP = tlane + K::TM_P + 128 * (ci & 1);
+#pragma unroll
+                    for (int cb = 0; cb < 4; ++cb) {
+                        // rows of this warp are 32q..32q+31, columns of the block 32cb..32cb+31
+                        const bool all_keep = p.reverse ? (cb > q) : (cb < q);
+                        const bool all_drop = p.reverse ? (cb < q) : (cb > q);
+                        if constexpr (!K::F16) {
+                            if (all_keep) continue;
+                            if (all_drop) {
+#pragma unroll
+                                for (int e = 0; e < 32; ++e) r[e] = 0u;
+                            } else {
+                                tmem_ld32(tP + 32 * cb, r);
+#pragma unroll
+                                for (int e = 0; e < 32; ++e) {
+                                    const bool keep = p.reverse ? (e >= lane) : (e <= lane);
+                                    r[e] = keep ? r[e] : 0u;
+                                }
+                            }
+                            tmem_st32(tP + 32 * cb, r);
+                        } else {
+                            uint32_t h[16];
+                            if (all_drop) {
+#pragma unroll
+                                for (int e = 0; e < 16; ++e) h[e] = 0u;
+                            } else {
+                                tmem_ld32(tP + 32 * cb, r);
+#pragma unroll
+                                for (int e = 0; e < 16; ++e) {
+                                    float x0 = __uint_as_float(r[2 * e]), x1 = __uint_as_float(r[2 * e + 1]);
+                                    if (!all_keep) {
+                                        const bool k0 = p.reverse ? (2 * e >= lane) : (2 * e <= lane);
+                                        const bool k1 = p.reverse ? (2 * e + 1 >= lane) : (2 * e + 1 <= lane);
+                                        x0 = k0 ? x0 : 0.f;
+                                        x1 = k1 ? x1 : 0.f;
+                                    }
+                                    __nv_bfloat162 hh = __floats2bfloat162_rn(x0, x1);
+                                    h[e] = *reinterpret_cast<uint32_t *>(&hh);
+                                }
+                            }
+                            tmem_st16(tP + 16 * cb, h);
+                        }
+                    }
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(bar_pready + 8 * (ci & 1));
+                    return true;
+                };
+
+                T *O = reinterpret_cast<T *>(p.out) + (int64_t)bn * p.so.n + (int64_t)bhh * p.so.h;
+                ok = mask_scores(0);
+                for (int ci = 0; ci < nchunk && ok; ++ci) {
+                    const int c = p.reverse ? nchunk - 1 - ci : ci;
+                    const int64_t row0 = seg_begin + (int64_t)c * C;
+                    const int ob = ci % K::NOBUF, ouse = ci / K::NOBUF;
+                    ok = mbar_wait(bar_ofull + 8 * ob, ouse & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const int64_t row = row0 + i;
+                    T *dst = O + row * p.so.l + n0;
+#pragma unroll
+                    for (int cb = 0; cb < DCT / 32; ++cb) {
+                        tmem_ld32(tlane + K::TM_O + ob * DCT + 32 * cb, r);
+                        if (row < seg_end) {
+                            if constexpr (K::F16) {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    uint4 v;
+                                    __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * e + 0]), __uint_as_float(r[8 * e + 1]));
+                                    __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * e + 2]), __uint_as_float(r[8 * e + 3]));
+                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * e + 4]), __uint_as_float(r[8 * e + 5]));
+                                    __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * e + 6]), __uint_as_float(r[8 * e + 7]));
+                                    v.x = *reinterpret_cast<uint32_t *>(&h0);
+                                    v.y = *reinterpret_cast<uint32_t *>(&h1);
+                                    v.z = *reinterpret_cast<uint32_t *>(&h2);
+                                    v.w = *reinterpret_cast<uint32_t *>(&h3);
+                                    *reinterpret_cast<uint4 *>(dst + 32 * cb + 8 * e) = v;
+                                }
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e)
+                                    *reinterpret_cast<uint4 *>(dst + 32 * cb + 4 * e) =
+                                        make_uint4(r[4 * e], r[4 * e + 1], r[4 * e + 2], r[4 * e + 3]);
+                            }
+                        }
+                    }
+                    tc_fence_before();
+                    mbar_arrive(bar_ofree + 8 * ob);
+                    // scores of the next chunk (their product is issued right after this chunk's
+                    // state update) are masked here, off the state-copy workers' path
+                    if (ci + 1 < nchunk) ok = mask_scores(ci + 1);
+                }
+            }
         } else {
-            // ================= workers: one TMEM lane (row) per thread ===========================
+            // ================= mask / state workers: one TMEM lane (row) per thread ==============
             const int q = warp & 3;
             const int i = 32 * q + lane;                       // row inside the chunk / lane
             const uint32_t tlane = tmem + ((uint32_t)(32 * q) << 16);
@@ -605,113 +722,19 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     mbar_arrive(bar_smready);
                 }
 
-                T *O = reinterpret_cast<T *>(p.out) + (int64_t)bn * p.so.n + (int64_t)bhh * p.so.h;
-                for (int ci = 0; ci < nchunk && ok; ++ci) {
-                    const int c = p.reverse ? nchunk - 1 - ci : ci;
-                    const int64_t row0 = seg_begin + (int64_t)c * C;
-                    // ---- causal mask on the scores, in place ------------------------------------
-                    ok = mbar_wait(bar_pfull + 8 * (ci & 1), (ci >> 1) & 1, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after();
-                    {
-                        const uint32_t tP = tlane + K::TM_P + 128 * (ci & 1);
-#pragma unroll
-                        for (int cb = 0; cb < 4; ++cb) {
-                            // rows of this warp are 32q..32q+31, columns of the block 32cb..32cb+31
-                            const bool all_keep = p.reverse ? (cb > q) : (cb < q);
-                            const bool all_drop = p.reverse ? (cb < q) : (cb > q);
-                            if constexpr (!K::F16) {
-                                if (all_keep) continue;
-                                if (all_drop) {
-#pragma unroll
-                                    for (int e = 0; e < 32; ++e) r[e] = 0u;
-                                } else {
-                                    tmem_ld32(tP + 32 * cb, r);
-#pragma unroll
-                                    for (int e = 0; e < 32; ++e) {
-                                        const bool keep = p.reverse ? (e >= lane) : (e <= lane);
-                                        r[e] = keep ? r[e] : 0u;
-                                    }
-                                }
-                                tmem_st32(tP + 32 * cb, r);
-                            } else {
-                                uint32_t h[16];
-                                if (all_drop) {
-#pragma unroll
-                                    for (int e = 0; e < 16; ++e) h[e] = 0u;
-                                } else {
-                                    tmem_ld32(tP + 32 * cb, r);
-#pragma unroll
-                                    for (int e = 0; e < 16; ++e) {
-                                        float x0 = __uint_as_float(r[2 * e]), x1 = __uint_as_float(r[2 * e + 1]);
-                                        if (!all_keep) {
-                                            const bool k0 = p.reverse ? (2 * e >= lane) : (2 * e <= lane);
-                                            const bool k1 = p.reverse ? (2 * e + 1 >= lane) : (2 * e + 1 <= lane);
-                                            x0 = k0 ? x0 : 0.f;
-                                            x1 = k1 ? x1 : 0.f;
-                                        }
-                                        __nv_bfloat162 hh = __floats2bfloat162_rn(x0, x1);
-                                        h[e] = *reinterpret_cast<uint32_t *>(&hh);
-                                    }
-                                }
-                                tmem_st16(tP + 16 * cb, h);
-                            }
-                        }
-                        tmem_wait_st();
-                        tc_fence_before();
-                        mbar_arrive(bar_pready + 8 * (ci & 1));
-                    }
+                for (int ci = 0; ci + 1 < nchunk && ok; ++ci) {
                     // ---- updated state -> shared-memory operand of the next chunk ---------------
                     ok = mbar_wait(bar_sfull, ci & 1, abort_flag);
                     if (!ok) break;
                     tc_fence_after();
-                    if (ci + 1 < nchunk) {
 #pragma unroll
-                        for (int cb = 0; cb < DCT / 32; ++cb) {
-                            tmem_ld32(tlane + K::TM_S + 32 * cb, r);
-                            store_state_operand(cb);
-                        }
-                        fence_proxy_async_smem();
-                        tc_fence_before();
-                        mbar_arrive(bar_smready);
+                    for (int cb = 0; cb < DCT / 32; ++cb) {
+                        tmem_ld32(tlane + K::TM_S + 32 * cb, r);
+                        store_state_operand(cb);
                     }
-                    // ---- output rows ------------------------------------------------------------
-                    const int ob = ci % K::NOBUF, ouse = ci / K::NOBUF;
-                    ok = mbar_wait(bar_ofull + 8 * ob, ouse & 1, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after();
-                    {
-                        const int64_t row = row0 + i;
-                        T *dst = O + row * p.so.l + n0;
-#pragma unroll
-                        for (int cb = 0; cb < DCT / 32; ++cb) {
-                            tmem_ld32(tlane + K::TM_O + ob * DCT + 32 * cb, r);
-                            if (row < seg_end) {
-                                if constexpr (K::F16) {
-#pragma unroll
-                                    for (int e = 0; e < 4; ++e) {
-                                        uint4 v;
-                                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * e + 0]), __uint_as_float(r[8 * e + 1]));
-                                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * e + 2]), __uint_as_float(r[8 * e + 3]));
-                                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * e + 4]), __uint_as_float(r[8 * e + 5]));
-                                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * e + 6]), __uint_as_float(r[8 * e + 7]));
-                                        v.x = *reinterpret_cast<uint32_t *>(&h0);
-                                        v.y = *reinterpret_cast<uint32_t *>(&h1);
-                                        v.z = *reinterpret_cast<uint32_t *>(&h2);
-                                        v.w = *reinterpret_cast<uint32_t *>(&h3);
-                                        *reinterpret_cast<uint4 *>(dst + 32 * cb + 8 * e) = v;
-                                    }
-                                } else {
-#pragma unroll
-                                    for (int e = 0; e < 8; ++e)
-                                        *reinterpret_cast<uint4 *>(dst + 32 * cb + 4 * e) =
-                                            make_uint4(r[4 * e], r[4 * e + 1], r[4 * e + 2], r[4 * e + 3]);
-                                }
-                            }
-                        }
-                        tc_fence_before();
-                        mbar_arrive(bar_ofree + 8 * ob);
-                    }
+                    fence_proxy_async_smem();
+                    tc_fence_before();
+                    mbar_arrive(bar_smready);
                 }
             }
         }
