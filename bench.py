@@ -41,6 +41,7 @@ def parse():
     ap.add_argument("--L", type=int, default=None, help="override the sequence length")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="time eager calls, not a CUDA graph")
     return ap.parse_args()
 
 
@@ -226,16 +227,40 @@ def main():
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    # One step is a handful of launches of ~50 us each, so the host would set the pace: the
+    # step is captured once into a CUDA graph (native launches go to the capturing stream like
+    # any other) and replayed.  --no-graph times the eager calls instead.
+    graph = None
+    launches_per_step = None
+    if not args.no_graph:
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        n0 = lib.ftb_launch_count()
+        with torch.cuda.graph(graph):
+            step()
+        launches_per_step = lib.ftb_launch_count() - n0
+        for _ in range(3):
+            graph.replay()
+        barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     launches0 = lib.ftb_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        step()
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
-    launches = lib.ftb_launch_count() - launches0
+    launches = (launches_per_step * args.steps if graph is not None
+                else lib.ftb_launch_count() - launches0)
     barrier()
     clocks = sampler.stop() if sampler else None
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
@@ -347,7 +372,7 @@ def main():
             "dtype": {"fp32": "f32", "mma": "tf32" if esize == 4 else "bf16"}[mode],
             "data": "synthetic (seeded)",
             "config": {"workload": name, "mode": mode, "io_dtype": str(Qd.dtype).replace("torch.", ""),
-                       "global_batch": shape["N"] * world, "sharding": "(batch, head) units per rank, no collective",
+                       "global_batch": shape["N"] * world, "cuda_graph": graph is not None, "sharding": "(batch, head) units per rank, no collective",
                        "l2": "inputs+outputs per step (%.0f MB) exceed the 126 MB L2; no flush" %
                              (step_alg_bytes / 1e6)},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,

@@ -332,6 +332,12 @@ int ftb_device_status(int reset) {
     return v;
 }
 
+#ifdef FTB_TIMESTAMPS
+int ftb_debug_read_timestamps(long long *dst, int n) {
+    return (int)cudaMemcpyFromSymbol(dst, mma::g_ts, sizeof(long long) * n);
+}
+#endif
+
 uint64_t ftb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 void ftb_timing_enable(int enable) {

@@ -40,6 +40,17 @@ constexpr int STAGES = 2;
 
 __device__ int g_device_status = 0;   // 0 ok, else FTB_ERR_* recorded by a kernel
 
+// Optional per-role event timestamps of CTA 0 (a tuning aid, compiled out by default).
+#ifdef FTB_TIMESTAMPS
+__device__ long long g_ts[8 * 64 * 8];
+#define FTB_TS(role, ci, ev)                                                        \
+    do {                                                                            \
+        if (blockIdx.x == 0 && (ci) < 64) g_ts[((role)*64 + (ci)) * 8 + (ev)] = clock64(); \
+    } while (0)
+#else
+#define FTB_TS(role, ci, ev) do { } while (0)
+#endif
+
 struct ScanParams {
     void *out;            // output tensor (scan) or nullptr (state only)
     Strides3 so;
@@ -351,6 +362,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const int s = ci & 1, use = ci >> 1;
                     ok = mbar_wait(bar_empty + 8 * s, (use & 1) ^ 1, abort_flag);
                     if (!ok) break;
+                    FTB_TS(0, ci, 0);
                     const int row = (int)(seg_begin + (int64_t)c * C);
                     const uint32_t st = stage0 + s * K::STAGE_BYTES;
                     if (!p.state_only) {
@@ -383,6 +395,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             // the score product of chunk ci-1 (issued right after the state update
                             // that freed this stage) has consumed the K-major image of b
                             ok = mbar_wait(bar_bkfree + 8 * ((ci - 1) & 1), ((ci - 1) >> 1) & 1, abort_flag);
+                            FTB_TS(0, ci, 1);
                             if (ok) load_b_mn(ci - 1);
                         }
                     }
@@ -404,18 +417,25 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 constexpr int KSTEP_BYTES = K::KROWS * 128;   // MN-major advance along K
                 const uint32_t tS = tmem + K::TM_S;
                 bool ok = true;
+                // Descriptors are built once per stage; each MMA then only adds a constant (the
+                // start-address field counts 16-byte units and cannot carry into the next field).
+                const uint64_t dAk0 = smem_desc(stage0, 16, 1024);
+                const uint64_t dBk0 = smem_desc(stage0 + K::A_BYTES, 16, 1024);
+                const uint64_t dBmn0 = smem_desc(stage0 + K::A_BYTES, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
+                const uint64_t dCmn0 = smem_desc(stage0 + 2 * K::A_BYTES, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
+                constexpr uint64_t STAGE_UNITS = (uint64_t)(K::STAGE_BYTES >> 4);
+                const uint64_t dSm = smem_desc(sm_state, K::SM_BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
 
                 auto issue_scores = [&](int ci) {
                     const int s = ci & 1;
-                    const uint32_t st = stage0 + s * K::STAGE_BYTES;
                     const uint32_t tP = tmem + K::TM_P + 128 * (ci & 1);
+                    const uint64_t a0 = dAk0 + s * STAGE_UNITS, b0 = dBk0 + s * STAGE_UNITS;
 #pragma unroll
                     for (int b = 0; b < K::A_BLKS; ++b)
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            uint64_t ad = smem_desc(st + b * K::BLK_BYTES + k * 32, 16, 1024);
-                            uint64_t bd = smem_desc(st + K::A_BYTES + b * K::BLK_BYTES + k * 32, 16, 1024);
-                            mma_ss<K::F16>(tP, ad, bd, ID_P, (b | k) ? 1u : 0u);
+                            const uint64_t off = (uint64_t)((b * K::BLK_BYTES + k * 32) >> 4);
+                            mma_ss<K::F16>(tP, a0 + off, b0 + off, ID_P, (b | k) ? 1u : 0u);
                         }
                     tc_commit(bar_pfull + 8 * (ci & 1));
                     if constexpr (K::RELOAD_B) tc_commit(bar_bkfree + 8 * (ci & 1));
@@ -428,12 +448,11 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (K::RELOAD_B && ok) ok = mbar_wait(bar_fullbmn + 8 * s, use & 1, abort_flag);
                         if (!ok) break;
                         tc_fence_after();
-                        const uint32_t st = stage0 + s * K::STAGE_BYTES;
+                        const uint64_t b0 = dBmn0 + s * STAGE_UNITS, c0 = dCmn0 + s * STAGE_UNITS;
 #pragma unroll
                         for (int k = 0; k < C / K::KROWS; ++k) {
-                            uint64_t ad = smem_desc(st + K::A_BYTES + k * KSTEP_BYTES, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
-                            uint64_t bd = smem_desc(st + 2 * K::A_BYTES + k * KSTEP_BYTES, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
-                            mma_ss<K::F16>(tS, ad, bd, ID_ST, (ci | k) ? 1u : 0u);
+                            const uint64_t off = (uint64_t)((k * KSTEP_BYTES) >> 4);
+                            mma_ss<K::F16>(tS, b0 + off, c0 + off, ID_ST, (ci | k) ? 1u : 0u);
                         }
                         tc_commit(bar_empty + 8 * s);
                     }
@@ -446,14 +465,17 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                     for (int ci = 0; ci < nchunk && ok; ++ci) {
                         const int s = ci & 1;
-                        const uint32_t st = stage0 + s * K::STAGE_BYTES;
+                        const uint64_t a0 = dAk0 + s * STAGE_UNITS, bmn0 = dBmn0 + s * STAGE_UNITS,
+                                       c0 = dCmn0 + s * STAGE_UNITS;
                         const int ob = ci % K::NOBUF, ouse = ci / K::NOBUF;
                         const uint32_t tO = tmem + K::TM_O + ob * DCT;
                         const uint32_t tP = tmem + K::TM_P + 128 * (ci & 1);
                         // O = a S   (needs the operand copy of the previous state and a free O)
+                        FTB_TS(1, ci, 0);
                         ok = mbar_wait(bar_smready, ci & 1, abort_flag) &&
                              mbar_wait(bar_ofree + 8 * ob, (ouse & 1) ^ 1, abort_flag);
                         if (!ok) break;
+                        FTB_TS(1, ci, 1);
                         tc_fence_after();
                         uint32_t acc = 0;
                         if (p.terms & 1) {
@@ -462,46 +484,49 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                                 for (int k = 0; k < 4; ++k) {
                                     const int krow = (b * K::EPB + k * K::KROWS);   // first state row
-                                    uint64_t ad = smem_desc(st + b * K::BLK_BYTES + k * 32, 16, 1024);
-                                    uint64_t bd = smem_desc(sm_state + krow * 128, K::SM_BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
-                                    mma_ss<K::F16>(tO, ad, bd, ID_AS, acc);
+                                    mma_ss<K::F16>(tO, a0 + (uint64_t)((b * K::BLK_BYTES + k * 32) >> 4),
+                                                   dSm + (uint64_t)((krow * 128) >> 4), ID_AS, acc);
                                     acc = 1;
                                 }
                         }
                         // O += mask(P) c
+                        FTB_TS(1, ci, 2);
                         ok = mbar_wait(bar_pready + 8 * (ci & 1), (ci >> 1) & 1, abort_flag) &&
                              mbar_wait(bar_fullc + 8 * s, (ci >> 1) & 1, abort_flag);
                         if (!ok) break;
+                        FTB_TS(1, ci, 3);
                         tc_fence_after();
                         if (p.terms & 2) {
 #pragma unroll
                             for (int k = 0; k < C / K::KROWS; ++k) {
-                                uint64_t bd = smem_desc(st + 2 * K::A_BYTES + k * KSTEP_BYTES, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
-                                mma_ts<K::F16>(tO, tP + k * 8, bd, ID_PC, acc);
+                                mma_ts<K::F16>(tO, tP + k * 8, c0 + (uint64_t)((k * KSTEP_BYTES) >> 4), ID_PC, acc);
                                 acc = 1;
                             }
                         }
                         tc_commit(bar_ofull + 8 * ob);
                         // S += b^T c
+                        FTB_TS(1, ci, 4);
                         if constexpr (K::RELOAD_B) {
                             ok = mbar_wait(bar_fullbmn + 8 * s, (ci >> 1) & 1, abort_flag);
                             if (!ok) break;
                             tc_fence_after();
                         }
+                        FTB_TS(1, ci, 5);
                         if (p.terms & 4) {
 #pragma unroll
                             for (int k = 0; k < C / K::KROWS; ++k) {
-                                uint64_t ad = smem_desc(st + K::A_BYTES + k * KSTEP_BYTES, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
-                                uint64_t bd = smem_desc(st + 2 * K::A_BYTES + k * KSTEP_BYTES, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
-                                mma_ss<K::F16>(tS, ad, bd, ID_ST, 1u);
+                                const uint64_t off = (uint64_t)((k * KSTEP_BYTES) >> 4);
+                                mma_ss<K::F16>(tS, bmn0 + off, c0 + off, ID_ST, 1u);
                             }
                         }
                         tc_commit(bar_sfull);
                         tc_commit(bar_empty + 8 * s);
                         // scores of the next chunk: masked while the state copy runs
+                        FTB_TS(1, ci, 6);
                         if (ci + 1 < nchunk) {
                             ok = mbar_wait(bar_full + 8 * ((ci + 1) & 1), ((ci + 1) >> 1) & 1, abort_flag);
                             if (!ok) break;
+                            FTB_TS(1, ci, 7);
                             tc_fence_after();
                             issue_scores(ci + 1);
                         }
@@ -519,6 +544,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 // causal mask on the scores of chunk ci, in place
                 auto mask_scores = [&](int ci) -> bool {
                     if (!mbar_wait(bar_pfull + 8 * (ci & 1), (ci >> 1) & 1, abort_flag)) return false;
+                    if (threadIdx.x == 192) FTB_TS(3, ci, 0);
                     tc_fence_after();
                     const uint32_t tP = tlane + K::TM_P + 128 * (ci & 1);
 #pragma unroll
@@ -566,6 +592,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     tmem_wait_st();
                     tc_fence_before();
                     mbar_arrive(bar_pready + 8 * (ci & 1));
+                    if (threadIdx.x == 192) FTB_TS(3, ci, 1);
                     return true;
                 };
 
@@ -577,6 +604,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const int ob = ci % K::NOBUF, ouse = ci / K::NOBUF;
                     ok = mbar_wait(bar_ofull + 8 * ob, ouse & 1, abort_flag);
                     if (!ok) break;
+                    if (threadIdx.x == 192) FTB_TS(3, ci, 2);
                     tc_fence_after();
                     const int64_t row = row0 + i;
                     T *dst = O + row * p.so.l + n0;
@@ -608,6 +636,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                     tc_fence_before();
                     mbar_arrive(bar_ofree + 8 * ob);
+                    if (threadIdx.x == 192) FTB_TS(3, ci, 3);
                     // scores of the next chunk (their product is issued right after this chunk's
                     // state update) are masked here, off the state-copy workers' path
                     if (ci + 1 < nchunk) ok = mask_scores(ci + 1);
@@ -726,6 +755,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     // ---- updated state -> shared-memory operand of the next chunk ---------------
                     ok = mbar_wait(bar_sfull, ci & 1, abort_flag);
                     if (!ok) break;
+                    if (threadIdx.x == 64) FTB_TS(2, ci, 0);
                     tc_fence_after();
 #pragma unroll
                     for (int cb = 0; cb < DCT / 32; ++cb) {
@@ -735,6 +765,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     fence_proxy_async_smem();
                     tc_fence_before();
                     mbar_arrive(bar_smready);
+                    if (threadIdx.x == 64) FTB_TS(2, ci, 1);
                 }
             }
         }
