@@ -203,8 +203,17 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     mode = args.mode or ftb.get_mode()
-    # every rank draws its own slice of the global batch (trial = rank)
-    Q, K, V, G = workloads.make_inputs(args.config, trial=rank, scale_L=args.L)
+    # Config 4 is ONE long sequence: with several ranks it is split over them (strong scaling,
+    # one exchange of (N,H,D,M) states per direction); the other configs give every rank its
+    # own slice of a global batch (weak scaling, no collective).
+    seq_parallel = args.config == 4 and world > 1
+    full_L = shape["L"]
+    if seq_parallel:
+        if full_L % world:
+            raise SystemExit("sequence length %d does not divide over %d ranks" % (full_L, world))
+        shape["L"] = full_L // world
+    # every rank draws its own slice (trial = rank)
+    Q, K, V, G = workloads.make_inputs(args.config, trial=rank, scale_L=shape["L"])
     pinned = [t.pin_memory() for t in (Q, K, V, G)]
     Qd, Kd, Vd, Gd = (t.to(dev) for t in (Q, K, V, G))
     Qd.requires_grad_(True), Kd.requires_grad_(True), Vd.requires_grad_(True)
@@ -212,10 +221,18 @@ def main():
     token_heads = tokens * shape["H"]
     esize = Qd.element_size()
 
+    if seq_parallel:
+        from fast_transformers_b200.sequence_parallel import (LocalOps,
+                                                              sequence_parallel_causal_dot_product)
+        sp_ops = LocalOps(mode)
+
     def step():
         Qd.grad = Kd.grad = Vd.grad = None
         with ftb.mode(mode):
-            out = causal_dot_product(Qd, Kd, Vd)
+            if seq_parallel:
+                out = sequence_parallel_causal_dot_product(Qd, Kd, Vd, ops=sp_ops)
+            else:
+                out = causal_dot_product(Qd, Kd, Vd)
             out.backward(Gd)
         return out
 
@@ -232,7 +249,7 @@ def main():
     # any other) and replayed.  --no-graph times the eager calls instead.
     graph = None
     launches_per_step = None
-    if not args.no_graph:
+    if not args.no_graph and not seq_parallel:
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
@@ -267,7 +284,8 @@ def main():
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = t.item() / args.steps
-    value = world * tokens / (ms_step * 1e-3) / 1e6
+    global_tokens = tokens * world   # sequence-parallel: the ranks' slices make up one sequence
+    value = global_tokens / (ms_step * 1e-3) / 1e6
 
     # ---- per-kernel device time (instrumented pass, after the timed region) --------------
     lib.ftb_timing_enable(1)
@@ -331,7 +349,10 @@ def main():
                 d.copy_(h, non_blocking=True)
             q, k, v = (d.detach().requires_grad_(True) for d in dq[:3])
             with ftb.mode(mode):
-                out = causal_dot_product(q, k, v)
+                if seq_parallel:
+                    out = sequence_parallel_causal_dot_product(q, k, v, ops=sp_ops)
+                else:
+                    out = causal_dot_product(q, k, v)
                 out.backward(dq[3])
             for h, d in zip(host_out, (out.detach(), q.grad, k.grad, v.grad)):
                 h.copy_(d, non_blocking=True)
@@ -350,7 +371,7 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = t.item() / n_e2e
         nbytes = sum(x.numel() * x.element_size() for x in pinned)
-        e2e = {"value": world * tokens / (e2e_ms * 1e-3) / 1e6, "unit": UNIT,
+        e2e = {"value": global_tokens / (e2e_ms * 1e-3) / 1e6, "unit": UNIT,
                "h2d_bytes_per_step": nbytes,
                "d2h_bytes_per_step": sum(h.numel() * h.element_size() for h in host_out),
                "ms_per_step": e2e_ms, "steps": n_e2e,
@@ -368,11 +389,15 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "strong" if args.config == 4 else "weak",
+            "vs_baseline": None,
             "dtype": {"fp32": "f32", "mma": "tf32" if esize == 4 else "bf16"}[mode],
             "data": "synthetic (seeded)",
             "config": {"workload": name, "mode": mode, "io_dtype": str(Qd.dtype).replace("torch.", ""),
-                       "global_batch": shape["N"] * world, "cuda_graph": graph is not None, "sharding": "(batch, head) units per rank, no collective",
+                       "global_batch": shape["N"] * (1 if seq_parallel else world), "cuda_graph": graph is not None,
+                       "sharding": ("sequence split over ranks, all_gather of per-rank states (NCCL) "
+                                    "per direction, L/rank=%d" % shape["L"]) if seq_parallel
+                       else "(batch, head) units per rank, no collective",
                        "l2": "inputs+outputs per step (%.0f MB) exceed the 126 MB L2; no flush" %
                              (step_alg_bytes / 1e6)},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
