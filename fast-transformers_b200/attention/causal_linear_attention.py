@@ -21,6 +21,7 @@ from ..attention_registry import (AttentionRegistry, Callable, EventDispatcherIn
 from ..causal_product import causal_dot_product
 from ..events import EventDispatcher
 from ..feature_maps import elu_feature_map
+from ..settings import get_mode
 
 
 def causal_linear(Q, K, V):
@@ -77,13 +78,18 @@ class CausalLinearAttention(Module):
         elif S < L:
             values = torch.cat([values, values.new_zeros(N, L - S, H, values.shape[3])], dim=1)
 
-        # One extra value column of ones: its output column is Q_i . sum_{j<=i} K_j, the
-        # denominator, so product and normaliser share one pass over Q and K.
         M = values.shape[3]
-        Vx = torch.cat([values, values.new_ones(N, L, H, 1)], dim=-1)
-        out = causal_linear(Q, K, Vx)
-        Z = 1 / (out[..., M] + self.eps)
-        return (out[..., :M] * Z[..., None]).contiguous()
+        if get_mode() == "fp32":
+            # One extra value column of ones: its output column is Q_i . sum_{j<=i} K_j, the
+            # denominator, so product and normaliser share one pass over Q and K.
+            Vx = torch.cat([values, values.new_ones(N, L, H, 1)], dim=-1)
+            out = causal_linear(Q, K, Vx)
+            Z = 1 / (out[..., M] + self.eps)
+            return (out[..., :M] * Z[..., None]).contiguous()
+        # The tensor-core kernels take D = M only, so the normaliser is computed as in the
+        # reference (:95): a cumulative sum of K and a row-wise dot product.
+        Z = 1 / (torch.einsum("nlhi,nlhi->nlh", Q, K.cumsum(1)) + self.eps)
+        return (causal_linear(Q, K, values) * Z[:, :, :, None]).contiguous()
 
 
 AttentionRegistry.register(
