@@ -11,7 +11,9 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libftb200.so")
 
-OK, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE, ERR_CUDA, ERR_TIMEOUT, ERR_INVALID = range(7)
+OK, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE, ERR_CUDA, ERR_TIMEOUT, ERR_INVALID, \
+    ERR_STATIC_LIMIT = range(8)
+STATIC_SCRATCH_BYTES = 16 * 1024 * 1024
 F32, BF16 = 0, 1
 MODE_FP32_SIMT, MODE_MMA = 0, 1
 MODE_IDS = {"fp32": MODE_FP32_SIMT, "mma": MODE_MMA}
@@ -21,6 +23,7 @@ EXPORTS = (
     "ftb_version", "ftb_status_string", "ftb_last_cuda_error", "ftb_causal_workspace_bytes",
     "ftb_causal_dot_product", "ftb_causal_dot_backward", "ftb_causal_state_sum",
     "ftb_launch_count", "ftb_timing_enable", "ftb_timing_read", "ftb_device_status",
+    "ftb_causal_dot_product_static",
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
                 "reserved6", "reserved7")
@@ -62,6 +65,9 @@ def lib():
     L.ftb_causal_state_sum.restype = _int
     L.ftb_causal_state_sum.argtypes = (
         [_vp] * 3 + [_i64] * 5 + [_i64p] * 2 + [_int, _int, _vp, _sz, _vp])
+    L.ftb_causal_dot_product_static.restype = _int
+    L.ftb_causal_dot_product_static.argtypes = (
+        [_vp] * 4 + [_i64] * 5 + [_i64p] * 4 + [_int, _int, _vp])
     L.ftb_launch_count.restype = ctypes.c_uint64
     L.ftb_device_status.restype = _int
     L.ftb_device_status.argtypes = [_int]

@@ -316,6 +316,8 @@ const char *ftb_status_string(int s) {
         case FTB_ERR_CUDA: return "CUDA runtime error";
         case FTB_ERR_TIMEOUT: return "device-side wait timed out";
         case FTB_ERR_INVALID: return "invalid argument";
+        case FTB_ERR_STATIC_LIMIT:
+            return "problem needs more scratch than the library's built-in static buffer holds";
         default: return "unknown status";
     }
 }
@@ -515,6 +517,52 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
     SegStates ss;
     return prepare_states(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, (float *)workspace,
                           nullptr, state, 0, st, &ss);
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Forward product for callers that must not allocate.
+//
+// Some callers cannot obtain device memory at call time: code running inside a memory pool it
+// does not own, a real-time or serving loop whose allocator is frozen after start-up, a plugin
+// host that forbids cudaMalloc from plugins.  For them the scratch of the forward product lives
+// in this file-scope device array, part of the library image: every GPU that loads the library
+// carries these FTB_STATIC_SCRATCH_BYTES until the process exits.
+//
+// In host code the array's name is only a stand-in symbol, not a device address, so its address
+// is looked up with cudaGetSymbolAddress -- once per device, with that device current -- and the
+// looked-up pointer is what the kernels receive.
+static __device__ __align__(256) unsigned char g_static_scratch[FTB_STATIC_SCRATCH_BYTES];
+
+static std::atomic<void *> g_static_scratch_ptr[64];   // per device ordinal, filled at first use
+
+int ftb_causal_dot_product_static(const void *q, const void *k, const void *v, void *out, int64_t N,
+                                  int64_t H, int64_t L, int64_t D, int64_t M, const int64_t *qs,
+                                  const int64_t *ks, const int64_t *vs, const int64_t *os, int dtype,
+                                  int mode, void *stream) {
+    int dev = -1;
+    FTB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return FTB_ERR_UNSUPPORTED;
+    // Set-up: the first call on a device (and the first call of each further host thread, which
+    // also gives that thread a bound context) resolves the symbol.  It is a synchronous lookup,
+    // so it should happen before any stream capture begins.
+    static thread_local int t_resolved_dev = -1;
+    void *scratch = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (scratch == nullptr || t_resolved_dev != dev) {
+        void *p = nullptr;
+        FTB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (p == nullptr) return FTB_ERR_CUDA;
+        g_static_scratch_ptr[dev].store(p, std::memory_order_release);
+        t_resolved_dev = dev;
+        scratch = p;
+    }
+    const size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, 0);
+    if (need > (size_t)FTB_STATIC_SCRATCH_BYTES) return FTB_ERR_STATIC_LIMIT;
+    // Nothing below allocates: tensor maps are encoded on the host stack, kernels are launched
+    // on `stream`, the per-segment states go to the static array.  Every value read from the
+    // array during a call was written earlier in the same call, so stale contents are harmless.
+    return ftb_causal_dot_product(q, k, v, out, N, H, L, D, M, qs, ks, vs, os, dtype, mode, nullptr,
+                                  nullptr, scratch, (size_t)FTB_STATIC_SCRATCH_BYTES, stream);
 }
 
 }  // extern "C"

@@ -52,6 +52,7 @@ extern "C" {
 #define FTB_ERR_CUDA 4        /* a CUDA runtime call failed (see ftb_last_cuda_error)*/
 #define FTB_ERR_TIMEOUT 5     /* a bounded device-side wait expired                  */
 #define FTB_ERR_INVALID 6     /* NULL pointer, negative size, unknown enum           */
+#define FTB_ERR_STATIC_LIMIT 7 /* scratch need exceeds FTB_STATIC_SCRATCH_BYTES      */
 
 #define FTB_F32 0
 #define FTB_BF16 1
@@ -154,6 +155,34 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
                          int64_t L, int64_t D, int64_t M, const int64_t *x_strides,
                          const int64_t *y_strides, int dtype, int mode, void *workspace,
                          size_t workspace_bytes, void *stream);
+
+/*
+ * Forward product that allocates nothing (it has no counterpart in the reference, whose kernels
+ * use no scratch memory at all).
+ *
+ * Meant for callers that cannot call cudaMalloc when the product runs: code living inside
+ * somebody else's memory pool, a serving or real-time loop whose allocator is frozen after
+ * start-up, plugin hosts that forbid allocation from plugins.  It computes exactly what
+ * ftb_causal_dot_product computes (no initial/final state), but its per-segment state scratch is
+ * a static device array inside the library instead of a caller workspace:
+ *
+ *   - limit: the scratch need, ftb_causal_workspace_bytes(N,H,L,D,M,dtype,mode,0,0), must not
+ *     exceed FTB_STATIC_SCRATCH_BYTES (16 MiB); larger problems return FTB_ERR_STATIC_LIMIT and
+ *     enqueue nothing.  Every GPU that loads the library holds those 16 MiB until exit.
+ *   - the first call on a device (and the first call of each host thread) resolves the array's
+ *     device address synchronously; make that call before starting any stream capture.
+ *   - all calls on a device share the one array: calls whose kernels can overlap on the GPU
+ *     (different streams, no ordering between them) race on it and must be serialised by the
+ *     caller.  Stale contents from an earlier call are harmless -- each call writes what it reads.
+ *   - it calls no cudaMalloc / cudaFree or other allocating routine; inputs and the output are
+ *     still the caller's buffers.
+ */
+#define FTB_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
+int ftb_causal_dot_product_static(const void *q, const void *k, const void *v, void *out,
+                                  int64_t N, int64_t H, int64_t L, int64_t D, int64_t M,
+                                  const int64_t *q_strides, const int64_t *k_strides,
+                                  const int64_t *v_strides, const int64_t *out_strides,
+                                  int dtype, int mode, void *stream);
 
 #ifdef __cplusplus
 }
