@@ -36,12 +36,14 @@ def parse():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 4, 5])
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5])
     ap.add_argument("--mode", default=None, choices=["fp32", "mma"])
     ap.add_argument("--L", type=int, default=None, help="override the sequence length")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time eager calls, not a CUDA graph")
+    ap.add_argument("--layers", type=int, default=None, help="config 3: override the layer count")
+    ap.add_argument("--batch", type=int, default=None, help="config 3: override the batch size")
     return ap.parse_args()
 
 
@@ -167,6 +169,126 @@ def run_reference(args, shape, inputs, name):
 
 
 # ------------------------------------------------------------------------------------------
+# config 3: the 16-layer causal-linear encoder built by TransformerEncoderBuilder
+# ------------------------------------------------------------------------------------------
+def run_encoder(args):
+    """Forward + backward of the encoder (16 layers, 8 heads x 64, FFN 2048, elu+1 feature map,
+    random-init weights, dropout 0) on X~U[0,1) of shape (16, 8192, 512), fp32, with a causal
+    mask.  Data parallel over ranks (each rank its own batch; no gradient all-reduce is timed:
+    the metric is the attention path inside a model, not an optimiser step)."""
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    import fast_transformers_b200 as ftb
+    from fast_transformers_b200 import _native, workloads
+    from fast_transformers_b200.builders import TransformerEncoderBuilder
+    from fast_transformers_b200.masking import LengthMask, TriangularCausalMask
+    lib = _native.lib()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    mode = args.mode or ftb.get_mode()
+    # In "mma" mode the attention runs TF32 tensor-core MMAs; the Linear layers (torch GEMMs)
+    # get the same arithmetic through torch's own switch, otherwise true-fp32 GEMMs dominate.
+    torch.backends.cuda.matmul.allow_tf32 = mode == "mma"
+    cfg = dict(workloads.ENCODER)
+    if args.layers:
+        cfg["n_layers"] = args.layers
+    io = dict(workloads.ENCODER_INPUT)
+    if args.batch:
+        io["N"] = args.batch
+    if args.L:
+        io["L"] = args.L
+    torch.manual_seed(3000 + rank)
+    model = TransformerEncoderBuilder.from_kwargs(**cfg).get().to(dev)
+    gen = workloads.generator(3, rank)
+    X = torch.rand(io["N"], io["L"], io["d_model"], generator=gen)
+    W = torch.randn(io["N"], io["L"], io["d_model"], generator=gen)
+    Xp = X.pin_memory()
+    Xd, Wd = X.to(dev), W.to(dev)
+    mask = TriangularCausalMask(io["L"], device=dev)
+    lengths = LengthMask(torch.full((io["N"],), io["L"], dtype=torch.int64, device=dev), max_len=io["L"])
+    tokens = io["N"] * io["L"]
+
+    def step(x):
+        model.zero_grad(set_to_none=True)
+        with ftb.mode(mode):
+            y = model(x, attn_mask=mask, length_mask=lengths)
+            loss = (y * Wd).sum()
+            loss.backward()
+        return loss
+
+    for _ in range(max(args.warmup, 3)):
+        step(Xd)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    n0 = lib.ftb_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step(Xd)
+    e1.record()
+    torch.cuda.synchronize()
+    launches = lib.ftb_launch_count() - n0
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    clocks = sampler.stop() if sampler else None
+    # device time of this library's kernels inside one step (events around every launch)
+    lib.ftb_timing_enable(1)
+    step(Xd)
+    torch.cuda.synchronize()
+    kinds = _native.timing_read()
+    lib.ftb_timing_enable(0)
+    # end to end: the input comes from pinned host memory, the loss goes back to the host
+    xd = torch.empty_like(Xd)
+    e0.record()
+    n_e2e = max(2, min(args.steps, 5))
+    for _ in range(n_e2e):
+        xd.copy_(Xp, non_blocking=True)
+        loss = step(xd)
+        loss.item()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / n_e2e
+    if rank == 0:
+        H, D = cfg["n_heads"], cfg["query_dimensions"]
+        attn_bytes = workloads.algorithmic_bytes(D, D, 4) * tokens * H * cfg["n_layers"]
+        print(json.dumps({
+            "metric": METRIC, "value": world * tokens / (ms_step * 1e-3) / 1e6, "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": {"fp32": "f32", "mma": "tf32"}[mode],
+            "data": "synthetic (seeded), random-init weights, dropout 0 (builder default 0.1)",
+            "config": {"workload": "config3 causal-linear encoder fwd+bwd %d layers H%d d%d FFN%d "
+                                   "X(%d,%d,%d) float32" % (cfg["n_layers"], H, D,
+                                                            cfg["feed_forward_dimensions"],
+                                                            io["N"], io["L"], io["d_model"]),
+                       "mode": mode, "global_batch": io["N"] * world, "cuda_graph": False,
+                       "linear_layers": "torch GEMMs, allow_tf32=%s" % (mode == "mma"),
+                       "l2": "activations per step far exceed the 126 MB L2; no flush"},
+            "roofline": {"bound": "hbm", "kernel": "whole model (GEMMs dominate)", "achieved": None,
+                         "peak": None, "unit": "GB/s", "frac": None, "traffic": None,
+                         "attention_algorithmic_bytes": attn_bytes,
+                         "attention_kernels_ms_per_step": {k: v[0] for k, v in kinds.items()},
+                         "attention_kernels_share_of_step": sum(v[0] for v in kinds.values()) / ms_step},
+            "cpu_baseline": None,
+            "e2e": {"value": world * tokens / (e2e_ms * 1e-3) / 1e6, "unit": UNIT,
+                    "h2d_bytes_per_step": X.numel() * 4, "d2h_bytes_per_step": 4,
+                    "ms_per_step": e2e_ms, "steps": n_e2e},
+            "gpu_launches": int(launches), "clocks": clocks}))
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+# ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
 def main():
@@ -176,6 +298,14 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
 
     from fast_transformers_b200 import workloads
+    if args.config == 3:
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable":
+                                  "config 3 (whole encoder) is not timed on the CPU; the reference "
+                                  "arm covers the causal_dot_product configs"}))
+            return 0
+        return run_encoder(args)
     shape = dict(workloads.SHAPES[args.config])
     if args.L:
         shape["L"] = args.L

@@ -58,13 +58,13 @@ def lib():
     L.ftb_causal_workspace_bytes.argtypes = [_i64] * 5 + [_int] * 4
     L.ftb_causal_dot_product.restype = _int
     L.ftb_causal_dot_product.argtypes = (
-        [_vp] * 4 + [_i64] * 5 + [_i64p] * 4 + [_int, _int, _vp, _vp, _vp, _sz, _vp])
+        [_vp] * 4 + [_i64] * 5 + [_i64p] * 4 + [_int, _int, _vp, _vp, _int, _vp, _sz, _vp])
     L.ftb_causal_dot_backward.restype = _int
     L.ftb_causal_dot_backward.argtypes = (
-        [_vp] * 7 + [_i64] * 5 + [_i64p] * 7 + [_int, _int, _vp, _vp, _vp, _vp, _sz, _vp])
+        [_vp] * 7 + [_i64] * 5 + [_i64p] * 7 + [_int, _int, _vp, _vp, _vp, _int, _vp, _sz, _vp])
     L.ftb_causal_state_sum.restype = _int
     L.ftb_causal_state_sum.argtypes = (
-        [_vp] * 3 + [_i64] * 5 + [_i64p] * 2 + [_int, _int, _vp, _sz, _vp])
+        [_vp] * 3 + [_i64] * 5 + [_i64p] * 2 + [_int, _int, _int, _vp, _sz, _vp])
     L.ftb_causal_dot_product_static.restype = _int
     L.ftb_causal_dot_product_static.argtypes = (
         [_vp] * 4 + [_i64] * 5 + [_i64p] * 4 + [_int, _int, _vp])

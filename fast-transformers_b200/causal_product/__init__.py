@@ -73,8 +73,15 @@ def _state_ok(s, N, H, D, M, dev, name):
     return s.contiguous()
 
 
+def workspace_bytes(N, H, L, D, M, dtype, mode=None, backward=False, want_state=False):
+    """Scratch bytes of one forward (or backward) call; see ``ftb_causal_workspace_bytes``."""
+    return _native.lib().ftb_causal_workspace_bytes(
+        N, H, L, D, M, _DTYPES[dtype], _mode_id(mode), int(backward), int(want_state))
+
+
 def causal_dot_product_cuda(queries, keys, values, product, mode=None, initial_state=None,
-                            final_state=None, keep_workspace=None):
+                            final_state=None, keep_workspace=None, workspace=None,
+                            workspace_has_states=False):
     """Fill ``product`` (N, H, L, M) in place -- the reference's native forward signature
     (``causal_product_cuda.cu:1273-1276``), plus optional fp32 states (N, H, D, M)."""
     dev = _check_cuda(queries, keys, values, product)
@@ -99,12 +106,17 @@ def causal_dot_product_cuda(queries, keys, values, product, mode=None, initial_s
     m = _mode_id(mode)
     with torch.cuda.device(dev):
         nbytes = L_.ftb_causal_workspace_bytes(N, H, L, D, M, dt, m, 0, int(final_state is not None))
-        ws, nbytes = _workspace(nbytes, dev)
+        if workspace is not None:
+            if workspace.numel() * workspace.element_size() < nbytes:
+                raise RuntimeError("workspace tensor is too small")
+            ws, nbytes = workspace, workspace.numel() * workspace.element_size()
+        else:
+            ws, nbytes = _workspace(nbytes, dev)
         st = L_.ftb_causal_dot_product(
             _ptr(q), _ptr(k), _ptr(v), _ptr(product), N, H, L, D, M,
             _native.strides3(q), _native.strides3(k), _native.strides3(v),
             _native.strides3(product), dt, m, _ptr(initial_state), _ptr(final_state),
-            _ptr(ws), nbytes, ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+            int(bool(workspace_has_states)), _ptr(ws), nbytes, ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     _native.check(st, "ftb_causal_dot_product")
     if keep_workspace is not None:
         # the per-segment forward states; the backward pass reuses them if handed back
@@ -113,7 +125,8 @@ def causal_dot_product_cuda(queries, keys, values, product, mode=None, initial_s
 
 def causal_dot_backward_cuda(queries, keys, values, grad_out, grad_queries, grad_keys,
                              grad_values, mode=None, initial_state=None,
-                             initial_grad_state=None, forward_workspace=None):
+                             initial_grad_state=None, forward_workspace=None, workspace=None,
+                             workspace_has_grad_states=False):
     """Fill the three gradients in place -- the reference's native backward signature
     (``causal_product_cuda.cu:1438-1444``).  ``grad_out`` may be any view (expanded,
     permuted); it is made row-contiguous only if its last stride is not 1."""
@@ -135,19 +148,25 @@ def causal_dot_backward_cuda(queries, keys, values, grad_out, grad_queries, grad
     m = _mode_id(mode)
     with torch.cuda.device(dev):
         nbytes = L_.ftb_causal_workspace_bytes(N, H, L, D, M, dt, m, 1, 0)
-        ws, nbytes = _workspace(nbytes, dev)
+        if workspace is not None:
+            if workspace.numel() * workspace.element_size() < nbytes:
+                raise RuntimeError("workspace tensor is too small")
+            ws, nbytes = workspace, workspace.numel() * workspace.element_size()
+        else:
+            ws, nbytes = _workspace(nbytes, dev)
         st = L_.ftb_causal_dot_backward(
             _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(grad_queries), _ptr(grad_keys),
             _ptr(grad_values), N, H, L, D, M,
             _native.strides3(q), _native.strides3(k), _native.strides3(v), _native.strides3(g),
             _native.strides3(grad_queries), _native.strides3(grad_keys),
             _native.strides3(grad_values), dt, m, _ptr(initial_state),
-            _ptr(initial_grad_state), _ptr(forward_workspace), _ptr(ws), nbytes,
+            _ptr(initial_grad_state), _ptr(forward_workspace),
+            int(bool(workspace_has_grad_states)), _ptr(ws), nbytes,
             ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     _native.check(st, "ftb_causal_dot_backward")
 
 
-def causal_state_sum(x, y, mode=None):
+def causal_state_sum(x, y, mode=None, workspace=None, reverse=False):
     """``sum_l x[n,h,l,:] (x) y[n,h,l,:]`` as a float32 (N, H, D, M) tensor: the state a
     range of positions contributes to the ranges after it (x=K, y=V) or before it
     (x=Q, y=grad_out)."""
@@ -163,10 +182,17 @@ def causal_state_sum(x, y, mode=None):
     m = _mode_id(mode)
     with torch.cuda.device(dev):
         nbytes = L_.ftb_causal_workspace_bytes(N, H, L, D, M, dt, m, 0, 1)
-        ws, nbytes = _workspace(nbytes, dev)
+        if workspace is not None:
+            # a caller-kept workspace: the per-segment states left in it can be handed to the
+            # forward (workspace_has_states) or backward (workspace_has_grad_states) call
+            if workspace.numel() * workspace.element_size() < nbytes:
+                raise RuntimeError("workspace tensor is too small")
+            ws, nbytes = workspace, workspace.numel() * workspace.element_size()
+        else:
+            ws, nbytes = _workspace(nbytes, dev)
         st = L_.ftb_causal_state_sum(
             _ptr(x), _ptr(y), _ptr(state), N, H, L, D, M, _native.strides3(x),
-            _native.strides3(y), dt, m, _ptr(ws), nbytes,
+            _native.strides3(y), dt, m, int(bool(reverse)), _ptr(ws), nbytes,
             ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
     _native.check(st, "ftb_causal_state_sum")
     return state

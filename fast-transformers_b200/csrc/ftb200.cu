@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <mutex>
 #include <vector>
 
 #include "mma_host.cuh"
@@ -25,24 +26,26 @@ static inline int cuda_fail(cudaError_t e) {
     } while (0)
 
 // ---- launch accounting --------------------------------------------------------------------
-// A process-wide count of kernel launches, and an optional per-thread recorder that brackets
-// every launch with CUDA events on the launching stream so a caller can attribute device
-// time to kernel kinds (FTB_KERNEL_*).  Off by default; it changes nothing else.
+// A process-wide count of kernel launches, and an optional recorder that brackets every
+// launch (of any host thread: autograd runs the backward on its own) with CUDA events on the
+// launching stream so a caller can attribute device time to kernel kinds (FTB_KERNEL_*).
+// Off by default; it changes nothing else.
 static std::atomic<uint64_t> g_launches{0};
 
 struct TimedSpan {
     int kind;
     cudaEvent_t beg, end;
 };
-static thread_local bool g_timing = false;
-static thread_local std::vector<TimedSpan> g_spans;
+static std::atomic<bool> g_timing{false};
+static std::mutex g_spans_mutex;
+static std::vector<TimedSpan> g_spans;
 
 struct LaunchScope {
     cudaStream_t st;
     cudaEvent_t end = nullptr;
     LaunchScope(int kind, cudaStream_t s) : st(s) {
         g_launches.fetch_add(1, std::memory_order_relaxed);
-        if (!g_timing) return;
+        if (!g_timing.load(std::memory_order_relaxed)) return;
         TimedSpan sp;
         sp.kind = kind;
         if (cudaEventCreate(&sp.beg) != cudaSuccess) return;
@@ -52,6 +55,7 @@ struct LaunchScope {
         }
         cudaEventRecord(sp.beg, st);
         end = sp.end;
+        std::lock_guard<std::mutex> lock(g_spans_mutex);
         g_spans.push_back(sp);
     }
     ~LaunchScope() {
@@ -115,13 +119,15 @@ static int simt_launch_state_sum(const void *x, const void *y, const int64_t *xs
     return FTB_OK;
 }
 
-static int launch_prefix(float *states, const float *init, float *total, int64_t BH, int nseg,
+static int launch_prefix(float *states, const float *init, float *total, const float *total_init,
+                         int64_t BH, int nseg,
                          int64_t DM, int reverse, cudaStream_t st) {
     int64_t n = BH * DM;
     if (n <= 0) return FTB_OK;
     int64_t blocks = (n + 255) / 256;
     LaunchScope scope(FTB_KERNEL_STATE_PREFIX, st);
-    state_prefix_kernel<<<(unsigned)blocks, 256, 0, st>>>(states, init, total, BH, nseg, DM, reverse);
+    state_prefix_kernel<<<(unsigned)blocks, 256, 0, st>>>(states, init, total, total_init, BH, nseg, DM,
+                                                             reverse);
     FTB_CUDA(cudaGetLastError());
     return FTB_OK;
 }
@@ -256,7 +262,10 @@ static inline bool sums_in_kernel(int mode, Plan pl) {
 static SegStates describe_states(int mode, Plan pl, const float *ws, const float *init) {
     if (pl.nseg == 1) return SegStates{nullptr, init, 0};
     if (sums_in_kernel(mode, pl)) return SegStates{ws, init, 1};
-    return SegStates{ws, nullptr, 0};   // exclusive prefixes with `init` folded in
+    // exclusive prefixes: the tensor-core kernel adds `init` itself, the fp32 kernel reads one
+    // block per segment, so there `init` is folded into the prefixes
+    if (mode == FTB_MODE_MMA) return SegStates{ws, init, 0};
+    return SegStates{ws, nullptr, 0};
 }
 
 // Per-segment totals of sum x (x) y into `ws`, turned into what the scans read; optionally the
@@ -281,8 +290,10 @@ static int prepare_states(int mode, const void *x, const void *y, const int64_t 
     }
     rc = launch_state_sum(mode, x, y, xs, ys, N, H, L, D, M, dtype, pl, ws, -1, st);
     if (rc) return rc;
-    rc = launch_prefix(ws, init, total, N * H, pl.nseg, (int64_t)D * M, reverse, st);
-    if (pl.nseg == 1) *out = SegStates{ws, nullptr, 0};
+    const bool fold = mode != FTB_MODE_MMA;
+    rc = launch_prefix(ws, fold ? init : nullptr, total, fold ? nullptr : init, N * H, pl.nseg,
+                       (int64_t)D * M, reverse, st);
+    if (pl.nseg == 1) *out = SegStates{ws, fold ? nullptr : init, 0};
     return rc;
 }
 
@@ -343,6 +354,7 @@ int ftb_debug_read_timestamps(long long *dst, int n) {
 uint64_t ftb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 void ftb_timing_enable(int enable) {
+    std::lock_guard<std::mutex> lock(g_spans_mutex);
     if (!enable) {
         for (auto &sp : g_spans) {
             cudaEventDestroy(sp.beg);
@@ -350,7 +362,7 @@ void ftb_timing_enable(int enable) {
         }
         g_spans.clear();
     }
-    g_timing = enable != 0;
+    g_timing.store(enable != 0);
 }
 
 int ftb_timing_read(float *ms_by_kind, int *launches_by_kind, int nkinds) {
@@ -360,6 +372,7 @@ int ftb_timing_read(float *ms_by_kind, int *launches_by_kind, int nkinds) {
         launches_by_kind[i] = 0;
     }
     int rc = FTB_OK;
+    std::lock_guard<std::mutex> lock(g_spans_mutex);
     for (auto &sp : g_spans) {
         float ms = 0.f;
         cudaError_t e = cudaEventSynchronize(sp.end);
@@ -393,7 +406,8 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
                            int64_t H, int64_t L, int64_t D, int64_t M, const int64_t *qs,
                            const int64_t *ks, const int64_t *vs, const int64_t *os, int dtype,
                            int mode, const float *initial_state, float *final_state,
-                           void *workspace, size_t workspace_bytes, void *stream) {
+                           int workspace_has_states, void *workspace, size_t workspace_bytes,
+                           void *stream) {
     int rc = check_common(N, H, L, D, M, dtype, mode);
     if (rc != FTB_OK) return rc;
     if (!qs || !ks || !vs || !os) return FTB_ERR_INVALID;
@@ -427,9 +441,14 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
         if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
     }
     SegStates ss;
-    rc = prepare_states(mode, k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, ws, initial_state,
-                        final_state, 0, st, &ss);
-    if (rc) return rc;
+    if (workspace_has_states && mode == FTB_MODE_MMA && !final_state) {
+        // ftb_causal_state_sum(k, v, ...) already left the per-segment states in `workspace`
+        ss = describe_states(mode, pl, ws, initial_state);
+    } else {
+        rc = prepare_states(mode, k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, ws, initial_state,
+                            final_state, 0, st, &ss);
+        if (rc) return rc;
+    }
     return launch_scan(mode, q, k, v, out, qs, ks, vs, os, N, H, L, (int)D, (int)M, dtype, pl, ss,
                        /*canon_is_DaDc=*/1, /*reverse=*/0, st);
 }
@@ -440,7 +459,8 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
                             const int64_t *gs, const int64_t *gqs, const int64_t *gks,
                             const int64_t *gvs, int dtype, int mode, const float *initial_state,
                             const float *initial_grad_state, const void *forward_workspace,
-                            void *workspace, size_t workspace_bytes, void *stream) {
+                            int workspace_has_grad_states, void *workspace, size_t workspace_bytes,
+                            void *stream) {
     int rc = check_common(N, H, L, D, M, dtype, mode);
     if (rc != FTB_OK) return rc;
     if (!qs || !ks || !vs || !gs || !gqs || !gks || !gvs) return FTB_ERR_INVALID;
@@ -480,9 +500,14 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
                             nullptr, 0, st, &sS);
         if (rc) return rc;
     }
-    rc = prepare_states(mode, q, g, qs, gs, N, H, L, (int)D, (int)M, dtype, pl, wsR, initial_grad_state,
-                        nullptr, 1, st, &sR);
-    if (rc) return rc;
+    if (workspace_has_grad_states && mode == FTB_MODE_MMA) {
+        // ftb_causal_state_sum(q, grad_out, ..., reverse=1, second half of `workspace`) ran before
+        sR = describe_states(mode, pl, wsR, initial_grad_state);
+    } else {
+        rc = prepare_states(mode, q, g, qs, gs, N, H, L, (int)D, (int)M, dtype, pl, wsR,
+                            initial_grad_state, nullptr, 1, st, &sR);
+        if (rc) return rc;
+    }
 
     // grad_Q_i = sum_{j<=i} (g_i . v_j) k_j + S_init g_i        state viewed as [M][D]
     rc = launch_scan(mode, g, v, k, gq, gs, vs, ks, gqs, N, H, L, (int)M, (int)D, dtype, pl, sS, 0, 0, st);
@@ -496,7 +521,7 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
 
 int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, int64_t H,
                          int64_t L, int64_t D, int64_t M, const int64_t *xs, const int64_t *ys,
-                         int dtype, int mode, void *workspace, size_t workspace_bytes,
+                         int dtype, int mode, int reverse, void *workspace, size_t workspace_bytes,
                          void *stream) {
     int rc = check_common(N, H, L, D, M, dtype, mode);
     if (rc != FTB_OK) return rc;
@@ -516,7 +541,7 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
     if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
     SegStates ss;
     return prepare_states(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, (float *)workspace,
-                          nullptr, state, 0, st, &ss);
+                          nullptr, state, reverse ? 1 : 0, st, &ss);
 }
 
 
@@ -562,7 +587,7 @@ int ftb_causal_dot_product_static(const void *q, const void *k, const void *v, v
     // on `stream`, the per-segment states go to the static array.  Every value read from the
     // array during a call was written earlier in the same call, so stale contents are harmless.
     return ftb_causal_dot_product(q, k, v, out, N, H, L, D, M, qs, ks, vs, os, dtype, mode, nullptr,
-                                  nullptr, scratch, (size_t)FTB_STATIC_SCRATCH_BYTES, stream);
+                                  nullptr, 0, scratch, (size_t)FTB_STATIC_SCRATCH_BYTES, stream);
 }
 
 }  // extern "C"

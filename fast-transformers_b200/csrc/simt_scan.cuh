@@ -366,10 +366,12 @@ __global__ void __launch_bounds__(NTHR) simt_state_sum_kernel(StateSumArgs p) {
 
 // ---------------------------------------------------------------------------------------
 // exclusive prefix (suffix) of the per-segment totals along the segment axis, in place;
-// `init` (per bh) is added to every entry, `total` (per bh) receives init + all segments.
+// `init` (per bh) is added to every entry, `total` (per bh) receives init + total_init + all
+// segments (total_init lets a caller keep the entries free of an initial state it adds later).
 // ---------------------------------------------------------------------------------------
 __global__ void state_prefix_kernel(float *states, const float *init, float *total,
-                                    int64_t BH, int nseg, int64_t DM, int reverse) {
+                                    const float *total_init, int64_t BH, int nseg, int64_t DM,
+                                    int reverse) {
     int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= BH * DM) return;
     int64_t bh = idx / DM, e = idx % DM;
@@ -388,7 +390,7 @@ __global__ void state_prefix_kernel(float *states, const float *init, float *tot
             run += t;
         }
     }
-    if (total) total[idx] = run;
+    if (total) total[idx] = run + (total_init ? total_init[idx] : 0.f);
 }
 
 // total[bh] = init[bh] + sum over all segments of the raw per-segment totals

@@ -24,29 +24,49 @@ import torch.distributed as dist
 
 
 class LocalOps(object):
-    """The three per-rank operations.  The default implementation is the native library."""
+    """The three per-rank operations.  The default implementation is the native library.
 
-    def state_sum(self, x, y):
-        from .causal_product import causal_state_sum
-        return causal_state_sum(x, y, mode=self.mode)
-
-    def forward(self, Q, K, V, initial_state):
-        from .causal_product import causal_dot_product_cuda
-        out = torch.empty(Q.shape[0], Q.shape[1], Q.shape[2], V.shape[3], device=Q.device,
-                          dtype=Q.dtype)
-        causal_dot_product_cuda(Q, K, V, out, self.mode, initial_state=initial_state)
-        return out
-
-    def backward(self, Q, K, V, G, initial_state, initial_grad_state):
-        from .causal_product import causal_dot_backward_cuda
-        gq, gk, gv = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(V)
-        causal_dot_backward_cuda(Q, K, V, G, gq, gk, gv, self.mode, initial_state=initial_state,
-                                 initial_grad_state=initial_grad_state)
-        return gq, gk, gv
+    ``state_sum`` returns the rank-local total and a token (the workspace holding the
+    per-segment states it computed on the way); ``forward`` / ``backward`` take the tokens back so
+    K, V (and Q, grad_out) are swept once, not twice."""
 
     def __init__(self, mode=None):
         from .settings import get_mode
         self.mode = mode or get_mode()
+
+    def _bytes(self, Q, V, backward):
+        from .causal_product import workspace_bytes
+        N, H, L, D = Q.shape
+        return workspace_bytes(N, H, L, D, V.shape[3], Q.dtype, self.mode, backward=backward,
+                               want_state=True)
+
+    def state_sum(self, x, y, reverse=False):
+        from .causal_product import causal_state_sum
+        if not reverse:
+            ws = torch.empty(max(self._bytes(x, y, False), 1), dtype=torch.uint8, device=x.device)
+            return causal_state_sum(x, y, mode=self.mode, workspace=ws), ws
+        # the backward's workspace: [forward-state half | grad-state half]
+        total = self._bytes(x, y, True)
+        ws = torch.empty(max(total, 1), dtype=torch.uint8, device=x.device)
+        half = ws[total // 2:]
+        return causal_state_sum(x, y, mode=self.mode, workspace=half, reverse=True), ws
+
+    def forward(self, Q, K, V, initial_state, token):
+        from .causal_product import causal_dot_product_cuda
+        out = torch.empty(Q.shape[0], Q.shape[1], Q.shape[2], V.shape[3], device=Q.device,
+                          dtype=Q.dtype)
+        causal_dot_product_cuda(Q, K, V, out, self.mode, initial_state=initial_state,
+                                workspace=token, workspace_has_states=True)
+        return out
+
+    def backward(self, Q, K, V, G, initial_state, initial_grad_state, fwd_token, bwd_token):
+        from .causal_product import causal_dot_backward_cuda
+        gq, gk, gv = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(V)
+        use_fwd = fwd_token if (fwd_token is not None and self.mode == "mma") else None
+        causal_dot_backward_cuda(Q, K, V, G, gq, gk, gv, self.mode, initial_state=initial_state,
+                                 initial_grad_state=initial_grad_state, forward_workspace=use_fwd,
+                                 workspace=bwd_token, workspace_has_grad_states=True)
+        return gq, gk, gv
 
 
 def exclusive_scan_over_ranks(local, group=None, reverse=False):
@@ -69,20 +89,21 @@ def exclusive_scan_over_ranks(local, group=None, reverse=False):
 class SequenceParallelCausalDotProduct(torch.autograd.Function):
     @staticmethod
     def forward(ctx, Q, K, V, group, ops):
-        T = ops.state_sum(K.detach(), V.detach())
+        T, token = ops.state_sum(K.detach(), V.detach(), reverse=False)
         S_init = exclusive_scan_over_ranks(T, group, reverse=False)
-        out = ops.forward(Q.detach(), K.detach(), V.detach(), S_init)
+        out = ops.forward(Q.detach(), K.detach(), V.detach(), S_init, token)
         ctx.save_for_backward(Q, K, V, S_init)
-        ctx.group, ctx.ops = group, ops
+        ctx.group, ctx.ops, ctx.token = group, ops, token
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         Q, K, V, S_init = ctx.saved_tensors
         G = grad_out if grad_out.dtype == Q.dtype else grad_out.to(Q.dtype)
-        U = ctx.ops.state_sum(Q.detach(), G)
+        U, bwd_token = ctx.ops.state_sum(Q.detach(), G, reverse=True)
         R_init = exclusive_scan_over_ranks(U, ctx.group, reverse=True)
-        gq, gk, gv = ctx.ops.backward(Q.detach(), K.detach(), V.detach(), G, S_init, R_init)
+        gq, gk, gv = ctx.ops.backward(Q.detach(), K.detach(), V.detach(), G, S_init, R_init,
+                                      ctx.token, bwd_token)
         return gq, gk, gv, None, None
 
 

@@ -72,8 +72,8 @@ int ftb_last_cuda_error(void);
 /*
  * Launch accounting (no counterpart in the reference; used by the benchmark).
  * ftb_launch_count: kernels launched by this library in this process so far.
- * ftb_timing_enable(1): from now on every launch made by THIS thread is bracketed by CUDA
- *   events on its stream.  ftb_timing_read synchronises those events, adds the elapsed
+ * ftb_timing_enable(1): from now on every launch (made by any host thread) is bracketed by
+ *   CUDA events on its stream.  ftb_timing_read synchronises those events, adds the elapsed
  *   milliseconds and launch counts per kernel kind into the two arrays (length nkinds),
  *   and forgets the recorded launches.  ftb_timing_enable(0) stops recording.
  */
@@ -110,14 +110,18 @@ size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, in
  * initial_state : optional (N,H,D,M) fp32 state added before position 0 (NULL = zeros);
  *                 used when a sequence is split across devices or continued.
  * final_state   : optional (N,H,D,M) fp32 output, S_init + sum over all L positions.
+ * workspace_has_states : non-zero when ftb_causal_state_sum(k, v, ...) has just been run with this
+ *                 same workspace, shape, dtype and mode (and final_state is NULL): the
+ *                 per-segment states it left there are used instead of sweeping K and V again.
+ *                 Honoured in FTB_MODE_MMA; ignored (recomputed) otherwise.
  */
 int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *out,
                            int64_t N, int64_t H, int64_t L, int64_t D, int64_t M,
                            const int64_t *q_strides, const int64_t *k_strides,
                            const int64_t *v_strides, const int64_t *out_strides,
                            int dtype, int mode, const float *initial_state,
-                           float *final_state, void *workspace, size_t workspace_bytes,
-                           void *stream);
+                           float *final_state, int workspace_has_states, void *workspace,
+                           size_t workspace_bytes, void *stream);
 
 /*
  * Backward: gq_i = S_i g_i ; gk_i = R_i v_i ; gv_i = R_i^T k_i with
@@ -133,6 +137,10 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
  *                      still intact.  It holds the per-segment forward states, which the
  *                      backward then does not recompute (one pass over K and V saved).
  *                      NULL = recompute.  The reference keeps nothing but Q, K, V either.
+ * workspace_has_grad_states : non-zero when ftb_causal_state_sum(q, grad_out, ..., reverse = 1)
+ *                      has just been run on the SECOND half of `workspace` (offset
+ *                      ftb_causal_workspace_bytes(..., backward = 1, 0) / 2); honoured in
+ *                      FTB_MODE_MMA, ignored otherwise.
  */
 int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const void *grad_out,
                             void *grad_q, void *grad_k, void *grad_v, int64_t N, int64_t H,
@@ -142,7 +150,8 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
                             const int64_t *gk_strides, const int64_t *gv_strides, int dtype,
                             int mode, const float *initial_state,
                             const float *initial_grad_state, const void *forward_workspace,
-                            void *workspace, size_t workspace_bytes, void *stream);
+                            int workspace_has_grad_states, void *workspace,
+                            size_t workspace_bytes, void *stream);
 
 /*
  * Whole-range state  state[n,h,:,:] = sum_l x[n,h,l,:] (x) y[n,h,l,:]   ((N,H,D,M) fp32).
@@ -150,11 +159,14 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
  * the shards after it; with (x, y) = (Q, grad_out) what it contributes to the backward
  * state of the shards before it.  The reference has no such entry point (it is single
  * device); the sum is the one accumulated by causal_product_cpu.cpp:107-113,186-192.
+ * The per-segment states it leaves in `workspace` can be handed to the forward / backward entry
+ * points (workspace_has_states / workspace_has_grad_states); pass reverse = 1 when they will seed
+ * the backward's descending scans (x = Q, y = grad_out).
  */
 int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, int64_t H,
                          int64_t L, int64_t D, int64_t M, const int64_t *x_strides,
-                         const int64_t *y_strides, int dtype, int mode, void *workspace,
-                         size_t workspace_bytes, void *stream);
+                         const int64_t *y_strides, int dtype, int mode, int reverse,
+                         void *workspace, size_t workspace_bytes, void *stream);
 
 /*
  * Forward product that allocates nothing (it has no counterpart in the reference, whose kernels

@@ -216,13 +216,13 @@ def test_workspace_error_code(native_lib):
     s = _native.strides3(Q)
     st = native_lib.ftb_causal_dot_product(
         Q.data_ptr(), Q.data_ptr(), Q.data_ptr(), out.data_ptr(), 1, 1, 4096, 8, 8, s, s, s, s,
-        _native.F32, _native.MODE_FP32_SIMT, None, None, None, 0, None)
+        _native.F32, _native.MODE_FP32_SIMT, None, None, 0, None, 0, None)
     assert st == _native.ERR_WORKSPACE
     torch.cuda.synchronize()
     assert out.abs().sum().item() == 0
     st = native_lib.ftb_causal_dot_product(
         Q.data_ptr(), Q.data_ptr(), Q.data_ptr(), out.data_ptr(), 1, 1, 16, 600, 8, s, s, s, s,
-        _native.F32, _native.MODE_FP32_SIMT, None, None, None, 0, None)
+        _native.F32, _native.MODE_FP32_SIMT, None, None, 0, None, 0, None)
     assert st == _native.ERR_UNSUPPORTED
 
 

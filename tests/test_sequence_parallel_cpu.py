@@ -27,15 +27,15 @@ def _free_port():
 class OracleOps(object):
     """fp64 stand-ins for the three local operations."""
 
-    def state_sum(self, x, y):
+    def state_sum(self, x, y, reverse=False):
         from oracle import causal_oracle as orc
-        return orc.local_states(None, x, y)
+        return orc.local_states(None, x, y), None
 
-    def forward(self, Q, K, V, initial_state):
+    def forward(self, Q, K, V, initial_state, token):
         from oracle import causal_oracle as orc
         return orc.chunked_forward(Q, K, V, chunk=16, initial_state=initial_state)
 
-    def backward(self, Q, K, V, G, initial_state, initial_grad_state):
+    def backward(self, Q, K, V, G, initial_state, initial_grad_state, fwd_token, bwd_token):
         from oracle import causal_oracle as orc
         return orc.chunked_backward(Q, K, V, G, chunk=16, initial_state=initial_state,
                                     final_grad_state=initial_grad_state)
