@@ -98,7 +98,7 @@ struct Plan {
 // Segments are whole chunks; one CTA walks one segment.  The count is chosen to minimise
 // waves x (chunks per segment + a fixed per-CTA cost) over the 148 SMs, with a small charge
 // per segment for its state traffic.  FTB200_MMA_SEGS=<n> forces the count (tuning only).
-constexpr int kSumInKernelMaxSegs = 8;   // up to here the scan kernel adds up raw totals itself
+constexpr int kSumInKernelMaxSegs = 16;  // up to here the scan kernel adds up raw totals itself
 
 static Plan plan(int64_t BH, int64_t L, int ntile) {
     Plan p;
