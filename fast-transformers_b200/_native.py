@@ -9,7 +9,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libftb200.so")
+LIB_PATH = os.environ.get("FTB200_LIB") or os.path.join(_HERE, "libftb200.so")
 
 OK, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE, ERR_CUDA, ERR_TIMEOUT, ERR_INVALID, \
     ERR_STATIC_LIMIT = range(8)

@@ -169,7 +169,7 @@ static int simt_launch_scan(const void *a, const void *b, const void *c, void *o
 static int mma_launch(const void *a, const void *b, const void *c, void *out, const int64_t *as,
                       const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H,
                       int64_t L, int Da, int Dc, int dtype, Plan pl, const float *states,
-                      const float *init, int sum_mode, float *state_out, int skip_seg,
+                      const float *init, int sum_mode, int sub, float *state_out, int skip_lo, int skip_hi,
                       int canon_is_DaDc, int reverse, cudaStream_t st) {
     const bool state_only = (a == nullptr);
     const int DCT = dtype == FTB_F32 ? 64 : 128;
@@ -202,7 +202,8 @@ static int mma_launch(const void *a, const void *b, const void *c, void *out, co
     p.H = (int)H; p.L = L; p.Dc = Dc;
     p.seg_len = pl.seg_len; p.nseg = pl.nseg;
     p.states = states; p.state_out = state_out;
-    p.init = init; p.sum_mode = sum_mode; p.skip_seg = skip_seg;
+    p.init = init; p.sum_mode = sum_mode; p.sub = sub < 1 ? 1 : sub;
+    p.skip_lo = skip_lo; p.skip_hi = skip_hi;
     p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = state_only ? 1 : 0;
     static const char *env = std::getenv("FTB200_MMA_TERMS");
     p.terms = env ? std::atoi(env) : 7;
@@ -229,10 +230,11 @@ static Plan choose_plan(int mode, int64_t BH, int64_t L) {
 
 static int launch_state_sum(int mode, const void *x, const void *y, const int64_t *xs,
                             const int64_t *ys, int64_t N, int64_t H, int64_t L, int D, int M,
-                            int dtype, Plan pl, float *states, int skip_seg, cudaStream_t st) {
+                            int dtype, Plan pl, float *states, int skip_lo, int skip_hi,
+                            cudaStream_t st) {
     if (mode == FTB_MODE_MMA)
         return mma_launch(nullptr, x, y, nullptr, nullptr, xs, ys, nullptr, N, H, L, D, M, dtype, pl,
-                          nullptr, nullptr, 0, states, skip_seg, 1, 0, st);
+                          nullptr, nullptr, 0, 1, states, skip_lo, skip_hi, 1, 0, st);
     return simt_launch_state_sum(x, y, xs, ys, N, H, L, D, M, dtype, pl, states, st);
 }
 
@@ -241,6 +243,7 @@ struct SegStates {
     const float *states;  // per (bh, seg) blocks, or nullptr
     const float *init;    // per bh block added on top, or nullptr
     int sum_mode;         // 1: `states` are raw totals the kernel adds up itself
+    int sub;              // sum_mode 1: blocks per segment
 };
 
 static int launch_scan(int mode, const void *a, const void *b, const void *c, void *out,
@@ -249,7 +252,7 @@ static int launch_scan(int mode, const void *a, const void *b, const void *c, vo
                        SegStates ss, int canon_is_DaDc, int reverse, cudaStream_t st) {
     if (mode == FTB_MODE_MMA)
         return mma_launch(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, ss.states, ss.init,
-                          ss.sum_mode, nullptr, -1, canon_is_DaDc, reverse, st);
+                          ss.sum_mode, ss.sub, nullptr, 0, 0, canon_is_DaDc, reverse, st);
     return simt_launch_scan(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl,
                             ss.states ? ss.states : ss.init, pl.nseg, canon_is_DaDc, reverse, st);
 }
@@ -258,14 +261,27 @@ static inline bool sums_in_kernel(int mode, Plan pl) {
     return mode == FTB_MODE_MMA && pl.nseg <= mma::kSumInKernelMaxSegs;
 }
 
-// Describe segment-start states that already sit in `ws` (written by prepare_states).
-static SegStates describe_states(int mode, Plan pl, const float *ws, const float *init) {
-    if (pl.nseg == 1) return SegStates{nullptr, init, 0};
-    if (sums_in_kernel(mode, pl)) return SegStates{ws, init, 1};
+// The state-only launch reads (D+M)/(2D+2M) of what a scan reads and skips one segment per head, so
+// on the scan's own segments it would leave most SMs idle: it runs on `sub` times finer segments
+// (sub blocks per segment in the workspace) unless per-head totals are wanted from the same data.
+static int state_sub(int mode, Plan pl, int64_t BH, bool totals) {
+    if (totals || !sums_in_kernel(mode, pl) || pl.nseg < 2) return 1;
+    const int64_t cps = pl.seg_len / mma::C;
+    for (int sub = 4; sub >= 2; --sub)
+        if (cps % sub == 0 && BH * (pl.nseg - 1) * sub <= 160 && pl.nseg * sub <= 16) return sub;
+    return 1;
+}
+
+// Describe segment-start states that already sit in `ws` (written by prepare_states, or -- when
+// `prepared` -- by ftb_causal_state_sum, which wants totals and therefore uses sub = 1).
+static SegStates describe_states(int mode, Plan pl, const float *ws, const float *init, int64_t BH,
+                                 bool prepared) {
+    if (pl.nseg == 1) return SegStates{nullptr, init, 0, 1};
+    if (sums_in_kernel(mode, pl)) return SegStates{ws, init, 1, state_sub(mode, pl, BH, prepared)};
     // exclusive prefixes: the tensor-core kernel adds `init` itself, the fp32 kernel reads one
     // block per segment, so there `init` is folded into the prefixes
-    if (mode == FTB_MODE_MMA) return SegStates{ws, init, 0};
-    return SegStates{ws, nullptr, 0};
+    if (mode == FTB_MODE_MMA) return SegStates{ws, init, 0, 1};
+    return SegStates{ws, nullptr, 0, 1};
 }
 
 // Per-segment totals of sum x (x) y into `ws`, turned into what the scans read; optionally the
@@ -274,12 +290,20 @@ static int prepare_states(int mode, const void *x, const void *y, const int64_t 
                           int64_t N, int64_t H, int64_t L, int D, int M, int dtype, Plan pl, float *ws,
                           const float *init, float *total, int reverse, cudaStream_t st,
                           SegStates *out) {
-    *out = describe_states(mode, pl, ws, init);
+    *out = describe_states(mode, pl, ws, init, N * H, total != nullptr);
     if (pl.nseg == 1 && !total) return FTB_OK;
     int rc;
     if (sums_in_kernel(mode, pl)) {
-        const int skip = total ? -1 : (reverse ? 0 : pl.nseg - 1);
-        rc = launch_state_sum(mode, x, y, xs, ys, N, H, L, D, M, dtype, pl, ws, skip, st);
+        const int sub = out->sub;
+        Plan fine = pl;
+        fine.seg_len = pl.seg_len / sub;
+        fine.nseg = pl.nseg * sub;
+        int skip_lo = 0, skip_hi = 0;   // the segment nobody reads from: last (forward) / first
+        if (!total) {
+            skip_lo = reverse ? 0 : (pl.nseg - 1) * sub;
+            skip_hi = skip_lo + sub;
+        }
+        rc = launch_state_sum(mode, x, y, xs, ys, N, H, L, D, M, dtype, fine, ws, skip_lo, skip_hi, st);
         if (rc || !total) return rc;
         int64_t n = N * H * (int64_t)D * M;
         LaunchScope scope(FTB_KERNEL_STATE_PREFIX, st);
@@ -288,12 +312,12 @@ static int prepare_states(int mode, const void *x, const void *y, const int64_t 
         FTB_CUDA(cudaGetLastError());
         return FTB_OK;
     }
-    rc = launch_state_sum(mode, x, y, xs, ys, N, H, L, D, M, dtype, pl, ws, -1, st);
+    rc = launch_state_sum(mode, x, y, xs, ys, N, H, L, D, M, dtype, pl, ws, 0, 0, st);
     if (rc) return rc;
     const bool fold = mode != FTB_MODE_MMA;
     rc = launch_prefix(ws, fold ? init : nullptr, total, fold ? nullptr : init, N * H, pl.nseg,
                        (int64_t)D * M, reverse, st);
-    if (pl.nseg == 1) *out = SegStates{ws, fold ? nullptr : init, 0};
+    if (pl.nseg == 1) *out = SegStates{ws, fold ? nullptr : init, 0, 1};
     return rc;
 }
 
@@ -395,7 +419,8 @@ size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, in
     if (N <= 0 || H <= 0 || L <= 0 || D <= 0 || M <= 0) return 0;
     {
         Plan pl = choose_plan(mode, N * H, L);
-        size_t one = align256((size_t)N * H * pl.nseg * D * M * sizeof(float));
+        size_t one = align256((size_t)N * H * pl.nseg * state_sub(mode, pl, N * H, false) * D * M *
+                              sizeof(float));
         if (backward) return 2 * one;
         return (pl.nseg > 1 || want_state) ? one : 0;
     }
@@ -443,7 +468,7 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
     SegStates ss;
     if (workspace_has_states && mode == FTB_MODE_MMA && !final_state) {
         // ftb_causal_state_sum(k, v, ...) already left the per-segment states in `workspace`
-        ss = describe_states(mode, pl, ws, initial_state);
+        ss = describe_states(mode, pl, ws, initial_state, N * H, true);
     } else {
         rc = prepare_states(mode, k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, ws, initial_state,
                             final_state, 0, st, &ss);
@@ -494,7 +519,8 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
     // forward states: taken from the forward call's workspace when the caller kept it
     SegStates sS, sR;
     if (forward_workspace && pl.nseg > 1) {
-        sS = describe_states(mode, pl, (const float *)forward_workspace, initial_state);
+        sS = describe_states(mode, pl, (const float *)forward_workspace, initial_state, N * H,
+                             workspace_has_grad_states != 0);
     } else {
         rc = prepare_states(mode, k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, wsS, initial_state,
                             nullptr, 0, st, &sS);
@@ -502,7 +528,7 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
     }
     if (workspace_has_grad_states && mode == FTB_MODE_MMA) {
         // ftb_causal_state_sum(q, grad_out, ..., reverse=1, second half of `workspace`) ran before
-        sR = describe_states(mode, pl, wsR, initial_grad_state);
+        sR = describe_states(mode, pl, wsR, initial_grad_state, N * H, true);
     } else {
         rc = prepare_states(mode, q, g, qs, gs, N, H, L, (int)D, (int)M, dtype, pl, wsR,
                             initial_grad_state, nullptr, 1, st, &sR);
@@ -536,7 +562,7 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
     if (!x || !y) return FTB_ERR_INVALID;
     Plan pl = choose_plan(mode, N * H, L);
     if (pl.nseg == 1)
-        return launch_state_sum(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, state, -1, st);
+        return launch_state_sum(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, state, 0, 0, st);
     size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, 1);
     if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
     SegStates ss;

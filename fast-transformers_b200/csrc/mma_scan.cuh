@@ -64,7 +64,9 @@ struct ScanParams {
     int sum_mode;         // 0: states[bh][seg] is the state the segment starts from;
                           // 1: states holds raw per-segment totals: the start state is their sum
                           //    over the segments before (reverse: after) this one
-    int skip_seg;         // state-only mode: segment whose total nobody reads (-1: none)
+    int skip_lo, skip_hi; // state-only mode: segments [skip_lo, skip_hi) whose totals nobody reads
+    int sub;              // sum_mode 1: `states` holds `sub` blocks per segment of this launch (the
+                          // state-only launch ran on `sub` times finer segments to fill more SMs)
     float *state_out;     // state-only mode: per (bh, seg) totals, canonical [DA][Dc]
     int canon_is_DaDc;    // canonical block is [DA][Dc] (1) or [Dc][DA] (0)
     int reverse;
@@ -332,7 +334,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int64_t seg_begin = (int64_t)seg * p.seg_len;
     const int64_t seg_end = min(p.L, seg_begin + p.seg_len);
     int nchunk = (int)((seg_end - seg_begin + C - 1) / C);
-    if (p.state_only && seg == p.skip_seg) nchunk = 0;
+    if (p.state_only && seg >= p.skip_lo && seg < p.skip_hi) nchunk = 0;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -782,10 +784,11 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const int64_t blk = (int64_t)DA * p.Dc;
                     // blocks to add up: the per-bh initial state and either this segment's own
                     // block or the raw totals of every segment before (after) it
-                    int s_lo = seg, s_hi = seg + 1;
+                    int s_lo = seg, s_hi = seg + 1, per_head = p.nseg;
                     if (p.sum_mode) {
-                        s_lo = p.reverse ? seg + 1 : 0;
-                        s_hi = p.reverse ? p.nseg : seg;
+                        per_head = p.nseg * p.sub;
+                        s_lo = p.reverse ? (seg + 1) * p.sub : 0;
+                        s_hi = p.reverse ? per_head : seg * p.sub;
                     }
                     if (!p.states) s_hi = s_lo;
 #pragma unroll
@@ -800,7 +803,7 @@ mma_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                     if (!p.init) continue;
                                     src = p.init + (int64_t)bh * blk;
                                 } else {
-                                    src = p.states + ((int64_t)bh * p.nseg + sb) * blk;
+                                    src = p.states + ((int64_t)bh * per_head + sb) * blk;
                                 }
                                 const int dc0 = n0 + 32 * cb;
                                 if (p.canon_is_DaDc) {
