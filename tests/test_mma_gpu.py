@@ -85,6 +85,14 @@ def test_bf16_ragged(L):
     check(Q, K, V, G)
 
 
+def test_config5_favor_features_tf32_reduced():
+    """D = 256 Favor features, M = 64 (config 5's recipe at N1 H2 L2048): the tensor-core mode
+    runs it as four 64-wide feature blocks."""
+    Q, K, V, G = workloads.make_inputs(5, scale_N=1, scale_H=2, scale_L=2048)
+    assert Q.shape[3] == 256 and V.shape[3] == 64
+    check(Q, K, V, G)
+
+
 def test_nlhd_storage_views_tf32():
     """(N, L, H, D) storage viewed as (N, H, L, D): the head stride is below the row stride."""
     g = torch.Generator().manual_seed(21)
