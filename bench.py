@@ -457,7 +457,12 @@ def main():
     roofline = {
         "bound": "hbm", "kernel": top_name, "achieved": achieved, "peak": peak_gbs,
         "unit": "GB/s", "frac": achieved / peak_gbs if peak_gbs else None,
-        "peak_source": peak_src, "traffic": None,
+        "peak_source": peak_src,
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel from the
+        # committed ncu capture of the same workload (profiles/); None where none was taken
+        "traffic": {(2, "mma", "mma_fwd"): 246.1e6, (2, "mma", "mma_bwd"): 246.1e6}.get(
+            (args.config, mode, top_name)) if not args.L else None,
+        "algorithmic_bytes_per_launch": alg_bytes_launch,
         "avg_launch_ms": avg_ms, "share_of_kernel_time": top_ms / total_kernel_ms,
         "kernels": {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
                     for k, v in kinds.items()},
