@@ -37,7 +37,9 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5])
-    ap.add_argument("--mode", default=None, choices=["fp32", "mma"])
+    ap.add_argument("--mode", default="mma", choices=["fp32", "mma"],
+                    help="arithmetic of the kernels: tensor cores (TF32 operands for fp32 tensors, "
+                         "bf16 for bf16; <= 2e-2 vs fp64) or fp32 CUDA cores (<= 1e-5)")
     ap.add_argument("--L", type=int, default=None, help="override the sequence length")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -513,6 +515,25 @@ def main():
                "api": "fast_transformers_b200.causal_product.causal_dot_product (autograd) with "
                       "pinned host tensors copied in and all four results copied out"}
 
+    # the other arithmetic mode on the same inputs, for reference (a few eager steps)
+    other = None
+    if world == 1 and args.config in (1, 2) and Qd.dtype == torch.float32:
+        om = "fp32" if mode == "mma" else "mma"
+        mode_saved, mode = mode, om
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(5):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        mode = mode_saved
+        oms = e0.elapsed_time(e1) / 5
+        other = {"mode": om, "dtype": "f32" if om == "fp32" else "tf32", "ms_per_step": oms,
+                 "value": tokens / (oms * 1e-3) / 1e6, "unit": UNIT, "cuda_graph": False,
+                 "tolerance_vs_fp64": 1e-5 if om == "fp32" else 2e-2}
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         sec, kind, cores, nst = cpu_arm(Q, K, V, G, budget_s=12.0)
@@ -536,7 +557,8 @@ def main():
                        "l2": "inputs+outputs per step (%.0f MB) exceed the 126 MB L2; no flush" %
                              (step_alg_bytes / 1e6)},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-            "gpu_launches": int(launches), "clocks": clocks,
+            "gpu_launches": int(launches), "clocks": clocks, "other_mode": other,
+            "tolerance_vs_fp64": 1e-5 if mode == "fp32" else 2e-2,
         }
         print(json.dumps(line))
     if dist is not None:
