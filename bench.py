@@ -428,8 +428,10 @@ def main():
                                                            causal_dot_product_cuda)
         o = torch.empty(shape["N"], shape["H"], shape["L"], shape["M"], device=dev, dtype=Qd.dtype)
         gq, gk, gv = torch.empty_like(Qd), torch.empty_like(Kd), torch.empty_like(Vd)
-        causal_dot_product_cuda(Qd.data, Kd.data, Vd.data, o, mode)
-        causal_dot_backward_cuda(Qd.data, Kd.data, Vd.data, Gd, gq, gk, gv, mode)
+        kept = []
+        causal_dot_product_cuda(Qd.data, Kd.data, Vd.data, o, mode, keep_workspace=kept)
+        causal_dot_backward_cuda(Qd.data, Kd.data, Vd.data, Gd, gq, gk, gv, mode,
+                                 forward_workspace=kept[0] if kept else None)
     kinds = _native.timing_read()
     lib.ftb_timing_enable(0)
     peaks = {}
@@ -451,6 +453,11 @@ def main():
         "mma_bwd": (2 * D + 2 * M),
         "state_sum": (D + M),
         "mma_state": (D + M),
+        # one grid with the grad_Q scan and the state-only sweep of (Q, grad_out): only the
+        # scan's bytes are counted
+        "mma_bwd_qr": (2 * D + 2 * M),
+        # one grid with grad_K and grad_V (and grad_Q when no sweep is needed)
+        "mma_bwd_multi": (2 if "mma_bwd_qr" in kinds else 3) * (2 * D + 2 * M),
     }.get(top_name, 0)
     alg_bytes_launch = per_launch_elems * esize * token_heads
     avg_ms = top_ms / top_n if top_n else 0.0

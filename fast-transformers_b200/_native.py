@@ -26,7 +26,7 @@ EXPORTS = (
     "ftb_causal_dot_product_static",
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
-                "reserved6", "reserved7")
+                "mma_bwd_qr", "mma_bwd_multi")
 
 _lib = None
 _i64, _vp, _int, _sz = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t

@@ -166,28 +166,41 @@ static int simt_launch_scan(const void *a, const void *b, const void *c, void *o
 }
 
 // ---- tensor-core launches -------------------------------------------------------------------
-static int mma_launch(const void *a, const void *b, const void *c, void *out, const int64_t *as,
-                      const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H,
-                      int64_t L, int Da, int Dc, int dtype, Plan pl, const float *states,
-                      const float *init, int sum_mode, int sub, float *state_out, int skip_lo, int skip_hi,
-                      int canon_is_DaDc, int reverse, cudaStream_t st) {
+// A launch carries up to mma::MAX_JOBS independent jobs over one problem shape.
+struct MmaBatch {
+    mma::ScanBatch b;
+    int dtype = FTB_F32;
+    int kind = FTB_KERNEL_MMA_FWD;
+    MmaBatch() { b.njobs = 0; b.first_block[0] = 0; b.interleave = 0; }
+};
+
+// Append one job (a scan, or a state-only sweep when `a` is null) to `batch`.
+static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void *c, void *out,
+                       const int64_t *as, const int64_t *bs, const int64_t *cs, const int64_t *os,
+                       int64_t N, int64_t H, int64_t L, int Da, int Dc, int dtype, Plan pl,
+                       const float *states, const float *init, int sum_mode, int sub, float *state_out,
+                       int skip_lo, int skip_hi, int canon_is_DaDc, int reverse) {
     const bool state_only = (a == nullptr);
     const int DCT = dtype == FTB_F32 ? 64 : 128;
     // fp32 (TF32) operands read MN-major need the 32-byte-atom swizzle; bf16 uses one image
     const bool atom32 = dtype == FTB_F32;
-    CUtensorMap ma, mb, mbmn, mc;
-    mma::ScanParams p;
-    int rc = mma::make_map(&mb, p.pos_b, b, N, H, L, Da, bs, dtype, false);
+    int64_t blocks = N * H * pl.nseg * (Dc / DCT);
+    if (blocks <= 0) return FTB_OK;
+    if (batch.b.njobs >= mma::MAX_JOBS) return FTB_ERR_INVALID;
+    if (batch.b.first_block[batch.b.njobs] + blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
+    mma::ScanJob &J = batch.b.job[batch.b.njobs];
+    mma::ScanParams &p = J.p;
+    int rc = mma::make_map(&J.mb, p.pos_b, b, N, H, L, Da, bs, dtype, false);
     if (rc) return rc;
-    rc = mma::make_map(&mbmn, p.pos_b, b, N, H, L, Da, bs, dtype, atom32);
+    rc = mma::make_map(&J.mbmn, p.pos_b, b, N, H, L, Da, bs, dtype, atom32);
     if (rc) return rc;
-    rc = mma::make_map(&mc, p.pos_c, c, N, H, L, Dc, cs, dtype, atom32);
+    rc = mma::make_map(&J.mc, p.pos_c, c, N, H, L, Dc, cs, dtype, atom32);
     if (rc) return rc;
     if (state_only) {
-        ma = mb;
+        J.ma = J.mb;
         for (int i = 0; i < 3; ++i) p.pos_a[i] = p.pos_b[i];
     } else {
-        rc = mma::make_map(&ma, p.pos_a, a, N, H, L, Da, as, dtype);
+        rc = mma::make_map(&J.ma, p.pos_a, a, N, H, L, Da, as, dtype);
         if (rc) return rc;
         const int64_t es = dtype == FTB_F32 ? 4 : 2;
         if (((uintptr_t)out & 15) || (os[0] * es) % 16 || (os[1] * es) % 16 || (os[2] * es) % 16) {
@@ -207,17 +220,45 @@ static int mma_launch(const void *a, const void *b, const void *c, void *out, co
     p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = state_only ? 1 : 0;
     static const char *env = std::getenv("FTB200_MMA_TERMS");
     p.terms = env ? std::atoi(env) : 7;
-    int64_t blocks = N * H * pl.nseg * (Dc / DCT);
-    if (blocks <= 0) return FTB_OK;
-    if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
-    LaunchScope scope(state_only ? FTB_KERNEL_MMA_STATE : (reverse ? FTB_KERNEL_MMA_BWD : FTB_KERNEL_MMA_FWD), st);
+    if (batch.b.njobs == 0) {
+        batch.dtype = dtype;
+        batch.kind = state_only ? FTB_KERNEL_MMA_STATE : (reverse ? FTB_KERNEL_MMA_BWD : FTB_KERNEL_MMA_FWD);
+    }
+    batch.b.first_block[batch.b.njobs + 1] = batch.b.first_block[batch.b.njobs] + (int)blocks;
+    ++batch.b.njobs;
+    return FTB_OK;
+}
+
+static int mma_launch_batch(MmaBatch &batch, cudaStream_t st) {
+    if (batch.b.njobs == 0) return FTB_OK;
+    for (int j = batch.b.njobs; j < mma::MAX_JOBS; ++j) batch.b.first_block[j + 1] = batch.b.first_block[j];
+    // equal-sized scans are interleaved block by block (shared tiles meet in L2)
+    static const char *no_il = std::getenv("FTB200_NO_INTERLEAVE");
+    bool equal = batch.b.njobs > 1 && !no_il;
+    for (int j = 0; j < batch.b.njobs && equal; ++j)
+        equal = !batch.b.job[j].p.state_only &&
+                batch.b.first_block[j + 1] - batch.b.first_block[j] == batch.b.first_block[1];
+    batch.b.interleave = equal ? 1 : 0;
+    LaunchScope scope(batch.kind, st);
     cudaError_t e;
-    if (dtype == FTB_F32)
-        e = mma::launch_t<float, 64, 64>(ma, mb, mbmn, mc, p, blocks, st);
+    if (batch.dtype == FTB_F32)
+        e = mma::launch_t<float, 64, 64>(batch.b, st);
     else
-        e = mma::launch_t<__nv_bfloat16, 128, 128>(ma, mb, mbmn, mc, p, blocks, st);
+        e = mma::launch_t<__nv_bfloat16, 128, 128>(batch.b, st);
     if (e != cudaSuccess) return cuda_fail(e);
     return FTB_OK;
+}
+
+static int mma_launch(const void *a, const void *b, const void *c, void *out, const int64_t *as,
+                      const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H,
+                      int64_t L, int Da, int Dc, int dtype, Plan pl, const float *states,
+                      const float *init, int sum_mode, int sub, float *state_out, int skip_lo, int skip_hi,
+                      int canon_is_DaDc, int reverse, cudaStream_t st) {
+    MmaBatch batch;
+    int rc = mma_add_job(batch, a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, states, init,
+                         sum_mode, sub, state_out, skip_lo, skip_hi, canon_is_DaDc, reverse);
+    if (rc) return rc;
+    return mma_launch_batch(batch, st);
 }
 
 static Plan choose_plan(int mode, int64_t BH, int64_t L) {
@@ -373,6 +414,9 @@ int ftb_device_status(int reset) {
 int ftb_debug_read_timestamps(long long *dst, int n) {
     return (int)cudaMemcpyFromSymbol(dst, mma::g_ts, sizeof(long long) * n);
 }
+int ftb_debug_read_cta_timestamps(long long *dst, int n) {
+    return (int)cudaMemcpyFromSymbol(dst, mma::g_cta, sizeof(long long) * n);
+}
 #endif
 
 uint64_t ftb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
@@ -526,13 +570,51 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
                             nullptr, 0, st, &sS);
         if (rc) return rc;
     }
+    // reverse states R = sum q (x) grad_out over the segments after each segment
+    bool r_with_grad_q = false;   // tensor-core mode: the totals are swept in grad_Q's own launch
     if (workspace_has_grad_states && mode == FTB_MODE_MMA) {
         // ftb_causal_state_sum(q, grad_out, ..., reverse=1, second half of `workspace`) ran before
         sR = describe_states(mode, pl, wsR, initial_grad_state, N * H, true);
+    } else if (mode == FTB_MODE_MMA && pl.nseg > 1 && sums_in_kernel(mode, pl)) {
+        sR = describe_states(mode, pl, wsR, initial_grad_state, N * H, false);
+        r_with_grad_q = true;
     } else {
         rc = prepare_states(mode, q, g, qs, gs, N, H, L, (int)D, (int)M, dtype, pl, wsR,
                             initial_grad_state, nullptr, 1, st, &sR);
         if (rc) return rc;
+    }
+
+    if (mode == FTB_MODE_MMA) {
+        // The three gradient scans are independent of each other; grad_Q does not read R.  They
+        // go out as one grid -- or, when R's segment totals are still to be computed, as
+        // {grad_Q scan + the state-only sweep of (q, grad_out)} followed by {grad_K, grad_V}:
+        // the short sweep runs on the SMs the scan leaves idle, and consecutive scans overlap
+        // where one's last CTAs would otherwise leave SMs empty.
+        MmaBatch first;
+        rc = mma_add_job(first, g, v, k, gq, gs, vs, ks, gqs, N, H, L, (int)M, (int)D, dtype, pl, sS.states,
+                         sS.init, sS.sum_mode, sS.sub, nullptr, 0, 0, 0, 0);
+        if (rc) return rc;
+        MmaBatch second;
+        MmaBatch &kv = r_with_grad_q ? second : first;
+        if (r_with_grad_q) {
+            Plan fine = pl;
+            fine.seg_len = pl.seg_len / sR.sub;
+            fine.nseg = pl.nseg * sR.sub;
+            rc = mma_add_job(first, nullptr, q, g, nullptr, nullptr, qs, gs, nullptr, N, H, L, (int)D, (int)M,
+                             dtype, fine, nullptr, nullptr, 0, 1, wsR, 0, sR.sub, 1, 0);
+            if (rc) return rc;
+            first.kind = FTB_KERNEL_MMA_BWD_QR;
+        }
+        rc = mma_add_job(kv, v, g, q, gk, vs, gs, qs, gks, N, H, L, (int)M, (int)D, dtype, pl, sR.states,
+                         sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 0, 1);
+        if (rc) return rc;
+        rc = mma_add_job(kv, k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl, sR.states,
+                         sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 1, 1);
+        if (rc) return rc;
+        kv.kind = FTB_KERNEL_MMA_BWD_MULTI;
+        rc = mma_launch_batch(first, st);
+        if (rc || !r_with_grad_q) return rc;
+        return mma_launch_batch(second, st);
     }
 
     // grad_Q_i = sum_{j<=i} (g_i . v_j) k_j + S_init g_i        state viewed as [M][D]

@@ -138,14 +138,12 @@ static bool supported(int dtype, int64_t Da, int64_t Dc) {
 }
 
 template <typename T, int DA, int DCT>
-static cudaError_t launch_t(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mbmn,
-                            const CUtensorMap &mc, const ScanParams &p, int64_t blocks,
-                            cudaStream_t st) {
+static cudaError_t launch_t(const ScanBatch &batch, cudaStream_t st) {
     using K = Cfg<T, DA, DCT>;
     auto kern = mma_scan_kernel<T, DA, DCT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)K::SMEM);
     if (e != cudaSuccess) return e;
-    kern<<<(unsigned)blocks, NTHREADS, K::SMEM, st>>>(ma, mb, mbmn, mc, p);
+    kern<<<(unsigned)batch.first_block[batch.njobs], NTHREADS, K::SMEM, st>>>(batch);
     return cudaGetLastError();
 }
 

@@ -83,6 +83,8 @@ int ftb_last_cuda_error(void);
 #define FTB_KERNEL_MMA_FWD 3      /* tcgen05 forward                                 */
 #define FTB_KERNEL_MMA_BWD 4      /* tcgen05 backward                                */
 #define FTB_KERNEL_MMA_STATE 5    /* tcgen05 per-segment totals                      */
+#define FTB_KERNEL_MMA_BWD_QR 6   /* tcgen05 grad_Q scan + reverse totals, one grid  */
+#define FTB_KERNEL_MMA_BWD_MULTI 7 /* tcgen05 two or three gradient scans, one grid  */
 #define FTB_KERNEL_KINDS 8
 uint64_t ftb_launch_count(void);
 /*

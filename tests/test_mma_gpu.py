@@ -85,6 +85,32 @@ def test_bf16_ragged(L):
     check(Q, K, V, G)
 
 
+def test_bf16_long_segments():
+    """Enough (batch, head) pairs that a segment is a whole sequence of 10 chunks (config 4 runs
+    228 chunks per segment): the barrier phases wrap several times.  Checked on four heads."""
+    g = torch.Generator().manual_seed(5)
+    H, L = 148, 1280
+    Q, K, V, G = (torch.rand(1, H, L, 128, generator=g).to(torch.bfloat16) for _ in range(4))
+    got = fwd_bwd(Q, K, V, G)
+    heads = [0, 1, 77, 147]
+    want = oracle(*(t[:, heads] for t in (Q, K, V, G)))
+    for name, a, b in zip(NAMES, got, want):
+        assert orc.rel_err(a[:, heads], b) < TOL, name
+
+
+def test_tf32_long_segments_three_scans_in_one_grid():
+    """128 heads -> one segment of 24 chunks per head, no state pass: the backward is one grid of
+    three interleaved scans."""
+    g = torch.Generator().manual_seed(6)
+    H, L = 128, 3072
+    Q, K, V, G = (torch.rand(1, H, L, 64, generator=g) for _ in range(4))
+    got = fwd_bwd(Q, K, V, G)
+    heads = [0, 63, 127]
+    want = oracle(*(t[:, heads] for t in (Q, K, V, G)))
+    for name, a, b in zip(NAMES, got, want):
+        assert orc.rel_err(a[:, heads], b) < TOL, name
+
+
 def test_config5_favor_features_tf32_reduced():
     """D = 256 Favor features, M = 64 (config 5's recipe at N1 H2 L2048): the tensor-core mode
     runs it as four 64-wide feature blocks."""
