@@ -347,8 +347,9 @@ struct Cfg {
     static constexpr int FMT = F16 ? 1 : 2;
     // MN-major operands: 16-bit types share the K-major tile image (layout 2, 8-row atoms);
     // TF32 needs the 32-byte-atom swizzle (layout 1, 4-row atoms), so the b tile -- read
-    // K-major by the score product and MN-major by the state update -- is fetched twice into
-    // the same slot, the second time once the score product has consumed the first image.
+    // K-major by the score product and MN-major by the state update -- needs a second image:
+    // the mask workers rearrange the tile in place once the score product has consumed it
+    // (a state-only launch loads the MN-major image directly).
     static constexpr bool RELOAD_B = !F16;
     // Where the running fp32 state lives.  REG_STATE: each chunk's increment b^T c goes to one of
     // two fresh TMEM accumulators and the state workers add it to the state they keep in
@@ -396,7 +397,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
     const uint32_t bar_full = bars, bar_empty = bars + 16, bar_pfull = bars + 32,
                    bar_pready = bars + 48, bar_ofull = bars + 64, bar_ofree = bars + 80,
                    bar_sfull = bars + 96, bar_smready = bars + 104, bar_fullc = bars + 112,
-                   bar_bkfree = bars + 128, bar_fullbmn = bars + 144, bar_pfree = bars + 160,
+                   bar_fullbmn = bars + 144, bar_pfree = bars + 160,
                    bar_smready2 = bars + 176, bar_smfree = bars + 184, bar_tfull = bars + 192,
                    bar_tfree = bars + 208;
 
@@ -414,11 +415,22 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
     const int64_t seg_begin = (int64_t)seg * p.seg_len;
     const int64_t seg_end = min(p.L, seg_begin + p.seg_len);
     int nchunk = (int)((seg_end - seg_begin + C - 1) / C);
-    if (p.state_only && seg >= p.skip_lo && seg < p.skip_hi) nchunk = 0;
+    const bool skipped = p.state_only && seg >= p.skip_lo && seg < p.skip_hi;
+    if (skipped || nchunk < 0) nchunk = 0;
+    if (p.state_only && nchunk == 0 && !skipped) {
+        // a segment without rows (the tail of a sequence that is not a whole number of
+        // segments): its totals are zero, and they are read like any other block.  (Done here,
+        // before the roles: at the end of the kernel it kept the block's coordinates alive
+        // through every loop and cost the bf16 scan a tenth of its speed.)
+        float *dst = p.state_out + ((int64_t)bh * p.nseg + seg) * ((int64_t)DA * p.Dc);
+        for (int e = threadIdx.x; e < DA * DCT; e += NTHREADS)
+            dst[(int64_t)(e / DCT) * p.Dc + n0 + e % DCT] = 0.f;
+    }
 
 #ifdef FTB_TIMESTAMPS
     if (threadIdx.x == 0 && blockIdx.x < 1024) {
         g_cta[4 * blockIdx.x] = ts_globaltimer();
+        FTB_TS(7, 0, 0);
     }
 #endif
     if (threadIdx.x == 0) {
@@ -434,8 +446,8 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
             mbar_init(bar_ofull + 8 * s, 1);
             mbar_init(bar_ofree + 8 * s, 128);
             mbar_init(bar_fullc + 8 * s, 1);
-            mbar_init(bar_bkfree + 8 * s, 1);
-            mbar_init(bar_fullbmn + 8 * s, 1);
+            // scan: the 128 mask-worker threads that rearrange b in place; state only: one TMA load
+            mbar_init(bar_fullbmn + 8 * s, p.state_only ? 1 : 128);
         }
         mbar_init(bar_sfull, 1);
         mbar_init(bar_smready, 128);
@@ -457,8 +469,8 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
             // ================= TMA producer =====================================================
             // bar_full[s]  : a and the K-major image of b have landed (score product, a S)
             // bar_fullc[s] : c has landed (mask(P) c, state update)
-            // bar_fullbmn[s]: the MN-major image of b has landed in b's slot (state update); it is
-            //                requested as soon as the score product has consumed the K-major image
+            // bar_fullbmn[s]: the MN-major image of b is in b's slot (state update): rearranged in
+            //                place by the mask workers (scan), or loaded as such (state only)
             if (lane == 0) {
                 auto load_b_mn = [&](int ci) {
                     const int c = p.reverse ? nchunk - 1 - ci : ci;
@@ -493,17 +505,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                 for (int ci = 0; ci < nchunk && ok; ++ci) {
                     const int c = p.reverse ? nchunk - 1 - ci : ci;
                     const int s = ci & 1, use = ci >> 1;
-                    if constexpr (K::RELOAD_B) {
-                        if (!p.state_only && ci >= 1) {
-                            // The score product of chunk ci-1 has consumed the K-major image of b:
-                            // request the MN-major image now, AHEAD of the next chunk's tiles in
-                            // the TMA queue -- the state update of chunk ci-1 is waiting for it.
-                            ok = mbar_wait(bar_bkfree + 8 * ((ci - 1) & 1), ((ci - 1) >> 1) & 1, abort_flag);
-                            if (!ok) break;
-                            FTB_TS(0, ci, 1);
-                            load_b_mn(ci - 1);
-                        }
-                    }
                     ok = mbar_wait(bar_empty + 8 * s, (use & 1) ^ 1, abort_flag);
                     if (!ok) break;
                     FTB_TS(0, ci, 0);
@@ -536,12 +537,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         if (p.state_only) load_b_mn(ci);
                     }
                     prefetch_chunk(ci + 2);
-                }
-                if constexpr (K::RELOAD_B) {
-                    if (ok && !p.state_only) {
-                        ok = mbar_wait(bar_bkfree + 8 * ((nchunk - 1) & 1), ((nchunk - 1) >> 1) & 1, abort_flag);
-                        if (ok) load_b_mn(nchunk - 1);
-                    }
                 }
             }
         } else if (warp == 1 || warp == 10) {
@@ -649,14 +644,12 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                                 mma_ss<K::F16>(tP, a0 + off, b0 + off, ID_P, (b | k) ? 1u : 0u);
                             }
                         tc_commit(bar_pfull + 8 * (ci & 1));
-                        if constexpr (K::RELOAD_B) tc_commit(bar_bkfree + 8 * (ci & 1));
                     };
                     // Two job queues, served in whichever order their inputs arrive: the score
                     // product of chunk `sc` (a, K-major b, a free score buffer) and the state
                     // increment of chunk `ds` (c, MN-major b, a free accumulator).  The score
-                    // product of chunk ds+1 must not sit behind the increment of chunk ds: its
-                    // completion is what requests the MN-major image of b for chunk ds+1, a
-                    // round trip to L2 that would otherwise be added to every chunk.
+                    // product of chunk ds+1 must not sit behind the increment of chunk ds: the
+                    // mask, the MN-major image of b and mask(P) c of chunk ds+1 all start from it.
                     int sc = 0, ds = 0;
                     long long t0 = 0;
                     uint32_t idle = 0;
@@ -729,6 +722,41 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     if (!mbar_wait(bar_pfull + 8 * (ci & 1), (ci >> 1) & 1, abort_flag)) break;
                     if (threadIdx.x == 352) FTB_TS(3, ci, 0);
                     tc_fence_after();
+                    if constexpr (K::RELOAD_B) {
+                        // The score product has consumed the K-major image of b (128-byte
+                        // swizzle: 16-byte chunk c of row r sits at c ^ (r & 7)).  The state
+                        // update reads b MN-major, which for TF32 exists only in the 32-byte-atom
+                        // swizzle (32-byte unit u of row r at u ^ (r & 3)).  Both keep a tile row
+                        // in the same 128 bytes, so the second image is a permutation of the 8
+                        // chunks of every row, done here in place: a warp instruction covers four
+                        // whole rows (no bank conflicts), reads them, then writes them back.
+                        uint8_t *bt = smem_gen + (ci & 1) * K::STAGE_BYTES + K::A_BYTES;
+                        const int t = threadIdx.x - 352;
+                        constexpr int NIT = K::A_BYTES / (128 * 16);   // 16-byte chunks per thread
+                        static_assert(NIT % 4 == 0, "chunks are moved four at a time");
+                        for (int it0 = 0; it0 < NIT; it0 += 4) {
+                            uint4 v[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int idx = (it0 + j) * 128 + t;   // 16-byte chunk of the tile
+                                v[j] = reinterpret_cast<const uint4 *>(bt + (size_t)(idx >> 3) * 128)[idx & 7];
+                            }
+                            __syncwarp();
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int idx = (it0 + j) * 128 + t;
+                                const int pk = idx & 7, row = (idx >> 3) & 127;
+                                const int c = pk ^ (row & 7);          // logical chunk held here
+                                const int pm = ((((c >> 1) ^ (row & 3)) << 1) | (c & 1));
+                                reinterpret_cast<uint4 *>(bt + (size_t)(idx >> 3) * 128)[pm] = v[j];
+                            }
+                            __syncwarp();
+                        }
+                        if (threadIdx.x == 352) FTB_TS(3, ci, 4);
+                        fence_proxy_async_smem();
+                        if (threadIdx.x == 352) FTB_TS(3, ci, 5);
+                        mbar_arrive(bar_fullbmn + 8 * (ci & 1));
+                    }
                     const uint32_t tP = tlane + K::TM_P + 128 * (ci & 1);
 #pragma unroll
                     for (int cb = 0; cb < 4; ++cb) {
@@ -1025,7 +1053,10 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
 #endif
     if (warp == 0) tmem_dealloc(tmem, 512);
 #ifdef FTB_TIMESTAMPS
-    if (threadIdx.x == 0 && blockIdx.x < 1024) g_cta[4 * blockIdx.x + 1] = ts_globaltimer();
+    if (threadIdx.x == 0 && blockIdx.x < 1024) {
+        g_cta[4 * blockIdx.x + 1] = ts_globaltimer();
+        FTB_TS(7, 0, 1);
+    }
 #endif
 }
 

@@ -111,6 +111,18 @@ def test_tf32_long_segments_three_scans_in_one_grid():
         assert orc.rel_err(a[:, heads], b) < TOL, name
 
 
+@pytest.mark.parametrize("L", [384, 640, 1152])
+def test_short_sequences_many_heads_tf32(L):
+    """64 (batch, head) pairs and a few chunks: segments of one or two chunks, an odd number of
+    chunks (the last segment is shorter, a sub-segment of the state sweep may be empty)."""
+    g = torch.Generator().manual_seed(L)
+    Q, K, V, G = (torch.rand(8, 8, L, 64, generator=g) for _ in range(4))
+    got = fwd_bwd(Q, K, V, G)
+    want = oracle(*(t[:2, 3:5] for t in (Q, K, V, G)))
+    for name, a, b in zip(NAMES, got, want):
+        assert orc.rel_err(a[:2, 3:5], b) < TOL, name
+
+
 def test_config5_favor_features_tf32_reduced():
     """D = 256 Favor features, M = 64 (config 5's recipe at N1 H2 L2048): the tensor-core mode
     runs it as four 64-wide feature blocks."""
