@@ -351,6 +351,11 @@ struct Cfg {
     // the mask workers rearrange the tile in place once the score product has consumed it
     // (a state-only launch loads the MN-major image directly).
     static constexpr bool RELOAD_B = !F16;
+    // state-only launches: the same ring memory as slots of b | c
+    static constexpr int SO_BYTES = A_BYTES + C_BYTES;
+    static constexpr int SO_STAGES = (STAGES * STAGE_BYTES) / SO_BYTES;
+    static_assert(SO_STAGES >= 2 && SO_STAGES <= 4, "state-only ring: barrier slots for up to 4 stages");
+    static_assert(SO_BYTES % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
     // Where the running fp32 state lives.  REG_STATE: each chunk's increment b^T c goes to one of
     // two fresh TMEM accumulators and the state workers add it to the state they keep in
     // registers (one row per thread) -- the state update of chunk c+1 then does not wait for the
@@ -399,7 +404,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                    bar_sfull = bars + 96, bar_smready = bars + 104, bar_fullc = bars + 112,
                    bar_fullbmn = bars + 144, bar_pfree = bars + 160,
                    bar_smready2 = bars + 176, bar_smfree = bars + 184, bar_tfull = bars + 192,
-                   bar_tfree = bars + 208;
+                   bar_tfree = bars + 208, bar_so_full = bars + 272, bar_so_empty = bars + 304;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -437,7 +442,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
         *abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, p.state_only ? 1 : 2);
+            mbar_init(bar_empty + 8 * s, 2);   // released by both issuers
             mbar_init(bar_pfree + 8 * s, 1);
             mbar_init(bar_tfull + 8 * s, 1);
             mbar_init(bar_tfree + 8 * s, 128);
@@ -446,8 +451,12 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
             mbar_init(bar_ofull + 8 * s, 1);
             mbar_init(bar_ofree + 8 * s, 128);
             mbar_init(bar_fullc + 8 * s, 1);
-            // scan: the 128 mask-worker threads that rearrange b in place; state only: one TMA load
-            mbar_init(bar_fullbmn + 8 * s, p.state_only ? 1 : 128);
+            // the 128 mask-worker threads that rearrange b in place
+            mbar_init(bar_fullbmn + 8 * s, 128);
+        }
+        for (int s = 0; s < K::SO_STAGES; ++s) {
+            mbar_init(bar_so_full + 8 * s, 1);
+            mbar_init(bar_so_empty + 8 * s, 1);
         }
         mbar_init(bar_sfull, 1);
         mbar_init(bar_smready, 128);
@@ -472,28 +481,12 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
             // bar_fullbmn[s]: the MN-major image of b is in b's slot (state update): rearranged in
             //                place by the mask workers (scan), or loaded as such (state only)
             if (lane == 0) {
-                auto load_b_mn = [&](int ci) {
-                    const int c = p.reverse ? nchunk - 1 - ci : ci;
-                    const int s = ci & 1;
-                    const int row = (int)(seg_begin + (int64_t)c * C);
-                    const uint32_t st = stage0 + s * K::STAGE_BYTES;
-                    mbar_expect_tx(bar_fullbmn + 8 * s, K::A_BYTES);
-#pragma unroll
-                    for (int b = 0; b < K::A_BLKS; ++b)
-                        tma_load_4d(st + K::A_BYTES + b * K::BLK_BYTES, &map_bmn, bar_fullbmn + 8 * s,
-                                    b * K::EPB, p.pos_b, row, bhh, bn);
-                };
-                // State-only launches: an L2 prefetch two chunks ahead of the loads into shared
-                // memory (measured: ~8 % faster there; no gain for the scan, which is not used).
+                // State-only launches: an L2 prefetch ahead of the loads into shared memory
+                // (measured: ~8 % faster there; no gain for the scan, where it is not used).
                 auto prefetch_chunk = [&](int ci) {
-                    if (ci >= nchunk || !p.state_only) return;
+                    if (ci >= nchunk) return;
                     const int c = p.reverse ? nchunk - 1 - ci : ci;
                     const int row = (int)(seg_begin + (int64_t)c * C);
-                    if (!p.state_only) {
-#pragma unroll
-                        for (int b = 0; b < K::A_BLKS; ++b)
-                            tma_prefetch_4d(&map_a, b * K::EPB, p.pos_a, row, bhh, bn);
-                    }
 #pragma unroll
                     for (int b = 0; b < K::A_BLKS; ++b)
                         tma_prefetch_4d(&map_b, b * K::EPB, p.pos_b, row, bhh, bn);
@@ -501,8 +494,33 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     for (int b = 0; b < K::C_BLKS; ++b)
                         tma_prefetch_4d(&map_c, n0 + b * K::EPB, p.pos_c, row, bhh, bn);
                 };
+                // One tile = `nblk` boxes of 128 bytes x C rows.  (Shorter boxes, so that the
+                // pieces of a row are requested closer together, were measured: 64 rows -2 %,
+                // 32 rows -6 %, 8 rows -54 %.)
+                auto load_tile = [&](uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0,
+                                     const int *pos, int row, int nblk) {
+                    for (int b = 0; b < nblk; ++b)
+                        tma_load_4d(dst + b * K::BLK_BYTES, map, bar, c0 + b * K::EPB, pos, row, bhh, bn);
+                };
                 bool ok = true;
-                for (int ci = 0; ci < nchunk && ok; ++ci) {
+                if (p.state_only) {
+                    // b and c only: the ring is cut into SO_STAGES slots of b | c (the a slots are
+                    // not needed), so one more chunk is in flight -- these launches wait for
+                    // loads and for little else
+                    for (int ci = 0; ci < nchunk && ok; ++ci) {
+                        const int c = p.reverse ? nchunk - 1 - ci : ci;
+                        const int s = ci % K::SO_STAGES, use = ci / K::SO_STAGES;
+                        ok = mbar_wait(bar_so_empty + 8 * s, (use & 1) ^ 1, abort_flag);
+                        if (!ok) break;
+                        const int row = (int)(seg_begin + (int64_t)c * C);
+                        const uint32_t st = stage0 + s * K::SO_BYTES;
+                        mbar_expect_tx(bar_so_full + 8 * s, K::A_BYTES + K::C_BYTES);
+                        load_tile(st, &map_bmn, bar_so_full + 8 * s, 0, p.pos_b, row, K::A_BLKS);
+                        load_tile(st + K::A_BYTES, &map_c, bar_so_full + 8 * s, n0, p.pos_c, row, K::C_BLKS);
+                        prefetch_chunk(ci + K::SO_STAGES);
+                    }
+                }
+                for (int ci = 0; ci < nchunk && ok && !p.state_only; ++ci) {
                     const int c = p.reverse ? nchunk - 1 - ci : ci;
                     const int s = ci & 1, use = ci >> 1;
                     ok = mbar_wait(bar_empty + 8 * s, (use & 1) ^ 1, abort_flag);
@@ -510,33 +528,11 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     FTB_TS(0, ci, 0);
                     const int row = (int)(seg_begin + (int64_t)c * C);
                     const uint32_t st = stage0 + s * K::STAGE_BYTES;
-                    if (!p.state_only) {
-                        mbar_expect_tx(bar_full + 8 * s, 2 * K::A_BYTES);
-#pragma unroll
-                        for (int b = 0; b < K::A_BLKS; ++b)
-                            tma_load_4d(st + b * K::BLK_BYTES, &map_a, bar_full + 8 * s, b * K::EPB,
-                                        p.pos_a, row, bhh, bn);
-#pragma unroll
-                        for (int b = 0; b < K::A_BLKS; ++b)
-                            tma_load_4d(st + K::A_BYTES + b * K::BLK_BYTES, &map_b, bar_full + 8 * s,
-                                        b * K::EPB, p.pos_b, row, bhh, bn);
-                    }
-                    const bool b_with_c = p.state_only && !K::RELOAD_B;
-                    mbar_expect_tx(bar_fullc + 8 * s, K::C_BYTES + (b_with_c ? K::A_BYTES : 0));
-#pragma unroll
-                    for (int b = 0; b < K::C_BLKS; ++b)
-                        tma_load_4d(st + 2 * K::A_BYTES + b * K::BLK_BYTES, &map_c, bar_fullc + 8 * s,
-                                    n0 + b * K::EPB, p.pos_c, row, bhh, bn);
-                    if (b_with_c) {
-#pragma unroll
-                        for (int b = 0; b < K::A_BLKS; ++b)
-                            tma_load_4d(st + K::A_BYTES + b * K::BLK_BYTES, &map_bmn, bar_fullc + 8 * s,
-                                        b * K::EPB, p.pos_b, row, bhh, bn);
-                    }
-                    if constexpr (K::RELOAD_B) {
-                        if (p.state_only) load_b_mn(ci);
-                    }
-                    prefetch_chunk(ci + 2);
+                    mbar_expect_tx(bar_full + 8 * s, 2 * K::A_BYTES);
+                    load_tile(st, &map_a, bar_full + 8 * s, 0, p.pos_a, row, K::A_BLKS);
+                    load_tile(st + K::A_BYTES, &map_b, bar_full + 8 * s, 0, p.pos_b, row, K::A_BLKS);
+                    mbar_expect_tx(bar_fullc + 8 * s, K::C_BYTES);
+                    load_tile(st + 2 * K::A_BYTES, &map_c, bar_fullc + 8 * s, n0, p.pos_c, row, K::C_BLKS);
                 }
             }
         } else if (warp == 1 || warp == 10) {
@@ -565,19 +561,21 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
 
                 if (p.state_only) {
                     if (warp == 1) {
+                        const uint64_t dSOb = smem_desc(stage0, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
+                        const uint64_t dSOc = smem_desc(stage0 + K::A_BYTES, K::BLK_BYTES, K::MN_SBO, K::MN_LAYOUT);
+                        constexpr uint64_t SO_UNITS = (uint64_t)(K::SO_BYTES >> 4);
                         for (int ci = 0; ci < nchunk && ok; ++ci) {
-                            const int s = ci & 1, use = ci >> 1;
-                            ok = mbar_wait(bar_fullc + 8 * s, use & 1, abort_flag);
-                            if (K::RELOAD_B && ok) ok = mbar_wait(bar_fullbmn + 8 * s, use & 1, abort_flag);
+                            const int s = ci % K::SO_STAGES, use = ci / K::SO_STAGES;
+                            ok = mbar_wait(bar_so_full + 8 * s, use & 1, abort_flag);
                             if (!ok) break;
                             tc_fence_after();
-                            const uint64_t b0 = dBmn0 + s * STAGE_UNITS, c0 = dCmn0 + s * STAGE_UNITS;
+                            const uint64_t b0 = dSOb + s * SO_UNITS, c0 = dSOc + s * SO_UNITS;
 #pragma unroll
                             for (int k = 0; k < C / K::KROWS; ++k) {
                                 const uint64_t off = (uint64_t)((k * KSTEP_BYTES) >> 4);
                                 mma_ss<K::F16>(tS, b0 + off, c0 + off, ID_ST, (ci | k) ? 1u : 0u);
                             }
-                            tc_commit(bar_empty + 8 * s);
+                            tc_commit(bar_so_empty + 8 * s);
                         }
                         tc_commit(bar_sfull);
                     }
