@@ -43,6 +43,8 @@ def parse():
     ap.add_argument("--L", type=int, default=None, help="override the sequence length")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-other-mode", action="store_true",
+                    help="skip the few eager steps in the other arithmetic mode")
     ap.add_argument("--no-graph", action="store_true", help="time eager calls, not a CUDA graph")
     ap.add_argument("--layers", type=int, default=None, help="config 3: override the layer count")
     ap.add_argument("--batch", type=int, default=None, help="config 3: override the batch size")
@@ -469,7 +471,8 @@ def main():
         "peak_source": peak_src,
         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel from the
         # committed ncu capture of the same workload (profiles/); None where none was taken
-        "traffic": {(2, "mma", "mma_fwd"): 246.1e6, (2, "mma", "mma_bwd"): 246.1e6}.get(
+        "traffic": {(2, "mma", "mma_fwd"): 247.8e6, (2, "mma", "mma_bwd_qr"): 308.7e6,
+                    (2, "mma", "mma_bwd_multi"): 376.4e6, (2, "mma", "mma_state"): 68.6e6}.get(
             (args.config, mode, top_name)) if not args.L else None,
         "algorithmic_bytes_per_launch": alg_bytes_launch,
         "avg_launch_ms": avg_ms, "share_of_kernel_time": top_ms / total_kernel_ms,
@@ -531,7 +534,7 @@ def main():
 
     # the other arithmetic mode on the same inputs, for reference (a few eager steps)
     other = None
-    if world == 1 and args.config in (1, 2) and Qd.dtype == torch.float32:
+    if world == 1 and args.config in (1, 2) and Qd.dtype == torch.float32 and not args.no_other_mode:
         om = "fp32" if mode == "mma" else "mma"
         mode_saved, mode = mode, om
         for _ in range(2):
