@@ -152,8 +152,13 @@ def causal_dot_backward_cuda(queries, keys, values, grad_out, grad_queries, grad
                              workspace_has_grad_states=False):
     """Fill the three gradients in place -- the reference's native backward signature
     (``causal_product_cuda.cu:1438-1444``).  ``grad_out`` may be any view (expanded,
-    permuted); it is made row-contiguous only if its last stride is not 1."""
-    dev = _check_cuda(queries, keys, values, grad_out, grad_queries, grad_keys, grad_values)
+    permuted); it is made row-contiguous only if its last stride is not 1.  A gradient buffer
+    given as ``None`` is not computed (the sequence-parallel path asks for grad_Q first and
+    for grad_K, grad_V once the reverse states have arrived)."""
+    wanted = [t for t in (grad_queries, grad_keys, grad_values) if t is not None]
+    if not wanted:
+        raise RuntimeError("no gradient was asked for")
+    dev = _check_cuda(queries, keys, values, grad_out, *wanted)
     dt = _dtype_id(queries)
     N, H, L, D = queries.shape
     M = values.shape[3]
@@ -163,6 +168,8 @@ def causal_dot_backward_cuda(queries, keys, values, grad_out, grad_queries, grad
         raise RuntimeError("grad_out has the wrong shape")
     nblk = _feature_blocks(queries, values, mode, initial_state, initial_grad_state,
                            forward_workspace, workspace)
+    if nblk and len(wanted) < 3:
+        raise RuntimeError("feature-block products compute all three gradients at once")
     if nblk:
         # gradients of a sum of block products: grad_Q and grad_K block by block (written
         # straight into the 64-wide column slices), grad_V summed over the blocks
@@ -176,7 +183,7 @@ def causal_dot_backward_cuda(queries, keys, values, grad_out, grad_queries, grad
                 grad_values += part
         return
     q, k, v, g = (_rowmajor(t) for t in (queries, keys, values, grad_out))
-    for t in (grad_queries, grad_keys, grad_values):
+    for t in wanted:
         if t.dtype != queries.dtype or (t.shape[3] > 1 and t.stride(3) != 1):
             raise RuntimeError("gradient buffers must match the input dtype and be row-contiguous")
     initial_state = _state_ok(initial_state, N, H, D, M, dev, "initial_state")
@@ -195,8 +202,9 @@ def causal_dot_backward_cuda(queries, keys, values, grad_out, grad_queries, grad
             _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(grad_queries), _ptr(grad_keys),
             _ptr(grad_values), N, H, L, D, M,
             _native.strides3(q), _native.strides3(k), _native.strides3(v), _native.strides3(g),
-            _native.strides3(grad_queries), _native.strides3(grad_keys),
-            _native.strides3(grad_values), dt, m, _ptr(initial_state),
+            _native.strides3(grad_queries if grad_queries is not None else q),
+            _native.strides3(grad_keys if grad_keys is not None else k),
+            _native.strides3(grad_values if grad_values is not None else v), dt, m, _ptr(initial_state),
             _ptr(initial_grad_state), _ptr(forward_workspace),
             int(bool(workspace_has_grad_states)), _ptr(ws), nbytes,
             ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))

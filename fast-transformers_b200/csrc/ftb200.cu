@@ -540,19 +540,22 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
         // one operand has no features: every gradient that has columns is zero
         for (int64_t n = 0; n < N; ++n)
             for (int64_t h = 0; h < H; ++h) {
-                if (D > 0) {
+                if (D > 0 && gq)
                     FTB_CUDA(cudaMemset2DAsync((char *)gq + (n * gqs[0] + h * gqs[1]) * es,
                                                gqs[2] * es, 0, D * es, L, st));
+                if (D > 0 && gk)
                     FTB_CUDA(cudaMemset2DAsync((char *)gk + (n * gks[0] + h * gks[1]) * es,
                                                gks[2] * es, 0, D * es, L, st));
-                }
-                if (M > 0)
+                if (M > 0 && gv)
                     FTB_CUDA(cudaMemset2DAsync((char *)gv + (n * gvs[0] + h * gvs[1]) * es,
                                                gvs[2] * es, 0, M * es, L, st));
             }
         return FTB_OK;
     }
-    if (!q || !k || !v || !g || !gq || !gk || !gv) return FTB_ERR_INVALID;
+    if (!q || !k || !v || !g) return FTB_ERR_INVALID;
+    // a null output pointer skips that gradient (and the states only it needs)
+    const bool want_q = gq != nullptr, want_kv = gk != nullptr || gv != nullptr;
+    if (!want_q && !want_kv) return FTB_ERR_INVALID;
 
     Plan pl = choose_plan(mode, N * H, L);
     size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 1, 0);
@@ -561,8 +564,10 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
     float *wsR = (float *)((char *)workspace + need / 2);
 
     // forward states: taken from the forward call's workspace when the caller kept it
-    SegStates sS, sR;
-    if (forward_workspace && pl.nseg > 1) {
+    SegStates sS{nullptr, initial_state, 0, 1}, sR{nullptr, initial_grad_state, 0, 1};
+    if (!want_q) {
+        // grad_Q is the only reader of the forward states
+    } else if (forward_workspace && pl.nseg > 1) {
         sS = describe_states(mode, pl, (const float *)forward_workspace, initial_state, N * H,
                              workspace_has_grad_states != 0);
     } else {
@@ -572,7 +577,9 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
     }
     // reverse states R = sum q (x) grad_out over the segments after each segment
     bool r_with_grad_q = false;   // tensor-core mode: the totals are swept in grad_Q's own launch
-    if (workspace_has_grad_states && mode == FTB_MODE_MMA) {
+    if (!want_kv) {
+        // grad_K and grad_V are the only readers of the reverse states
+    } else if (workspace_has_grad_states && mode == FTB_MODE_MMA) {
         // ftb_causal_state_sum(q, grad_out, ..., reverse=1, second half of `workspace`) ran before
         sR = describe_states(mode, pl, wsR, initial_grad_state, N * H, true);
     } else if (mode == FTB_MODE_MMA && pl.nseg > 1 && sums_in_kernel(mode, pl)) {
@@ -591,9 +598,12 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
         // the short sweep runs on the SMs the scan leaves idle, and consecutive scans overlap
         // where one's last CTAs would otherwise leave SMs empty.
         MmaBatch first;
-        rc = mma_add_job(first, g, v, k, gq, gs, vs, ks, gqs, N, H, L, (int)M, (int)D, dtype, pl, sS.states,
-                         sS.init, sS.sum_mode, sS.sub, nullptr, 0, 0, 0, 0);
-        if (rc) return rc;
+        if (want_q) {
+            rc = mma_add_job(first, g, v, k, gq, gs, vs, ks, gqs, N, H, L, (int)M, (int)D, dtype, pl,
+                             sS.states, sS.init, sS.sum_mode, sS.sub, nullptr, 0, 0, 0, 0);
+            if (rc) return rc;
+            first.kind = FTB_KERNEL_MMA_BWD;
+        }
         MmaBatch second;
         MmaBatch &kv = r_with_grad_q ? second : first;
         if (r_with_grad_q) {
@@ -603,28 +613,39 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
             rc = mma_add_job(first, nullptr, q, g, nullptr, nullptr, qs, gs, nullptr, N, H, L, (int)D, (int)M,
                              dtype, fine, nullptr, nullptr, 0, 1, wsR, 0, sR.sub, 1, 0);
             if (rc) return rc;
-            first.kind = FTB_KERNEL_MMA_BWD_QR;
+            first.kind = want_q ? FTB_KERNEL_MMA_BWD_QR : FTB_KERNEL_MMA_STATE;
         }
-        rc = mma_add_job(kv, v, g, q, gk, vs, gs, qs, gks, N, H, L, (int)M, (int)D, dtype, pl, sR.states,
-                         sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 0, 1);
-        if (rc) return rc;
-        rc = mma_add_job(kv, k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl, sR.states,
-                         sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 1, 1);
-        if (rc) return rc;
-        kv.kind = FTB_KERNEL_MMA_BWD_MULTI;
+        if (gk) {
+            rc = mma_add_job(kv, v, g, q, gk, vs, gs, qs, gks, N, H, L, (int)M, (int)D, dtype, pl, sR.states,
+                             sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 0, 1);
+            if (rc) return rc;
+        }
+        if (gv) {
+            rc = mma_add_job(kv, k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl, sR.states,
+                             sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 1, 1);
+            if (rc) return rc;
+        }
+        if (want_kv) kv.kind = (&kv == &first && want_q) || (gk && gv) ? FTB_KERNEL_MMA_BWD_MULTI
+                                                                      : FTB_KERNEL_MMA_BWD;
         rc = mma_launch_batch(first, st);
         if (rc || !r_with_grad_q) return rc;
         return mma_launch_batch(second, st);
     }
 
     // grad_Q_i = sum_{j<=i} (g_i . v_j) k_j + S_init g_i        state viewed as [M][D]
-    rc = launch_scan(mode, g, v, k, gq, gs, vs, ks, gqs, N, H, L, (int)M, (int)D, dtype, pl, sS, 0, 0, st);
-    if (rc) return rc;
+    if (gq) {
+        rc = launch_scan(mode, g, v, k, gq, gs, vs, ks, gqs, N, H, L, (int)M, (int)D, dtype, pl, sS, 0, 0, st);
+        if (rc) return rc;
+    }
     // grad_K_j = sum_{i>=j} (v_j . g_i) q_i + R_init v_j        state viewed as [M][D]
-    rc = launch_scan(mode, v, g, q, gk, vs, gs, qs, gks, N, H, L, (int)M, (int)D, dtype, pl, sR, 0, 1, st);
-    if (rc) return rc;
+    if (gk) {
+        rc = launch_scan(mode, v, g, q, gk, vs, gs, qs, gks, N, H, L, (int)M, (int)D, dtype, pl, sR, 0, 1, st);
+        if (rc) return rc;
+    }
     // grad_V_j = sum_{i>=j} (k_j . q_i) g_i + R_init^T k_j      state viewed as [D][M]
-    return launch_scan(mode, k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl, sR, 1, 1, st);
+    if (gv)
+        rc = launch_scan(mode, k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl, sR, 1, 1, st);
+    return rc;
 }
 
 int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, int64_t H,

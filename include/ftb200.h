@@ -132,6 +132,8 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
  * grad_values) (causal_product_cuda.cu:1438-1467 / causal_product_cpu.cpp:133-209).
  *
  * initial_state      : optional (N,H,D,M) fp32, the same S_init the forward used.
+ * grad_q, grad_k, grad_v : a NULL pointer skips that gradient (and the state sweep only it
+ *                      needs); at least one must be given.
  * initial_grad_state : optional (N,H,D,M) fp32, R contributed by positions AFTER this
  *                      range (sequence split across devices); NULL = zeros.
  * forward_workspace  : optional; the workspace buffer the forward call on the same

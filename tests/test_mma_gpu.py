@@ -188,6 +188,26 @@ def test_forward_workspace_reuse_is_bitwise_equal_to_recompute():
         assert torch.equal(x, y)
 
 
+@pytest.mark.parametrize("mode", ["mma", "fp32"])
+def test_gradients_asked_for_separately_equal_the_joint_call(mode):
+    """A gradient buffer given as None is skipped; what is computed is bitwise what the call for
+    all three computes (config 1: two segments per head, so both state sweeps are involved)."""
+    Q, K, V, G = (t.cuda() for t in workloads.make_inputs(1))
+    full = [torch.empty_like(t) for t in (Q, K, V)]
+    causal_dot_backward_cuda(Q, K, V, G, *full, mode)
+    gq = torch.full_like(Q, float("nan"))
+    gk, gv = torch.full_like(K, float("nan")), torch.full_like(V, float("nan"))
+    causal_dot_backward_cuda(Q, K, V, G, gq, None, None, mode)
+    causal_dot_backward_cuda(Q, K, V, G, None, gk, gv, mode)
+    for a, b in zip(full, (gq, gk, gv)):
+        assert torch.equal(a, b)
+    only_v = torch.full_like(V, float("nan"))
+    causal_dot_backward_cuda(Q, K, V, G, None, None, only_v, mode)
+    assert torch.equal(only_v, full[2])
+    with pytest.raises(RuntimeError):
+        causal_dot_backward_cuda(Q, K, V, G, None, None, None, mode)
+
+
 def test_determinism_tf32():
     Q, K, V, G = workloads.make_inputs(1)
     a, b = fwd_bwd(Q, K, V, G), fwd_bwd(Q, K, V, G)
