@@ -1,6 +1,7 @@
 """Generate the golden fixtures in this directory from the UNMODIFIED reference.
 
-Run in a container that has the reference checkout (default ``/root/reference``):
+Run where the reference checkout is available (its location: the environment variable
+``FAST_TRANSFORMERS_REFERENCE``):
 
     python oracle/build_ref.py            # compiles the reference CPU extension in place
     python tests/golden/make_golden.py    # writes tests/golden/*.npz
