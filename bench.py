@@ -107,11 +107,24 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------
 # CPU arm (the reference's own OpenMP kernel, or the C port when it is not built)
 # ------------------------------------------------------------------------------------------
+def use_all_host_threads():
+    """OpenMP threads for the CPU arm: every core this process may run on.  A launcher that
+    exports OMP_NUM_THREADS=1 for its ranks (torch.distributed.run does) would otherwise pin the
+    reference's OpenMP kernel to one thread."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(n)
+    return n
+
+
 def cpu_arm(Q, K, V, G, budget_s, min_steps=2, max_steps=1000, warmup=1):
     """fwd+bwd of the CPU implementation on the host cores; returns (seconds per step,
     kind, cores, steps timed)."""
     from oracle import causal_oracle as orc
     kind = "reference" if orc.reference_ext() is not None else "port"
+    threads = use_all_host_threads()
     Q, K, V, G = (t.float().contiguous() for t in (Q, K, V, G))
     if kind == "reference":
         def step():
@@ -129,7 +142,7 @@ def cpu_arm(Q, K, V, G, budget_s, min_steps=2, max_steps=1000, warmup=1):
         t0 = time.perf_counter()
         step()
         times.append(time.perf_counter() - t0)
-    cores = int(os.environ.get("OMP_NUM_THREADS", 0)) or os.cpu_count()
+    cores = threads if kind == "reference" else 1
     return statistics.median(times), kind, cores, len(times)
 
 
@@ -138,6 +151,7 @@ def run_reference(args, shape, inputs, name):
     tokens = shape["N"] * shape["L"]
     from oracle import causal_oracle as orc
     kind = "reference" if orc.reference_ext() is not None else "port"
+    threads = use_all_host_threads()
     Qf, Kf, Vf, Gf = (t.float().contiguous() for t in (Q, K, V, G))
 
     def step():
@@ -154,7 +168,7 @@ def run_reference(args, shape, inputs, name):
     for _ in range(args.steps):
         step()
     dt = (time.perf_counter() - t0) / args.steps
-    cores = int(os.environ.get("OMP_NUM_THREADS", 0)) or os.cpu_count()
+    cores = threads if kind == "reference" else 1
     value = tokens / dt / 1e6
     sample = "%d steps of the full workload (%s), fp32, all (batch, head) units" % (args.steps, name)
     line = {
