@@ -37,6 +37,9 @@ def parse():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5])
+    ap.add_argument("--recurrent", action="store_true",
+                    help="time the recurrent step (decode) instead of the batch product: "
+                         "N256 H16 D=M=128 fp32, one token per sequence and step")
     ap.add_argument("--mode", default="mma", choices=["fp32", "mma"],
                     help="arithmetic of the kernels: tensor cores (TF32 operands for fp32 tensors, "
                          "bf16 for bf16; <= 2e-2 vs fp64) or fp32 CUDA cores (<= 1e-5)")
@@ -307,10 +310,133 @@ def run_encoder(args):
 
 
 # ------------------------------------------------------------------------------------------
+# The recurrent step (the same attention as a fixed-state recurrent model, one token per call)
+# ------------------------------------------------------------------------------------------
+def run_recurrent(args):
+    """Decode steps of RecurrentLinearAttention: N sequences advance by one token per step.
+    The state (N,H,D,M fp32 = 268 MB here, larger than L2) is read and written once per step,
+    which is the algorithmic traffic: 2*D*M*4 bytes per (sequence, head)."""
+    N, H, D, M = 256, 16, 128, 128
+    unit = "Mtokens/s"
+    name = "recurrent linear-attn step N%d H%d D%d M%d float32 (one token per sequence and step)" % (N, H, D, M)
+    gq = torch.Generator().manual_seed(6000)
+    q, k = (torch.randn(N, H, D, generator=gq) for _ in range(2))
+    v = torch.randn(N, H, M, generator=gq)
+    if args.impl == "reference":
+        from oracle import causal_oracle as orc
+        threads = use_all_host_threads()
+        state = None
+        for _ in range(max(1, min(args.warmup, 2))):
+            _, state = orc.recurrent_step(q, k, v, state, dtype=torch.float32)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            _, state = orc.recurrent_step(q, k, v, state, dtype=torch.float32)
+        dt = (time.perf_counter() - t0) / args.steps
+        value = N / dt / 1e6
+        print(json.dumps({
+            "impl": "reference", "metric": "recurrent linear-attn step Mtokens/s", "value": value,
+            "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic (seeded)", "config": {"workload": name, "device": "host CPU"},
+            "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "port",
+                             "sample": "%d steps; the reference module's torch arithmetic restated "
+                                       "(oracle.recurrent_step, fp32)" % args.steps},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}))
+        return 0
+    import fast_transformers_b200 as ftb  # noqa: F401
+    from fast_transformers_b200 import _native
+    from fast_transformers_b200.recurrent.attention import RecurrentLinearAttention
+    lib = _native.lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.set_grad_enabled(False)
+    qd, kd, vd = (t.to(dev) for t in (q, k, v))
+    att = RecurrentLinearAttention(D)
+    _, state = att(qd, kd, vd)
+    per_graph = 10
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(per_graph):
+            y, state = att(qd, kd, vd, state)
+    for _ in range(max(3, args.warmup)):
+        graph.replay()
+    sampler = ClockSampler(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms_step = e0.elapsed_time(e1) / (args.steps * per_graph)
+    launches = args.steps * per_graph
+    alg_bytes = N * H * (2 * D * M + 3 * D + 2 * D + 2 * M) * 4
+    peaks = {}
+    ppath = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(ppath):
+        peaks = json.load(open(ppath))
+    peak = peaks.get("hbm_gbs", 6650.0)
+    achieved = alg_bytes / (ms_step * 1e-3) / 1e9
+    # end to end: the step's inputs from pinned host memory, its output back
+    pin = [t.pin_memory() for t in (q, k, v)]
+    hout = torch.empty(N, H, M).pin_memory()
+    for _ in range(3):
+        for d_, h_ in zip((qd, kd, vd), pin):
+            d_.copy_(h_, non_blocking=True)
+        y, state = att(qd, kd, vd, state)
+        hout.copy_(y, non_blocking=True)
+    torch.cuda.synchronize()
+    e0.record()
+    n_e2e = 50
+    for _ in range(n_e2e):
+        for d_, h_ in zip((qd, kd, vd), pin):
+            d_.copy_(h_, non_blocking=True)
+        y, state = att(qd, kd, vd, state)
+        hout.copy_(y, non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / n_e2e
+    # CPU baseline: the reference module's arithmetic restated, fp32, on the host cores
+    from oracle import causal_oracle as orc
+    threads = use_all_host_threads()
+    cstate = None
+    _, cstate = orc.recurrent_step(q, k, v, cstate, dtype=torch.float32)
+    t0 = time.perf_counter()
+    n_cpu = 5
+    for _ in range(n_cpu):
+        _, cstate = orc.recurrent_step(q, k, v, cstate, dtype=torch.float32)
+    cpu_dt = (time.perf_counter() - t0) / n_cpu
+    print(json.dumps({
+        "metric": "recurrent linear-attn step Mtokens/s", "value": N / (ms_step * 1e-3) / 1e6, "unit": unit,
+        "n_gpus": 1, "steps": args.steps * per_graph, "warmup": max(3, args.warmup) * per_graph,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic (seeded)",
+        "config": {"workload": name, "cuda_graph": True,
+                   "l2": "the state (%d MB) exceeds the 126 MB L2; no flush" % (N * H * D * M * 4 // 2 ** 20)},
+        "roofline": {"bound": "hbm", "kernel": "recurrent_step", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "algorithmic_bytes_per_launch": alg_bytes, "avg_launch_ms": ms_step},
+        "cpu_baseline": {"value": N / cpu_dt / 1e6, "unit": unit, "cores": threads, "kind": "port",
+                         "sample": "%d steps; the reference module's torch arithmetic restated "
+                                   "(oracle.recurrent_step, fp32)" % n_cpu},
+        "e2e": {"value": N / (e2e_ms * 1e-3) / 1e6, "unit": unit,
+                "h2d_bytes_per_step": sum(t.numel() * 4 for t in pin), "d2h_bytes_per_step": hout.numel() * 4,
+                "ms_per_step": e2e_ms, "steps": n_e2e,
+                "api": "RecurrentLinearAttention.forward with the step's q, k, v copied in from pinned "
+                       "host memory and its output copied out"},
+        "gpu_launches": launches, "clocks": clocks}))
+    return 0
+
+
+# ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
 def main():
     args = parse()
+    if args.recurrent:
+        return run_recurrent(args)
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))

@@ -23,10 +23,10 @@ EXPORTS = (
     "ftb_version", "ftb_status_string", "ftb_last_cuda_error", "ftb_causal_workspace_bytes",
     "ftb_causal_dot_product", "ftb_causal_dot_backward", "ftb_causal_state_sum",
     "ftb_launch_count", "ftb_timing_enable", "ftb_timing_read", "ftb_device_status",
-    "ftb_causal_dot_product_static",
+    "ftb_causal_dot_product_static", "ftb_recurrent_linear_step",
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
-                "mma_bwd_qr", "mma_bwd_multi")
+                "mma_bwd_qr", "mma_bwd_multi", "recurrent_step")
 
 _lib = None
 _i64, _vp, _int, _sz = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
@@ -68,6 +68,9 @@ def lib():
     L.ftb_causal_dot_product_static.restype = _int
     L.ftb_causal_dot_product_static.argtypes = (
         [_vp] * 4 + [_i64] * 5 + [_i64p] * 4 + [_int, _int, _vp])
+    L.ftb_recurrent_linear_step.restype = _int
+    L.ftb_recurrent_linear_step.argtypes = (
+        [_vp] * 6 + [_i64] * 4 + [_i64p] * 4 + [_int, _int, ctypes.c_float, _vp])
     L.ftb_launch_count.restype = ctypes.c_uint64
     L.ftb_device_status.restype = _int
     L.ftb_device_status.argtypes = [_int]
@@ -86,6 +89,14 @@ def timing_read():
     cnt = (_int * n)()
     check(lib().ftb_timing_read(ms, cnt, n), "ftb_timing_read")
     return {KERNEL_KINDS[i]: (ms[i], cnt[i]) for i in range(n) if cnt[i]}
+
+
+FEATURE_NONE, FEATURE_ELU1 = 0, 1
+
+
+def strides2(t):
+    s = t.stride()
+    return (ctypes.c_int64 * 2)(s[0], s[1])
 
 
 def strides3(t):

@@ -132,3 +132,6 @@ class Registry(object):
 
 
 AttentionRegistry = Registry()
+# attention implementations that process one position at a time and carry a state
+# (fast_transformers/attention_registry/__init__.py:12-15)
+RecurrentAttentionRegistry = Registry()

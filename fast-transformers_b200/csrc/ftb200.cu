@@ -9,6 +9,7 @@
 #include <vector>
 
 #include "mma_host.cuh"
+#include "recurrent_step.cuh"
 #include "simt_scan.cuh"
 
 namespace ftb {
@@ -673,6 +674,38 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
                           nullptr, state, reverse ? 1 : 0, st, &ss);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// One recurrent step (the same attention as a fixed-state recurrent model).
+// ---------------------------------------------------------------------------------------------
+int ftb_recurrent_linear_step(const void *q, const void *k, const void *v, float *S, float *z,
+                              void *out, int64_t N, int64_t H, int64_t D, int64_t M,
+                              const int64_t *qs, const int64_t *ks, const int64_t *vs,
+                              const int64_t *os, int dtype, int feature_map, float eps,
+                              void *stream) {
+    if (N < 0 || H < 0 || D < 0 || M < 0) return FTB_ERR_INVALID;
+    if (dtype != FTB_F32 && dtype != FTB_BF16) return FTB_ERR_INVALID;
+    if (feature_map != FTB_FEATURE_NONE && feature_map != FTB_FEATURE_ELU1) return FTB_ERR_INVALID;
+    if (!qs || !ks || !vs || !os) return FTB_ERR_INVALID;
+    if (D > kStepMaxD) return FTB_ERR_UNSUPPORTED;
+    if (N == 0 || H == 0 || M == 0) return FTB_OK;
+    if (N * H > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
+    if (!v || !out || (D > 0 && (!q || !k || !S || !z))) return FTB_ERR_INVALID;
+    if (M % 4 == 0 && ((uintptr_t)S & 15)) return FTB_ERR_ALIGNMENT;   // rows of S are read 16 bytes wide
+    cudaStream_t st = (cudaStream_t)stream;
+    const Strides2 a{qs[0], qs[1]}, b{ks[0], ks[1]}, c{vs[0], vs[1]}, o{os[0], os[1]};
+    LaunchScope scope(FTB_KERNEL_RECURRENT_STEP, st);
+    if (dtype == FTB_F32)
+        recurrent_step_kernel<float><<<(unsigned)(N * H), kStepThreads, 0, st>>>(
+            (const float *)q, (const float *)k, (const float *)v, S, z, (float *)out, (int)H, (int)D, (int)M,
+            a, b, c, o, feature_map, eps);
+    else
+        recurrent_step_kernel<__nv_bfloat16><<<(unsigned)(N * H), kStepThreads, 0, st>>>(
+            (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v, S, z,
+            (__nv_bfloat16 *)out, (int)H, (int)D, (int)M, a, b, c, o, feature_map, eps);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Forward product for callers that must not allocate.

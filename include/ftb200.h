@@ -85,7 +85,8 @@ int ftb_last_cuda_error(void);
 #define FTB_KERNEL_MMA_STATE 5    /* tcgen05 per-segment totals                      */
 #define FTB_KERNEL_MMA_BWD_QR 6   /* tcgen05 grad_Q scan + reverse totals, one grid  */
 #define FTB_KERNEL_MMA_BWD_MULTI 7 /* tcgen05 two or three gradient scans, one grid  */
-#define FTB_KERNEL_KINDS 8
+#define FTB_KERNEL_RECURRENT_STEP 8 /* one recurrent step                              */
+#define FTB_KERNEL_KINDS 9
 uint64_t ftb_launch_count(void);
 /*
  * Device-side status word of the current device: 0, or the FTB_ERR_* code recorded by a kernel
@@ -171,6 +172,30 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
                          int64_t L, int64_t D, int64_t M, const int64_t *x_strides,
                          const int64_t *y_strides, int dtype, int mode, int reverse,
                          void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * One step of the same attention as a recurrent model with a fixed-size state.  Replaces the
+ * arithmetic of RecurrentLinearAttention.forward
+ * (fast_transformers/recurrent/attention/self_attention/linear_attention.py:55-90), which the
+ * reference writes as torch calls:  Q = phi(q), K = phi(k);  z += K;  S += K (x) v;
+ * y = (Q . S) / (Q . z + eps).
+ *
+ * q, k : (N,H,D), v, out : (N,H,M), fp32 or bf16, last dimension contiguous, element strides of
+ *        {batch, head} given per tensor.
+ * S    : (N,H,D,M) fp32 contiguous, z : (N,H,D) fp32 contiguous -- the state, UPDATED IN PLACE
+ *        (zeros for a new sequence; ftb_causal_dot_product's final_state plus the sum of the
+ *        key features continue a prefix that was processed in batch form).
+ * feature_map : FTB_FEATURE_NONE (q, k are features already) or FTB_FEATURE_ELU1
+ *        (phi(x) = elu(x) + 1, the reference's default, applied inside the kernel).
+ * D <= 512 (FTB_ERR_UNSUPPORTED beyond).  Inference only: no gradient entry point.
+ */
+#define FTB_FEATURE_NONE 0
+#define FTB_FEATURE_ELU1 1
+int ftb_recurrent_linear_step(const void *q, const void *k, const void *v, float *S, float *z,
+                              void *out, int64_t N, int64_t H, int64_t D, int64_t M,
+                              const int64_t *q_strides, const int64_t *k_strides,
+                              const int64_t *v_strides, const int64_t *out_strides, int dtype,
+                              int feature_map, float eps, void *stream);
 
 /*
  * Forward product that allocates nothing (it has no counterpart in the reference, whose kernels

@@ -297,5 +297,27 @@ def layer_forward(queries, keys, values, key_lengths=None, feature=elu_features,
     return out * Z[:, :, :, None]
 
 
+def recurrent_step(query, key, value, state=None, feature=elu_features, eps=1e-6,
+                   dtype=torch.float64):
+    """One step of ``RecurrentLinearAttention.forward``
+    (recurrent/attention/self_attention/linear_attention.py:55-90): inputs (N, H, E),
+    (N, H, E), (N, H, M) and the state ``[S (N,H,E,M), z (N,H,E)]`` or None (zeros, :64-67);
+    ``z += K; S += K (x) v`` (:78-83), ``Z = 1 / (Q . z + eps)``, ``y = (Q . S) Z`` (:86-87).
+    Returns ``(y, [S, z])`` in ``dtype``; the inputs are not modified."""
+    Q = feature(query.detach().to("cpu", dtype))
+    K = feature(key.detach().to("cpu", dtype))
+    v = value.detach().to("cpu", dtype)
+    N, H, E = Q.shape
+    if state is None:
+        S = Q.new_zeros(N, H, E, v.shape[2])
+        z = Q.new_zeros(N, H, E)
+    else:
+        S, z = (t.detach().to("cpu", dtype).clone() for t in state)
+    z = z + K
+    S = S + torch.einsum("nhd,nhm->nhdm", K, v)
+    Z = 1.0 / (torch.einsum("nhd,nhd->nh", Q, z) + eps)
+    return torch.einsum("nhd,nhdm,nh->nhm", Q, S, Z), [S, z]
+
+
 def to_numpy(*ts):
     return [np.asarray(t.detach().cpu()) for t in ts]

@@ -150,5 +150,56 @@ def main():
             print(f_, os.path.getsize(os.path.join(HERE, f_)), "bytes")
 
 
+def import_reference_recurrent():
+    """The reference's RecurrentLinearAttention (recurrent/attention/self_attention/
+    linear_attention.py).  The package ``__init__`` files above it import every recurrent
+    attention flavour, so they are replaced by empty packages as for ``attention``."""
+    import_reference()
+    root = build_ref.reference_root()
+    pkg_dir = os.path.join(root, "fast_transformers")
+    for name, rel in (("recurrent", "recurrent"), ("recurrent.attention", "recurrent/attention"),
+                      ("recurrent.attention.self_attention", "recurrent/attention/self_attention")):
+        m = types.ModuleType("fast_transformers." + name)
+        m.__path__ = [os.path.join(pkg_dir, rel)]
+        sys.modules["fast_transformers." + name] = m
+    import fast_transformers.recurrent.attention.self_attention.linear_attention as rla
+    return rla
+
+
+def recurrent():
+    """``recurrent.npz``: the reference module stepped over a short sequence (inputs, every
+    output, the final state), once from an empty state and once from a given one, and the
+    reference's own check that the steps reproduce the batch form."""
+    rla = import_reference_recurrent()
+    import fast_transformers.attention.causal_linear_attention as cla
+    import fast_transformers.masking as masking
+    torch.set_num_threads(1)
+    g = torch.Generator().manual_seed(606)
+    N, H, E, M, L = 3, 4, 25, 64, 12          # the reference test's E and M
+    q, k, v = (torch.rand(N, L, H, d, generator=g) for d in (E, E, M))
+    S0, z0 = torch.rand(N, H, E, M, generator=g), torch.rand(N, H, E, generator=g)
+    att = rla.RecurrentLinearAttention(E).eval()
+    blob = {"q": np_(q), "k": np_(k), "v": np_(v), "S0": np_(S0), "z0": np_(z0)}
+    with torch.no_grad():
+        for tag, state in (("empty", None), ("given", [S0.clone(), z0.clone()])):
+            ys = []
+            for i in range(L):
+                y, state = att(q[:, i], k[:, i], v[:, i], state)
+                ys.append(y)
+            blob[tag + "_y"] = np_(torch.stack(ys, 1))
+            blob[tag + "_S"] = np_(state[0])
+            blob[tag + "_z"] = np_(state[1])
+        batch = cla.CausalLinearAttention(E).eval()
+        lm = masking.LengthMask(torch.full((N,), L, dtype=torch.long))
+        blob["batch_y"] = np_(batch(q, k, v, masking.TriangularCausalMask(L), lm, lm))
+    assert np.abs(blob["batch_y"] - blob["empty_y"]).max() < 1e-5   # the reference's own bound
+    np.savez_compressed(os.path.join(HERE, "recurrent.npz"), **blob)
+    print("recurrent.npz", os.path.getsize(os.path.join(HERE, "recurrent.npz")), "bytes")
+
+
 if __name__ == "__main__":
-    main()
+    if sys.argv[1:] == ["recurrent"]:
+        recurrent()
+    else:
+        main()
+        recurrent()

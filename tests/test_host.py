@@ -174,3 +174,27 @@ def test_events():
     assert len(seen) == 1 and seen[0].values == 3
     assert EventDispatcher.get("") is EventDispatcher.get("")
     assert EventDispatcher.get(ed) is ed
+
+
+def test_recurrent_registry_entry_and_host_checks():
+    """The recurrent mirror: registry key "linear" with the reference's parameter list
+    (recurrent/attention/self_attention/linear_attention.py:95-102), the deprecated ``memory``
+    argument, and the loud refusals (CPU tensors, gradients)."""
+    import warnings
+    from fast_transformers_b200.attention_registry import RecurrentAttentionRegistry
+    from fast_transformers_b200.recurrent.attention import RecurrentLinearAttention
+    from fast_transformers_b200.recurrent._utils import check_state
+    assert "linear" in RecurrentAttentionRegistry.keys
+    cls, params = RecurrentAttentionRegistry["linear"]
+    assert cls is RecurrentLinearAttention
+    assert params == ["query_dimensions", "feature_map", "event_dispatcher"]
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        assert check_state(None, [1, 2]) == [1, 2]
+        assert any(issubclass(x.category, DeprecationWarning) for x in w)
+    att = RecurrentLinearAttention(8)
+    q, k, v = torch.rand(2, 3, 8), torch.rand(2, 3, 8), torch.rand(2, 3, 5)
+    with pytest.raises(RuntimeError):
+        att(q.requires_grad_(True), k, v)          # no gradients through the native step
+    with torch.no_grad(), pytest.raises(RuntimeError):
+        att(q, k, v)                               # CPU tensors: there is no CPU path

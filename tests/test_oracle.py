@@ -107,3 +107,22 @@ def test_states_compose():
                                 initial_state=S0)
     for a, b, c in zip(first, last, gf):
         assert orc.rel_err(torch.cat([a, b], dim=2), c) < 1e-13
+
+
+def test_recurrent_step_oracle_vs_reference(golden):
+    """The fp64 restatement of the recurrent step against the reference module's outputs and
+    states (from an empty and from a given state), and the reference's own property that the
+    steps reproduce the batch layer (test_linear_attention.py:54-79, bound 1e-5)."""
+    g = golden("recurrent")
+    q, k, v = (T(g[n]) for n in "qkv")
+    L = q.shape[1]
+    for tag, state in (("empty", None), ("given", [T(g["S0"]), T(g["z0"])])):
+        ys = []
+        for i in range(L):
+            y, state = orc.recurrent_step(q[:, i], k[:, i], v[:, i], state)
+            ys.append(y)
+        assert (torch.stack(ys, 1) - T(g[tag + "_y"])).abs().max() < 1e-5
+        assert orc.rel_err(state[0], T(g[tag + "_S"])) < 1e-6
+        assert orc.rel_err(state[1], T(g[tag + "_z"])) < 1e-6
+    assert (orc.layer_forward(q, k, v) - T(g["batch_y"])).abs().max() < 1e-5
+    assert (T(g["empty_y"]) - T(g["batch_y"])).abs().max() < 1e-5
