@@ -24,9 +24,10 @@ EXPORTS = (
     "ftb_causal_dot_product", "ftb_causal_dot_backward", "ftb_causal_state_sum",
     "ftb_launch_count", "ftb_timing_enable", "ftb_timing_read", "ftb_device_status",
     "ftb_causal_dot_product_static", "ftb_recurrent_linear_step",
+    "ftb_causal_normaliser_workspace_bytes", "ftb_causal_normaliser", "ftb_causal_normaliser_backward",
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
-                "mma_bwd_qr", "mma_bwd_multi", "recurrent_step")
+                "mma_bwd_qr", "mma_bwd_multi", "recurrent_step", "normaliser")
 
 _lib = None
 _i64, _vp, _int, _sz = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
@@ -71,6 +72,13 @@ def lib():
     L.ftb_recurrent_linear_step.restype = _int
     L.ftb_recurrent_linear_step.argtypes = (
         [_vp] * 6 + [_i64] * 4 + [_i64p] * 4 + [_int, _int, ctypes.c_float, _vp])
+    L.ftb_causal_normaliser_workspace_bytes.restype = _sz
+    L.ftb_causal_normaliser_workspace_bytes.argtypes = [_i64] * 4 + [_int]
+    L.ftb_causal_normaliser.restype = _int
+    L.ftb_causal_normaliser.argtypes = [_vp] * 3 + [_i64] * 4 + [_i64p] * 3 + [_int, _vp, _sz, _vp]
+    L.ftb_causal_normaliser_backward.restype = _int
+    L.ftb_causal_normaliser_backward.argtypes = (
+        [_vp] * 5 + [_i64] * 4 + [_i64p] * 5 + [_int, _vp, _sz, _vp])
     L.ftb_launch_count.restype = ctypes.c_uint64
     L.ftb_device_status.restype = _int
     L.ftb_device_status.argtypes = [_int]

@@ -18,7 +18,7 @@ from torch.nn import Module
 
 from ..attention_registry import (AttentionRegistry, Callable, EventDispatcherInstance, Int,
                                   Optional)
-from ..causal_product import causal_dot_product
+from ..causal_product import causal_dot_product, causal_normaliser
 from ..events import EventDispatcher
 from ..feature_maps import elu_feature_map
 from ..settings import get_mode
@@ -86,9 +86,13 @@ class CausalLinearAttention(Module):
             out = causal_linear(Q, K, Vx)
             Z = 1 / (out[..., M] + self.eps)
             return (out[..., :M] * Z[..., None]).contiguous()
-        # The tensor-core kernels take D = M only, so the normaliser is computed as in the
-        # reference (:95): a cumulative sum of K and a row-wise dot product.
-        Z = 1 / (torch.einsum("nlhi,nlhi->nlh", Q, K.cumsum(1)) + self.eps)
+        # The tensor-core kernels take D = M only, so the column of ones cannot ride along: the
+        # denominator Q_i . sum_{j<=i} K_j comes from a streaming kernel of its own (and so do
+        # its gradients).  The reference's way (:95) -- a cumulative sum of K and a row-wise dot
+        # product as torch calls, plus their autograd -- took half of an encoder step here
+        # (12 ms of 24 ms per layer at N16 L8192 H8 E64).
+        den = causal_normaliser(Q.permute(0, 2, 1, 3), K.permute(0, 2, 1, 3))      # (N, H, L)
+        Z = 1 / (den.permute(0, 2, 1) + self.eps)
         return (causal_linear(Q, K, values) * Z[:, :, :, None]).contiguous()
 
 

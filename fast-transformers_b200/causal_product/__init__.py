@@ -276,11 +276,17 @@ class CausalDotProduct(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         Q, K, V = ctx.saved_tensors
-        grad_Q = torch.empty(Q.shape, device=Q.device, dtype=Q.dtype)
-        grad_K = torch.empty(K.shape, device=K.device, dtype=K.dtype)
-        grad_V = torch.empty(V.shape, device=V.device, dtype=V.dtype)
         bwd = CausalDotProduct.dot_backward[Q.device.type]
-        if bwd is causal_dot_backward_cuda:
+        native = bwd is causal_dot_backward_cuda
+        # the native function skips a gradient whose buffer is None (a constant V, for example
+        # the column of ones behind the layer's normaliser, costs no grad_V scan)
+        need = list(ctx.needs_input_grad[:3])
+        if not native or not any(need) or _feature_blocks(Q, V, ctx.mode, None, None, None, None):
+            need = [True, True, True]
+        grad_Q = torch.empty(Q.shape, device=Q.device, dtype=Q.dtype) if need[0] else None
+        grad_K = torch.empty(K.shape, device=K.device, dtype=K.dtype) if need[1] else None
+        grad_V = torch.empty(V.shape, device=V.device, dtype=V.dtype) if need[2] else None
+        if native:
             bwd(Q.data, K.data, V.data, grad_out, grad_Q, grad_K, grad_V, ctx.mode,
                 forward_workspace=ctx.forward_workspace)
         else:
@@ -290,3 +296,65 @@ class CausalDotProduct(torch.autograd.Function):
 
 # Alias the autograd functions to python style snake case naming
 causal_dot_product = CausalDotProduct.apply
+
+
+def _strides_nhl(t):
+    s = t.stride()
+    return (ctypes.c_int64 * 3)(s[0], s[1], s[2])
+
+
+class CausalNormaliser(torch.autograd.Function):
+    """``den[n,h,l] = Q[n,h,l] . sum_{j<=l} K[n,h,j]`` for (N, H, L, D) views: the denominator of
+    the attention layer, which the reference computes as
+    ``torch.einsum("nlhi,nlhi->nlh", Q, K.cumsum(1))`` (``causal_linear_attention.py:95``).
+    Forward and backward are native streaming kernels (fp32 accumulation, every tensor read
+    once); saves only Q and K."""
+
+    @staticmethod
+    def forward(ctx, Q, K):
+        dev = _check_cuda(Q, K)
+        if Q.shape != K.shape or Q.dtype != K.dtype:
+            raise RuntimeError("Q and K must have one shape and dtype")
+        dt = _dtype_id(Q)
+        N, H, L, D = Q.shape
+        q, k = _rowmajor(Q.data), _rowmajor(K.data)
+        den = torch.empty((N, H, L), device=dev, dtype=Q.dtype)
+        L_ = _native.lib()
+        with torch.cuda.device(dev):
+            nbytes = L_.ftb_causal_normaliser_workspace_bytes(N, H, L, D, 0)
+            ws, nbytes = _workspace(nbytes, dev)
+            st = L_.ftb_causal_normaliser(
+                _ptr(q), _ptr(k), _ptr(den), N, H, L, D, _native.strides3(q), _native.strides3(k),
+                _strides_nhl(den), dt, _ptr(ws), nbytes,
+                ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        _native.check(st, "ftb_causal_normaliser")
+        ctx.save_for_backward(Q, K)
+        return den
+
+    @staticmethod
+    def backward(ctx, grad_den):
+        Q, K = ctx.saved_tensors
+        dev = Q.device
+        dt = _dtype_id(Q)
+        N, H, L, D = Q.shape
+        q, k = _rowmajor(Q.data), _rowmajor(K.data)
+        g = grad_den if grad_den.dtype == Q.dtype else grad_den.to(Q.dtype)
+        need_q, need_k = ctx.needs_input_grad
+        gq = torch.empty(Q.shape, device=dev, dtype=Q.dtype) if need_q else None
+        gk = torch.empty(K.shape, device=dev, dtype=K.dtype) if need_k else None
+        if gq is None and gk is None:
+            return None, None
+        L_ = _native.lib()
+        with torch.cuda.device(dev):
+            nbytes = L_.ftb_causal_normaliser_workspace_bytes(N, H, L, D, 1)
+            ws, nbytes = _workspace(nbytes, dev)
+            st = L_.ftb_causal_normaliser_backward(
+                _ptr(q), _ptr(k), _ptr(g), _ptr(gq), _ptr(gk), N, H, L, D, _native.strides3(q),
+                _native.strides3(k), _strides_nhl(g), _native.strides3(gq if gq is not None else q),
+                _native.strides3(gk if gk is not None else k), dt, _ptr(ws), nbytes,
+                ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        _native.check(st, "ftb_causal_normaliser_backward")
+        return gq, gk
+
+
+causal_normaliser = CausalNormaliser.apply

@@ -9,6 +9,7 @@
 #include <vector>
 
 #include "mma_host.cuh"
+#include "normaliser.cuh"
 #include "recurrent_step.cuh"
 #include "simt_scan.cuh"
 
@@ -378,6 +379,50 @@ static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 }  // namespace ftb
 
+namespace ftb {
+struct NormPlan {
+    int nseg;
+    int64_t seg_len;
+};
+static NormPlan norm_plan(int64_t BH, int64_t L) {
+    // enough CTAs for eight per SM, segments of whole 32-row tiles, at most 64 segments per sequence
+    int64_t want = (148 * 8 + BH - 1) / BH;
+    if (want < 1) want = 1;
+    if (want > 64) want = 64;
+    int64_t seg = (L + want - 1) / want;
+    seg = (seg + kNormRows - 1) / kNormRows * kNormRows;
+    if (seg < 8 * kNormRows) seg = 8 * kNormRows;
+    NormPlan pl;
+    pl.seg_len = seg;
+    pl.nseg = (int)((L + seg - 1) / seg);
+    if (pl.nseg < 1) pl.nseg = 1;
+    return pl;
+}
+template <typename T>
+static int norm_launch(NormParams p, int64_t BH, cudaStream_t st) {
+    const int64_t blocks = BH * p.nseg;
+    if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
+    if (p.nseg > 1) {
+        LaunchScope scope(FTB_KERNEL_NORMALISER, st);
+        norm_totals_kernel<T><<<(unsigned)blocks, kNormThreads, 0, st>>>(p);
+        FTB_CUDA(cudaGetLastError());
+    }
+    const size_t smem = 2 * (size_t)kNormRows * (p.D + 1) * sizeof(float);
+    if (smem > 48 * 1024)
+        FTB_CUDA(cudaFuncSetAttribute(norm_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LaunchScope scope(FTB_KERNEL_NORMALISER, st);
+    norm_scan_kernel<T><<<(unsigned)blocks, kNormThreads, smem, st>>>(p);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+static int norm_check(int64_t N, int64_t H, int64_t L, int64_t D, int dtype) {
+    if (N < 0 || H < 0 || L < 0 || D < 0) return FTB_ERR_INVALID;
+    if (dtype != FTB_F32 && dtype != FTB_BF16) return FTB_ERR_INVALID;
+    if (D > kNormMaxD) return FTB_ERR_UNSUPPORTED;
+    return FTB_OK;
+}
+}  // namespace ftb
+
 using namespace ftb;
 
 extern "C" {
@@ -674,6 +719,71 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
                           nullptr, state, reverse ? 1 : 0, st, &ss);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// The denominator Q_l . sum_{j<=l} K_j and its gradients.
+// ---------------------------------------------------------------------------------------------
+size_t ftb_causal_normaliser_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, int backward) {
+    if (N <= 0 || H <= 0 || L <= 0 || D <= 0) return 0;
+    NormPlan pl = norm_plan(N * H, L);
+    if (pl.nseg <= 1) return 0;
+    size_t one = align256((size_t)N * H * pl.nseg * D * sizeof(float));
+    return backward ? 2 * one : one;
+}
+
+int ftb_causal_normaliser(const void *q, const void *k, void *den, int64_t N, int64_t H, int64_t L,
+                          int64_t D, const int64_t *qs, const int64_t *ks, const int64_t *dens,
+                          int dtype, void *workspace, size_t workspace_bytes, void *stream) {
+    int rc = norm_check(N, H, L, D, dtype);
+    if (rc) return rc;
+    if (!qs || !ks || !dens) return FTB_ERR_INVALID;
+    if (N == 0 || H == 0 || L == 0) return FTB_OK;
+    if (!den || (D > 0 && (!q || !k))) return FTB_ERR_INVALID;
+    size_t need = ftb_causal_normaliser_workspace_bytes(N, H, L, D, 0);
+    if (need && (!workspace || workspace_bytes < need)) return FTB_ERR_WORKSPACE;
+    NormPlan pl = norm_plan(N * H, L);
+    NormParams p{};
+    p.q = q; p.k = k; p.g = nullptr; p.out = den;
+    p.qs = Strides3n{qs[0], qs[1], qs[2]}; p.ks = Strides3n{ks[0], ks[1], ks[2]};
+    p.gs = Strides3n{0, 0, 0}; p.os = Strides3n{dens[0], dens[1], dens[2]};
+    p.H = (int)H; p.D = (int)D; p.nseg = pl.nseg; p.L = L; p.seg_len = pl.seg_len;
+    p.totals = (float *)workspace; p.mode = NORM_FWD;
+    cudaStream_t st = (cudaStream_t)stream;
+    return dtype == FTB_F32 ? norm_launch<float>(p, N * H, st) : norm_launch<__nv_bfloat16>(p, N * H, st);
+}
+
+int ftb_causal_normaliser_backward(const void *q, const void *k, const void *grad_den, void *gq,
+                                   void *gk, int64_t N, int64_t H, int64_t L, int64_t D,
+                                   const int64_t *qs, const int64_t *ks, const int64_t *gdens,
+                                   const int64_t *gqs, const int64_t *gks, int dtype, void *workspace,
+                                   size_t workspace_bytes, void *stream) {
+    int rc = norm_check(N, H, L, D, dtype);
+    if (rc) return rc;
+    if (!qs || !ks || !gdens || !gqs || !gks) return FTB_ERR_INVALID;
+    if (N == 0 || H == 0 || L == 0 || D == 0) return FTB_OK;
+    if (!q || !k || !grad_den || (!gq && !gk)) return FTB_ERR_INVALID;
+    size_t need = ftb_causal_normaliser_workspace_bytes(N, H, L, D, 1);
+    if (need && (!workspace || workspace_bytes < need)) return FTB_ERR_WORKSPACE;
+    NormPlan pl = norm_plan(N * H, L);
+    cudaStream_t st = (cudaStream_t)stream;
+    NormParams p{};
+    p.q = q; p.k = k; p.g = grad_den;
+    p.qs = Strides3n{qs[0], qs[1], qs[2]}; p.ks = Strides3n{ks[0], ks[1], ks[2]};
+    p.gs = Strides3n{gdens[0], gdens[1], gdens[2]};
+    p.H = (int)H; p.D = (int)D; p.nseg = pl.nseg; p.L = L; p.seg_len = pl.seg_len;
+    if (gq) {   // gQ_l = g_l * sum_{j<=l} K_j
+        p.out = gq; p.os = Strides3n{gqs[0], gqs[1], gqs[2]};
+        p.totals = (float *)workspace; p.mode = NORM_BWD_Q;
+        rc = dtype == FTB_F32 ? norm_launch<float>(p, N * H, st) : norm_launch<__nv_bfloat16>(p, N * H, st);
+        if (rc) return rc;
+    }
+    if (gk) {   // gK_j = sum_{l>=j} g_l * Q_l
+        p.out = gk; p.os = Strides3n{gks[0], gks[1], gks[2]};
+        p.totals = (float *)((char *)workspace + need / 2); p.mode = NORM_BWD_K;
+        rc = dtype == FTB_F32 ? norm_launch<float>(p, N * H, st) : norm_launch<__nv_bfloat16>(p, N * H, st);
+    }
+    return rc;
+}
 
 // ---------------------------------------------------------------------------------------------
 // One recurrent step (the same attention as a fixed-state recurrent model).

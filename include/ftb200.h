@@ -86,7 +86,8 @@ int ftb_last_cuda_error(void);
 #define FTB_KERNEL_MMA_BWD_QR 6   /* tcgen05 grad_Q scan + reverse totals, one grid  */
 #define FTB_KERNEL_MMA_BWD_MULTI 7 /* tcgen05 two or three gradient scans, one grid  */
 #define FTB_KERNEL_RECURRENT_STEP 8 /* one recurrent step                              */
-#define FTB_KERNEL_KINDS 9
+#define FTB_KERNEL_NORMALISER 9   /* denominator Q . cumsum(K) and its gradients      */
+#define FTB_KERNEL_KINDS 10
 uint64_t ftb_launch_count(void);
 /*
  * Device-side status word of the current device: 0, or the FTB_ERR_* code recorded by a kernel
@@ -172,6 +173,30 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
                          int64_t L, int64_t D, int64_t M, const int64_t *x_strides,
                          const int64_t *y_strides, int dtype, int mode, int reverse,
                          void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * The denominator of the attention layer, den[n,h,l] = Q_l . sum_{j<=l} K_j, and its gradients
+ * gQ_l = g_l * sum_{j<=l} K_j, gK_j = sum_{l>=j} g_l * Q_l.  Replaces the torch calls of
+ * fast_transformers/attention/causal_linear_attention.py:95
+ * (`torch.einsum("nlhi,nlhi->nlh", Q, K.cumsum(1))`) and their autograd.
+ *
+ * q, k, grad_q, grad_k : (N,H,L,D) views, fp32 or bf16, last dimension contiguous, element strides
+ *        of {batch, head, position}; den, grad_den : (N,H,L) views with strides of the same three.
+ * D <= 256 (FTB_ERR_UNSUPPORTED beyond).  fp32 accumulation; every tensor is streamed once.
+ * workspace: ftb_causal_normaliser_workspace_bytes(N,H,L,D,backward) bytes (per-segment sums).
+ * In the backward a NULL grad_q or grad_k skips that gradient.
+ */
+size_t ftb_causal_normaliser_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, int backward);
+int ftb_causal_normaliser(const void *q, const void *k, void *den, int64_t N, int64_t H, int64_t L,
+                          int64_t D, const int64_t *q_strides, const int64_t *k_strides,
+                          const int64_t *den_strides, int dtype, void *workspace,
+                          size_t workspace_bytes, void *stream);
+int ftb_causal_normaliser_backward(const void *q, const void *k, const void *grad_den, void *grad_q,
+                                   void *grad_k, int64_t N, int64_t H, int64_t L, int64_t D,
+                                   const int64_t *q_strides, const int64_t *k_strides,
+                                   const int64_t *grad_den_strides, const int64_t *grad_q_strides,
+                                   const int64_t *grad_k_strides, int dtype, void *workspace,
+                                   size_t workspace_bytes, void *stream);
 
 /*
  * One step of the same attention as a recurrent model with a fixed-size state.  Replaces the

@@ -297,6 +297,14 @@ def layer_forward(queries, keys, values, key_lengths=None, feature=elu_features,
     return out * Z[:, :, :, None]
 
 
+def normaliser(Q, K, dtype=torch.float64):
+    """``den[n,h,l] = Q[n,h,l] . sum_{j<=l} K[n,h,j]`` for (N, H, L, D) tensors -- the argument of
+    the reciprocal in causal_linear_attention.py:95 (there in (N, L, H, D) layout)."""
+    q = Q.detach().to("cpu", dtype)
+    k = K.detach().to("cpu", dtype)
+    return torch.einsum("nhld,nhld->nhl", q, k.cumsum(2))
+
+
 def recurrent_step(query, key, value, state=None, feature=elu_features, eps=1e-6,
                    dtype=torch.float64):
     """One step of ``RecurrentLinearAttention.forward``

@@ -101,3 +101,46 @@ def test_encoder_tensor_core_mode_close_to_reference():
     # values), one rounded to TF32 and one not, and two layers compound it: measured 3.3e-2.
     assert orc.rel_err(gm, g32) < 1e-1
     assert not torch.equal(ym, y32)   # the two modes really are different code paths
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 333, 64), (1, 2, 5000, 16), (3, 1, 31, 100), (1, 1, 1, 1),
+                                   (2, 2, 700, 256)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_native_normaliser_against_fp64(shape, dtype):
+    """den = Q . cumsum(K) and its gradients (causal_linear_attention.py:95 and its autograd) from
+    the streaming kernels, on (N, L, H, E) storage viewed as (N, H, L, E), one and several
+    segments per sequence."""
+    from fast_transformers_b200.causal_product import causal_normaliser
+    N, H, L, E = shape
+    g = torch.Generator().manual_seed(L)
+    qs = torch.rand(N, L, H, E, generator=g).to(dtype)
+    ks = torch.rand(N, L, H, E, generator=g).to(dtype)
+    w = torch.randn(N, H, L, generator=g).to(dtype)
+    q = qs.cuda().permute(0, 2, 1, 3).requires_grad_(True)
+    k = ks.cuda().permute(0, 2, 1, 3).requires_grad_(True)
+    den = causal_normaliser(q, k)
+    assert den.shape == (N, H, L) and den.dtype == dtype
+    den.backward(w.cuda())
+    qd = qs.double().permute(0, 2, 1, 3).requires_grad_(True)
+    kd = ks.double().permute(0, 2, 1, 3).requires_grad_(True)
+    want = torch.einsum("nhld,nhld->nhl", qd, kd.cumsum(2))
+    want.backward(w.double())
+    assert orc.rel_err(orc.normaliser(qs.permute(0, 2, 1, 3), ks.permute(0, 2, 1, 3)), want) < 1e-12
+    tol = 1e-5 if dtype == torch.float32 else 1e-2     # bf16: rounding of the stored results
+    assert orc.rel_err(den, want) < tol
+    assert orc.rel_err(q.grad, qd.grad) < tol and orc.rel_err(k.grad, kd.grad) < tol
+
+
+def test_native_normaliser_partial_gradients_and_limits():
+    from fast_transformers_b200 import _native
+    from fast_transformers_b200.causal_product import causal_normaliser
+    q = torch.rand(1, 2, 300, 32, device="cuda", requires_grad=True)
+    k = torch.rand(1, 2, 300, 32, device="cuda")            # no gradient asked for K
+    causal_normaliser(q, k).sum().backward()
+    want = k.double().cumsum(2)
+    assert orc.rel_err(q.grad, want) < 1e-5
+    wide = torch.rand(1, 1, 8, 300, device="cuda")
+    with pytest.raises(_native.NativeError) as e:
+        causal_normaliser(wide, wide)
+    assert e.value.status == _native.ERR_UNSUPPORTED
+    assert causal_normaliser(torch.rand(0, 2, 5, 4, device="cuda"), torch.rand(0, 2, 5, 4, device="cuda")).shape == (0, 2, 5)
