@@ -384,22 +384,73 @@ struct NormPlan {
     int nseg;
     int64_t seg_len;
 };
-static NormPlan norm_plan(int64_t BH, int64_t L) {
-    // enough CTAs for eight per SM, segments of whole 32-row tiles, at most 64 segments per sequence
-    int64_t want = (148 * 8 + BH - 1) / BH;
+constexpr int kNormMaxSegs = 64;
+// `ctas_wanted`: how many (sequence, segment) work items should exist; segments are whole 32-row
+// tiles, at least `min_rows` long, at most kNormMaxSegs per sequence
+static NormPlan norm_plan(int64_t BH, int64_t L, int64_t items_wanted, int64_t min_rows) {
+    int64_t want = (items_wanted + BH - 1) / BH;
     if (want < 1) want = 1;
-    if (want > 64) want = 64;
+    if (want > kNormMaxSegs) want = kNormMaxSegs;
     int64_t seg = (L + want - 1) / want;
     seg = (seg + kNormRows - 1) / kNormRows * kNormRows;
-    if (seg < 8 * kNormRows) seg = 8 * kNormRows;
+    if (seg < min_rows) seg = min_rows;
     NormPlan pl;
     pl.seg_len = seg;
     pl.nseg = (int)((L + seg - 1) / seg);
     if (pl.nseg < 1) pl.nseg = 1;
     return pl;
 }
+// The register-streaming kernels take D in {16, 32, 64, 128} with rows that start on 16-byte
+// (fp32) / 8-byte (bf16) boundaries; everything else goes through the shared-memory kernels.
+static bool norm_fast_ok(const NormParams &p, int dtype, bool vec_out) {
+    if (p.D != 16 && p.D != 32 && p.D != 64 && p.D != 128) return false;
+    const uintptr_t a = dtype == FTB_F32 ? 15 : 7;
+    auto ok = [&](const void *ptr, const Strides3n &s) {
+        return ((uintptr_t)ptr & a) == 0 && s.n % 4 == 0 && s.h % 4 == 0 && s.l % 4 == 0;
+    };
+    if (!ok(p.q, p.qs) || !ok(p.k, p.ks)) return false;
+    if (vec_out && !ok(p.out, p.os)) return false;
+    static const char *off = std::getenv("FTB200_NORM_GENERIC");
+    return off == nullptr;
+}
+template <typename T, int LPR, int MODE>
+static int norm_launch_fast_mode(const NormParams &p, int64_t groups, int64_t blocks, cudaStream_t st) {
+    if (p.nseg > 1) {
+        LaunchScope scope(FTB_KERNEL_NORMALISER, st);
+        norm_stream_kernel<T, LPR, MODE, true><<<(unsigned)blocks, kNormThreads, 0, st>>>(p, groups);
+        FTB_CUDA(cudaGetLastError());
+    }
+    LaunchScope scope(FTB_KERNEL_NORMALISER, st);
+    norm_stream_kernel<T, LPR, MODE, false><<<(unsigned)blocks, kNormThreads, 0, st>>>(p, groups);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+template <typename T, int LPR>
+static int norm_launch_fast(NormParams p, int64_t BH, cudaStream_t st) {
+    constexpr int per_cta = kNormThreads / LPR;
+    NormPlan pl = norm_plan(BH, p.L, (int64_t)148 * 4 * per_cta, 2 * kNormRows);
+    p.nseg = pl.nseg;
+    p.seg_len = pl.seg_len;
+    const int64_t groups = BH * p.nseg;
+    const int64_t blocks = (groups + per_cta - 1) / per_cta;
+    if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
+    if (p.mode == NORM_FWD) return norm_launch_fast_mode<T, LPR, NORM_FWD>(p, groups, blocks, st);
+    if (p.mode == NORM_BWD_Q) return norm_launch_fast_mode<T, LPR, NORM_BWD_Q>(p, groups, blocks, st);
+    return norm_launch_fast_mode<T, LPR, NORM_BWD_K>(p, groups, blocks, st);
+}
 template <typename T>
-static int norm_launch(NormParams p, int64_t BH, cudaStream_t st) {
+static int norm_launch(NormParams p, int64_t BH, int dtype, cudaStream_t st) {
+    if (norm_fast_ok(p, dtype, p.mode != NORM_FWD)) {
+        switch (p.D) {
+            case 16: return norm_launch_fast<T, 4>(p, BH, st);
+            case 32: return norm_launch_fast<T, 8>(p, BH, st);
+            case 64: return norm_launch_fast<T, 16>(p, BH, st);
+            default: return norm_launch_fast<T, 32>(p, BH, st);
+        }
+    }
+    NormPlan pl = norm_plan(BH, p.L, 148 * 8, 8 * kNormRows);
+    p.nseg = pl.nseg;
+    p.seg_len = pl.seg_len;
     const int64_t blocks = BH * p.nseg;
     if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
     if (p.nseg > 1) {
@@ -725,9 +776,8 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
 // ---------------------------------------------------------------------------------------------
 size_t ftb_causal_normaliser_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, int backward) {
     if (N <= 0 || H <= 0 || L <= 0 || D <= 0) return 0;
-    NormPlan pl = norm_plan(N * H, L);
-    if (pl.nseg <= 1) return 0;
-    size_t one = align256((size_t)N * H * pl.nseg * D * sizeof(float));
+    // per-segment sums for the most segments either kernel family may use
+    size_t one = align256((size_t)N * H * kNormMaxSegs * D * sizeof(float));
     return backward ? 2 * one : one;
 }
 
@@ -741,15 +791,15 @@ int ftb_causal_normaliser(const void *q, const void *k, void *den, int64_t N, in
     if (!den || (D > 0 && (!q || !k))) return FTB_ERR_INVALID;
     size_t need = ftb_causal_normaliser_workspace_bytes(N, H, L, D, 0);
     if (need && (!workspace || workspace_bytes < need)) return FTB_ERR_WORKSPACE;
-    NormPlan pl = norm_plan(N * H, L);
     NormParams p{};
     p.q = q; p.k = k; p.g = nullptr; p.out = den;
     p.qs = Strides3n{qs[0], qs[1], qs[2]}; p.ks = Strides3n{ks[0], ks[1], ks[2]};
     p.gs = Strides3n{0, 0, 0}; p.os = Strides3n{dens[0], dens[1], dens[2]};
-    p.H = (int)H; p.D = (int)D; p.nseg = pl.nseg; p.L = L; p.seg_len = pl.seg_len;
+    p.H = (int)H; p.D = (int)D; p.L = L;
     p.totals = (float *)workspace; p.mode = NORM_FWD;
     cudaStream_t st = (cudaStream_t)stream;
-    return dtype == FTB_F32 ? norm_launch<float>(p, N * H, st) : norm_launch<__nv_bfloat16>(p, N * H, st);
+    return dtype == FTB_F32 ? norm_launch<float>(p, N * H, dtype, st)
+                            : norm_launch<__nv_bfloat16>(p, N * H, dtype, st);
 }
 
 int ftb_causal_normaliser_backward(const void *q, const void *k, const void *grad_den, void *gq,
@@ -764,23 +814,24 @@ int ftb_causal_normaliser_backward(const void *q, const void *k, const void *gra
     if (!q || !k || !grad_den || (!gq && !gk)) return FTB_ERR_INVALID;
     size_t need = ftb_causal_normaliser_workspace_bytes(N, H, L, D, 1);
     if (need && (!workspace || workspace_bytes < need)) return FTB_ERR_WORKSPACE;
-    NormPlan pl = norm_plan(N * H, L);
     cudaStream_t st = (cudaStream_t)stream;
     NormParams p{};
     p.q = q; p.k = k; p.g = grad_den;
     p.qs = Strides3n{qs[0], qs[1], qs[2]}; p.ks = Strides3n{ks[0], ks[1], ks[2]};
     p.gs = Strides3n{gdens[0], gdens[1], gdens[2]};
-    p.H = (int)H; p.D = (int)D; p.nseg = pl.nseg; p.L = L; p.seg_len = pl.seg_len;
+    p.H = (int)H; p.D = (int)D; p.L = L;
     if (gq) {   // gQ_l = g_l * sum_{j<=l} K_j
         p.out = gq; p.os = Strides3n{gqs[0], gqs[1], gqs[2]};
         p.totals = (float *)workspace; p.mode = NORM_BWD_Q;
-        rc = dtype == FTB_F32 ? norm_launch<float>(p, N * H, st) : norm_launch<__nv_bfloat16>(p, N * H, st);
+        rc = dtype == FTB_F32 ? norm_launch<float>(p, N * H, dtype, st)
+                              : norm_launch<__nv_bfloat16>(p, N * H, dtype, st);
         if (rc) return rc;
     }
     if (gk) {   // gK_j = sum_{l>=j} g_l * Q_l
         p.out = gk; p.os = Strides3n{gks[0], gks[1], gks[2]};
         p.totals = (float *)((char *)workspace + need / 2); p.mode = NORM_BWD_K;
-        rc = dtype == FTB_F32 ? norm_launch<float>(p, N * H, st) : norm_launch<__nv_bfloat16>(p, N * H, st);
+        rc = dtype == FTB_F32 ? norm_launch<float>(p, N * H, dtype, st)
+                              : norm_launch<__nv_bfloat16>(p, N * H, dtype, st);
     }
     return rc;
 }

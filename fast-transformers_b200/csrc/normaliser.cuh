@@ -169,4 +169,121 @@ norm_scan_kernel(const NormParams p) {
     }
 }
 
+// ---- the fast path: D in {16, 32, 64, 128}, 16-byte (fp32) / 8-byte (bf16) aligned rows ------------
+// A group of LPR = D / 4 lanes owns one (batch, head, segment); every lane keeps four features of
+// the running sum in registers and streams down (up) the rows, U rows of loads in flight at a
+// time.  No shared memory, no block-wide barriers; the per-row dot product of the forward is a
+// shuffle reduction inside the group.
+template <typename T>
+__device__ __forceinline__ float4 norm_load4(const T *p);
+template <>
+__device__ __forceinline__ float4 norm_load4<float>(const float *p) {
+    return *reinterpret_cast<const float4 *>(p);
+}
+template <>
+__device__ __forceinline__ float4 norm_load4<__nv_bfloat16>(const __nv_bfloat16 *p) {
+    const uint2 v = *reinterpret_cast<const uint2 *>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162 *>(&v.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162 *>(&v.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void norm_store4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ void norm_store4(__nv_bfloat16 *p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t *>(&a);
+    o.y = *reinterpret_cast<uint32_t *>(&b);
+    *reinterpret_cast<uint2 *>(p) = o;
+}
+
+// totals == true: only the sum of the segment's rows is produced (into p.totals)
+template <typename T, int LPR, int MODE, bool TOTALS>
+__global__ void __launch_bounds__(kNormThreads, 2)
+norm_stream_kernel(const NormParams p, int64_t ngroups) {
+    constexpr int U = LPR < 8 ? 4 : 8;                 // rows in flight
+    const int lane = threadIdx.x & 31;
+    const int gl = lane % LPR;                         // lane inside the group
+    const unsigned gmask = LPR == 32 ? 0xffffffffu : (((1u << LPR) - 1u) << (lane / LPR * LPR));
+    const int64_t gid = (int64_t)blockIdx.x * (kNormThreads / LPR) + threadIdx.x / LPR;
+    if (gid >= ngroups) return;
+    const int seg = (int)(gid % p.nseg);
+    const int64_t bh = gid / p.nseg;
+    const int64_t n = bh / p.H, h = bh % p.H;
+    const int64_t r0 = (int64_t)seg * p.seg_len, r1 = min(p.L, r0 + p.seg_len);
+    constexpr int mode = MODE;
+    constexpr bool rev = MODE == NORM_BWD_K;
+    const int d = 4 * gl;
+    const T *qp = reinterpret_cast<const T *>(p.q) + n * p.qs.n + h * p.qs.h + d;
+    const T *kp = reinterpret_cast<const T *>(p.k) + n * p.ks.n + h * p.ks.h + d;
+    const T *gp = reinterpret_cast<const T *>(p.g) + n * p.gs.n + h * p.gs.h;
+    T *op = reinterpret_cast<T *>(p.out) + n * p.os.n + h * p.os.h;
+    float *tot = p.totals + bh * p.nseg * p.D + d;
+
+    float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!TOTALS && p.nseg > 1) {
+        if (!rev) {
+            for (int s = 0; s < seg; ++s) {
+                const float4 v = *reinterpret_cast<const float4 *>(tot + (int64_t)s * p.D);
+                run.x += v.x; run.y += v.y; run.z += v.z; run.w += v.w;
+            }
+        } else {
+            for (int s = p.nseg - 1; s > seg; --s) {
+                const float4 v = *reinterpret_cast<const float4 *>(tot + (int64_t)s * p.D);
+                run.x += v.x; run.y += v.y; run.z += v.z; run.w += v.w;
+            }
+        }
+    }
+
+    const int64_t nrows = r1 - r0;
+    for (int64_t b0 = 0; b0 < nrows; b0 += U) {
+        float4 x[U], y[U];
+        float gx[U];
+        int64_t row[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            // ascending: rows r0 + b0 + u; descending: rows r1 - 1 - b0 - u
+            row[u] = rev ? r1 - 1 - b0 - u : r0 + b0 + u;
+            const bool ok = b0 + u < nrows;
+            x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            y[u] = x[u];
+            gx[u] = 0.f;
+            if (ok) {
+                if (mode == NORM_BWD_K) {
+                    x[u] = norm_load4(qp + row[u] * p.qs.l);
+                } else {
+                    x[u] = norm_load4(kp + row[u] * p.ks.l);
+                    if (mode == NORM_FWD && !TOTALS) y[u] = norm_load4(qp + row[u] * p.qs.l);
+                }
+                if (mode != NORM_FWD) gx[u] = step_load(gp + row[u] * p.gs.l);
+            }
+        }
+        float keep = 0.f;   // forward: lane u of the group keeps the result of row u
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const bool ok = b0 + u < nrows;
+            if (mode == NORM_BWD_K) {
+                run.x += gx[u] * x[u].x; run.y += gx[u] * x[u].y;
+                run.z += gx[u] * x[u].z; run.w += gx[u] * x[u].w;
+            } else {
+                run.x += x[u].x; run.y += x[u].y; run.z += x[u].z; run.w += x[u].w;
+            }
+            if (TOTALS) continue;
+            if (mode == NORM_FWD) {
+                float acc = y[u].x * run.x + y[u].y * run.y + y[u].z * run.z + y[u].w * run.w;
+#pragma unroll
+                for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(gmask, acc, o);
+                if (gl == u) keep = acc;
+            } else if (ok) {
+                const float4 v = mode == NORM_BWD_Q
+                                     ? make_float4(gx[u] * run.x, gx[u] * run.y, gx[u] * run.z, gx[u] * run.w)
+                                     : run;
+                norm_store4(op + row[u] * p.os.l + d, v);
+            }
+        }
+        if (!TOTALS && mode == NORM_FWD && gl < U && b0 + gl < nrows)
+            step_store(op + (r0 + b0 + gl) * p.os.l, keep);
+    }
+    if (TOTALS) *reinterpret_cast<float4 *>(tot + (int64_t)seg * p.D) = run;
+}
+
 }  // namespace ftb

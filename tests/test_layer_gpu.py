@@ -104,7 +104,8 @@ def test_encoder_tensor_core_mode_close_to_reference():
 
 
 @pytest.mark.parametrize("shape", [(2, 3, 333, 64), (1, 2, 5000, 16), (3, 1, 31, 100), (1, 1, 1, 1),
-                                   (2, 2, 700, 256)])
+                                   (2, 2, 700, 256), (1, 2, 1000, 128), (2, 1, 257, 32),
+                                   (16, 8, 2048, 64)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_native_normaliser_against_fp64(shape, dtype):
     """den = Q . cumsum(K) and its gradients (causal_linear_attention.py:95 and its autograd) from
