@@ -262,8 +262,12 @@ class CausalDotProduct(torch.autograd.Function):
         ctx.mode = get_mode()
         N, H, L, _ = Q.shape
         M = V.shape[3]
-        # the reference allocates zeros (its fallback kernels accumulate); ours overwrite
-        product = torch.empty((N, H, L, M), device=Q.device, dtype=Q.dtype)
+        # the reference allocates zeros (its fallback kernels accumulate); ours overwrite.  The
+        # result takes the memory order of V (the layer passes (N, L, H, M) storage viewed as
+        # (N, H, L, M)): the kernels write through strides, and the caller's permute back is
+        # then contiguous instead of a copy
+        product = torch.empty_like(V) if V.shape == (N, H, L, M) else \
+            torch.empty((N, H, L, M), device=Q.device, dtype=Q.dtype)
         kept = []
         fwd = CausalDotProduct.dot[Q.device.type]
         if fwd is causal_dot_product_cuda:
@@ -283,9 +287,10 @@ class CausalDotProduct(torch.autograd.Function):
         need = list(ctx.needs_input_grad[:3])
         if not native or not any(need) or _feature_blocks(Q, V, ctx.mode, None, None, None, None):
             need = [True, True, True]
-        grad_Q = torch.empty(Q.shape, device=Q.device, dtype=Q.dtype) if need[0] else None
-        grad_K = torch.empty(K.shape, device=K.device, dtype=K.dtype) if need[1] else None
-        grad_V = torch.empty(V.shape, device=V.device, dtype=V.dtype) if need[2] else None
+        # gradients in the memory order of their inputs (see forward)
+        grad_Q = torch.empty_like(Q) if need[0] else None
+        grad_K = torch.empty_like(K) if need[1] else None
+        grad_V = torch.empty_like(V) if need[2] else None
         if native:
             bwd(Q.data, K.data, V.data, grad_out, grad_Q, grad_K, grad_V, ctx.mode,
                 forward_workspace=ctx.forward_workspace)
@@ -318,7 +323,7 @@ class CausalNormaliser(torch.autograd.Function):
         dt = _dtype_id(Q)
         N, H, L, D = Q.shape
         q, k = _rowmajor(Q.data), _rowmajor(K.data)
-        den = torch.empty((N, H, L), device=dev, dtype=Q.dtype)
+        den = torch.empty_like(Q[..., 0]) if D > 0 else torch.empty((N, H, L), device=dev, dtype=Q.dtype)
         L_ = _native.lib()
         with torch.cuda.device(dev):
             nbytes = L_.ftb_causal_normaliser_workspace_bytes(N, H, L, D, 0)
@@ -340,8 +345,8 @@ class CausalNormaliser(torch.autograd.Function):
         q, k = _rowmajor(Q.data), _rowmajor(K.data)
         g = grad_den if grad_den.dtype == Q.dtype else grad_den.to(Q.dtype)
         need_q, need_k = ctx.needs_input_grad
-        gq = torch.empty(Q.shape, device=dev, dtype=Q.dtype) if need_q else None
-        gk = torch.empty(K.shape, device=dev, dtype=K.dtype) if need_k else None
+        gq = torch.empty_like(Q) if need_q else None
+        gk = torch.empty_like(K) if need_k else None
         if gq is None and gk is None:
             return None, None
         L_ = _native.lib()
