@@ -25,9 +25,10 @@ EXPORTS = (
     "ftb_launch_count", "ftb_timing_enable", "ftb_timing_read", "ftb_device_status",
     "ftb_causal_dot_product_static", "ftb_recurrent_linear_step",
     "ftb_causal_normaliser_workspace_bytes", "ftb_causal_normaliser", "ftb_causal_normaliser_backward",
+    "ftb_elu_feature_map", "ftb_elu_feature_map_backward",
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
-                "mma_bwd_qr", "mma_bwd_multi", "recurrent_step", "normaliser")
+                "mma_bwd_qr", "mma_bwd_multi", "recurrent_step", "normaliser", "feature_map")
 
 _lib = None
 _i64, _vp, _int, _sz = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
@@ -79,6 +80,10 @@ def lib():
     L.ftb_causal_normaliser_backward.restype = _int
     L.ftb_causal_normaliser_backward.argtypes = (
         [_vp] * 5 + [_i64] * 4 + [_i64p] * 5 + [_int, _vp, _sz, _vp])
+    L.ftb_elu_feature_map.restype = _int
+    L.ftb_elu_feature_map.argtypes = [_vp, _vp, _vp, _i64, _i64, _int, _vp]
+    L.ftb_elu_feature_map_backward.restype = _int
+    L.ftb_elu_feature_map_backward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp]
     L.ftb_launch_count.restype = ctypes.c_uint64
     L.ftb_device_status.restype = _int
     L.ftb_device_status.argtypes = [_int]

@@ -20,7 +20,7 @@ from ..attention_registry import (AttentionRegistry, Callable, EventDispatcherIn
                                   Optional)
 from ..causal_product import causal_dot_product, causal_normaliser
 from ..events import EventDispatcher
-from ..feature_maps import elu_feature_map
+from ..feature_maps import elu_feature_map, elu_plus_one_native, is_default_elu_map
 from ..settings import get_mode
 
 
@@ -60,12 +60,17 @@ class CausalLinearAttention(Module):
 
     def forward(self, queries, keys, values, attn_mask, query_lengths, key_lengths):
         self.feature_map.new_feature_map(queries.device)
-        Q = self.feature_map.forward_queries(queries)
-        K = self.feature_map.forward_keys(keys)
-
         if not attn_mask.lower_triangular:
             raise RuntimeError("CausalLinearAttention only supports full lower triangular masks")
-        K = K * key_lengths.float_matrix[:, :, None, None]
+        if (is_default_elu_map(self.feature_map) and queries.is_cuda
+                and queries.dtype in (torch.float32, torch.bfloat16)):
+            # elu(x) + 1 and the key-length mask in one native pass each (and one each backward)
+            Q = elu_plus_one_native(queries)
+            K = elu_plus_one_native(keys, key_lengths.float_matrix)
+        else:
+            Q = self.feature_map.forward_queries(queries)
+            K = self.feature_map.forward_keys(keys)
+            K = K * key_lengths.float_matrix[:, :, None, None]
         Q, K = self._make_sizes_compatible(Q, K)
 
         # Bring V to L rows as well.  The reference leaves V as it is (for L > S its kernel

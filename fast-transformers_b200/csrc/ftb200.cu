@@ -8,8 +8,8 @@
 #include <mutex>
 #include <vector>
 
+#include "feature_map.cuh"
 #include "mma_host.cuh"
-#include "normaliser.cuh"
 #include "recurrent_step.cuh"
 #include "simt_scan.cuh"
 
@@ -834,6 +834,74 @@ int ftb_causal_normaliser_backward(const void *q, const void *k, const void *gra
                               : norm_launch<__nv_bfloat16>(p, N * H, dtype, st);
     }
     return rc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// phi(x) = elu(x) + 1 with the key-length mask folded in, and its gradient.
+// ---------------------------------------------------------------------------------------------
+static int elu1_launch(const void *x, const void *g, void *out, const float *mask, int64_t total,
+                       int64_t inner_per_mask, int dtype, bool backward, cudaStream_t st) {
+    if (total < 0 || (dtype != FTB_F32 && dtype != FTB_BF16)) return FTB_ERR_INVALID;
+    if (mask && inner_per_mask <= 0) return FTB_ERR_INVALID;
+    if (total == 0) return FTB_OK;
+    if (!x || !out || (backward && !g)) return FTB_ERR_INVALID;
+    const int64_t blocks = (total + 1023) / 1024;
+    if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
+    LaunchScope scope(FTB_KERNEL_FEATURE_MAP, st);
+    const uintptr_t am = dtype == FTB_F32 ? 15 : 7;
+    const bool vec = total % 4 == 0 && (!mask || inner_per_mask % 4 == 0) && ((uintptr_t)x & am) == 0 &&
+                     ((uintptr_t)out & am) == 0 && (!backward || ((uintptr_t)g & am) == 0);
+    if (vec) {
+        if (dtype == FTB_F32) {
+            if (backward)
+                elu1_vec_kernel<float, true><<<(unsigned)blocks, 256, 0, st>>>(
+                    (const float *)x, (const float *)g, (float *)out, mask, total, inner_per_mask);
+            else
+                elu1_vec_kernel<float, false><<<(unsigned)blocks, 256, 0, st>>>(
+                    (const float *)x, nullptr, (float *)out, mask, total, inner_per_mask);
+        } else {
+            using B = __nv_bfloat16;
+            if (backward)
+                elu1_vec_kernel<B, true><<<(unsigned)blocks, 256, 0, st>>>((const B *)x, (const B *)g, (B *)out,
+                                                                          mask, total, inner_per_mask);
+            else
+                elu1_vec_kernel<B, false><<<(unsigned)blocks, 256, 0, st>>>((const B *)x, nullptr, (B *)out, mask,
+                                                                           total, inner_per_mask);
+        }
+        FTB_CUDA(cudaGetLastError());
+        return FTB_OK;
+    }
+    if (dtype == FTB_F32) {
+        if (backward)
+            elu1_kernel<float, true><<<(unsigned)blocks, 256, 0, st>>>((const float *)x, (const float *)g,
+                                                                      (float *)out, mask, total, inner_per_mask);
+        else
+            elu1_kernel<float, false><<<(unsigned)blocks, 256, 0, st>>>((const float *)x, nullptr, (float *)out,
+                                                                       mask, total, inner_per_mask);
+    } else {
+        using B = __nv_bfloat16;
+        if (backward)
+            elu1_kernel<B, true><<<(unsigned)blocks, 256, 0, st>>>((const B *)x, (const B *)g, (B *)out, mask,
+                                                                  total, inner_per_mask);
+        else
+            elu1_kernel<B, false><<<(unsigned)blocks, 256, 0, st>>>((const B *)x, nullptr, (B *)out, mask, total,
+                                                                   inner_per_mask);
+    }
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+
+int ftb_elu_feature_map(const void *x, void *y, const float *row_mask, int64_t total,
+                        int64_t elements_per_mask_entry, int dtype, void *stream) {
+    return elu1_launch(x, nullptr, y, row_mask, total, elements_per_mask_entry, dtype, false,
+                       (cudaStream_t)stream);
+}
+
+int ftb_elu_feature_map_backward(const void *x, const void *grad_y, void *grad_x, const float *row_mask,
+                                 int64_t total, int64_t elements_per_mask_entry, int dtype,
+                                 void *stream) {
+    return elu1_launch(x, grad_y, grad_x, row_mask, total, elements_per_mask_entry, dtype, true,
+                       (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------------

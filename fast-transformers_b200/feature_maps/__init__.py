@@ -61,6 +61,66 @@ elu_feature_map = ActivationFunctionFeatureMap.factory(_elu_plus_one)
 _elu_plus_one.fused_id = "elu+1"
 
 
+class _EluPlusOneNative(torch.autograd.Function):
+    """``(elu(x) + 1) * w`` with ``w`` one weight per leading-dimension row (or none) in one native
+    pass, gradient ``g * w * (x > 0 ? 1 : exp(x))`` in another: the default feature map with the
+    layer's key-length mask folded in (``feature_maps/base.py:71-73``,
+    ``attention/causal_linear_attention.py:83``)."""
+
+    @staticmethod
+    def forward(ctx, x, weights):
+        import ctypes
+        from .. import _native
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        w = None if weights is None else weights.to(torch.float32).contiguous()
+        per = xc.numel() // w.numel() if w is not None and w.numel() else 1
+        with torch.cuda.device(xc.device):
+            st = _native.lib().ftb_elu_feature_map(
+                ctypes.c_void_p(xc.data_ptr()), ctypes.c_void_p(y.data_ptr()),
+                ctypes.c_void_p(w.data_ptr()) if w is not None else None, xc.numel(), per,
+                0 if xc.dtype == torch.float32 else 1,
+                ctypes.c_void_p(torch.cuda.current_stream(xc.device).cuda_stream))
+        _native.check(st, "ftb_elu_feature_map")
+        ctx.save_for_backward(xc, w)
+        ctx.per = per
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        import ctypes
+        from .. import _native
+        xc, w = ctx.saved_tensors
+        g = grad_y.contiguous()
+        gx = torch.empty_like(xc)
+        with torch.cuda.device(xc.device):
+            st = _native.lib().ftb_elu_feature_map_backward(
+                ctypes.c_void_p(xc.data_ptr()), ctypes.c_void_p(g.data_ptr()),
+                ctypes.c_void_p(gx.data_ptr()),
+                ctypes.c_void_p(w.data_ptr()) if w is not None else None, xc.numel(), ctx.per,
+                0 if xc.dtype == torch.float32 else 1,
+                ctypes.c_void_p(torch.cuda.current_stream(xc.device).cuda_stream))
+        _native.check(st, "ftb_elu_feature_map_backward")
+        return gx, None
+
+
+def elu_plus_one_native(x, row_weights=None):
+    """``(elu(x) + 1) * row_weights[..., None, None]`` for a CUDA tensor ``x`` of float32 or
+    bfloat16; ``row_weights`` has the shape of ``x``'s leading dimensions (for (N, S, H, E) keys
+    the (N, S) key-length mask) or is None."""
+    if not x.is_cuda or x.dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError("elu_plus_one_native needs a float32 or bfloat16 CUDA tensor")
+    if row_weights is not None and (row_weights.numel() == 0 or x.numel() % row_weights.numel()):
+        raise RuntimeError("row_weights does not match the leading dimensions of x")
+    return _EluPlusOneNative.apply(x, row_weights)
+
+
+def is_default_elu_map(feature_map):
+    """True for the default map phi(x) = elu(x) + 1, which the native kernels apply themselves."""
+    f = getattr(feature_map, "activation_function", None)
+    return getattr(f, "fused_id", None) == "elu+1"
+
+
 def orthogonal_random_matrix_(w):
     """Fill ``w`` (rows x columns) in place with blocks of ``rows`` orthogonal columns whose
     norms follow the chi distribution with ``rows`` degrees of freedom

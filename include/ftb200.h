@@ -87,7 +87,8 @@ int ftb_last_cuda_error(void);
 #define FTB_KERNEL_MMA_BWD_MULTI 7 /* tcgen05 two or three gradient scans, one grid  */
 #define FTB_KERNEL_RECURRENT_STEP 8 /* one recurrent step                              */
 #define FTB_KERNEL_NORMALISER 9   /* denominator Q . cumsum(K) and its gradients      */
-#define FTB_KERNEL_KINDS 10
+#define FTB_KERNEL_FEATURE_MAP 10 /* elu(x)+1 (x key-length mask) and its gradient    */
+#define FTB_KERNEL_KINDS 11
 uint64_t ftb_launch_count(void);
 /*
  * Device-side status word of the current device: 0, or the FTB_ERR_* code recorded by a kernel
@@ -197,6 +198,19 @@ int ftb_causal_normaliser_backward(const void *q, const void *k, const void *gra
                                    const int64_t *grad_den_strides, const int64_t *grad_q_strides,
                                    const int64_t *grad_k_strides, int dtype, void *workspace,
                                    size_t workspace_bytes, void *stream);
+
+/*
+ * The default feature map phi(x) = elu(x) + 1 (fast_transformers/feature_maps/base.py:71-73) with
+ * the layer's key-length mask (fast_transformers/attention/causal_linear_attention.py:83) folded
+ * in, and its gradient grad_x = grad_y * w * (x > 0 ? 1 : exp(x)).  x, y (grad_y, grad_x):
+ * contiguous tensors of `total` elements, fp32 or bf16.  row_mask: NULL, or fp32 weights, one per
+ * `elements_per_mask_entry` consecutive elements (for (N,L,H,E) keys and an (N,L) mask: H*E).
+ */
+int ftb_elu_feature_map(const void *x, void *y, const float *row_mask, int64_t total,
+                        int64_t elements_per_mask_entry, int dtype, void *stream);
+int ftb_elu_feature_map_backward(const void *x, const void *grad_y, void *grad_x,
+                                 const float *row_mask, int64_t total,
+                                 int64_t elements_per_mask_entry, int dtype, void *stream);
 
 /*
  * One step of the same attention as a recurrent model with a fixed-size state.  Replaces the

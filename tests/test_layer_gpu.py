@@ -145,3 +145,28 @@ def test_native_normaliser_partial_gradients_and_limits():
         causal_normaliser(wide, wide)
     assert e.value.status == _native.ERR_UNSUPPORTED
     assert causal_normaliser(torch.rand(0, 2, 5, 4, device="cuda"), torch.rand(0, 2, 5, 4, device="cuda")).shape == (0, 2, 5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_native_elu_feature_map_with_key_length_mask(dtype):
+    """(elu(x) + 1) * mask and its gradient in one pass each, against torch in fp64
+    (feature_maps/base.py:71-73, causal_linear_attention.py:83); odd sizes so that groups of four
+    elements straddle mask entries."""
+    from fast_transformers_b200.feature_maps import elu_plus_one_native
+    g = torch.Generator().manual_seed(31)
+    for shape in ((3, 50, 2, 7), (2, 33, 4, 64), (1, 1, 1, 1)):
+        x = (torch.randn(shape, generator=g) * 2).to(dtype)
+        lengths = torch.randint(1, shape[1] + 1, (shape[0],), generator=g)
+        mask = (torch.arange(shape[1])[None, :] < lengths[:, None]).float()
+        w = torch.randn(shape, generator=g).to(dtype)
+        for m in (None, mask):
+            xd = x.cuda().requires_grad_(True)
+            y = elu_plus_one_native(xd, None if m is None else m.cuda())
+            y.backward(w.cuda())
+            x64 = x.double().requires_grad_(True)
+            want = torch.nn.functional.elu(x64) + 1
+            if m is not None:
+                want = want * m.double()[:, :, None, None]
+            want.backward(w.double())
+            tol = 1e-6 if dtype == torch.float32 else 1e-2
+            assert orc.rel_err(y, want) < tol and orc.rel_err(xd.grad, x64.grad) < tol
