@@ -9,9 +9,11 @@ with the same parameter tuple (:109-116).
     out_i = Z_i * Q_i . sum_{j<=i} K_j^T V_j
 
 What differs from the reference is data movement only: the kernels take (N, L, H, dim)
-storage through strides, so the four permute+contiguous copies of ``causal_linear`` are
-views here, and the normaliser comes out of the same kernel launch as the product (V is
-extended by a column of ones, whose output column is Q_i . cumsum(K)_i).
+storage through strides and write their results in that order, so the four
+permute+contiguous copies of ``causal_linear`` are views here; the default feature map and
+the key-length mask are one native pass; and the normaliser comes out of the same kernel
+launch as the product in ``"fp32"`` mode (V is extended by a column of ones, whose output
+column is Q_i . cumsum(K)_i) or out of streaming kernels of its own in ``"mma"`` mode.
 """
 import torch
 from torch.nn import Module
