@@ -86,17 +86,25 @@ class CausalLinearAttention(Module):
             values = torch.cat([values, values.new_zeros(N, L - S, H, values.shape[3])], dim=1)
 
         M = values.shape[3]
-        if get_mode() == "fp32":
+        E = Q.shape[3]
+        fp32_mode = get_mode() == "fp32"
+        if fp32_mode and (M % 64 != 0 or E > 256):
             # One extra value column of ones: its output column is Q_i . sum_{j<=i} K_j, the
-            # denominator, so product and normaliser share one pass over Q and K.
+            # denominator, so product and normaliser share one pass over Q and K.  (Free while
+            # M + 1 columns still fit the kernel's 64-column tile; at M = 64 it would cost a
+            # second tile, i.e. the whole product again.)
             Vx = torch.cat([values, values.new_ones(N, L, H, 1)], dim=-1)
             out = causal_linear(Q, K, Vx)
             Z = 1 / (out[..., M] + self.eps)
             return (out[..., :M] * Z[..., None]).contiguous()
-        # The tensor-core kernels take D = M only, so the column of ones cannot ride along: the
-        # denominator Q_i . sum_{j<=i} K_j comes from a streaming kernel of its own (and so do
-        # its gradients).  The reference's way (:95) -- a cumulative sum of K and a row-wise dot
-        # product as torch calls, plus their autograd -- took half of an encoder step here
+        if E > 256:
+            # wider than the denominator kernels take: the reference's formulation (:95)
+            Z = 1 / (torch.einsum("nlhi,nlhi->nlh", Q, K.cumsum(1)) + self.eps)
+            return (causal_linear(Q, K, values) * Z[:, :, :, None]).contiguous()
+        # The denominator Q_i . sum_{j<=i} K_j from streaming kernels of its own (and so its
+        # gradients): the tensor-core kernels take D = M only, so the column of ones cannot
+        # ride along there.  The reference's way (:95) -- a cumulative sum of K and a row-wise
+        # dot product as torch calls, plus their autograd -- took half of an encoder step here
         # (12 ms of 24 ms per layer at N16 L8192 H8 E64).
         den = causal_normaliser(Q.permute(0, 2, 1, 3), K.permute(0, 2, 1, 3))      # (N, H, L)
         Z = 1 / (den.permute(0, 2, 1) + self.eps)
