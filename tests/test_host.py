@@ -198,3 +198,13 @@ def test_recurrent_registry_entry_and_host_checks():
         att(q.requires_grad_(True), k, v)          # no gradients through the native step
     with torch.no_grad(), pytest.raises(RuntimeError):
         att(q, k, v)                               # CPU tensors: there is no CPU path
+
+
+def test_kernel_kind_table_matches_header():
+    """The names ftb_timing_read's slots are reported under follow the header's FTB_KERNEL_*."""
+    header = open(os.path.join(ROOT, "include", "ftb200.h")).read()
+    kinds = dict(re.findall(r"#define FTB_KERNEL_([A-Z_0-9]+)\s+(\d+)", header))
+    count = int(kinds.pop("KINDS"))
+    assert count == len(_native.KERNEL_KINDS)
+    for name, idx in kinds.items():
+        assert _native.KERNEL_KINDS[int(idx)] == name.lower()
