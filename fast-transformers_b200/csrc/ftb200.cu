@@ -173,6 +173,7 @@ struct MmaBatch {
     mma::ScanBatch b;
     int dtype = FTB_F32;
     int kind = FTB_KERNEL_MMA_FWD;
+    bool after_own_launch = false;   // see mma::launch_t
     MmaBatch() { b.njobs = 0; b.first_block[0] = 0; b.interleave = 0; }
 };
 
@@ -244,9 +245,9 @@ static int mma_launch_batch(MmaBatch &batch, cudaStream_t st) {
     LaunchScope scope(batch.kind, st);
     cudaError_t e;
     if (batch.dtype == FTB_F32)
-        e = mma::launch_t<float, 64, 64>(batch.b, st);
+        e = mma::launch_t<float, 64, 64>(batch.b, st, batch.after_own_launch);
     else
-        e = mma::launch_t<__nv_bfloat16, 128, 128>(batch.b, st);
+        e = mma::launch_t<__nv_bfloat16, 128, 128>(batch.b, st, batch.after_own_launch);
     if (e != cudaSuccess) return cuda_fail(e);
     return FTB_OK;
 }
@@ -255,8 +256,9 @@ static int mma_launch(const void *a, const void *b, const void *c, void *out, co
                       const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H,
                       int64_t L, int Da, int Dc, int dtype, Plan pl, const float *states,
                       const float *init, int sum_mode, int sub, float *state_out, int skip_lo, int skip_hi,
-                      int canon_is_DaDc, int reverse, cudaStream_t st) {
+                      int canon_is_DaDc, int reverse, cudaStream_t st, bool after_own_launch = false) {
     MmaBatch batch;
+    batch.after_own_launch = after_own_launch;
     int rc = mma_add_job(batch, a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, states, init,
                          sum_mode, sub, state_out, skip_lo, skip_hi, canon_is_DaDc, reverse);
     if (rc) return rc;
@@ -287,6 +289,7 @@ struct SegStates {
     const float *init;    // per bh block added on top, or nullptr
     int sum_mode;         // 1: `states` are raw totals the kernel adds up itself
     int sub;              // sum_mode 1: blocks per segment
+    int fresh = 0;        // written by a launch of this call, directly in front of the scan's
 };
 
 static int launch_scan(int mode, const void *a, const void *b, const void *c, void *out,
@@ -295,7 +298,7 @@ static int launch_scan(int mode, const void *a, const void *b, const void *c, vo
                        SegStates ss, int canon_is_DaDc, int reverse, cudaStream_t st) {
     if (mode == FTB_MODE_MMA)
         return mma_launch(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, ss.states, ss.init,
-                          ss.sum_mode, ss.sub, nullptr, 0, 0, canon_is_DaDc, reverse, st);
+                          ss.sum_mode, ss.sub, nullptr, 0, 0, canon_is_DaDc, reverse, st, ss.fresh != 0);
     return simt_launch_scan(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl,
                             ss.states ? ss.states : ss.init, pl.nseg, canon_is_DaDc, reverse, st);
 }
@@ -347,6 +350,7 @@ static int prepare_states(int mode, const void *x, const void *y, const int64_t 
             skip_hi = skip_lo + sub;
         }
         rc = launch_state_sum(mode, x, y, xs, ys, N, H, L, D, M, dtype, fine, ws, skip_lo, skip_hi, st);
+        out->fresh = 1;
         if (rc || !total) return rc;
         int64_t n = N * H * (int64_t)D * M;
         LaunchScope scope(FTB_KERNEL_STATE_PREFIX, st);
@@ -361,6 +365,7 @@ static int prepare_states(int mode, const void *x, const void *y, const int64_t 
     rc = launch_prefix(ws, fold ? init : nullptr, total, fold ? nullptr : init, N * H, pl.nseg,
                        (int64_t)D * M, reverse, st);
     if (pl.nseg == 1) *out = SegStates{ws, fold ? nullptr : init, 0, 1};
+    out->fresh = 1;
     return rc;
 }
 
@@ -724,8 +729,10 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
         }
         if (want_kv) kv.kind = (&kv == &first && want_q) || (gk && gv) ? FTB_KERNEL_MMA_BWD_MULTI
                                                                       : FTB_KERNEL_MMA_BWD;
+        first.after_own_launch = sS.fresh || sR.fresh;   // a sweep of this call is directly in front
         rc = mma_launch_batch(first, st);
         if (rc || !r_with_grad_q) return rc;
+        second.after_own_launch = true;   // directly behind {grad_Q scan + sweep}
         return mma_launch_batch(second, st);
     }
 

@@ -137,14 +137,32 @@ static bool supported(int dtype, int64_t Da, int64_t Dc) {
     return Da == 128 && Dc % 128 == 0 && Dc >= 128;
 }
 
+// `after_own_launch`: the launch directly in front of this one in the stream is this library's
+// own (the state-only sweep of the same call).  The grid is then started with programmatic stream
+// serialisation: its blocks may begin while that launch drains and wait for it only where they
+// read what it wrote.
 template <typename T, int DA, int DCT>
-static cudaError_t launch_t(const ScanBatch &batch, cudaStream_t st) {
+static cudaError_t launch_t(const ScanBatch &batch, cudaStream_t st, bool after_own_launch) {
     using K = Cfg<T, DA, DCT>;
     auto kern = mma_scan_kernel<T, DA, DCT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)K::SMEM);
     if (e != cudaSuccess) return e;
-    kern<<<(unsigned)batch.first_block[batch.njobs], NTHREADS, K::SMEM, st>>>(batch);
-    return cudaGetLastError();
+    static const char *no_pdl = std::getenv("FTB200_NO_PDL");
+    if (!after_own_launch || no_pdl) {
+        kern<<<(unsigned)batch.first_block[batch.njobs], NTHREADS, K::SMEM, st>>>(batch);
+        return cudaGetLastError();
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)batch.first_block[batch.njobs]);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = K::SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, batch);
 }
 
 }  // namespace mma

@@ -386,6 +386,9 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
         while (job + 1 < batch.njobs && (int)blockIdx.x >= batch.first_block[job + 1]) ++job;
         job_block = (int)blockIdx.x - batch.first_block[job];
     }
+    // let a grid launched behind this one with programmatic stream serialisation start as SMs
+    // become free (it waits for this grid's results where it needs them)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const ScanJob &J = batch.job[job];
     const ScanParams &p = J.p;
     const CUtensorMap &map_a = J.ma, &map_b = J.mb, &map_bmn = J.mbmn, &map_c = J.mc;
@@ -946,6 +949,11 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         s_hi = p.reverse ? per_head : seg * p.sub;
                     }
                     if (!p.states) s_hi = s_lo;
+                    // Programmatic dependent launch: this grid may have been started before the
+                    // launch in front of it (the state-only sweep that writes these totals) has
+                    // finished -- its tiles, scores and masks do not depend on it.  The totals do:
+                    // wait for that grid here (returns at once after an ordinary launch).
+                    if (s_hi > s_lo) asm volatile("griddepcontrol.wait;" ::: "memory");
 #pragma unroll
                     for (int cb = 0; cb < DCT / 32; ++cb) {
                         float acc[32];
@@ -1050,6 +1058,9 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
     if (threadIdx.x == 0 && blockIdx.x < 1024) g_cta[4 * blockIdx.x + 3] = ts_globaltimer();
 #endif
     if (warp == 0) tmem_dealloc(tmem, 512);
+    // no block of a programmatically launched grid ends before the grid in front of it has, so
+    // that whatever is launched behind this grid is ordered after both
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
 #ifdef FTB_TIMESTAMPS
     if (threadIdx.x == 0 && blockIdx.x < 1024) {
         g_cta[4 * blockIdx.x + 1] = ts_globaltimer();
