@@ -49,6 +49,9 @@ def parse():
     ap.add_argument("--no-other-mode", action="store_true",
                     help="skip the few eager steps in the other arithmetic mode")
     ap.add_argument("--no-graph", action="store_true", help="time eager calls, not a CUDA graph")
+    ap.add_argument("--graph-steps", type=int, default=0,
+                    help="steps captured per CUDA graph (default: the largest divisor of --steps that keeps "
+                         "the graph under about 8 ms, at most 10)")
     ap.add_argument("--layers", type=int, default=None, help="config 3: override the layer count")
     ap.add_argument("--batch", type=int, default=None, help="config 3: override the batch size")
     return ap.parse_args()
@@ -522,6 +525,7 @@ def main():
     # step is captured once into a CUDA graph (native launches go to the capturing stream like
     # any other) and replayed.  --no-graph times the eager calls instead.
     graph = None
+    per_graph = 1
     launches_per_step = None
     if not args.no_graph and not seq_parallel:
         side = torch.cuda.Stream(device=dev)
@@ -530,11 +534,22 @@ def main():
             step()
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize()
+        # the graph holds as many whole steps as divide --steps (at most 10), so that the gap
+        # between two graph launches is not paid once per 0.2 ms step
+        # (graphs longer than a few milliseconds gained nothing and one of 10 x 3.8 ms ran slower).
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        step()
+        t1.record()
+        torch.cuda.synchronize()
+        most = args.graph_steps or max(1, min(10, int(8.0 / max(t0.elapsed_time(t1), 1e-3))))
+        per_graph = next(d for d in range(most, 0, -1) if args.steps % d == 0)
         graph = torch.cuda.CUDAGraph()
         n0 = lib.ftb_launch_count()
         with torch.cuda.graph(graph):
-            step()
-        launches_per_step = lib.ftb_launch_count() - n0
+            for _ in range(per_graph):
+                step()
+        launches_per_step = (lib.ftb_launch_count() - n0) // per_graph
         for _ in range(3):
             graph.replay()
         barrier()
@@ -542,10 +557,11 @@ def main():
     launches0 = lib.ftb_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        if graph is not None:
+    if graph is not None:
+        for _ in range(args.steps // per_graph):
             graph.replay()
-        else:
+    else:
+        for _ in range(args.steps):
             step()
     e1.record()
     torch.cuda.synchronize()
@@ -708,6 +724,7 @@ def main():
             "data": "synthetic (seeded)",
             "config": {"workload": name, "mode": mode, "io_dtype": str(Qd.dtype).replace("torch.", ""),
                        "global_batch": shape["N"] * (1 if seq_parallel else world), "cuda_graph": graph is not None,
+                       "steps_per_graph": per_graph if graph is not None else 0,
                        "sharding": ("sequence split over ranks, all_gather of per-rank states (NCCL) "
                                     "per direction, L/rank=%d" % shape["L"]) if seq_parallel
                        else "(batch, head) units per rank, no collective",

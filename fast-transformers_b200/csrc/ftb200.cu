@@ -174,7 +174,7 @@ struct MmaBatch {
     int dtype = FTB_F32;
     int kind = FTB_KERNEL_MMA_FWD;
     bool after_own_launch = false;   // see mma::launch_t
-    MmaBatch() { b.njobs = 0; b.first_block[0] = 0; b.interleave = 0; }
+    MmaBatch() { b.njobs = 0; b.first_block[0] = 0; b.interleave = 0; b.wait_first = 0; }
 };
 
 // Append one job (a scan, or a state-only sweep when `a` is null) to `batch`.

@@ -137,21 +137,25 @@ static bool supported(int dtype, int64_t Da, int64_t Dc) {
     return Da == 128 && Dc % 128 == 0 && Dc >= 128;
 }
 
-// `after_own_launch`: the launch directly in front of this one in the stream is this library's
-// own (the state-only sweep of the same call).  The grid is then started with programmatic stream
-// serialisation: its blocks may begin while that launch drains and wait for it only where they
-// read what it wrote.
+// Every grid is started with programmatic stream serialisation: its blocks may be placed while
+// the launch in front of it in the stream drains.  `after_own_launch`: that launch is this
+// library's own, of the same call (the state-only sweep): the blocks wait for it only where they
+// read what it wrote.  Otherwise they wait for it before they touch global memory at all
+// (ScanBatch::wait_first), which is safe behind any kernel and overlaps the block set-up only.
 template <typename T, int DA, int DCT>
-static cudaError_t launch_t(const ScanBatch &batch, cudaStream_t st, bool after_own_launch) {
+static cudaError_t launch_t(ScanBatch &batch, cudaStream_t st, bool after_own_launch) {
     using K = Cfg<T, DA, DCT>;
     auto kern = mma_scan_kernel<T, DA, DCT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)K::SMEM);
     if (e != cudaSuccess) return e;
     static const char *no_pdl = std::getenv("FTB200_NO_PDL");
-    if (!after_own_launch || no_pdl) {
+    static const char *late_only = std::getenv("FTB200_PDL_OWN_ONLY");
+    batch.wait_first = 0;
+    if (no_pdl || (late_only && !after_own_launch)) {
         kern<<<(unsigned)batch.first_block[batch.njobs], NTHREADS, K::SMEM, st>>>(batch);
         return cudaGetLastError();
     }
+    batch.wait_first = after_own_launch ? 0 : 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)batch.first_block[batch.njobs]);
     cfg.blockDim = dim3(NTHREADS);

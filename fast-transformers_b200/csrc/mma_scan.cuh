@@ -104,6 +104,11 @@ struct ScanBatch {
     int first_block[MAX_JOBS + 1];
     int njobs;
     int interleave;   // jobs have equal block counts: block i belongs to job i % njobs
+    // Programmatic stream serialisation.  0: the launch in front is this call's own (or the launch
+    // is an ordinary one): blocks start at once and wait only where they read that launch's totals.
+    // 1: the launch in front may be anybody's: every block waits for it before its first access to
+    // global memory, and only its set-up (barriers, tensor memory) overlaps the other grid's tail.
+    int wait_first;
 };
 
 // ---- small PTX wrappers -------------------------------------------------------------------
@@ -388,7 +393,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
     }
     // let a grid launched behind this one with programmatic stream serialisation start as SMs
     // become free (it waits for this grid's results where it needs them)
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!batch.wait_first) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const ScanJob &J = batch.job[job];
     const ScanParams &p = J.p;
     const CUtensorMap &map_a = J.ma, &map_b = J.mb, &map_bmn = J.mbmn, &map_c = J.mc;
@@ -431,6 +436,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
         // before the roles: at the end of the kernel it kept the block's coordinates alive
         // through every loop and cost the bf16 scan a tenth of its speed.)
         float *dst = p.state_out + ((int64_t)bh * p.nseg + seg) * ((int64_t)DA * p.Dc);
+        if (batch.wait_first) asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int e = threadIdx.x; e < DA * DCT; e += NTHREADS)
             dst[(int64_t)(e / DCT) * p.Dc + n0 + e % DCT] = 0.f;
     }
@@ -472,6 +478,13 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    if (batch.wait_first) {
+        // Nothing above touched global memory.  From here on the grid in front has finished (and,
+        // through its own last wait, every grid before it); only now may a grid behind this one
+        // start, so that it never runs ahead of a launch that is not this library's.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
 #ifdef FTB_TIMESTAMPS
     if (threadIdx.x == 0 && blockIdx.x < 1024) g_cta[4 * blockIdx.x + 2] = ts_globaltimer();
 #endif
