@@ -2,8 +2,10 @@
 the registry by name.
 
 Mirror of ``fast_transformers/builders`` for the encoder path: ``BaseBuilder``
-(``base.py:10-67``), ``AttentionBuilder`` (``attention_builders.py:15-121``) and
-``TransformerEncoderBuilder`` (``transformer_builders.py:24-286``).  Kept behaviours:
+(``base.py:10-67``), ``AttentionBuilder`` / ``RecurrentAttentionBuilder``
+(``attention_builders.py:15-130``), ``TransformerEncoderBuilder`` and ``RecurrentEncoderBuilder``
+(``transformer_builders.py:24-320``; same parameters, the recurrent one assembles the
+one-position-at-a-time classes from the recurrent registry).  Kept behaviours:
 attribute-style parameters; unknown keys raise ``ValueError`` from ``from_kwargs`` /
 ``from_dictionary`` unless ``strict=False`` (``from_namespace`` defaults to non-strict);
 attributes that are not builder properties are forwarded to the attention builder, which
@@ -17,7 +19,10 @@ from collections import defaultdict
 from torch.nn import LayerNorm
 
 from ..attention import AttentionLayer
-from ..attention_registry import AttentionRegistry
+from ..attention_registry import AttentionRegistry, RecurrentAttentionRegistry
+from ..recurrent.attention import RecurrentAttentionLayer
+from ..recurrent.transformers import (RecurrentTransformerEncoder,
+                                      RecurrentTransformerEncoderLayer)
 from ..transformers import TransformerEncoder, TransformerEncoderLayer
 
 
@@ -95,6 +100,11 @@ class AttentionBuilder(BaseAttentionBuilder):
         super().__init__(AttentionRegistry)
 
 
+class RecurrentAttentionBuilder(BaseAttentionBuilder):
+    def __init__(self):
+        super().__init__(RecurrentAttentionRegistry)
+
+
 class TransformerEncoderBuilder(BaseBuilder):
     """``TransformerEncoderBuilder.from_kwargs(n_layers=..., attention_type="causal-linear",
     ...).get()`` returns a ``TransformerEncoder``."""
@@ -102,6 +112,11 @@ class TransformerEncoderBuilder(BaseBuilder):
     _PROPERTIES = ("n_layers", "n_heads", "feed_forward_dimensions", "query_dimensions",
                    "value_dimensions", "model_dimensions", "dropout", "activation",
                    "final_normalization", "event_dispatcher", "attention_type")
+    # what get() assembles (transformer_builders.py:166-181: the _get_*_class hooks)
+    _ATTENTION_BUILDER = AttentionBuilder
+    _ATTENTION_LAYER = AttentionLayer
+    _ENCODER_LAYER = TransformerEncoderLayer
+    _ENCODER = TransformerEncoder
 
     def __init__(self):
         self._n_layers = 4
@@ -114,7 +129,7 @@ class TransformerEncoderBuilder(BaseBuilder):
         self._activation = "relu"
         self._final_norm = True
         self._event_dispatcher = ""
-        self._attention_builder = AttentionBuilder()
+        self._attention_builder = self._ATTENTION_BUILDER()
         self._attention_type = "full"
 
     # plain parameters -----------------------------------------------------------------
@@ -191,8 +206,8 @@ class TransformerEncoderBuilder(BaseBuilder):
         self.attention.event_dispatcher = self.event_dispatcher
         d_model = self.model_dimensions
         layers = [
-            TransformerEncoderLayer(
-                AttentionLayer(
+            self._ENCODER_LAYER(
+                self._ATTENTION_LAYER(
                     self.attention.get(self.attention_type), d_model, self.n_heads,
                     d_keys=self.query_dimensions, d_values=self.value_dimensions,
                     event_dispatcher=self.event_dispatcher),
@@ -201,4 +216,16 @@ class TransformerEncoderBuilder(BaseBuilder):
             for _ in range(self.n_layers)
         ]
         norm = LayerNorm(d_model) if self.final_normalization else None
-        return TransformerEncoder(layers, norm, event_dispatcher=self.event_dispatcher)
+        return self._ENCODER(layers, norm, event_dispatcher=self.event_dispatcher)
+
+
+class RecurrentEncoderBuilder(TransformerEncoderBuilder):
+    """``RecurrentEncoderBuilder.from_kwargs(attention_type="causal-linear", ...).get()`` returns a
+    ``RecurrentTransformerEncoder``: the same parameters and the same weights as the batch
+    encoder (``load_state_dict`` of one into the other), evaluated one position at a time
+    (``transformer_builders.py:289-320``)."""
+
+    _ATTENTION_BUILDER = RecurrentAttentionBuilder
+    _ATTENTION_LAYER = RecurrentAttentionLayer
+    _ENCODER_LAYER = RecurrentTransformerEncoderLayer
+    _ENCODER = RecurrentTransformerEncoder

@@ -103,22 +103,76 @@ class RecurrentLinearAttention(Module):
         V = recurrent_linear_step(Q, K, value, Si, Zi, self.eps, elu_plus_one=fused)
         return V, [Si, Zi]
 
-    @torch.no_grad()
-    def state_after(self, keys, values, key_lengths=None):
-        """The state ``[S, z]`` after a whole prefix processed in batch form: ``keys`` (N,L,H,E)
-        and ``values`` (N,L,H,M) as ``CausalLinearAttention`` takes them.  Steps of this module
-        continue the sequence from there (prefill in batch form, then decode token by token)."""
+    def _state_of(self, keys, values, key_lengths):
         from ....causal_product import causal_state_sum
-        self.feature_map.new_feature_map(keys.device)
         K = self.feature_map.forward_keys(keys)
         if key_lengths is not None:
             K = K * key_lengths.float_matrix[:, :, None, None]
         S = causal_state_sum(K.permute(0, 2, 1, 3), values.permute(0, 2, 1, 3), mode="fp32")
         return [S, K.sum(dim=1).float().contiguous()]
 
+    @torch.no_grad()
+    def state_after(self, keys, values, key_lengths=None):
+        """The state ``[S, z]`` after a whole prefix processed in batch form: ``keys`` (N,L,H,E)
+        and ``values`` (N,L,H,M) as ``CausalLinearAttention`` takes them.  Steps of this module
+        continue the sequence from there (prefill in batch form, then decode token by token)."""
+        self.feature_map.new_feature_map(keys.device)
+        return self._state_of(keys, values, key_lengths)
+
+    @torch.no_grad()
+    def prefill(self, queries, keys, values, key_lengths=None):
+        """A whole prefix in batch form: ``queries``, ``keys`` (N,L,H,E) and ``values`` (N,L,H,M).
+        Returns what ``CausalLinearAttention`` gives for it, (N,L,H,M), and the state ``[S, z]``
+        after it, both under ONE draw of a random feature map (``new_feature_map`` is called
+        once, as at the first step of a sequence, :64-66 of the reference module)."""
+        from ....attention.causal_linear_attention import CausalLinearAttention
+        from ....masking import LengthMask, TriangularCausalMask
+        N, L = queries.shape[0], queries.shape[1]
+        if key_lengths is None:
+            key_lengths = LengthMask(queries.new_full((N,), L, dtype=torch.int64))
+        self.feature_map.new_feature_map(queries.device)
+        same_map = _SameFeatureMap(self.feature_map)
+        batch = CausalLinearAttention(queries.shape[3], feature_map=lambda dims: same_map,
+                                      eps=self.eps, event_dispatcher=self.event_dispatcher)
+        out = batch(queries, keys, values, TriangularCausalMask(L, device=queries.device),
+                    key_lengths, key_lengths)
+        return out, self._state_of(keys, values, key_lengths)
+
+
+class _SameFeatureMap(object):
+    """An attention's feature map as the batch layer sees it during ``prefill``: the same
+    parameters, and no resampling when the layer starts its forward pass."""
+
+    def __init__(self, feature_map):
+        self._feature_map = feature_map
+
+    def new_feature_map(self, device):
+        return
+
+    def forward_queries(self, x):
+        return self._feature_map.forward_queries(x)
+
+    def forward_keys(self, x):
+        return self._feature_map.forward_keys(x)
+
+    @property
+    def activation_function(self):
+        # lets the batch layer recognise the default map and use its native elu(x) + 1 pass
+        return getattr(self._feature_map, "activation_function", None)
+
 
 RecurrentAttentionRegistry.register(
     "linear", RecurrentLinearAttention,
+    [
+        ("query_dimensions", Int),
+        ("feature_map", Optional(Callable)),
+        ("event_dispatcher", Optional(EventDispatcherInstance, ""))
+    ]
+)
+# the reference registers the same class under the causal layer's name as well
+# (recurrent/attention/self_attention/linear_attention.py:103-110)
+RecurrentAttentionRegistry.register(
+    "causal-linear", RecurrentLinearAttention,
     [
         ("query_dimensions", Int),
         ("feature_map", Optional(Callable)),

@@ -187,6 +187,7 @@ def test_recurrent_registry_entry_and_host_checks():
     assert "linear" in RecurrentAttentionRegistry.keys
     cls, params = RecurrentAttentionRegistry["linear"]
     assert cls is RecurrentLinearAttention
+    assert RecurrentAttentionRegistry["causal-linear"][0] is RecurrentLinearAttention
     assert params == ["query_dimensions", "feature_map", "event_dispatcher"]
     with warnings.catch_warnings(record=True) as w:
         warnings.simplefilter("always")
