@@ -142,6 +142,8 @@ static bool supported(int dtype, int64_t Da, int64_t Dc) {
 // library's own, of the same call (the state-only sweep): the blocks wait for it only where they
 // read what it wrote.  Otherwise they wait for it before they touch global memory at all
 // (ScanBatch::wait_first), which is safe behind any kernel and overlaps the block set-up only.
+// Environment (tuning and fault finding): FTB200_NO_PDL=1 ordinary launches throughout,
+// FTB200_PDL_OWN_ONLY=1 ordinary launches for the first grid of a call.
 template <typename T, int DA, int DCT>
 static cudaError_t launch_t(ScanBatch &batch, cudaStream_t st, bool after_own_launch) {
     using K = Cfg<T, DA, DCT>;
@@ -166,7 +168,13 @@ static cudaError_t launch_t(ScanBatch &batch, cudaStream_t st, bool after_own_la
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, batch);
+    e = cudaLaunchKernelEx(&cfg, kern, batch);
+    if (e == cudaSuccess) return e;
+    // a context that does not take the attribute: the same grid as an ordinary launch
+    (void)cudaGetLastError();
+    batch.wait_first = 0;
+    kern<<<(unsigned)batch.first_block[batch.njobs], NTHREADS, K::SMEM, st>>>(batch);
+    return cudaGetLastError();
 }
 
 }  // namespace mma

@@ -29,6 +29,11 @@
  *     up to 512) or FTB_MODE_MMA (tcgen05 tensor cores: TF32 operands for fp32 I/O, bf16
  *     operands for bf16 I/O, fp32 accumulation and fp32 running state).
  *   - `stream` is a cudaStream_t passed as void*; work is enqueued, not synchronised.
+ *     FTB_MODE_MMA grids are launched with programmatic stream serialisation: their blocks
+ *     may be placed on SMs while the kernel in front of them in the stream drains, but the
+ *     first grid of a call touches no global memory before that kernel has completed, so
+ *     the ordering a caller observes is that of ordinary launches (also under stream
+ *     capture).  FTB200_NO_PDL=1 in the environment selects ordinary launches.
  *   - `workspace` is caller-provided scratch of at least ftb_causal_workspace_bytes(...)
  *     bytes, 256-byte aligned; it may be NULL when that function returns 0.
  *   - Return value: FTB_OK or one of the error codes below.  Nothing is enqueued when an
