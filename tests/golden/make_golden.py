@@ -197,9 +197,50 @@ def recurrent():
     print("recurrent.npz", os.path.getsize(os.path.join(HERE, "recurrent.npz")), "bytes")
 
 
+def recurrent_encoder():
+    """``recurrent_encoder.npz``: the reference's ``RecurrentTransformerEncoder`` (two layers of
+    ``RecurrentTransformerEncoderLayer(RecurrentAttentionLayer(RecurrentLinearAttention))``, final
+    LayerNorm) stepped over a short sequence: its weights, the inputs, every output and the
+    per-layer states after the 7th and after the last position."""
+    rla = import_reference_recurrent()
+    import fast_transformers.recurrent.attention.self_attention.attention_layer as ral
+    import fast_transformers.recurrent.transformers as rtr
+    torch.set_num_threads(1)
+    torch.manual_seed(707)
+    heads, dq, d_model, d_ff, N, L, P = 4, 16, 64, 96, 3, 12, 7
+    enc = rtr.RecurrentTransformerEncoder(
+        [rtr.RecurrentTransformerEncoderLayer(
+            ral.RecurrentAttentionLayer(rla.RecurrentLinearAttention(dq), d_model, heads,
+                                        d_keys=dq, d_values=dq),
+            d_model, d_ff, dropout=0.0, activation="gelu")
+         for _ in range(2)],
+        torch.nn.LayerNorm(d_model)).eval()
+    x = torch.randn(N, L, d_model, generator=torch.Generator().manual_seed(708))
+    blob = {"sd__" + k: np_(v) for k, v in enc.state_dict().items()}
+    blob["x"] = np_(x)
+    with torch.no_grad():
+        state, ys = None, []
+        for i in range(L):
+            y, state = enc(x[:, i], state)
+            ys.append(y)
+            if i in (P - 1, L - 1):
+                tag = "mid" if i == P - 1 else "end"
+                for layer, (S, z) in enumerate(state):
+                    # copies: the reference updates the state tensors in place on the next step
+                    blob["%s_S%d" % (tag, layer)] = np_(S.clone())
+                    blob["%s_z%d" % (tag, layer)] = np_(z.clone())
+    blob["y"] = np_(torch.stack(ys, 1))
+    blob["prefix"] = np.int64(P)
+    np.savez_compressed(os.path.join(HERE, "recurrent_encoder.npz"), **blob)
+    print("recurrent_encoder.npz", os.path.getsize(os.path.join(HERE, "recurrent_encoder.npz")), "bytes")
+
+
 if __name__ == "__main__":
     if sys.argv[1:] == ["recurrent"]:
         recurrent()
+    elif sys.argv[1:] == ["recurrent_encoder"]:
+        recurrent_encoder()
     else:
         main()
         recurrent()
+        recurrent_encoder()

@@ -5,6 +5,7 @@ is under test is everything around them: head splitting, residuals and norms, wh
 which layer, the hand-over from ``prefill`` to the steps, and the interchange of weights with the
 batch encoder.  Method of the reference's tests/recurrent/test_transformer_encoder.py (batch
 model against the recurrent model on the same weights)."""
+import numpy as np
 import pytest
 import torch
 
@@ -121,3 +122,42 @@ def test_memory_is_the_old_name_of_state(oracle_kernels):
             y1, _ = rec(x, memory=[[t.clone() for t in s] for s in state])
         y2, _ = rec(x, state)
     assert torch.equal(y1, y2)
+
+
+def _golden_model(g):
+    model = RecurrentEncoderBuilder.from_kwargs(
+        n_layers=2, n_heads=4, query_dimensions=16, value_dimensions=16,
+        feed_forward_dimensions=96, activation="gelu", dropout=0.0,
+        attention_type="causal-linear").get().eval()
+    model.load_state_dict({k[4:]: torch.from_numpy(np.asarray(g[k])) for k in g.files
+                           if k.startswith("sd__")})
+    return model
+
+
+@torch.no_grad()
+def test_against_the_reference_recurrent_encoder(oracle_kernels, golden):
+    """Weights, inputs, outputs and states of the reference's RecurrentTransformerEncoder
+    (tests/golden/make_golden.py, ``recurrent_encoder``): token by token, and with the first
+    ``prefix`` positions handed over by ``prefill``."""
+    g = golden("recurrent_encoder")
+    T = lambda name: torch.from_numpy(np.asarray(g[name]))     # noqa: E731
+    model, x, want, P = _golden_model(g), T("x"), T("y"), int(g["prefix"])
+    state, ys = None, []
+    for i in range(x.shape[1]):
+        y, state = model(x[:, i], state)
+        ys.append(y)
+    assert orc.rel_err(torch.stack(ys, 1), want) < 1e-5
+    for layer, (S, z) in enumerate(state):
+        assert orc.rel_err(S, T("end_S%d" % layer)) < 1e-5
+        assert orc.rel_err(z, T("end_z%d" % layer)) < 1e-5
+
+    y0, state = model.prefill(x[:, :P])
+    assert orc.rel_err(y0, want[:, :P]) < 1e-5
+    for layer, (S, z) in enumerate(state):
+        assert orc.rel_err(S, T("mid_S%d" % layer)) < 1e-5
+        assert orc.rel_err(z, T("mid_z%d" % layer)) < 1e-5
+    ys = []
+    for i in range(P, x.shape[1]):
+        y, state = model(x[:, i], state)
+        ys.append(y)
+    assert orc.rel_err(torch.stack(ys, 1), want[:, P:]) < 1e-5

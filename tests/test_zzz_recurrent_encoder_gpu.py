@@ -2,6 +2,7 @@
 with the same weights (the method of the reference's tests/recurrent/test_transformer_encoder.py),
 token by token from the start and after a prompt handed over by ``prefill``.  The file name sorts
 after the kernel tests: it composes what they check one by one (batch layer, state sum, step)."""
+import numpy as np
 import pytest
 import torch
 
@@ -77,3 +78,34 @@ def test_prefill_with_prompts_of_different_lengths():
     for s_all, s_short in zip(state, short):
         assert orc.rel_err(s_all[0][1:], s_short[0]) < 1e-5
         assert orc.rel_err(s_all[1][1:], s_short[1]) < 1e-5
+
+
+@torch.no_grad()
+def test_against_the_reference_recurrent_encoder(golden):
+    """The reference's RecurrentTransformerEncoder on the same weights and inputs
+    (tests/golden/make_golden.py, ``recurrent_encoder``): outputs and per-layer states, token by
+    token and with the first ``prefix`` positions handed over by ``prefill``."""
+    g = golden("recurrent_encoder")
+    T = lambda name: torch.from_numpy(np.asarray(g[name])).cuda()     # noqa: E731
+    model = RecurrentEncoderBuilder.from_kwargs(
+        n_layers=2, n_heads=4, query_dimensions=16, value_dimensions=16,
+        feed_forward_dimensions=96, activation="gelu", dropout=0.0,
+        attention_type="causal-linear").get().eval()
+    model.load_state_dict({k[4:]: torch.from_numpy(np.asarray(g[k])) for k in g.files
+                           if k.startswith("sd__")})
+    model = model.cuda()
+    x, want, P = T("x"), T("y"), int(g["prefix"])
+    state, ys = None, []
+    for i in range(x.shape[1]):
+        y, state = model(x[:, i], state)
+        ys.append(y)
+    assert orc.rel_err(torch.stack(ys, 1), want) < 1e-4
+    for layer, (S, z) in enumerate(state):
+        assert orc.rel_err(S, T("end_S%d" % layer)) < 1e-4
+        assert orc.rel_err(z, T("end_z%d" % layer)) < 1e-4
+    with ftb.mode("fp32"):
+        y0, state = model.prefill(x[:, :P])
+    assert orc.rel_err(y0, want[:, :P]) < 1e-4
+    for layer, (S, z) in enumerate(state):
+        assert orc.rel_err(S, T("mid_S%d" % layer)) < 1e-4
+        assert orc.rel_err(z, T("mid_z%d" % layer)) < 1e-4
