@@ -537,12 +537,15 @@ def main():
         # the graph holds as many whole steps as divide --steps (at most 10), so that the gap
         # between two graph launches is not paid once per 0.2 ms step
         # (graphs longer than a few milliseconds gained nothing and one of 10 x 3.8 ms ran slower).
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        step()
-        t1.record()
-        torch.cuda.synchronize()
-        most = args.graph_steps or max(1, min(10, int(8.0 / max(t0.elapsed_time(t1), 1e-3))))
+        eager_ms = []
+        for _ in range(3):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            step()
+            t1.record()
+            torch.cuda.synchronize()
+            eager_ms.append(t0.elapsed_time(t1))
+        most = args.graph_steps or max(1, min(10, int(8.0 / max(min(eager_ms), 1e-3))))
         per_graph = next(d for d in range(most, 0, -1) if args.steps % d == 0)
         graph = torch.cuda.CUDAGraph()
         n0 = lib.ftb_launch_count()
