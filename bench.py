@@ -49,6 +49,9 @@ def parse():
     ap.add_argument("--no-other-mode", action="store_true",
                     help="skip the few eager steps in the other arithmetic mode")
     ap.add_argument("--no-graph", action="store_true", help="time eager calls, not a CUDA graph")
+    ap.add_argument("--exchange", choices=["nccl", "peer"], default="nccl",
+                    help="config 4 on several GPUs: how the per-rank states travel (all_gather, "
+                         "or stores into the peers' buffers by this library's own kernels)")
     ap.add_argument("--graph-steps", type=int, default=0,
                     help="steps captured per CUDA graph (default: the largest divisor of --steps that keeps "
                          "the graph under about 8 ms, at most 10)")
@@ -502,12 +505,17 @@ def main():
         from fast_transformers_b200.sequence_parallel import (LocalOps,
                                                               sequence_parallel_causal_dot_product)
         sp_ops = LocalOps(mode)
+        sp_exchange = None
+        if args.exchange == "peer":
+            from fast_transformers_b200.sequence_parallel import PeerExchange
+            sp_exchange = PeerExchange((shape["N"], shape["H"], shape["D"], shape["M"]))
 
     def step():
         Qd.grad = Kd.grad = Vd.grad = None
         with ftb.mode(mode):
             if seq_parallel:
-                out = sequence_parallel_causal_dot_product(Qd, Kd, Vd, ops=sp_ops)
+                out = sequence_parallel_causal_dot_product(Qd, Kd, Vd, ops=sp_ops,
+                                                           exchange=sp_exchange)
             else:
                 out = causal_dot_product(Qd, Kd, Vd)
             out.backward(Gd)
@@ -654,7 +662,8 @@ def main():
             q, k, v = (d.detach().requires_grad_(True) for d in (dq_, dk_, dv_))
             with ftb.mode(mode):
                 if seq_parallel:
-                    out = sequence_parallel_causal_dot_product(q, k, v, ops=sp_ops)
+                    out = sequence_parallel_causal_dot_product(q, k, v, ops=sp_ops,
+                                                               exchange=sp_exchange)
                 else:
                     out = causal_dot_product(q, k, v)
                 out.backward(dg_)
@@ -728,8 +737,10 @@ def main():
             "config": {"workload": name, "mode": mode, "io_dtype": str(Qd.dtype).replace("torch.", ""),
                        "global_batch": shape["N"] * (1 if seq_parallel else world), "cuda_graph": graph is not None,
                        "steps_per_graph": per_graph if graph is not None else 0,
-                       "sharding": ("sequence split over ranks, all_gather of per-rank states (NCCL) "
-                                    "per direction, L/rank=%d" % shape["L"]) if seq_parallel
+                       "sharding": ("sequence split over ranks, %s per direction, L/rank=%d" % (
+                           "per-rank states stored into the peers' buffers (own kernels)"
+                           if args.exchange == "peer" else "all_gather of per-rank states (NCCL)",
+                           shape["L"])) if seq_parallel
                        else "(batch, head) units per rank, no collective",
                        "l2": "inputs+outputs per step (%.0f MB) exceed the 126 MB L2; no flush" %
                              (step_alg_bytes / 1e6)},
@@ -738,6 +749,8 @@ def main():
             "tolerance_vs_fp64": 1e-5 if mode == "fp32" else 2e-2,
         }
         print(json.dumps(line))
+    if seq_parallel and sp_exchange is not None:
+        sp_exchange.close()
     if dist is not None:
         dist.destroy_process_group()
     return 0

@@ -26,9 +26,12 @@ EXPORTS = (
     "ftb_causal_dot_product_static", "ftb_recurrent_linear_step",
     "ftb_causal_normaliser_workspace_bytes", "ftb_causal_normaliser", "ftb_causal_normaliser_backward",
     "ftb_elu_feature_map", "ftb_elu_feature_map_backward",
+    "ftb_exchange_bytes", "ftb_exchange_create", "ftb_exchange_open", "ftb_exchange_close",
+    "ftb_exchange_destroy", "ftb_exchange_push", "ftb_exchange_receive",
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
-                "mma_bwd_qr", "mma_bwd_multi", "recurrent_step", "normaliser", "feature_map")
+                "mma_bwd_qr", "mma_bwd_multi", "recurrent_step", "normaliser", "feature_map",
+                "rank_exchange")
 
 _lib = None
 _i64, _vp, _int, _sz = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
@@ -84,6 +87,20 @@ def lib():
     L.ftb_elu_feature_map.argtypes = [_vp, _vp, _vp, _i64, _i64, _int, _vp]
     L.ftb_elu_feature_map_backward.restype = _int
     L.ftb_elu_feature_map_backward.argtypes = [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp]
+    L.ftb_exchange_bytes.restype = _sz
+    L.ftb_exchange_bytes.argtypes = [_int, _i64]
+    L.ftb_exchange_create.restype = _int
+    L.ftb_exchange_create.argtypes = [_int, _i64, ctypes.POINTER(_vp), ctypes.c_char_p]
+    L.ftb_exchange_open.restype = _int
+    L.ftb_exchange_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(_vp)]
+    L.ftb_exchange_close.restype = _int
+    L.ftb_exchange_close.argtypes = [_vp]
+    L.ftb_exchange_destroy.restype = _int
+    L.ftb_exchange_destroy.argtypes = [_vp]
+    L.ftb_exchange_push.restype = _int
+    L.ftb_exchange_push.argtypes = [_vp, _i64, ctypes.POINTER(_vp), _int, _int, _int, _vp]
+    L.ftb_exchange_receive.restype = _int
+    L.ftb_exchange_receive.argtypes = [_vp, _vp, _i64, _int, _int, _int, _vp]
     L.ftb_launch_count.restype = ctypes.c_uint64
     L.ftb_device_status.restype = _int
     L.ftb_device_status.argtypes = [_int]
@@ -105,6 +122,7 @@ def timing_read():
 
 
 FEATURE_NONE, FEATURE_ELU1 = 0, 1
+EXCHANGE_HANDLE_BYTES = 64
 
 
 def strides2(t):

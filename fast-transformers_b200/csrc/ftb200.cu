@@ -4,12 +4,15 @@
 
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
 #include "feature_map.cuh"
 #include "mma_host.cuh"
+#include "rank_exchange.cuh"
 #include "recurrent_step.cuh"
 #include "simt_scan.cuh"
 
@@ -986,6 +989,103 @@ int ftb_causal_dot_product_static(const void *q, const void *k, const void *v, v
     // array during a call was written earlier in the same call, so stale contents are harmless.
     return ftb_causal_dot_product(q, k, v, out, N, H, L, D, M, qs, ks, vs, os, dtype, mode, nullptr,
                                   nullptr, 0, scratch, (size_t)FTB_STATIC_SCRATCH_BYTES, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Exchange of per-rank states between the GPUs of one node (csrc/rank_exchange.cuh).
+// ---------------------------------------------------------------------------------------------
+static int exchange_check(int world, int64_t elems) {
+    if (world < 1 || elems < 0) return FTB_ERR_INVALID;
+    if (world > xchg::kMaxRanks) return FTB_ERR_UNSUPPORTED;
+    if (elems % 4) return FTB_ERR_ALIGNMENT;   // moved 16 bytes at a time
+    return FTB_OK;
+}
+
+size_t ftb_exchange_bytes(int world, int64_t elems) {
+    if (exchange_check(world, elems) != FTB_OK) return 0;
+    return xchg::layout(world, elems).bytes;
+}
+
+int ftb_exchange_create(int world, int64_t elems, void **buffer, unsigned char *handle) {
+    if (!buffer || !handle) return FTB_ERR_INVALID;
+    int rc = exchange_check(world, elems);
+    if (rc) return rc;
+    static_assert(sizeof(cudaIpcMemHandle_t) == FTB_EXCHANGE_HANDLE_BYTES, "IPC handle size");
+    const size_t bytes = xchg::layout(world, elems).bytes;
+    void *p = nullptr;
+    FTB_CUDA(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        FTB_CUDA(e);
+    }
+    std::memcpy(handle, &h, sizeof(h));
+    *buffer = p;
+    return FTB_OK;
+}
+
+int ftb_exchange_open(const unsigned char *handle, void **peer_buffer) {
+    if (!handle || !peer_buffer) return FTB_ERR_INVALID;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    FTB_CUDA(cudaIpcOpenMemHandle(peer_buffer, h, cudaIpcMemLazyEnablePeerAccess));
+    return FTB_OK;
+}
+
+int ftb_exchange_close(void *peer_buffer) {
+    if (!peer_buffer) return FTB_ERR_INVALID;
+    FTB_CUDA(cudaIpcCloseMemHandle(peer_buffer));
+    return FTB_OK;
+}
+
+int ftb_exchange_destroy(void *buffer) {
+    if (!buffer) return FTB_ERR_INVALID;
+    FTB_CUDA(cudaFree(buffer));
+    return FTB_OK;
+}
+
+int ftb_exchange_push(const float *state, int64_t elems, void *const *buffers, int rank, int world,
+                      int reverse, void *stream) {
+    int rc = exchange_check(world, elems);
+    if (rc) return rc;
+    if (!buffers || rank < 0 || rank >= world || (elems > 0 && !state)) return FTB_ERR_INVALID;
+    if ((uintptr_t)state & 15) return FTB_ERR_ALIGNMENT;
+    xchg::Peers peers;
+    for (int r = 0; r < xchg::kMaxRanks; ++r) peers.buf[r] = r < world ? buffers[r] : nullptr;
+    for (int r = 0; r < world; ++r)
+        if (!peers.buf[r]) return FTB_ERR_INVALID;
+    const int targets = reverse ? rank : world - 1 - rank;
+    const int64_t n4 = elems / 4;
+    int64_t per_target = (n4 + (int64_t)xchg::kThreads * 4 - 1) / ((int64_t)xchg::kThreads * 4);
+    per_target = std::max<int64_t>(1, std::min<int64_t>(per_target, 32));
+    const dim3 grid(targets ? (unsigned)per_target : 1u, targets ? (unsigned)targets : 1u);
+    cudaStream_t st = (cudaStream_t)stream;
+    LaunchScope scope(FTB_KERNEL_RANK_EXCHANGE, st);
+    xchg::push_kernel<<<grid, xchg::kThreads, 0, st>>>(state, elems, peers, rank, world, reverse ? 1 : 0);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+
+int ftb_exchange_receive(void *buffer, float *out, int64_t elems, int rank, int world, int reverse,
+                         void *stream) {
+    int rc = exchange_check(world, elems);
+    if (rc) return rc;
+    if (!buffer || rank < 0 || rank >= world || (elems > 0 && !out)) return FTB_ERR_INVALID;
+    if ((uintptr_t)out & 15) return FTB_ERR_ALIGNMENT;
+    int *status = nullptr;
+    FTB_CUDA(cudaGetSymbolAddress((void **)&status, mma::g_device_status));
+    const int64_t n4 = elems / 4;
+    int64_t blocks = (n4 + (int64_t)xchg::kThreads * 2 - 1) / ((int64_t)xchg::kThreads * 2);
+    blocks = std::max<int64_t>(1, std::min<int64_t>(blocks, 148));
+    cudaStream_t st = (cudaStream_t)stream;
+    LaunchScope scope(FTB_KERNEL_RANK_EXCHANGE, st);
+    xchg::receive_kernel<<<(unsigned)blocks, xchg::kThreads, 0, st>>>(buffer, out, elems, rank, world,
+                                                                      reverse ? 1 : 0, status);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
 }
 
 }  // extern "C"

@@ -18,7 +18,14 @@ reference is single-device and has no counterpart; the recurrence that is being 
 
 The three local operations are injectable so the host logic (which rank adds what, autograd
 wiring, failure behaviour) can be exercised without a GPU.
+
+``PeerExchange`` is the same exclusive prefix / suffix without a library collective: the ranks
+of one node store their states into each other's buffers (peer memory mapped through CUDA IPC)
+and a small kernel adds up what has arrived -- two launches per direction, no host
+synchronisation, nothing that a CUDA graph cannot hold.  Pass it as ``exchange=``.
 """
+import ctypes
+
 import torch
 import torch.distributed as dist
 
@@ -86,14 +93,101 @@ def exclusive_scan_over_ranks(local, group=None, reverse=False):
     return part.sum(dim=0)
 
 
+class PeerExchange(object):
+    """``exclusive_scan_over_ranks`` for states of one fixed shape, over peer memory instead of
+    ``all_gather``: ``ftb_exchange_push`` + ``ftb_exchange_receive`` on the current stream.
+
+    All ranks of ``group`` must be processes of ONE node, each on a GPU of its own, and must
+    construct, use (same order of calls) and ``close`` the object together; construction and
+    ``close`` contain host collectives (the exchange of the buffers' IPC handles, barriers).
+    A rank that never delivers makes the others' receive give up after about a second: the
+    result is then not written and ``ftb_device_status`` reports the timeout (checked by
+    ``check()``, which synchronises)."""
+
+    def __init__(self, state_shape, group=None, device=None):
+        from . import _native
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        self._lib = _native.lib()
+        self._native = _native
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.shape = tuple(int(d) for d in state_shape)
+        self.elems = 1
+        for d in self.shape:
+            self.elems *= d
+        self.device = (torch.device(device) if device is not None
+                       else torch.device("cuda", torch.cuda.current_device()))
+        self._own = ctypes.c_void_p()
+        self._peers = [None] * self.world
+        handle = ctypes.create_string_buffer(_native.EXCHANGE_HANDLE_BYTES)
+        with torch.cuda.device(self.device):
+            _native.check(self._lib.ftb_exchange_create(self.world, self.elems,
+                                                        ctypes.byref(self._own), handle),
+                          "ftb_exchange_create")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self._bufs = (ctypes.c_void_p * self.world)()
+        with torch.cuda.device(self.device):
+            for r in range(self.world):
+                if r == self.rank:
+                    self._bufs[r] = self._own.value
+                    continue
+                ptr = ctypes.c_void_p()
+                _native.check(self._lib.ftb_exchange_open(handles[r], ctypes.byref(ptr)),
+                              "ftb_exchange_open")
+                self._peers[r] = ptr
+                self._bufs[r] = ptr.value
+        dist.barrier(group=group)      # nobody pushes into a buffer that is not mapped everywhere
+
+    def exclusive_scan(self, local, reverse=False):
+        """Sum of ``local`` over the ranks before this one (after it when ``reverse``)."""
+        if self._own is None:
+            raise RuntimeError("this exchange has been closed")
+        if tuple(local.shape) != self.shape or local.dtype != torch.float32 or not local.is_cuda:
+            raise RuntimeError("expected a float32 CUDA state of shape %r" % (self.shape,))
+        local = local.contiguous()
+        out = torch.empty_like(local)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(local.device).cuda_stream)
+        with torch.cuda.device(local.device):
+            self._native.check(self._lib.ftb_exchange_push(
+                ctypes.c_void_p(local.data_ptr()), self.elems, self._bufs, self.rank, self.world,
+                int(bool(reverse)), stream), "ftb_exchange_push")
+            self._native.check(self._lib.ftb_exchange_receive(
+                self._own, ctypes.c_void_p(out.data_ptr()), self.elems, self.rank, self.world,
+                int(bool(reverse)), stream), "ftb_exchange_receive")
+        return out
+
+    def check(self):
+        """Synchronise this device and raise if a receive gave up waiting for a peer."""
+        with torch.cuda.device(self.device):
+            self._native.check(self._lib.ftb_device_status(1), "sequence-parallel exchange")
+
+    def close(self):
+        if self._own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)             # every rank is done with every buffer
+        with torch.cuda.device(self.device):
+            for ptr in self._peers:
+                if ptr is not None:
+                    self._lib.ftb_exchange_close(ptr)
+        dist.barrier(group=self.group)             # every mapping is gone before a buffer is freed
+        with torch.cuda.device(self.device):
+            self._lib.ftb_exchange_destroy(self._own)
+        self._own, self._peers = None, []
+
+
 class SequenceParallelCausalDotProduct(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, Q, K, V, group, ops):
+    def forward(ctx, Q, K, V, group, ops, exchange):
         T, token = ops.state_sum(K.detach(), V.detach(), reverse=False)
-        S_init = exclusive_scan_over_ranks(T, group, reverse=False)
+        S_init = (exchange.exclusive_scan(T, reverse=False) if exchange is not None
+                  else exclusive_scan_over_ranks(T, group, reverse=False))
         out = ops.forward(Q.detach(), K.detach(), V.detach(), S_init, token)
         ctx.save_for_backward(Q, K, V, S_init)
-        ctx.group, ctx.ops, ctx.token = group, ops, token
+        ctx.group, ctx.ops, ctx.token, ctx.exchange = group, ops, token, exchange
         return out
 
     @staticmethod
@@ -101,20 +195,23 @@ class SequenceParallelCausalDotProduct(torch.autograd.Function):
         Q, K, V, S_init = ctx.saved_tensors
         G = grad_out if grad_out.dtype == Q.dtype else grad_out.to(Q.dtype)
         U, bwd_token = ctx.ops.state_sum(Q.detach(), G, reverse=True)
-        R_init = exclusive_scan_over_ranks(U, ctx.group, reverse=True)
+        R_init = (ctx.exchange.exclusive_scan(U, reverse=True) if ctx.exchange is not None
+                  else exclusive_scan_over_ranks(U, ctx.group, reverse=True))
         gq, gk, gv = ctx.ops.backward(Q.detach(), K.detach(), V.detach(), G, S_init, R_init,
                                       ctx.token, bwd_token)
-        return gq, gk, gv, None, None
+        return gq, gk, gv, None, None, None
 
 
-def sequence_parallel_causal_dot_product(Q, K, V, group=None, ops=None):
+def sequence_parallel_causal_dot_product(Q, K, V, group=None, ops=None, exchange=None):
     """``causal_dot_product`` for this rank's slice (N, H, L/P, dim) of a sequence split in rank
     order over ``group``.  Every rank must call it (it contains collectives), in forward and in
     backward.  Errors of the collectives (a rank that never joins: the process group's timeout)
-    surface as exceptions on the host; no kernel waits on another rank."""
+    surface as exceptions on the host; no kernel waits on another rank -- unless ``exchange`` is a
+    ``PeerExchange`` (states of shape (N, H, D, M)), whose receive kernel waits, bounded, for the
+    peers' stores instead of the collective."""
     if not dist.is_initialized():
         raise RuntimeError("torch.distributed is not initialised")
-    return SequenceParallelCausalDotProduct.apply(Q, K, V, group, ops or LocalOps())
+    return SequenceParallelCausalDotProduct.apply(Q, K, V, group, ops or LocalOps(), exchange)
 
 
 def shard_sequence(t, rank, world, dim=2):

@@ -93,7 +93,8 @@ int ftb_last_cuda_error(void);
 #define FTB_KERNEL_RECURRENT_STEP 8 /* one recurrent step                              */
 #define FTB_KERNEL_NORMALISER 9   /* denominator Q . cumsum(K) and its gradients      */
 #define FTB_KERNEL_FEATURE_MAP 10 /* elu(x)+1 (x key-length mask) and its gradient    */
-#define FTB_KERNEL_KINDS 11
+#define FTB_KERNEL_RANK_EXCHANGE 11 /* push / receive of per-rank states over peer memory */
+#define FTB_KERNEL_KINDS 12
 uint64_t ftb_launch_count(void);
 /*
  * Device-side status word of the current device: 0, or the FTB_ERR_* code recorded by a kernel
@@ -240,6 +241,43 @@ int ftb_recurrent_linear_step(const void *q, const void *k, const void *v, float
                               const int64_t *q_strides, const int64_t *k_strides,
                               const int64_t *v_strides, const int64_t *out_strides, int dtype,
                               int feature_map, float eps, void *stream);
+
+/*
+ * Exchange of per-rank states between the GPUs of ONE node without a library collective, for a
+ * sequence split across devices (no counterpart in the reference, which is single device; the
+ * quantity exchanged is the state of ftb_causal_state_sum).  Every rank creates one buffer and
+ * maps the buffers of its peers:
+ *
+ *   ftb_exchange_create   allocates and zeroes the buffer for states of `elems` floats (a multiple
+ *                         of 4) among `world` ranks (<= 16) on the current device and writes its
+ *                         FTB_EXCHANGE_HANDLE_BYTES-byte inter-process handle; synchronous.
+ *   ftb_exchange_open     maps a peer's buffer from its handle (another process of the same node);
+ *                         ftb_exchange_close unmaps it; ftb_exchange_destroy frees the own buffer,
+ *                         after every peer has closed it.
+ *   ftb_exchange_push     stores `state` into the slot of this rank in the buffers of the ranks
+ *                         after it (before it when reverse != 0) and then releases a per-slot
+ *                         counter; `buffers` holds `world` pointers in rank order, this rank's own
+ *                         buffer at [rank].
+ *   ftb_exchange_receive  waits until the ranks before this one (after it when reverse != 0) have
+ *                         delivered, and writes the sum of their states to `out` (zeros when there
+ *                         are none).  The wait is bounded (about a second); on expiry `out` is left
+ *                         unwritten and FTB_ERR_TIMEOUT is recorded in the device status word.
+ *
+ * All ranks must issue the same sequence of push / receive pairs, each rank its push before its
+ * receive on one stream.  The exchange number lives in the buffers and is advanced by the kernels,
+ * so a captured pair can be replayed.  Every rank must be running on a GPU of its own: a receive
+ * waits for kernels of OTHER GPUs only.
+ */
+#define FTB_EXCHANGE_HANDLE_BYTES 64
+size_t ftb_exchange_bytes(int world, int64_t elems);
+int ftb_exchange_create(int world, int64_t elems, void **buffer, unsigned char *handle);
+int ftb_exchange_open(const unsigned char *handle, void **peer_buffer);
+int ftb_exchange_close(void *peer_buffer);
+int ftb_exchange_destroy(void *buffer);
+int ftb_exchange_push(const float *state, int64_t elems, void *const *buffers, int rank, int world,
+                      int reverse, void *stream);
+int ftb_exchange_receive(void *buffer, float *out, int64_t elems, int rank, int world, int reverse,
+                         void *stream);
 
 /*
  * Forward product that allocates nothing (it has no counterpart in the reference, whose kernels

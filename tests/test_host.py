@@ -209,3 +209,15 @@ def test_kernel_kind_table_matches_header():
     assert count == len(_native.KERNEL_KINDS)
     for name, idx in kinds.items():
         assert _native.KERNEL_KINDS[int(idx)] == name.lower()
+
+
+def test_exchange_buffer_size_and_argument_checks():
+    """ftb_exchange_bytes is a pure function of (ranks, state elements): a 512-byte control block,
+    2 x ranks counters rounded up to 256 bytes, 2 x ranks slots; 0 for what the exchange refuses."""
+    lib = _native.lib()
+    assert lib.ftb_exchange_bytes(8, 262144) == 512 + 256 + 2 * 8 * 262144 * 4
+    assert lib.ftb_exchange_bytes(16, 4) == 512 + 256 + 2 * 16 * 4 * 4
+    assert lib.ftb_exchange_bytes(17, 4) == 0          # more than 16 ranks
+    assert lib.ftb_exchange_bytes(2, 6) == 0           # states move 16 bytes at a time
+    assert lib.ftb_exchange_push(None, 4, None, 0, 2, 0, None) == _native.ERR_INVALID
+    assert lib.ftb_exchange_receive(None, None, 4, 0, 2, 0, None) == _native.ERR_INVALID

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, mode, dtype_name, errq):
+def _worker(rank, world, port, mode, dtype_name, errq, peer_exchange=False):
     try:
         sys.path.insert(0, ROOT)
         os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -34,23 +34,43 @@ def _worker(rank, world, port, mode, dtype_name, errq):
         want = (orc.chunked_forward(Q.float(), K.float(), V.float()),) + tuple(
             orc.chunked_backward(Q.float(), K.float(), V.float(), G.float()))
         q, k, v = (sp.shard_sequence(t, rank, world).cuda().requires_grad_(True) for t in (Q, K, V))
+        exchange = sp.PeerExchange((N, H, D, D)) if peer_exchange else None
         with ftb.mode(mode):
-            out = sp.sequence_parallel_causal_dot_product(q, k, v)
-            out.backward(sp.shard_sequence(G, rank, world).cuda())
+            for _ in range(3 if peer_exchange else 1):     # the slots alternate: use both twice
+                q.grad = k.grad = v.grad = None
+                out = sp.sequence_parallel_causal_dot_product(q, k, v, exchange=exchange)
+                out.backward(sp.shard_sequence(G, rank, world).cuda())
         torch.cuda.synchronize()
+        if exchange is not None:
+            exchange.check()
         tol = 1e-5 if (mode == "fp32" and dtype == torch.float32) else 2e-2
         for name, a, b in zip(("out", "gQ", "gK", "gV"), (out, q.grad, k.grad, v.grad), want):
             # error relative to the largest magnitude of the WHOLE tensor, as everywhere else
             ref = sp.shard_sequence(b, rank, world)
             err = (a.double().cpu() - ref).abs().max().item() / b.abs().max().item()
             assert err < tol, "%s rank %d: %.3e" % (name, rank, err)
+        if exchange is not None:
+            exchange.close()
         dist.destroy_process_group()
     except Exception:
         errq.put("rank %d: %s" % (rank, traceback.format_exc()))
 
 
+def test_two_ranks_peer_exchange():
+    """The same split with the states exchanged through peer memory (``PeerExchange``) instead
+    of ``all_gather``.  Opt-in (FTB200_TEST_PEER_EXCHANGE=1) until it has been run on this kind
+    of machine: it maps device memory between processes."""
+    if not os.environ.get("FTB200_TEST_PEER_EXCHANGE"):
+        pytest.skip("set FTB200_TEST_PEER_EXCHANGE=1 to run")
+    _run_two_ranks("mma", "bfloat16", True)
+
+
 @pytest.mark.parametrize("mode,dtype_name", [("fp32", "float32"), ("mma", "float32"), ("mma", "bfloat16")])
 def test_two_ranks_match_whole_sequence(mode, dtype_name):
+    _run_two_ranks(mode, dtype_name, False)
+
+
+def _run_two_ranks(mode, dtype_name, peer_exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -60,7 +80,8 @@ def test_two_ranks_match_whole_sequence(mode, dtype_name):
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, dtype_name, errq)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, dtype_name, errq, peer_exchange))
+             for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
