@@ -52,6 +52,8 @@ def parse():
     ap.add_argument("--exchange", choices=["nccl", "peer"], default="nccl",
                     help="config 4 on several GPUs: how the per-rank states travel (all_gather, "
                          "or stores into the peers' buffers by this library's own kernels)")
+    ap.add_argument("--sp-graph", action="store_true",
+                    help="with --exchange peer: capture the sequence-parallel step in a CUDA graph")
     ap.add_argument("--graph-steps", type=int, default=0,
                     help="steps captured per CUDA graph (default: the largest divisor of --steps that keeps "
                          "the graph under about 8 ms, at most 10)")
@@ -535,7 +537,9 @@ def main():
     graph = None
     per_graph = 1
     launches_per_step = None
-    if not args.no_graph and not seq_parallel:
+    # (the sequence split is captured only on request, and only with the peer-memory exchange:
+    # a step with NCCL calls in it did not capture here)
+    if not args.no_graph and (not seq_parallel or (args.sp_graph and sp_exchange is not None)):
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
@@ -554,6 +558,10 @@ def main():
             torch.cuda.synchronize()
             eager_ms.append(t0.elapsed_time(t1))
         most = args.graph_steps or max(1, min(10, int(8.0 / max(min(eager_ms), 1e-3))))
+        if dist is not None:      # the same on every rank (ranks that exchange must stay in step)
+            m = torch.tensor([most], device=dev)
+            dist.all_reduce(m, op=dist.ReduceOp.MIN)
+            most = int(m.item())
         per_graph = next(d for d in range(most, 0, -1) if args.steps % d == 0)
         graph = torch.cuda.CUDAGraph()
         n0 = lib.ftb_launch_count()
