@@ -1063,8 +1063,11 @@ int ftb_exchange_push(const float *state, int64_t elems, void *const *buffers, i
     per_target = std::max<int64_t>(1, std::min<int64_t>(per_target, 32));
     const dim3 grid(targets ? (unsigned)per_target : 1u, targets ? (unsigned)targets : 1u);
     cudaStream_t st = (cudaStream_t)stream;
+    int *status = nullptr;
+    FTB_CUDA(cudaGetSymbolAddress((void **)&status, mma::g_device_status));
     LaunchScope scope(FTB_KERNEL_RANK_EXCHANGE, st);
-    xchg::push_kernel<<<grid, xchg::kThreads, 0, st>>>(state, elems, peers, rank, world, reverse ? 1 : 0);
+    xchg::push_kernel<<<grid, xchg::kThreads, 0, st>>>(state, elems, peers, rank, world, reverse ? 1 : 0,
+                                                       status);
     FTB_CUDA(cudaGetLastError());
     return FTB_OK;
 }

@@ -4,8 +4,9 @@
 // of the ranks before (forward) or after (backward) each rank.  Here every rank owns one device
 // buffer that its peers map through CUDA IPC:
 //
-//   [control block, 512 B, used by the owner only]
-//       u64 [0]  exchanges pushed by the owner          u64 [1]  exchanges received by the owner
+//   [control block, 512 B, written by the owner only]
+//       u64 [0]  exchanges pushed by the owner
+//       u64 [1]  exchanges received by the owner (the peers read it before they reuse a slot)
 //       u32 at byte 64 + 4 p   blocks that finished the push to rank p
 //       u32 at byte 128        ranks the current push has finished with
 //       u32 at byte 132        blocks that finished the current receive
@@ -16,13 +17,18 @@
 // stores over NVLink -- and then releases flag[e & 1][r] = e at system scope; receive_kernel waits
 // (bounded) until the flags of the ranks it needs have reached e and adds their slots up in rank
 // order.  e comes from counters in the owner's control block, advanced by the kernels themselves,
-// so the pair can be captured in a CUDA graph and replayed.  Two slots per source, alternating
-// with e, are enough: a rank can deliver exchange e + 1 before a peer has read exchange e (other
-// slot), but not e + 2, which it can only start after that peer has delivered e + 1 itself, i.e.
-// after the peer's receive of e has ended (stream order on the peer).
+// so the pair can be captured in a CUDA graph and replayed.  There are two slots per source,
+// alternating with e, so a rank may deliver exchange e + 1 before a peer has read exchange e;
+// before it overwrites a slot with exchange e, push_kernel checks that the target has finished
+// its receive of e - 2 (the target's "received" counter, read through the mapping).  In a
+// training step, where directions alternate, that is already true (a rank cannot get two
+// exchanges ahead of a peer it also receives from); in a run of forward-only exchanges the first
+// rank receives from nobody and would otherwise run away.
 //
-// No kernel here waits on another launch of the same GPU; the only wait is on flags written by
-// OTHER GPUs, it gives up after about a second and records FTB_ERR_TIMEOUT in the device status.
+// No kernel here waits on another launch of the same GPU; the waits are on counters written by
+// OTHER GPUs, they give up after about a second and record FTB_ERR_TIMEOUT in the device status.
+// Dependencies point from an exchange to the same or an earlier one only (receive e needs the
+// peers' push e; push e needs the peers' receive e - 2), so the waits cannot form a cycle.
 #pragma once
 
 #include <cstddef>
@@ -65,7 +71,8 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
 // grid (blocks per target, targets); targets = the ranks after this one (before it when reverse).
 // A rank without targets launches one block, which only advances the counter.
 __global__ void __launch_bounds__(kThreads)
-push_kernel(const float *__restrict__ state, int64_t elems, Peers peers, int rank, int world, int reverse) {
+push_kernel(const float *__restrict__ state, int64_t elems, Peers peers, int rank, int world, int reverse,
+            int *device_status) {
     char *own = static_cast<char *>(peers.buf[rank]);
     volatile unsigned long long *ctl = reinterpret_cast<volatile unsigned long long *>(own);
     const unsigned long long epoch = ctl[0] + 1;   // no block writes ctl[0] before all have read it
@@ -82,19 +89,43 @@ push_kernel(const float *__restrict__ state, int64_t elems, Peers peers, int ran
                                              ((int64_t)parity * world + rank) * elems);
     const float4 *src = reinterpret_cast<const float4 *>(state);
     const int64_t n4 = elems / 4;
-    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n4; i += (int64_t)gridDim.x * kThreads)
-        dst[i] = src[i];
+    // the slot still holds exchange e - 2 until the target has received it
+    __shared__ int s_fail;
+    if (threadIdx.x == 0) {
+        int fail = 0;
+        const unsigned long long *received = reinterpret_cast<const unsigned long long *>(peer) + 1;
+        long long spins = 0;
+        while (ld_acquire_sys(received) + 2 < epoch) {
+            if (++spins > kSpinLimit) {
+                fail = 1;
+                break;
+            }
+            __nanosleep(200);
+        }
+        if (fail) atomicExch(device_status, 5 /* FTB_ERR_TIMEOUT */);
+        s_fail = fail;
+    }
+    __syncthreads();
+    const bool deliver = !s_fail;
+    if (deliver)
+        for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n4; i += (int64_t)gridDim.x * kThreads)
+            dst[i] = src[i];
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
         unsigned *blocks_done = reinterpret_cast<unsigned *>(own + 64) + p;
         unsigned *targets_done = reinterpret_cast<unsigned *>(own + 128);
-        if (atomicAdd(blocks_done, 1u) == gridDim.x - 1) {
+        // low half: blocks done; high half: blocks that gave up waiting
+        const unsigned mine = deliver ? 1u : 0x10001u;
+        const unsigned before = atomicAdd(blocks_done, mine);
+        if ((before & 0xffffu) == gridDim.x - 1) {
             // the last block of this target: every block's stores are fenced; publish them
+            // (not after a time-out: the target's receive then times out as well)
             *blocks_done = 0;
             __threadfence_system();
-            st_release_sys(reinterpret_cast<unsigned long long *>(peer + l.flags_off) + parity * world + rank,
-                           epoch);
+            if (((before + mine) >> 16) == 0)
+                st_release_sys(reinterpret_cast<unsigned long long *>(peer + l.flags_off) + parity * world + rank,
+                               epoch);
             if (atomicAdd(targets_done, 1u) == gridDim.y - 1) {
                 *targets_done = 0;
                 ctl[0] = epoch;
@@ -149,12 +180,15 @@ receive_kernel(void *own_buf, float *__restrict__ out, int64_t elems, int rank, 
             out4[i] = acc;
         }
     }
+    __syncthreads();   // every thread of the block is done with the slots
     if (threadIdx.x == 0) {
         unsigned *blocks_done = reinterpret_cast<unsigned *>(own + 132);
-        __threadfence();
+        __threadfence_system();
         if (atomicAdd(blocks_done, 1u) == gridDim.x - 1) {
+            // every block has read ctl[1] and the slots by now: the peers may reuse the slots
             *blocks_done = 0;
-            ctl[1] = epoch;   // every block has read ctl[1] by now
+            __threadfence_system();
+            st_release_sys(reinterpret_cast<unsigned long long *>(own) + 1, epoch);
         }
     }
 }

@@ -221,3 +221,46 @@ def test_exchange_buffer_size_and_argument_checks():
     assert lib.ftb_exchange_bytes(2, 6) == 0           # states move 16 bytes at a time
     assert lib.ftb_exchange_push(None, 4, None, 0, 2, 0, None) == _native.ERR_INVALID
     assert lib.ftb_exchange_receive(None, None, 4, 0, 2, 0, None) == _native.ERR_INVALID
+
+
+def test_exchange_protocol_two_slots_suffice():
+    """A model of the peer-memory exchange (csrc/rank_exchange.cuh): every rank runs
+    push(e), receive(e), push(e+1), ... in order; a push writes slot[e & 1][src] and then
+    flag[e & 1][src] = e in the buffers of the ranks it feeds, once each of them has finished
+    its receive of e - 2; a receive can run once the flags of its sources have reached e.  Ranks
+    advance in random order as far as those rules allow, with any sequence of directions
+    (alternating as in training, or forward only).  Whatever the interleaving, a receive must
+    find the values of ITS exchange in the slots, and everybody must get to the end."""
+    import random
+    rng = random.Random(5)
+    for world in (2, 3, 5):
+        for trial in range(150):
+            exchanges = 7
+            directions = [rng.random() < (0.5 if trial % 3 else 0.0) for _ in range(exchanges)]
+            slot = [[[None] * world for _ in range(2)] for _ in range(world)]   # [owner][parity][src]
+            flag = [[[0] * world for _ in range(2)] for _ in range(world)]
+            received = [0] * world
+            pc = [0] * world            # operations completed per rank: push, receive, push, ...
+            idle = 0
+            while any(c < exchanges * 2 for c in pc):
+                r = rng.randrange(world)
+                idle += 1
+                assert idle < 100000, "stuck"
+                if pc[r] >= exchanges * 2:
+                    continue
+                e, reverse = pc[r] // 2 + 1, directions[pc[r] // 2]
+                feeds = range(0, r) if reverse else range(r + 1, world)
+                sources = range(r + 1, world) if reverse else range(0, r)
+                if pc[r] % 2 == 0:                                      # push(e)
+                    if any(received[p] + 2 < e for p in feeds):
+                        continue                                        # a slot is still in use
+                    for p in feeds:
+                        slot[p][e & 1][r] = (r, e)
+                        flag[p][e & 1][r] = e
+                else:                                                   # receive(e)
+                    if any(flag[r][e & 1][p] < e for p in sources):
+                        continue                                        # still waiting
+                    assert all(slot[r][e & 1][p] == (p, e) for p in sources), (world, trial, r, e)
+                    received[r] = e
+                pc[r] += 1
+                idle = 0
