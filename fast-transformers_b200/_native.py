@@ -28,6 +28,7 @@ EXPORTS = (
     "ftb_elu_feature_map", "ftb_elu_feature_map_backward",
     "ftb_exchange_bytes", "ftb_exchange_create", "ftb_exchange_open", "ftb_exchange_close",
     "ftb_exchange_destroy", "ftb_exchange_push", "ftb_exchange_receive",
+    "ftb_exchange_wait_limit_ms",
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
                 "mma_bwd_qr", "mma_bwd_multi", "recurrent_step", "normaliser", "feature_map",
@@ -101,6 +102,8 @@ def lib():
     L.ftb_exchange_push.argtypes = [_vp, _i64, ctypes.POINTER(_vp), _int, _int, _int, _vp]
     L.ftb_exchange_receive.restype = _int
     L.ftb_exchange_receive.argtypes = [_vp, _vp, _i64, _int, _int, _int, _vp]
+    L.ftb_exchange_wait_limit_ms.restype = _int
+    L.ftb_exchange_wait_limit_ms.argtypes = [_int]
     L.ftb_launch_count.restype = ctypes.c_uint64
     L.ftb_device_status.restype = _int
     L.ftb_device_status.argtypes = [_int]

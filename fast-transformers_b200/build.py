@@ -16,7 +16,7 @@ LIB = os.path.join(PKG, "libftb200.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "--use_fast_math=false", "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC", "-shared",
 ]
 
 
@@ -48,8 +48,7 @@ def build(force=False, verbose=False, extra_flags=()):
     """Compile every ``.cu`` under ``csrc/`` into ``libftb200.so``; returns its path."""
     if not force and is_current():
         return LIB
-    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
-    cmd = [nvcc_path(), *flags, *extra_flags, "-I", os.path.join(ROOT, "include"), "-I", CSRC,
+    cmd = [nvcc_path(), *NVCC_FLAGS, *extra_flags, "-I", os.path.join(ROOT, "include"), "-I", CSRC,
            "-o", LIB, *sources(), "-lcuda"]
     env = dict(os.environ)
     # the image's default host compiler lacks some runtime pieces; use the system one

@@ -50,6 +50,16 @@ def _rowmajor(t):
     return t if (t.shape[3] <= 1 or t.stride(3) == 1) else t.contiguous()
 
 
+def _like(t):
+    """An uninitialised buffer of ``t``'s shape that the kernels can write: in the memory order
+    of ``t`` when its rows are contiguous (the layer's (N, L, H, dim) storage viewed as
+    (N, H, L, dim) keeps its order, and the caller's permute back is then a view), row-major
+    otherwise (a transposed input, say)."""
+    if t.shape[3] <= 1 or t.stride(3) == 1:
+        return torch.empty_like(t)
+    return torch.empty(t.shape, dtype=t.dtype, device=t.device)
+
+
 def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
@@ -266,7 +276,7 @@ class CausalDotProduct(torch.autograd.Function):
         # result takes the memory order of V (the layer passes (N, L, H, M) storage viewed as
         # (N, H, L, M)): the kernels write through strides, and the caller's permute back is
         # then contiguous instead of a copy
-        product = torch.empty_like(V) if V.shape == (N, H, L, M) else \
+        product = _like(V) if V.shape == (N, H, L, M) else \
             torch.empty((N, H, L, M), device=Q.device, dtype=Q.dtype)
         kept = []
         fwd = CausalDotProduct.dot[Q.device.type]
@@ -288,9 +298,9 @@ class CausalDotProduct(torch.autograd.Function):
         if not native or not any(need) or _feature_blocks(Q, V, ctx.mode, None, None, None, None):
             need = [True, True, True]
         # gradients in the memory order of their inputs (see forward)
-        grad_Q = torch.empty_like(Q) if need[0] else None
-        grad_K = torch.empty_like(K) if need[1] else None
-        grad_V = torch.empty_like(V) if need[2] else None
+        grad_Q = _like(Q) if need[0] else None
+        grad_K = _like(K) if need[1] else None
+        grad_V = _like(V) if need[2] else None
         if native:
             bwd(Q.data, K.data, V.data, grad_out, grad_Q, grad_K, grad_V, ctx.mode,
                 forward_workspace=ctx.forward_workspace)

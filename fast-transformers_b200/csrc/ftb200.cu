@@ -74,7 +74,6 @@ struct Plan {
     int nseg;
 };
 
-constexpr int64_t kTargetCtas = 148 * 4;
 constexpr int64_t kMinSegRows = 4 * CH;
 constexpr int kSimtMaxDim = 512;
 
@@ -85,7 +84,7 @@ static Plan simt_plan(int64_t BH, int64_t L) {
         p.nseg = 1;
         return p;
     }
-    int64_t want = (kTargetCtas + BH - 1) / BH;
+    int64_t want = ((int64_t)mma::sm_count() * 4 + BH - 1) / BH;
     if (want < 1) want = 1;
     int64_t len = (L + want - 1) / want;
     len = (len + CH - 1) / CH * CH;
@@ -224,8 +223,7 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
     p.init = init; p.sum_mode = sum_mode; p.sub = sub < 1 ? 1 : sub;
     p.skip_lo = skip_lo; p.skip_hi = skip_hi;
     p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = state_only ? 1 : 0;
-    static const char *env = std::getenv("FTB200_MMA_TERMS");
-    p.terms = env ? std::atoi(env) : 7;
+    p.terms = 7;
     if (batch.b.njobs == 0) {
         batch.dtype = dtype;
         batch.kind = state_only ? FTB_KERNEL_MMA_STATE : (reverse ? FTB_KERNEL_MMA_BWD : FTB_KERNEL_MMA_FWD);
@@ -239,8 +237,7 @@ static int mma_launch_batch(MmaBatch &batch, cudaStream_t st) {
     if (batch.b.njobs == 0) return FTB_OK;
     for (int j = batch.b.njobs; j < mma::MAX_JOBS; ++j) batch.b.first_block[j + 1] = batch.b.first_block[j];
     // equal-sized scans are interleaved block by block (shared tiles meet in L2)
-    static const char *no_il = std::getenv("FTB200_NO_INTERLEAVE");
-    bool equal = batch.b.njobs > 1 && !no_il;
+    bool equal = batch.b.njobs > 1;
     for (int j = 0; j < batch.b.njobs && equal; ++j)
         equal = !batch.b.job[j].p.state_only &&
                 batch.b.first_block[j + 1] - batch.b.first_block[j] == batch.b.first_block[1];
@@ -310,23 +307,23 @@ static inline bool sums_in_kernel(int mode, Plan pl) {
     return mode == FTB_MODE_MMA && pl.nseg <= mma::kSumInKernelMaxSegs;
 }
 
-// The state-only launch reads (D+M)/(2D+2M) of what a scan reads and skips one segment per head, so
-// on the scan's own segments it would leave most SMs idle: it runs on `sub` times finer segments
-// (sub blocks per segment in the workspace) unless per-head totals are wanted from the same data.
-static int state_sub(int mode, Plan pl, int64_t BH, bool totals) {
-    if (totals || !sums_in_kernel(mode, pl) || pl.nseg < 2) return 1;
+// The state-only launch reads (D+M)/(2D+2M) of what a scan reads, so on the scan's own segments it
+// would leave most SMs idle: it runs on `sub` times finer segments (sub blocks per segment in the
+// workspace).  `sub` is a function of the shape alone, so whoever wrote the states of a workspace
+// (a forward call with or without final_state, ftb_causal_state_sum) and whoever reads them later
+// (the scan of the same call, a backward call given `forward_workspace`) agree on the layout.
+static int state_sub(int mode, Plan pl, int64_t BH) {
+    if (!sums_in_kernel(mode, pl) || pl.nseg < 2) return 1;
     const int64_t cps = pl.seg_len / mma::C;
     for (int sub = 4; sub >= 2; --sub)
-        if (cps % sub == 0 && BH * (pl.nseg - 1) * sub <= 160 && pl.nseg * sub <= 16) return sub;
+        if (cps % sub == 0 && BH * (pl.nseg - 1) * sub <= (int64_t)mma::sm_count() * 13 / 12 && pl.nseg * sub <= 16) return sub;
     return 1;
 }
 
-// Describe segment-start states that already sit in `ws` (written by prepare_states, or -- when
-// `prepared` -- by ftb_causal_state_sum, which wants totals and therefore uses sub = 1).
-static SegStates describe_states(int mode, Plan pl, const float *ws, const float *init, int64_t BH,
-                                 bool prepared) {
+// Describe segment-start states that sit in `ws` (written by prepare_states).
+static SegStates describe_states(int mode, Plan pl, const float *ws, const float *init, int64_t BH) {
     if (pl.nseg == 1) return SegStates{nullptr, init, 0, 1};
-    if (sums_in_kernel(mode, pl)) return SegStates{ws, init, 1, state_sub(mode, pl, BH, prepared)};
+    if (sums_in_kernel(mode, pl)) return SegStates{ws, init, 1, state_sub(mode, pl, BH)};
     // exclusive prefixes: the tensor-core kernel adds `init` itself, the fp32 kernel reads one
     // block per segment, so there `init` is folded into the prefixes
     if (mode == FTB_MODE_MMA) return SegStates{ws, init, 0, 1};
@@ -339,7 +336,7 @@ static int prepare_states(int mode, const void *x, const void *y, const int64_t 
                           int64_t N, int64_t H, int64_t L, int D, int M, int dtype, Plan pl, float *ws,
                           const float *init, float *total, int reverse, cudaStream_t st,
                           SegStates *out) {
-    *out = describe_states(mode, pl, ws, init, N * H, total != nullptr);
+    *out = describe_states(mode, pl, ws, init, N * H);
     if (pl.nseg == 1 && !total) return FTB_OK;
     int rc;
     if (sums_in_kernel(mode, pl)) {
@@ -357,7 +354,7 @@ static int prepare_states(int mode, const void *x, const void *y, const int64_t 
         if (rc || !total) return rc;
         int64_t n = N * H * (int64_t)D * M;
         LaunchScope scope(FTB_KERNEL_STATE_PREFIX, st);
-        state_total_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ws, init, total, N * H, pl.nseg,
+        state_total_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ws, init, total, N * H, fine.nseg,
                                                                        (int64_t)D * M);
         FTB_CUDA(cudaGetLastError());
         return FTB_OK;
@@ -418,8 +415,7 @@ static bool norm_fast_ok(const NormParams &p, int dtype, bool vec_out) {
     };
     if (!ok(p.q, p.qs) || !ok(p.k, p.ks)) return false;
     if (vec_out && !ok(p.out, p.os)) return false;
-    static const char *off = std::getenv("FTB200_NORM_GENERIC");
-    return off == nullptr;
+    return true;
 }
 template <typename T, int LPR, int MODE>
 static int norm_launch_fast_mode(const NormParams &p, int64_t groups, int64_t blocks, cudaStream_t st) {
@@ -436,7 +432,7 @@ static int norm_launch_fast_mode(const NormParams &p, int64_t groups, int64_t bl
 template <typename T, int LPR>
 static int norm_launch_fast(NormParams p, int64_t BH, cudaStream_t st) {
     constexpr int per_cta = kNormThreads / LPR;
-    NormPlan pl = norm_plan(BH, p.L, (int64_t)148 * 4 * per_cta, 2 * kNormRows);
+    NormPlan pl = norm_plan(BH, p.L, (int64_t)mma::sm_count() * 4 * per_cta, 2 * kNormRows);
     p.nseg = pl.nseg;
     p.seg_len = pl.seg_len;
     const int64_t groups = BH * p.nseg;
@@ -456,7 +452,7 @@ static int norm_launch(NormParams p, int64_t BH, int dtype, cudaStream_t st) {
             default: return norm_launch_fast<T, 32>(p, BH, st);
         }
     }
-    NormPlan pl = norm_plan(BH, p.L, 148 * 8, 8 * kNormRows);
+    NormPlan pl = norm_plan(BH, p.L, (int64_t)mma::sm_count() * 8, 8 * kNormRows);
     p.nseg = pl.nseg;
     p.seg_len = pl.seg_len;
     const int64_t blocks = BH * p.nseg;
@@ -507,6 +503,8 @@ int ftb_last_cuda_error(void) { return g_last_cuda_error; }
 
 int ftb_device_status(int reset) {
     int v = 0;
+    // every stream of the device, non-blocking ones included, has drained before the word is read
+    if (cudaDeviceSynchronize() != cudaSuccess) return FTB_ERR_CUDA;
     if (cudaMemcpyFromSymbol(&v, mma::g_device_status, sizeof(int)) != cudaSuccess) return FTB_ERR_CUDA;
     if (reset && v) {
         int z = 0;
@@ -514,15 +512,6 @@ int ftb_device_status(int reset) {
     }
     return v;
 }
-
-#ifdef FTB_TIMESTAMPS
-int ftb_debug_read_timestamps(long long *dst, int n) {
-    return (int)cudaMemcpyFromSymbol(dst, mma::g_ts, sizeof(long long) * n);
-}
-int ftb_debug_read_cta_timestamps(long long *dst, int n) {
-    return (int)cudaMemcpyFromSymbol(dst, mma::g_cta, sizeof(long long) * n);
-}
-#endif
 
 uint64_t ftb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
@@ -568,7 +557,7 @@ size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, in
     if (N <= 0 || H <= 0 || L <= 0 || D <= 0 || M <= 0) return 0;
     {
         Plan pl = choose_plan(mode, N * H, L);
-        size_t one = align256((size_t)N * H * pl.nseg * state_sub(mode, pl, N * H, false) * D * M *
+        size_t one = align256((size_t)N * H * pl.nseg * state_sub(mode, pl, N * H) * D * M *
                               sizeof(float));
         if (backward) return 2 * one;
         return (pl.nseg > 1 || want_state) ? one : 0;
@@ -617,7 +606,7 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
     SegStates ss;
     if (workspace_has_states && mode == FTB_MODE_MMA && !final_state) {
         // ftb_causal_state_sum(k, v, ...) already left the per-segment states in `workspace`
-        ss = describe_states(mode, pl, ws, initial_state, N * H, true);
+        ss = describe_states(mode, pl, ws, initial_state, N * H);
     } else {
         rc = prepare_states(mode, k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, ws, initial_state,
                             final_state, 0, st, &ss);
@@ -673,8 +662,7 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
     if (!want_q) {
         // grad_Q is the only reader of the forward states
     } else if (forward_workspace && pl.nseg > 1) {
-        sS = describe_states(mode, pl, (const float *)forward_workspace, initial_state, N * H,
-                             workspace_has_grad_states != 0);
+        sS = describe_states(mode, pl, (const float *)forward_workspace, initial_state, N * H);
     } else {
         rc = prepare_states(mode, k, v, ks, vs, N, H, L, (int)D, (int)M, dtype, pl, wsS, initial_state,
                             nullptr, 0, st, &sS);
@@ -686,9 +674,9 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
         // grad_K and grad_V are the only readers of the reverse states
     } else if (workspace_has_grad_states && mode == FTB_MODE_MMA) {
         // ftb_causal_state_sum(q, grad_out, ..., reverse=1, second half of `workspace`) ran before
-        sR = describe_states(mode, pl, wsR, initial_grad_state, N * H, true);
+        sR = describe_states(mode, pl, wsR, initial_grad_state, N * H);
     } else if (mode == FTB_MODE_MMA && pl.nseg > 1 && sums_in_kernel(mode, pl)) {
-        sR = describe_states(mode, pl, wsR, initial_grad_state, N * H, false);
+        sR = describe_states(mode, pl, wsR, initial_grad_state, N * H);
         r_with_grad_q = true;
     } else {
         rc = prepare_states(mode, q, g, qs, gs, N, H, L, (int)D, (int)M, dtype, pl, wsR,
@@ -969,17 +957,15 @@ int ftb_causal_dot_product_static(const void *q, const void *k, const void *v, v
     int dev = -1;
     FTB_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return FTB_ERR_UNSUPPORTED;
-    // Set-up: the first call on a device (and the first call of each further host thread, which
-    // also gives that thread a bound context) resolves the symbol.  It is a synchronous lookup,
-    // so it should happen before any stream capture begins.
-    static thread_local int t_resolved_dev = -1;
+    // Set-up: the first call on a device resolves the symbol, with that device current.  It is a
+    // synchronous lookup, so it should happen before any stream capture begins.  The address is
+    // kept per device ordinal, so a host thread that alternates between GPUs looks nothing up again.
     void *scratch = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
-    if (scratch == nullptr || t_resolved_dev != dev) {
+    if (scratch == nullptr) {
         void *p = nullptr;
         FTB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
         if (p == nullptr) return FTB_ERR_CUDA;
         g_static_scratch_ptr[dev].store(p, std::memory_order_release);
-        t_resolved_dev = dev;
         scratch = p;
     }
     const size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, 0);
@@ -994,6 +980,26 @@ int ftb_causal_dot_product_static(const void *q, const void *k, const void *v, v
 // ---------------------------------------------------------------------------------------------
 // Exchange of per-rank states between the GPUs of one node (csrc/rank_exchange.cuh).
 // ---------------------------------------------------------------------------------------------
+// Device address of the status word of the current device, looked up once per device ordinal (the
+// lookup is a synchronous runtime call, so ftb_exchange_create makes it and the launches below,
+// which may be issued while a stream is being captured, only read the cached value).
+static std::atomic<int *> g_status_ptr[64];
+static int device_status_ptr(int **out) {
+    int dev = -1;
+    FTB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return FTB_ERR_UNSUPPORTED;
+    int *p = g_status_ptr[dev].load(std::memory_order_acquire);
+    if (!p) {
+        FTB_CUDA(cudaGetSymbolAddress((void **)&p, mma::g_device_status));
+        if (!p) return FTB_ERR_CUDA;
+        g_status_ptr[dev].store(p, std::memory_order_release);
+    }
+    *out = p;
+    return FTB_OK;
+}
+
+static std::atomic<long long> g_exchange_wait_ns{xchg::kDefaultWaitNs};
+
 static int exchange_check(int world, int64_t elems) {
     if (world < 1 || elems < 0) return FTB_ERR_INVALID;
     if (world > xchg::kMaxRanks) return FTB_ERR_UNSUPPORTED;
@@ -1011,6 +1017,9 @@ int ftb_exchange_create(int world, int64_t elems, void **buffer, unsigned char *
     int rc = exchange_check(world, elems);
     if (rc) return rc;
     static_assert(sizeof(cudaIpcMemHandle_t) == FTB_EXCHANGE_HANDLE_BYTES, "IPC handle size");
+    int *status = nullptr;
+    rc = device_status_ptr(&status);
+    if (rc) return rc;
     const size_t bytes = xchg::layout(world, elems).bytes;
     void *p = nullptr;
     FTB_CUDA(cudaMalloc(&p, bytes));
@@ -1047,6 +1056,12 @@ int ftb_exchange_destroy(void *buffer) {
     return FTB_OK;
 }
 
+int ftb_exchange_wait_limit_ms(int ms) {
+    const long long before = g_exchange_wait_ns.load();
+    if (ms > 0) g_exchange_wait_ns.store((long long)ms * 1000000LL);
+    return (int)(before / 1000000LL);
+}
+
 int ftb_exchange_push(const float *state, int64_t elems, void *const *buffers, int rank, int world,
                       int reverse, void *stream) {
     int rc = exchange_check(world, elems);
@@ -1064,10 +1079,11 @@ int ftb_exchange_push(const float *state, int64_t elems, void *const *buffers, i
     const dim3 grid(targets ? (unsigned)per_target : 1u, targets ? (unsigned)targets : 1u);
     cudaStream_t st = (cudaStream_t)stream;
     int *status = nullptr;
-    FTB_CUDA(cudaGetSymbolAddress((void **)&status, mma::g_device_status));
+    rc = device_status_ptr(&status);
+    if (rc) return rc;
     LaunchScope scope(FTB_KERNEL_RANK_EXCHANGE, st);
     xchg::push_kernel<<<grid, xchg::kThreads, 0, st>>>(state, elems, peers, rank, world, reverse ? 1 : 0,
-                                                       status);
+                                                       status, g_exchange_wait_ns.load());
     FTB_CUDA(cudaGetLastError());
     return FTB_OK;
 }
@@ -1079,14 +1095,16 @@ int ftb_exchange_receive(void *buffer, float *out, int64_t elems, int rank, int 
     if (!buffer || rank < 0 || rank >= world || (elems > 0 && !out)) return FTB_ERR_INVALID;
     if ((uintptr_t)out & 15) return FTB_ERR_ALIGNMENT;
     int *status = nullptr;
-    FTB_CUDA(cudaGetSymbolAddress((void **)&status, mma::g_device_status));
+    rc = device_status_ptr(&status);
+    if (rc) return rc;
     const int64_t n4 = elems / 4;
     int64_t blocks = (n4 + (int64_t)xchg::kThreads * 2 - 1) / ((int64_t)xchg::kThreads * 2);
-    blocks = std::max<int64_t>(1, std::min<int64_t>(blocks, 148));
+    blocks = std::max<int64_t>(1, std::min<int64_t>(blocks, mma::sm_count()));
     cudaStream_t st = (cudaStream_t)stream;
     LaunchScope scope(FTB_KERNEL_RANK_EXCHANGE, st);
     xchg::receive_kernel<<<(unsigned)blocks, xchg::kThreads, 0, st>>>(buffer, out, elems, rank, world,
-                                                                      reverse ? 1 : 0, status);
+                                                                      reverse ? 1 : 0, status,
+                                                                      g_exchange_wait_ns.load());
     FTB_CUDA(cudaGetLastError());
     return FTB_OK;
 }

@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <utility>
@@ -95,25 +96,42 @@ struct Plan {
     int nseg;
 };
 
+// Number of SMs of the calling thread's current device (looked up once per device ordinal; 148, a
+// whole B200, when no device can be asked -- a workspace query made on a machine without a GPU).
+static int sm_count() {
+    static std::atomic<int> cached[64];
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        (void)cudaGetLastError();
+        return 148;
+    }
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n > 0) return n;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        return 148;
+    }
+    cached[dev].store(n, std::memory_order_relaxed);
+    return n;
+}
+
 // Segments are whole chunks; one CTA walks one segment.  The count is chosen to minimise
-// waves x (chunks per segment + a fixed per-CTA cost) over the 148 SMs, with a small charge
-// per segment for its state traffic.  FTB200_MMA_SEGS=<n> forces the count (tuning only).
+// waves x (chunks per segment + a fixed per-CTA cost) over the device's SMs, with a small charge
+// per segment for its state traffic.
 constexpr int kSumInKernelMaxSegs = 16;  // up to here the scan kernel adds up raw totals itself
 
 static Plan plan(int64_t BH, int64_t L, int ntile) {
     Plan p;
     const int64_t chunks = (L + C - 1) / C;
     int64_t best = 1;
-    static const char *env = std::getenv("FTB200_MMA_SEGS");
-    if (env && std::atoi(env) > 0) {
-        best = std::atoi(env);
-    } else if (chunks > 1 && BH > 0) {
+    if (chunks > 1 && BH > 0) {
+        const int64_t sms = sm_count();
         double best_cost = 1e30;
         for (int64_t t = 1; t <= chunks && t <= 64; ++t) {
             const int64_t cps = (chunks + t - 1) / t;
             const int64_t n = (chunks + cps - 1) / cps;
             const int64_t ctas = BH * n * ntile;
-            const int64_t waves = (ctas + 147) / 148;
+            const int64_t waves = (ctas + sms - 1) / sms;
             const double cost = (double)waves * ((double)cps + 1.0) + 0.3 * (double)n;
             if (cost < best_cost - 1e-9) {
                 best_cost = cost;
@@ -142,8 +160,7 @@ static bool supported(int dtype, int64_t Da, int64_t Dc) {
 // library's own, of the same call (the state-only sweep): the blocks wait for it only where they
 // read what it wrote.  Otherwise they wait for it before they touch global memory at all
 // (ScanBatch::wait_first), which is safe behind any kernel and overlaps the block set-up only.
-// Environment (tuning and fault finding): FTB200_NO_PDL=1 ordinary launches throughout,
-// FTB200_PDL_OWN_ONLY=1 ordinary launches for the first grid of a call.
+// Environment (fault finding): FTB200_NO_PDL=1 ordinary launches throughout.
 template <typename T, int DA, int DCT>
 static cudaError_t launch_t(ScanBatch &batch, cudaStream_t st, bool after_own_launch) {
     using K = Cfg<T, DA, DCT>;
@@ -151,9 +168,8 @@ static cudaError_t launch_t(ScanBatch &batch, cudaStream_t st, bool after_own_la
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)K::SMEM);
     if (e != cudaSuccess) return e;
     static const char *no_pdl = std::getenv("FTB200_NO_PDL");
-    static const char *late_only = std::getenv("FTB200_PDL_OWN_ONLY");
     batch.wait_first = 0;
-    if (no_pdl || (late_only && !after_own_launch)) {
+    if (no_pdl) {
         kern<<<(unsigned)batch.first_block[batch.njobs], NTHREADS, K::SMEM, st>>>(batch);
         return cudaGetLastError();
     }

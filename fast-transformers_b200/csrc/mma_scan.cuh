@@ -44,27 +44,6 @@ constexpr int STAGES = 2;
 
 __device__ int g_device_status = 0;   // 0 ok, else FTB_ERR_* recorded by a kernel
 
-// Optional per-role event timestamps of CTA 0 (a tuning aid, compiled out by default).
-#ifdef FTB_TIMESTAMPS
-__device__ long long g_ts[8 * 64 * 8];
-__device__ long long g_cta[1024 * 4];   // per CTA (ns): start, end, set-up done, roles done
-__device__ __forceinline__ long long ts_globaltimer() {
-    long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ int ts_smid() {
-    int s;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(s));
-    return s;
-}
-#define FTB_TS(role, ci, ev)                                                        \
-    do {                                                                            \
-        if (blockIdx.x == 0 && (ci) < 64) g_ts[((role)*64 + (ci)) * 8 + (ev)] = clock64(); \
-    } while (0)
-#else
-#define FTB_TS(role, ci, ev) do { } while (0)
-#endif
 
 struct ScanParams {
     void *out;            // output tensor (scan) or nullptr (state only)
@@ -163,13 +142,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (clock64() - t0 > 4000000000LL) {
                 *abort_flag = 1;
                 atomicExch(&g_device_status, 5 /* FTB_ERR_TIMEOUT */);
-#ifdef FTB_TIMESTAMPS
-                // which wait gave up: barrier offset, parity, thread, block
-                atomicCAS(reinterpret_cast<unsigned long long *>(&g_ts[8 * 64 * 8 - 1]), 0ULL,
-                          (unsigned long long)(bar & 1023u) | ((unsigned long long)parity << 12) |
-                              ((unsigned long long)threadIdx.x << 16) |
-                              ((unsigned long long)blockIdx.x << 32) | (1ULL << 62));
-#endif
                 return false;
             }
         }
@@ -441,12 +413,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
             dst[(int64_t)(e / DCT) * p.Dc + n0 + e % DCT] = 0.f;
     }
 
-#ifdef FTB_TIMESTAMPS
-    if (threadIdx.x == 0 && blockIdx.x < 1024) {
-        g_cta[4 * blockIdx.x] = ts_globaltimer();
-        FTB_TS(7, 0, 0);
-    }
-#endif
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
@@ -485,9 +451,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
-#ifdef FTB_TIMESTAMPS
-    if (threadIdx.x == 0 && blockIdx.x < 1024) g_cta[4 * blockIdx.x + 2] = ts_globaltimer();
-#endif
 
     if (nchunk > 0) {
         if (warp == 0) {
@@ -541,7 +504,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     const int s = ci & 1, use = ci >> 1;
                     ok = mbar_wait(bar_empty + 8 * s, (use & 1) ^ 1, abort_flag);
                     if (!ok) break;
-                    FTB_TS(0, ci, 0);
                     const int row = (int)(seg_begin + (int64_t)c * C);
                     const uint32_t st = stage0 + s * K::STAGE_BYTES;
                     mbar_expect_tx(bar_full + 8 * s, 2 * K::A_BYTES);
@@ -604,12 +566,10 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         const uint32_t tO = tmem + K::TM_O + ob * DCT;
                         const uint32_t tP = tmem + K::TM_P + 128 * (ci & 1);
                         // O = a S: the a tile, the operand copy of the previous state, a free O
-                        FTB_TS(1, ci, 0);
                         ok = mbar_wait(bar_full + 8 * s, (ci >> 1) & 1, abort_flag) &&
                              mbar_wait(bar_smready, ci & 1, abort_flag) &&
                              mbar_wait(bar_ofree + 8 * ob, (ouse & 1) ^ 1, abort_flag);
                         if (!ok) break;
-                        FTB_TS(1, ci, 1);
                         tc_fence_after();
                         uint32_t acc = 0;
                         if (p.terms & 1) {
@@ -626,11 +586,9 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         // the state operand in shared memory may now be replaced by the next state
                         tc_commit(bar_smfree);
                         // O += mask(P) c
-                        FTB_TS(1, ci, 2);
                         ok = mbar_wait(bar_pready + 8 * (ci & 1), (ci >> 1) & 1, abort_flag) &&
                              mbar_wait(bar_fullc + 8 * s, (ci >> 1) & 1, abort_flag);
                         if (!ok) break;
-                        FTB_TS(1, ci, 3);
                         tc_fence_after();
                         if (p.terms & 2) {
 #pragma unroll
@@ -642,7 +600,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         tc_commit(bar_ofull + 8 * ob);       // output workers
                         tc_commit(bar_pfree + 8 * (ci & 1)); // this score buffer may be overwritten
                         tc_commit(bar_empty + 8 * s);        // one of the two releases of the stage
-                        FTB_TS(1, ci, 4);
                     }
                 } else {
                     // ---- state issuer --------------------------------------------------------
@@ -671,7 +628,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         if (sc < nchunk && sc <= ds + 1 &&
                             mbar_test(bar_full + 8 * (sc & 1), (sc >> 1) & 1) &&
                             (sc < 2 || mbar_test(bar_pfree + 8 * (sc & 1), ((sc - 2) >> 1) & 1))) {
-                            FTB_TS(4, sc, 3);
                             tc_fence_after();
                             issue_scores(sc);
                             ++sc;
@@ -689,7 +645,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         if (ds < sc && acc_free && mbar_test(bar_fullc + 8 * s, (ds >> 1) & 1) &&
                             (!K::RELOAD_B || mbar_test(bar_fullbmn + 8 * s, (ds >> 1) & 1))) {
                             const uint64_t bmn0 = dBmn0 + s * STAGE_UNITS, c0 = dCmn0 + s * STAGE_UNITS;
-                            FTB_TS(4, ds, 1);
                             tc_fence_after();
                             if (p.terms & 4) {
                                 const uint32_t tT = K::REG_STATE ? tS + s * DCT : tS;
@@ -702,7 +657,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                             if constexpr (K::REG_STATE) tc_commit(bar_tfull + 8 * s);
                             else tc_commit(bar_sfull);
                             tc_commit(bar_empty + 8 * s);        // the other release of the stage
-                            FTB_TS(4, ds, 2);
                             ++ds;
                             idle = 0;
                             continue;
@@ -714,11 +668,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                             if (clock64() - t0 > 4000000000LL) {
                                 *abort_flag = 1;
                                 atomicExch(&g_device_status, 5 /* FTB_ERR_TIMEOUT */);
-#ifdef FTB_TIMESTAMPS
-                                atomicCAS(reinterpret_cast<unsigned long long *>(&g_ts[8 * 64 * 8 - 1]), 0ULL,
-                                          1023ULL | ((unsigned long long)sc << 12) | ((unsigned long long)ds << 22) |
-                                              ((unsigned long long)blockIdx.x << 32) | (1ULL << 62));
-#endif
                                 break;
                             }
                         }
@@ -734,7 +683,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                 uint32_t r[32];
                 for (int ci = 0; ci < nchunk; ++ci) {
                     if (!mbar_wait(bar_pfull + 8 * (ci & 1), (ci >> 1) & 1, abort_flag)) break;
-                    if (threadIdx.x == 352) FTB_TS(3, ci, 0);
                     tc_fence_after();
                     if constexpr (K::RELOAD_B) {
                         // The score product has consumed the K-major image of b (128-byte
@@ -766,9 +714,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                             }
                             __syncwarp();
                         }
-                        if (threadIdx.x == 352) FTB_TS(3, ci, 4);
                         fence_proxy_async_smem();
-                        if (threadIdx.x == 352) FTB_TS(3, ci, 5);
                         mbar_arrive(bar_fullbmn + 8 * (ci & 1));
                     }
                     const uint32_t tP = tlane + K::TM_P + 128 * (ci & 1);
@@ -817,7 +763,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     tmem_wait_st();
                     tc_fence_before();
                     mbar_arrive(bar_pready + 8 * (ci & 1));
-                    if (threadIdx.x == 352) FTB_TS(3, ci, 1);
                 }
             }
         } else if (warp >= 6 && warp < 10) {
@@ -835,7 +780,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     const int ob = ci % K::NOBUF, ouse = ci / K::NOBUF;
                     ok = mbar_wait(bar_ofull + 8 * ob, ouse & 1, abort_flag);
                     if (!ok) break;
-                    if (threadIdx.x == 192) FTB_TS(3, ci, 2);
                     tc_fence_after();
                     if constexpr (!K::F16 && DCT == 64) {
                         // fp32 rows: read the accumulator in the 16x256b shape (a thread gets
@@ -888,7 +832,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     }
                     tc_fence_before();
                     mbar_arrive(bar_ofree + 8 * ob);
-                    if (threadIdx.x == 192) FTB_TS(3, ci, 3);
                 }
             }
         } else if (warp >= 2 && warp < 6) {
@@ -1023,7 +966,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         // operand slot: its accumulator is handed back at once
                         ok = mbar_wait(bar_tfull + 8 * (ci & 1), (ci >> 1) & 1, abort_flag);
                         if (!ok) break;
-                        if (threadIdx.x == 64) FTB_TS(2, ci, 0);
                         tc_fence_after();
 #pragma unroll
                         for (int cb = 0; cb < DCT / 32; ++cb) {
@@ -1045,7 +987,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         ok = mbar_wait(bar_sfull, ci & 1, abort_flag);
                         if (ok) ok = mbar_wait(bar_smfree, ci & 1, abort_flag);
                         if (!ok) break;
-                        if (threadIdx.x == 64) FTB_TS(2, ci, 0);
                         tc_fence_after();
 #pragma unroll
                         for (int cb = 0; cb < DCT / 32; ++cb) {
@@ -1057,7 +998,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     tc_fence_before();
                     mbar_arrive(bar_smready);
                     mbar_arrive(bar_smready2);
-                    if (threadIdx.x == 64) FTB_TS(2, ci, 1);
                 }
             }
         }
@@ -1067,19 +1007,10 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-#ifdef FTB_TIMESTAMPS
-    if (threadIdx.x == 0 && blockIdx.x < 1024) g_cta[4 * blockIdx.x + 3] = ts_globaltimer();
-#endif
     if (warp == 0) tmem_dealloc(tmem, 512);
     // no block of a programmatically launched grid ends before the grid in front of it has, so
     // that whatever is launched behind this grid is ordered after both
     if (threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
-#ifdef FTB_TIMESTAMPS
-    if (threadIdx.x == 0 && blockIdx.x < 1024) {
-        g_cta[4 * blockIdx.x + 1] = ts_globaltimer();
-        FTB_TS(7, 0, 1);
-    }
-#endif
 }
 
 }  // namespace mma

@@ -26,7 +26,9 @@
 // rank receives from nobody and would otherwise run away.
 //
 // No kernel here waits on another launch of the same GPU; the waits are on counters written by
-// OTHER GPUs, they give up after about a second and record FTB_ERR_TIMEOUT in the device status.
+// OTHER GPUs.  They give up after `wait_ns` nanoseconds of the global timer (a second by default,
+// see ftb_exchange_wait_limit_ms), record FTB_ERR_TIMEOUT in the device status word, and a
+// receive that gave up fills its result with NaN so that the failure cannot pass for data.
 // Dependencies point from an exchange to the same or an earlier one only (receive e needs the
 // peers' push e; push e needs the peers' receive e - 2), so the waits cannot form a cycle.
 #pragma once
@@ -42,7 +44,7 @@ namespace xchg {
 constexpr int kMaxRanks = 16;
 constexpr int kThreads = 256;
 constexpr size_t kCtlBytes = 512;
-constexpr long long kSpinLimit = 1000000;   // x (200 ns sleep + one local load) ~ 1 s
+constexpr long long kDefaultWaitNs = 1000000000LL;   // one second
 
 struct Layout {
     size_t flags_off, slots_off, bytes;
@@ -67,12 +69,30 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
     asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ long long global_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Poll *p (system scope) until it reaches `want`; false once `wait_ns` have passed.  The spin count
+// is bounded as well, in case the timer does not advance.
+__device__ __forceinline__ bool wait_reaches(const unsigned long long *p, unsigned long long want,
+                                             long long wait_ns, unsigned long long add = 0) {
+    if (ld_acquire_sys(p) + add >= want) return true;
+    const long long t0 = global_ns();
+    for (long long spins = 0; spins < 200000000LL; ++spins) {
+        if (ld_acquire_sys(p) + add >= want) return true;
+        if ((spins & 15) == 15 && global_ns() - t0 > wait_ns) return false;
+        __nanosleep(200);
+    }
+    return false;
+}
 
 // grid (blocks per target, targets); targets = the ranks after this one (before it when reverse).
 // A rank without targets launches one block, which only advances the counter.
 __global__ void __launch_bounds__(kThreads)
 push_kernel(const float *__restrict__ state, int64_t elems, Peers peers, int rank, int world, int reverse,
-            int *device_status) {
+            int *device_status, long long wait_ns) {
     char *own = static_cast<char *>(peers.buf[rank]);
     volatile unsigned long long *ctl = reinterpret_cast<volatile unsigned long long *>(own);
     const unsigned long long epoch = ctl[0] + 1;   // no block writes ctl[0] before all have read it
@@ -92,16 +112,8 @@ push_kernel(const float *__restrict__ state, int64_t elems, Peers peers, int ran
     // the slot still holds exchange e - 2 until the target has received it
     __shared__ int s_fail;
     if (threadIdx.x == 0) {
-        int fail = 0;
         const unsigned long long *received = reinterpret_cast<const unsigned long long *>(peer) + 1;
-        long long spins = 0;
-        while (ld_acquire_sys(received) + 2 < epoch) {
-            if (++spins > kSpinLimit) {
-                fail = 1;
-                break;
-            }
-            __nanosleep(200);
-        }
+        const int fail = wait_reaches(received, epoch, wait_ns, 2) ? 0 : 1;
         if (fail) atomicExch(device_status, 5 /* FTB_ERR_TIMEOUT */);
         s_fail = fail;
     }
@@ -138,7 +150,7 @@ push_kernel(const float *__restrict__ state, int64_t elems, Peers peers, int ran
 // when there are none.  Any number of blocks; each waits for the flags itself.
 __global__ void __launch_bounds__(kThreads)
 receive_kernel(void *own_buf, float *__restrict__ out, int64_t elems, int rank, int world, int reverse,
-               int *device_status) {
+               int *device_status, long long wait_ns) {
     char *own = static_cast<char *>(own_buf);
     volatile unsigned long long *ctl = reinterpret_cast<volatile unsigned long long *>(own);
     const unsigned long long epoch = ctl[1] + 1;
@@ -150,21 +162,19 @@ receive_kernel(void *own_buf, float *__restrict__ out, int64_t elems, int rank, 
         int fail = 0;
         const unsigned long long *flags =
             reinterpret_cast<const unsigned long long *>(own + l.flags_off) + parity * world;
-        for (int p = lo; p < hi && !fail; ++p) {
-            long long spins = 0;
-            while (ld_acquire_sys(flags + p) < epoch) {
-                if (++spins > kSpinLimit) {
-                    fail = 1;
-                    break;
-                }
-                __nanosleep(200);
-            }
-        }
+        for (int p = lo; p < hi && !fail; ++p)
+            if (!wait_reaches(flags + p, epoch, wait_ns)) fail = 1;
         if (fail) atomicExch(device_status, 5 /* FTB_ERR_TIMEOUT */);
         s_fail = fail;
     }
     __syncthreads();
-    if (!s_fail) {
+    if (s_fail) {
+        // gave up: the result must not pass for data
+        float4 *out4 = reinterpret_cast<float4 *>(out);
+        const float nan = __int_as_float(0x7fc00000);
+        for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < elems / 4; i += (int64_t)gridDim.x * kThreads)
+            out4[i] = make_float4(nan, nan, nan, nan);
+    } else {
         const float *slots = reinterpret_cast<const float *>(own + l.slots_off) + (int64_t)parity * world * elems;
         float4 *out4 = reinterpret_cast<float4 *>(out);
         const int64_t n4 = elems / 4;

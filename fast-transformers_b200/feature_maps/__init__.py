@@ -110,8 +110,12 @@ def elu_plus_one_native(x, row_weights=None):
     the (N, S) key-length mask) or is None."""
     if not x.is_cuda or x.dtype not in (torch.float32, torch.bfloat16):
         raise RuntimeError("elu_plus_one_native needs a float32 or bfloat16 CUDA tensor")
-    if row_weights is not None and (row_weights.numel() == 0 or x.numel() % row_weights.numel()):
-        raise RuntimeError("row_weights does not match the leading dimensions of x")
+    if row_weights is not None and (
+            row_weights.dim() > x.dim() or
+            tuple(row_weights.shape) != tuple(x.shape[:row_weights.dim()])):
+        # the reference's K * float_matrix[:, :, None, None] fails to broadcast in this case
+        raise RuntimeError("row_weights of shape %r does not match the leading dimensions of x %r"
+                           % (tuple(row_weights.shape), tuple(x.shape)))
     return _EluPlusOneNative.apply(x, row_weights)
 
 

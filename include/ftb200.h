@@ -37,8 +37,12 @@
  *   - `workspace` is caller-provided scratch of at least ftb_causal_workspace_bytes(...)
  *     bytes, 256-byte aligned; it may be NULL when that function returns 0.
  *   - Return value: FTB_OK or one of the error codes below.  Nothing is enqueued when an
- *     error is returned.  The library is re-entrant and holds no mutable global state, so
- *     forward (caller thread) and backward (autograd thread) may run concurrently.
+ *     error is returned.  The library is re-entrant: forward (caller thread) and backward
+ *     (autograd thread) may run concurrently.  What it keeps between calls is small and listed
+ *     here: per-device caches of looked-up values (SM count, the addresses of the device status
+ *     word and of the static scratch array), the launch counter and -- while ftb_timing_enable
+ *     is on -- the list of recorded events, the device status word itself, and the static
+ *     scratch array of ftb_causal_dot_product_static (shared by all calls on a device).
  */
 #ifndef FTB200_H
 #define FTB200_H
@@ -98,7 +102,8 @@ int ftb_last_cuda_error(void);
 uint64_t ftb_launch_count(void);
 /*
  * Device-side status word of the current device: 0, or the FTB_ERR_* code recorded by a kernel
- * whose bounded wait expired (FTB_ERR_TIMEOUT).  Synchronises the device.  reset != 0 clears it.
+ * whose bounded wait expired (FTB_ERR_TIMEOUT).  Synchronises the whole device first (every stream,
+ * non-blocking ones included).  reset != 0 clears it.
  * The reference has no counterpart (its kernels contain no waits).
  */
 int ftb_device_status(int reset);
@@ -260,8 +265,13 @@ int ftb_recurrent_linear_step(const void *q, const void *k, const void *v, float
  *                         buffer at [rank].
  *   ftb_exchange_receive  waits until the ranks before this one (after it when reverse != 0) have
  *                         delivered, and writes the sum of their states to `out` (zeros when there
- *                         are none).  The wait is bounded (about a second); on expiry `out` is left
- *                         unwritten and FTB_ERR_TIMEOUT is recorded in the device status word.
+ *                         are none).  The wait is bounded (a second unless changed with
+ *                         ftb_exchange_wait_limit_ms); on expiry `out` is filled with NaN and
+ *                         FTB_ERR_TIMEOUT is recorded in the device status word (read it with
+ *                         ftb_device_status before trusting a step).
+ *   ftb_exchange_wait_limit_ms  sets how long the kernels launched from now on wait for a peer
+ *                         (milliseconds, > 0; process-wide) and returns the previous limit; 0 or a
+ *                         negative value only reads it.
  *
  * All ranks must issue the same sequence of push / receive pairs, each rank its push before its
  * receive on one stream.  The exchange number lives in the buffers and is advanced by the kernels,
@@ -274,6 +284,7 @@ int ftb_exchange_create(int world, int64_t elems, void **buffer, unsigned char *
 int ftb_exchange_open(const unsigned char *handle, void **peer_buffer);
 int ftb_exchange_close(void *peer_buffer);
 int ftb_exchange_destroy(void *buffer);
+int ftb_exchange_wait_limit_ms(int ms);
 int ftb_exchange_push(const float *state, int64_t elems, void *const *buffers, int rank, int world,
                       int reverse, void *stream);
 int ftb_exchange_receive(void *buffer, float *out, int64_t elems, int rank, int world, int reverse,
@@ -292,8 +303,8 @@ int ftb_exchange_receive(void *buffer, float *out, int64_t elems, int rank, int 
  *   - limit: the scratch need, ftb_causal_workspace_bytes(N,H,L,D,M,dtype,mode,0,0), must not
  *     exceed FTB_STATIC_SCRATCH_BYTES (16 MiB); larger problems return FTB_ERR_STATIC_LIMIT and
  *     enqueue nothing.  Every GPU that loads the library holds those 16 MiB until exit.
- *   - the first call on a device (and the first call of each host thread) resolves the array's
- *     device address synchronously; make that call before starting any stream capture.
+ *   - the first call on a device resolves the array's device address synchronously (once per
+ *     device, whichever host thread makes it); make that call before starting any stream capture.
  *   - all calls on a device share the one array: calls whose kernels can overlap on the GPU
  *     (different streams, no ordering between them) race on it and must be serialised by the
  *     caller.  Stale contents from an earlier call are harmless -- each call writes what it reads.
