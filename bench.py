@@ -57,6 +57,10 @@ def parse():
     ap.add_argument("--graph-steps", type=int, default=0,
                     help="steps captured per CUDA graph (default: the largest divisor of --steps that keeps "
                          "the graph under about 8 ms, at most 10)")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the additional records of a default run: on one GPU configs 1, 4 and 5 "
+                         "(`configs`), on several GPUs config 4 with the sequence split over the ranks "
+                         "(`sequence_parallel`)")
     ap.add_argument("--layers", type=int, default=None, help="config 3: override the layer count")
     ap.add_argument("--batch", type=int, default=None, help="config 3: override the batch size")
     return ap.parse_args()
@@ -438,6 +442,218 @@ def run_recurrent(args):
     return 0
 
 
+
+# ------------------------------------------------------------------------------------------
+# helpers shared by the legs of the GPU arm
+# ------------------------------------------------------------------------------------------
+def hbm_peak():
+    """(GB/s, where the figure comes from)"""
+    ppath = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(ppath):
+        peaks = json.load(open(ppath))
+        if "hbm_gbs" in peaks:
+            return float(peaks["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback 6650 GB/s"
+
+
+def time_steps(step, steps, warmup, dev, dist=None, graph_steps=0):
+    """Device time per step of ``step()`` (CUDA events on the current stream, max over ranks):
+    ``warmup`` untimed steps, then ``steps`` timed ones; with ``graph_steps`` > 0 that many steps
+    are captured into one CUDA graph which is replayed ``steps // graph_steps`` times."""
+    for _ in range(max(warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    graph = None
+    if graph_steps:
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(graph_steps):
+                step()
+        for _ in range(3):
+            graph.replay()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    if graph is not None:
+        n = max(1, steps // graph_steps)
+        for _ in range(n):
+            graph.replay()
+        done = n * graph_steps
+    else:
+        for _ in range(steps):
+            step()
+        done = steps
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / done], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+    return t.item()
+
+
+def oracle_errors(Q, K, V, G, got, heads, chunk=512):
+    """max|x - x64| / max|x64| of (out, gQ, gK, gV) on the (batch 0) heads ``heads`` against the
+    fp64 blocked recurrence on the host (every core: a launcher may have set OMP_NUM_THREADS=1)."""
+    from oracle import causal_oracle as orc
+    use_all_host_threads()
+    errs = dict.fromkeys(("out", "gQ", "gK", "gV"), 0.0)
+    for i, h in enumerate(heads):
+        sub = [t[:1, h:h + 1].float().cpu() for t in (Q, K, V, G)]
+        want = (orc.chunked_forward(*sub[:3], chunk=chunk),) + tuple(orc.chunked_backward(*sub, chunk=chunk))
+        for name, a, b in zip(errs, got, want):
+            errs[name] = max(errs[name], orc.rel_err(a[:1, i:i + 1], b))
+    return errs
+
+
+def product_record(cfg, mode, dev, steps, heads=None, trial=0):
+    """One more configuration on this GPU: device-resident fwd+bwd through the autograd Function,
+    captured in a CUDA graph; with ``heads`` also the error of those heads against the fp64 oracle."""
+    import fast_transformers_b200 as ftb
+    from fast_transformers_b200 import workloads
+    from fast_transformers_b200.causal_product import causal_dot_product
+    shape = workloads.SHAPES[cfg]
+    Q, K, V, G = workloads.make_inputs(cfg, trial=trial)
+    Qd, Kd, Vd, Gd = (t.to(dev) for t in (Q, K, V, G))
+    Qd.requires_grad_(True), Kd.requires_grad_(True), Vd.requires_grad_(True)
+    last = {}
+
+    def step():
+        Qd.grad = Kd.grad = Vd.grad = None
+        with ftb.mode(mode):
+            out = causal_dot_product(Qd, Kd, Vd)
+            out.backward(Gd)
+        last["out"] = out
+
+    step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    step()
+    e1.record()
+    torch.cuda.synchronize()
+    per_graph = max(1, min(10, int(8.0 / max(e0.elapsed_time(e1), 1e-3))))
+    n = max(steps, per_graph) // per_graph * per_graph
+    ms = time_steps(step, n, 3, dev, graph_steps=per_graph)
+    token_heads = shape["N"] * shape["H"] * shape["L"]
+    alg = workloads.algorithmic_bytes(shape["D"], shape["M"], Qd.element_size()) * token_heads
+    peak, _ = hbm_peak()
+    rec = {"workload": workload_name(cfg, shape), "mode": mode, "ms_per_step": ms,
+           "value": shape["N"] * shape["L"] / (ms * 1e-3) / 1e6, "unit": UNIT,
+           "steps": n, "steps_per_graph": per_graph, "algorithmic_bytes": alg,
+           "achieved_GBps": alg / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": alg / (ms * 1e-3) / 1e9 / peak}
+    if heads:
+        got = [t[:1, heads].detach() for t in (last["out"], Qd.grad, Kd.grad, Vd.grad)]
+        rec["rel_err_vs_fp64"] = oracle_errors(Q, K, V, G, got, heads)
+        rec["rel_err_heads"] = list(heads)
+        rec["tolerance_vs_fp64"] = 1e-5 if mode == "fp32" else 2e-2
+    return rec
+
+
+def sequence_parallel_record(args, dev, dist, rank, world, mode, lib):
+    """Config 4 (ONE sequence of 262 144 positions, 16 heads, D = M = 128, bf16) with the sequence
+    split over the ranks: every rank holds L / world positions, one exchange of the (N,H,D,M)
+    fp32 states per direction.  Reports the time of the split step (max over ranks), the time of
+    the SAME whole sequence on rank 0 alone in this process, the efficiency t1 / (world * tN), and
+    the error of two heads against the fp64 oracle of the whole sequence."""
+    import fast_transformers_b200 as ftb
+    from fast_transformers_b200 import workloads
+    from fast_transformers_b200.causal_product import causal_dot_product
+    from fast_transformers_b200.sequence_parallel import (LocalOps, PeerExchange,
+                                                          sequence_parallel_causal_dot_product)
+    shape = dict(workloads.SHAPES[4])
+    L = shape["L"]
+    if L % world:
+        return {"skipped": "sequence length %d does not divide over %d ranks" % (L, world)}
+    Lr = L // world
+    Q, K, V, G = (t.to(dev) for t in workloads.make_inputs(4, trial=rank, scale_L=Lr))
+    Q.requires_grad_(True), K.requires_grad_(True), V.requires_grad_(True)
+    ops = LocalOps(mode)
+    exchange = PeerExchange((shape["N"], shape["H"], shape["D"], shape["M"])) if args.exchange == "peer" else None
+    last = {}
+
+    def step():
+        Q.grad = K.grad = V.grad = None
+        with ftb.mode(mode):
+            out = sequence_parallel_causal_dot_product(Q, K, V, ops=ops, exchange=exchange)
+            out.backward(G)
+        last["out"] = out
+
+    steps = max(args.steps, 10)
+    graph_steps = 0
+    if exchange is not None and args.sp_graph:
+        graph_steps = next(d for d in range(min(10, steps), 0, -1) if steps % d == 0)
+    valid, why = True, None
+    try:
+        step()
+        if exchange is not None:
+            exchange.check()
+        tN = time_steps(step, steps, 3, dev, dist, graph_steps=graph_steps)
+        if exchange is not None:
+            exchange.check()        # a receive that gave up waiting leaves NaN and a status word
+        else:
+            ftb.check_device_status(dev)
+    except Exception as e:          # reported, not hidden: the record is marked invalid
+        valid, why, tN = False, "%s: %s" % (type(e).__name__, e), float("nan")
+    flag = torch.tensor([0 if valid else 1], device=dev)
+    dist.all_reduce(flag)
+    if flag.item():
+        if exchange is not None:
+            exchange.close()
+        return {"valid": False, "error": why or "another rank failed"}
+
+    # the whole sequence on rank 0: inputs and the split results of two heads
+    heads = [0, 11]
+    full, got = None, None
+    gathered = []
+    for t in (Q.detach(), K.detach(), V.detach(), G):
+        parts = [torch.empty_like(t) for _ in range(world)] if rank == 0 else None
+        dist.gather(t.contiguous(), parts, dst=0)
+        gathered.append(torch.cat(parts, dim=2) if rank == 0 else None)
+    split = []
+    for t in (last["out"].detach(), Q.grad, K.grad, V.grad):
+        piece = t[:, heads].contiguous()
+        parts = [torch.empty_like(piece) for _ in range(world)] if rank == 0 else None
+        dist.gather(piece, parts, dst=0)
+        split.append(torch.cat(parts, dim=2) if rank == 0 else None)
+    rec = None
+    if rank == 0:
+        Qf, Kf, Vf, Gf = gathered
+        Qf.requires_grad_(True), Kf.requires_grad_(True), Vf.requires_grad_(True)
+
+        def whole():
+            Qf.grad = Kf.grad = Vf.grad = None
+            with ftb.mode(mode):
+                causal_dot_product(Qf, Kf, Vf).backward(Gf)
+
+        t1 = time_steps(whole, 6, 3, dev, graph_steps=2)
+        errs = oracle_errors(Qf.detach(), Kf.detach(), Vf.detach(), Gf, split, heads)
+        token_heads = shape["N"] * shape["H"] * L
+        alg = workloads.algorithmic_bytes(shape["D"], shape["M"], 2) * token_heads
+        peak, _ = hbm_peak()
+        rec = {"valid": True, "workload": workload_name(4, shape) + ", sequence split over %d ranks" % world,
+               "mode": mode, "ms_per_step": tN, "value": shape["N"] * L / (tN * 1e-3) / 1e6, "unit": UNIT,
+               "steps": steps, "cuda_graph": bool(graph_steps), "positions_per_rank": Lr,
+               "exchange": ("stores into the peers' buffers by this library's kernels (PeerExchange)"
+                            if exchange is not None else "all_gather of the per-rank states (NCCL)"),
+               "t1_ms": t1, "t1_how": "the same sequence on rank 0 alone, same process, CUDA graph of 2 steps",
+               "efficiency": t1 / (world * tN), "efficiency_formula": "t1_ms / (n_gpus * ms_per_step)",
+               "frac_of_hbm_peak_per_gpu": alg / world / (tN * 1e-3) / 1e9 / peak,
+               "rel_err_vs_fp64": errs, "rel_err_heads": heads, "tolerance_vs_fp64": 2e-2}
+    dist.barrier()
+    if exchange is not None:
+        exchange.close()
+    return rec
+
+
 # ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
@@ -531,6 +747,8 @@ def main():
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    if seq_parallel and sp_exchange is not None:
+        sp_exchange.check()      # raises if a receive gave up waiting for a peer during warm-up
     # One step is a handful of launches of ~50 us each, so the host would set the pace: the
     # step is captured once into a CUDA graph (native launches go to the capturing stream like
     # any other) and replayed.  --no-graph times the eager calls instead.
@@ -589,6 +807,12 @@ def main():
                 else lib.ftb_launch_count() - launches0)
     barrier()
     clocks = sampler.stop() if sampler else None
+    # no kernel of the timed region gave up a bounded wait (a timed-out exchange leaves NaN
+    # behind and a status word; the number would be meaningless)
+    if seq_parallel and sp_exchange is not None:
+        sp_exchange.check()
+    else:
+        ftb.check_device_status(dev)
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -611,48 +835,71 @@ def main():
                                  forward_workspace=kept[0] if kept else None)
     kinds = _native.timing_read()
     lib.ftb_timing_enable(0)
-    peaks = {}
-    ppath = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(ppath):
-        peaks = json.load(open(ppath))
-    peak_gbs = peaks.get("hbm_gbs", 6650.0)
-    peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+    peak_gbs, peak_src = hbm_peak()
     total_kernel_ms = sum(v[0] for v in kinds.values()) or 1.0
     top = max(kinds.items(), key=lambda kv: kv[1][0]) if kinds else ("none", (0.0, 0))
     top_name, (top_ms, top_n) = top
-    # algorithmic bytes one launch of the dominant kernel moves: every launch of a scan
-    # kernel reads three operand tensors and writes one (forward: Q,K,V -> out, and the three
-    # gradient scans likewise); the fused tensor-core kernels move the whole pass.
+    # Algorithmic bytes of one launch: every DISTINCT tensor the grid reads or writes, once
+    # (elements per token-head; D-wide: Q, K, grad_Q, grad_K; M-wide: V, grad_out, out, grad_V).
     D, M = shape["D"], shape["M"]
+    with_qr = "mma_bwd_qr" in kinds
     per_launch_elems = {
-        "simt_scan": (2 * D + 2 * M),               # averaged over the four role permutations
-        "mma_fwd": (2 * D + 2 * M),
+        "simt_scan": (2 * D + 2 * M),               # three operand tensors in, one out (averaged
+                                                    # over the four role permutations)
+        "mma_fwd": (2 * D + 2 * M),                 # Q, K, V -> out
         "mma_bwd": (2 * D + 2 * M),
         "state_sum": (D + M),
-        "mma_state": (D + M),
-        # one grid with the grad_Q scan and the state-only sweep of (Q, grad_out): only the
-        # scan's bytes are counted
-        "mma_bwd_qr": (2 * D + 2 * M),
-        # one grid with grad_K and grad_V (and grad_Q when no sweep is needed)
-        "mma_bwd_multi": (2 if "mma_bwd_qr" in kinds else 3) * (2 * D + 2 * M),
+        "mma_state": (D + M),                       # K, V (or Q, grad_out) -> totals
+        # grad_Q scan (grad_out, V, K -> grad_Q) with the sweep of (Q, grad_out) beside it
+        "mma_bwd_qr": (3 * D + 2 * M),
+        # grad_K and grad_V in one grid: Q, K, V, grad_out -> grad_K, grad_V; with grad_Q in the
+        # same grid (no sweep needed) one more output
+        "mma_bwd_multi": (3 * D + 3 * M) if with_qr else (4 * D + 3 * M),
     }.get(top_name, 0)
     alg_bytes_launch = per_launch_elems * esize * token_heads
     avg_ms = top_ms / top_n if top_n else 0.0
     achieved = alg_bytes_launch / (avg_ms * 1e-3) / 1e9 if avg_ms else 0.0
     step_alg_bytes = workloads.algorithmic_bytes(D, M, esize) * token_heads
+    fwd_ms = sum(kinds.get(k, (0.0, 0))[0] for k in ("mma_state", "mma_fwd")) / args.steps
+    bwd_ms = sum(kinds.get(k, (0.0, 0))[0] for k in ("mma_bwd", "mma_bwd_qr", "mma_bwd_multi")) / args.steps
+    if mode != "mma":
+        fwd_ms = bwd_ms = 0.0     # the fp32 kernels are not told apart by direction
+
+    def frac_of(elems, ms_):
+        if not ms_:
+            return None
+        return elems * esize * token_heads / (ms_ * 1e-3) / 1e9 / peak_gbs
+
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu capture
+    # recorded in profiles/dram_bytes_per_launch.json -- reported only while the kernel source is
+    # the one that capture was taken from
+    traffic, traffic_note = None, "no ncu capture recorded for this kernel and workload"
+    tpath = os.path.join(ROOT, "profiles", "dram_bytes_per_launch.json")
+    if os.path.exists(tpath) and not args.L:
+        import hashlib
+        table = json.load(open(tpath))
+        src = os.path.join(ROOT, "fast-transformers_b200", "csrc", table.get("source_file", ""))
+        sha = hashlib.sha256(open(src, "rb").read()).hexdigest()[:16] if os.path.isfile(src) else None
+        entry = table.get("entries", {}).get("config%d/%s/%s" % (args.config, mode, top_name))
+        if entry is not None and sha == table.get("source_sha16"):
+            traffic, traffic_note = entry["dram_bytes"], entry.get("from")
+        elif entry is not None:
+            traffic_note = "the recorded capture predates the current kernel source"
     roofline = {
         "bound": "hbm", "kernel": top_name, "achieved": achieved, "peak": peak_gbs,
         "unit": "GB/s", "frac": achieved / peak_gbs if peak_gbs else None,
-        "peak_source": peak_src,
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel from the
-        # committed ncu capture of the same workload (profiles/); None where none was taken
-        "traffic": {(2, "mma", "mma_fwd"): 247.8e6, (2, "mma", "mma_bwd_qr"): 308.7e6,
-                    (2, "mma", "mma_bwd_multi"): 376.4e6, (2, "mma", "mma_state"): 68.6e6}.get(
-            (args.config, mode, top_name)) if not args.L else None,
+        "peak_source": peak_src, "traffic": traffic, "traffic_source": traffic_note,
         "algorithmic_bytes_per_launch": alg_bytes_launch,
+        "algorithmic_bytes_rule": "every distinct tensor a grid reads or writes, once",
         "avg_launch_ms": avg_ms, "share_of_kernel_time": top_ms / total_kernel_ms,
         "kernels": {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
                     for k, v in kinds.items()},
+        "forward": {"algorithmic_bytes": (2 * D + 2 * M) * esize * token_heads,
+                    "kernel_ms": fwd_ms or None, "frac_of_hbm_peak": frac_of(2 * D + 2 * M, fwd_ms),
+                    "how": "sum of the forward's launches, each timed alone by CUDA events"},
+        "backward": {"algorithmic_bytes": (4 * D + 3 * M) * esize * token_heads,
+                     "kernel_ms": bwd_ms or None, "frac_of_hbm_peak": frac_of(4 * D + 3 * M, bwd_ms),
+                     "how": "sum of the backward's launches, each timed alone by CUDA events"},
         "whole_step": {"algorithmic_bytes": step_alg_bytes,
                        "achieved_GBps": step_alg_bytes / (ms_step * 1e-3) / 1e9,
                        "frac_of_hbm_peak": step_alg_bytes / (ms_step * 1e-3) / 1e9 / peak_gbs,
@@ -734,6 +981,18 @@ def main():
                         "sample": "%d timed steps of the full workload (%s) after 1 warm-up, "
                                   "median" % (nst, name), "ms_per_step": sec * 1e3}
 
+    # ---- further records of a default run ------------------------------------------------
+    configs_rec, sp_rec = None, None
+    if args.config == 2 and not args.no_extra and not args.L and mode == "mma":
+        if world == 1:
+            # the other single-GPU configurations, device-resident (config 4 with two heads checked
+            # against the fp64 oracle at its full length)
+            configs_rec = {"config1": product_record(1, mode, dev, 200),
+                           "config4": product_record(4, mode, dev, 6, heads=[0, 11]),
+                           "config5": product_record(5, mode, dev, 10)}
+        else:
+            sp_rec = sequence_parallel_record(args, dev, dist, rank, world, mode, lib)
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
@@ -756,6 +1015,10 @@ def main():
             "gpu_launches": int(launches), "clocks": clocks, "other_mode": other,
             "tolerance_vs_fp64": 1e-5 if mode == "fp32" else 2e-2,
         }
+        if configs_rec is not None:
+            line["configs"] = configs_rec
+        if sp_rec is not None:
+            line["sequence_parallel"] = sp_rec
         print(json.dumps(line))
     if seq_parallel and sp_exchange is not None:
         sp_exchange.close()

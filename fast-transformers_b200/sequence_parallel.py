@@ -100,9 +100,10 @@ class PeerExchange(object):
     All ranks of ``group`` must be processes of ONE node, each on a GPU of its own, and must
     construct, use (same order of calls) and ``close`` the object together; construction and
     ``close`` contain host collectives (the exchange of the buffers' IPC handles, barriers).
-    A rank that never delivers makes the others' receive give up after about a second: the
-    result is then not written and ``ftb_device_status`` reports the timeout (checked by
-    ``check()``, which synchronises)."""
+    A rank that never delivers makes the others' receive give up after about a second
+    (``ftb_exchange_wait_limit_ms``): the result is then NaN and ``ftb_device_status`` reports the
+    timeout.  The kernels cannot raise, so call ``check()`` (it synchronises the device) before a
+    step's results are trusted -- once per step, or once per timed region in a benchmark."""
 
     def __init__(self, state_shape, group=None, device=None):
         from . import _native
@@ -160,7 +161,9 @@ class PeerExchange(object):
         return out
 
     def check(self):
-        """Synchronise this device and raise if a receive gave up waiting for a peer."""
+        """Synchronise this device (all streams) and raise if a push or receive gave up waiting
+        for a peer."""
+        torch.cuda.synchronize(self.device)
         with torch.cuda.device(self.device):
             self._native.check(self._lib.ftb_device_status(1), "sequence-parallel exchange")
 

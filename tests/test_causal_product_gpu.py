@@ -239,3 +239,23 @@ def test_linearity_property_config2_fp32():
     assert orc.rel_err(o1[:, :, -1:], last) < 1e-5
     first = (Q[:, :, :1].double() * K[:, :, :1].double()).sum(-1, keepdim=True) * V[:, :, :1].double()
     assert orc.rel_err(o1[:, :, :1], first) < 1e-6
+
+
+@pytest.mark.parametrize("mode", ["fp32", "mma"])
+def test_inputs_whose_last_dimension_is_not_contiguous(mode):
+    """Q, K, V given as transposes (last stride != 1): the reference accepts any strides through
+    its accessors (causal_product_cpu.cpp:88-99); here such inputs are copied row-major and the
+    results come back in row-major buffers."""
+    g = torch.Generator().manual_seed(77)
+    N, H, L, D = 1, 2, 300, 64
+    Qt, Kt, Vt, Gt = (torch.rand(N, H, D, L, generator=g) for _ in range(4))
+    Q, K, V, G = (t.transpose(-1, -2) for t in (Qt, Kt, Vt, Gt))
+    assert Q.stride(3) != 1
+    q, k, v = (t.cuda().transpose(-1, -2).requires_grad_(True) for t in (Qt, Kt, Vt))
+    with ftb.mode(mode):
+        out = causal_dot_product(q, k, v)
+        out.backward(Gt.cuda().transpose(-1, -2))
+    torch.cuda.synchronize()
+    want = (orc.dense_forward(Q, K, V),) + tuple(orc.dense_backward(Q, K, V, G))
+    for name, a, b in zip(("out", "gQ", "gK", "gV"), (out, q.grad, k.grad, v.grad), want):
+        assert orc.rel_err(a, b) < TOL[mode], name

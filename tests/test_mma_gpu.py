@@ -243,3 +243,46 @@ def test_linearity_config2_full_size_tf32():
     assert orc.rel_err(o1[:, :, -1:], Q[:, :, -1:].double() @ S) < TOL
     first = (Q[:, :, :1].double() * K[:, :, :1].double()).sum(-1, keepdim=True) * V[:, :, :1].double()
     assert orc.rel_err(o1[:, :, :1], first) < TOL
+
+
+def test_kept_states_are_read_in_the_layout_they_were_written_in():
+    """Two (batch, head) pairs, L = 2048: eight segments per pair and two state blocks per segment.
+    Whoever wrote the per-segment states -- a forward call that also returns its final state, or
+    ``causal_state_sum`` followed by a forward call that reuses its workspace -- the backward call
+    given that workspace must read them as they were written (against the oracle, all gradients)."""
+    g = torch.Generator().manual_seed(41)
+    N, H, L, D = 1, 2, 2048, 64
+    Q, K, V, G = (torch.rand(N, H, L, D, generator=g) for _ in range(4))
+    Qd, Kd, Vd, Gd = (t.cuda() for t in (Q, K, V, G))
+    want = oracle(Q, K, V, G)
+
+    def backward_with(ws):
+        grads = [torch.full_like(t, float("nan")) for t in (Qd, Kd, Vd)]
+        causal_dot_backward_cuda(Qd, Kd, Vd, Gd, *grads, "mma", forward_workspace=ws)
+        return grads
+
+    # (a) forward with final_state, workspace kept, backward reuses it
+    out = torch.empty_like(Vd)
+    fin = torch.empty(N, H, D, D, device="cuda")
+    kept = []
+    causal_dot_product_cuda(Qd, Kd, Vd, out, "mma", final_state=fin, keep_workspace=kept)
+    assert kept[0] is not None
+    for name, a, b in zip(NAMES, [out] + backward_with(kept[0]), want):
+        assert orc.rel_err(a, b) < TOL, "(a) " + name
+    assert orc.rel_err(fin, orc.local_states(None, K, V)) < TOL
+    # (b) causal_state_sum first, forward on its workspace, backward reuses it
+    from fast_transformers_b200.causal_product import workspace_bytes
+    ws = torch.empty(workspace_bytes(N, H, L, D, D, torch.float32, "mma", want_state=True),
+                     dtype=torch.uint8, device="cuda")
+    total = causal_state_sum(Kd, Vd, mode="mma", workspace=ws)
+    assert orc.rel_err(total, fin) < 1e-5
+    out2 = torch.full_like(Vd, float("nan"))
+    causal_dot_product_cuda(Qd, Kd, Vd, out2, "mma", workspace=ws, workspace_has_states=True)
+    for name, a, b in zip(NAMES, [out2] + backward_with(ws), want):
+        assert orc.rel_err(a, b) < TOL, "(b) " + name
+    # (c) the plain forward's workspace (no final state)
+    kept = []
+    out3 = torch.empty_like(Vd)
+    causal_dot_product_cuda(Qd, Kd, Vd, out3, "mma", keep_workspace=kept)
+    for name, a, b in zip(NAMES, [out3] + backward_with(kept[0]), want):
+        assert orc.rel_err(a, b) < TOL, "(c) " + name
