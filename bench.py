@@ -531,7 +531,7 @@ def product_record(cfg, mode, dev, steps, heads=None, trial=0):
         with ftb.mode(mode):
             out = causal_dot_product(Qd, Kd, Vd)
             out.backward(Gd)
-        last["out"] = out
+        last["out"] = out.detach()   # (not `out`: it would keep the autograd graph of the step alive)
 
     step()
     torch.cuda.synchronize()
@@ -585,7 +585,7 @@ def sequence_parallel_record(args, dev, dist, rank, world, mode, lib):
         with ftb.mode(mode):
             out = sequence_parallel_causal_dot_product(Q, K, V, ops=ops, exchange=exchange)
             out.backward(G)
-        last["out"] = out
+        last["out"] = out.detach()   # (not `out`: it would keep the autograd graph of the step alive)
 
     steps = max(args.steps, 10)
     graph_steps = 0

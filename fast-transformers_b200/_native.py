@@ -28,11 +28,11 @@ EXPORTS = (
     "ftb_elu_feature_map", "ftb_elu_feature_map_backward",
     "ftb_exchange_bytes", "ftb_exchange_create", "ftb_exchange_open", "ftb_exchange_close",
     "ftb_exchange_destroy", "ftb_exchange_push", "ftb_exchange_receive",
-    "ftb_exchange_wait_limit_ms",
+    "ftb_exchange_wait_limit_ms", "ftb_linear_apply_state", "ftb_recurrent_cross_linear_step",
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
                 "mma_bwd_qr", "mma_bwd_multi", "recurrent_step", "normaliser", "feature_map",
-                "rank_exchange")
+                "rank_exchange", "apply_state")
 
 _lib = None
 _i64, _vp, _int, _sz = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
@@ -102,6 +102,11 @@ def lib():
     L.ftb_exchange_push.argtypes = [_vp, _i64, ctypes.POINTER(_vp), _int, _int, _int, _vp]
     L.ftb_exchange_receive.restype = _int
     L.ftb_exchange_receive.argtypes = [_vp, _vp, _i64, _int, _int, _int, _vp]
+    L.ftb_linear_apply_state.restype = _int
+    L.ftb_linear_apply_state.argtypes = [_vp] * 3 + [_i64] * 5 + [_i64p] * 2 + [_int, _int, _int, _vp]
+    L.ftb_recurrent_cross_linear_step.restype = _int
+    L.ftb_recurrent_cross_linear_step.argtypes = (
+        [_vp] * 4 + [_i64] * 4 + [_i64p] * 2 + [_int, _int, ctypes.c_float, _vp])
     L.ftb_exchange_wait_limit_ms.restype = _int
     L.ftb_exchange_wait_limit_ms.argtypes = [_int]
     L.ftb_launch_count.restype = ctypes.c_uint64

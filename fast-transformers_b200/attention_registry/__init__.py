@@ -135,3 +135,5 @@ AttentionRegistry = Registry()
 # attention implementations that process one position at a time and carry a state
 # (fast_transformers/attention_registry/__init__.py:12-15)
 RecurrentAttentionRegistry = Registry()
+# attention over a fixed memory, one query per call (same file, :16)
+RecurrentCrossAttentionRegistry = Registry()

@@ -10,6 +10,7 @@
 #include <mutex>
 #include <vector>
 
+#include "apply_state.cuh"
 #include "feature_map.cuh"
 #include "mma_host.cuh"
 #include "rank_exchange.cuh"
@@ -176,6 +177,7 @@ struct MmaBatch {
     int dtype = FTB_F32;
     int kind = FTB_KERNEL_MMA_FWD;
     bool after_own_launch = false;   // see mma::launch_t
+    bool apply = false;              // out = a S_init only (the APPLY instantiation)
     MmaBatch() { b.njobs = 0; b.first_block[0] = 0; b.interleave = 0; b.wait_first = 0; }
 };
 
@@ -186,6 +188,7 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
                        const float *states, const float *init, int sum_mode, int sub, float *state_out,
                        int skip_lo, int skip_hi, int canon_is_DaDc, int reverse) {
     const bool state_only = (a == nullptr);
+    const bool apply_only = (b == nullptr);   // out = a S_init: only `a` is read
     const int DCT = dtype == FTB_F32 ? 64 : 128;
     // fp32 (TF32) operands read MN-major need the 32-byte-atom swizzle; bf16 uses one image
     const bool atom32 = dtype == FTB_F32;
@@ -195,18 +198,26 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
     if (batch.b.first_block[batch.b.njobs] + blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
     mma::ScanJob &J = batch.b.job[batch.b.njobs];
     mma::ScanParams &p = J.p;
-    int rc = mma::make_map(&J.mb, p.pos_b, b, N, H, L, Da, bs, dtype, false);
-    if (rc) return rc;
-    rc = mma::make_map(&J.mbmn, p.pos_b, b, N, H, L, Da, bs, dtype, atom32);
-    if (rc) return rc;
-    rc = mma::make_map(&J.mc, p.pos_c, c, N, H, L, Dc, cs, dtype, atom32);
-    if (rc) return rc;
+    int rc = FTB_OK;
+    if (!apply_only) {
+        rc = mma::make_map(&J.mb, p.pos_b, b, N, H, L, Da, bs, dtype, false);
+        if (rc) return rc;
+        rc = mma::make_map(&J.mbmn, p.pos_b, b, N, H, L, Da, bs, dtype, atom32);
+        if (rc) return rc;
+        rc = mma::make_map(&J.mc, p.pos_c, c, N, H, L, Dc, cs, dtype, atom32);
+        if (rc) return rc;
+    }
     if (state_only) {
         J.ma = J.mb;
         for (int i = 0; i < 3; ++i) p.pos_a[i] = p.pos_b[i];
     } else {
         rc = mma::make_map(&J.ma, p.pos_a, a, N, H, L, Da, as, dtype);
         if (rc) return rc;
+        if (apply_only) {
+            J.mb = J.mbmn = J.mc = J.ma;   // never dereferenced by the APPLY instantiation
+            for (int i = 0; i < 3; ++i) p.pos_b[i] = p.pos_c[i] = p.pos_a[i];
+            batch.apply = true;
+        }
         const int64_t es = dtype == FTB_F32 ? 4 : 2;
         if (((uintptr_t)out & 15) || (os[0] * es) % 16 || (os[1] * es) % 16 || (os[2] * es) % 16) {
             if (std::getenv("FTB200_DEBUG"))
@@ -223,7 +234,6 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
     p.init = init; p.sum_mode = sum_mode; p.sub = sub < 1 ? 1 : sub;
     p.skip_lo = skip_lo; p.skip_hi = skip_hi;
     p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = state_only ? 1 : 0;
-    p.terms = 7;
     if (batch.b.njobs == 0) {
         batch.dtype = dtype;
         batch.kind = state_only ? FTB_KERNEL_MMA_STATE : (reverse ? FTB_KERNEL_MMA_BWD : FTB_KERNEL_MMA_FWD);
@@ -244,7 +254,13 @@ static int mma_launch_batch(MmaBatch &batch, cudaStream_t st) {
     batch.b.interleave = equal ? 1 : 0;
     LaunchScope scope(batch.kind, st);
     cudaError_t e;
-    if (batch.dtype == FTB_F32)
+    if (batch.apply) {
+        batch.b.interleave = 0;
+        if (batch.dtype == FTB_F32)
+            e = mma::launch_t<float, 64, 64, true>(batch.b, st, false);
+        else
+            e = mma::launch_t<__nv_bfloat16, 128, 128, true>(batch.b, st, false);
+    } else if (batch.dtype == FTB_F32)
         e = mma::launch_t<float, 64, 64>(batch.b, st, batch.after_own_launch);
     else
         e = mma::launch_t<__nv_bfloat16, 128, 128>(batch.b, st, batch.after_own_launch);
@@ -930,6 +946,87 @@ int ftb_recurrent_linear_step(const void *q, const void *k, const void *v, float
         recurrent_step_kernel<__nv_bfloat16><<<(unsigned)(N * H), kStepThreads, 0, st>>>(
             (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v, S, z,
             (__nv_bfloat16 *)out, (int)H, (int)D, (int)M, a, b, c, o, feature_map, eps);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// One fixed state applied to every position (the non-causal form), and a read-only step.
+// ---------------------------------------------------------------------------------------------
+int ftb_linear_apply_state(const void *a, const float *state, void *out, int64_t N, int64_t H, int64_t L,
+                           int64_t Da, int64_t Dc, const int64_t *as, const int64_t *os, int dtype,
+                           int mode, int state_is_transposed, void *stream) {
+    if (N < 0 || H < 0 || L < 0 || Da < 0 || Dc < 0) return FTB_ERR_INVALID;
+    if (dtype != FTB_F32 && dtype != FTB_BF16) return FTB_ERR_INVALID;
+    if (mode != FTB_MODE_FP32_SIMT && mode != FTB_MODE_MMA) return FTB_ERR_INVALID;
+    if (!as || !os) return FTB_ERR_INVALID;
+    if (mode == FTB_MODE_MMA && Da > 0 && Dc > 0 && !mma::supported(dtype, Da, Dc)) return FTB_ERR_UNSUPPORTED;
+    if (N == 0 || H == 0 || L == 0 || Dc == 0) return FTB_OK;
+    if (!out || (Da > 0 && (!a || !state))) return FTB_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t es = dtype == FTB_F32 ? 4 : 2;
+    if (Da == 0) {   // nothing to contract: zeros
+        for (int64_t n = 0; n < N; ++n)
+            for (int64_t h = 0; h < H; ++h)
+                FTB_CUDA(cudaMemset2DAsync((char *)out + (n * os[0] + h * os[1]) * es, os[2] * es, 0,
+                                           Dc * es, L, st));
+        return FTB_OK;
+    }
+    if (mode == FTB_MODE_MMA) {
+        Plan pl = choose_plan(mode, N * H, L);
+        MmaBatch batch;
+        int rc = mma_add_job(batch, a, nullptr, nullptr, out, as, nullptr, nullptr, os, N, H, L, (int)Da,
+                             (int)Dc, dtype, pl, nullptr, state, 0, 1, nullptr, 0, 0,
+                             state_is_transposed ? 0 : 1, 0);
+        if (rc) return rc;
+        batch.kind = FTB_KERNEL_APPLY_STATE;
+        return mma_launch_batch(batch, st);
+    }
+    if (N * H > 65535) return FTB_ERR_UNSUPPORTED;
+    ApplyArgs p;
+    p.a = a; p.out = out; p.state = state;
+    p.sa = S3(as); p.so = S3(os);
+    p.H = (int)H; p.L = L; p.Da = (int)Da; p.Dc = (int)Dc;
+    p.canon_is_DaDc = state_is_transposed ? 0 : 1;
+    p.vec_out = dtype == FTB_F32 && Dc % 4 == 0 && ((uintptr_t)out & 15) == 0 && os[0] % 4 == 0 &&
+                os[1] % 4 == 0 && os[2] % 4 == 0;
+    const dim3 grid((unsigned)((L + kApplyRows - 1) / kApplyRows), (unsigned)((Dc + kApplyCols - 1) / kApplyCols),
+                    (unsigned)(N * H));
+    if (grid.y > 65535) return FTB_ERR_UNSUPPORTED;
+    LaunchScope scope(FTB_KERNEL_APPLY_STATE, st);
+    if (dtype == FTB_F32)
+        apply_state_kernel<float><<<grid, kApplyThreads, 0, st>>>(p);
+    else
+        apply_state_kernel<__nv_bfloat16><<<grid, kApplyThreads, 0, st>>>(p);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+
+int ftb_recurrent_cross_linear_step(const void *q, const float *S, const float *z, void *out, int64_t N,
+                                    int64_t H, int64_t D, int64_t M, const int64_t *qs, const int64_t *os,
+                                    int dtype, int feature_map, float eps, void *stream) {
+    if (N < 0 || H < 0 || D < 0 || M < 0) return FTB_ERR_INVALID;
+    if (dtype != FTB_F32 && dtype != FTB_BF16) return FTB_ERR_INVALID;
+    if (feature_map != FTB_FEATURE_NONE && feature_map != FTB_FEATURE_ELU1) return FTB_ERR_INVALID;
+    if (!qs || !os) return FTB_ERR_INVALID;
+    if (D > kStepMaxD) return FTB_ERR_UNSUPPORTED;
+    if (N == 0 || H == 0 || M == 0) return FTB_OK;
+    if (N * H > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
+    if (!out || (D > 0 && (!q || !S || !z))) return FTB_ERR_INVALID;
+    if (M % 4 == 0 && ((uintptr_t)S & 15)) return FTB_ERR_ALIGNMENT;
+    cudaStream_t st = (cudaStream_t)stream;
+    const Strides2 a{qs[0], qs[1]}, o{os[0], os[1]}, none{0, 0};
+    // the read-only instantiation never writes through its state pointers
+    float *Sw = const_cast<float *>(S), *zw = const_cast<float *>(z);
+    LaunchScope scope(FTB_KERNEL_RECURRENT_STEP, st);
+    if (dtype == FTB_F32)
+        recurrent_step_kernel<float, false><<<(unsigned)(N * H), kStepThreads, 0, st>>>(
+            (const float *)q, nullptr, nullptr, Sw, zw, (float *)out, (int)H, (int)D, (int)M, a, none, none, o,
+            feature_map, eps);
+    else
+        recurrent_step_kernel<__nv_bfloat16, false><<<(unsigned)(N * H), kStepThreads, 0, st>>>(
+            (const __nv_bfloat16 *)q, nullptr, nullptr, Sw, zw, (__nv_bfloat16 *)out, (int)H, (int)D, (int)M, a,
+            none, none, o, feature_map, eps);
     FTB_CUDA(cudaGetLastError());
     return FTB_OK;
 }

@@ -161,10 +161,10 @@ static bool supported(int dtype, int64_t Da, int64_t Dc) {
 // read what it wrote.  Otherwise they wait for it before they touch global memory at all
 // (ScanBatch::wait_first), which is safe behind any kernel and overlaps the block set-up only.
 // Environment (fault finding): FTB200_NO_PDL=1 ordinary launches throughout.
-template <typename T, int DA, int DCT>
+template <typename T, int DA, int DCT, bool APPLY = false>
 static cudaError_t launch_t(ScanBatch &batch, cudaStream_t st, bool after_own_launch) {
     using K = Cfg<T, DA, DCT>;
-    auto kern = mma_scan_kernel<T, DA, DCT>;
+    auto kern = mma_scan_kernel<T, DA, DCT, APPLY>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)K::SMEM);
     if (e != cudaSuccess) return e;
     static const char *no_pdl = std::getenv("FTB200_NO_PDL");

@@ -65,7 +65,6 @@ struct ScanParams {
     int canon_is_DaDc;    // canonical block is [DA][Dc] (1) or [Dc][DA] (0)
     int reverse;
     int state_only;
-    int terms;            // bit0: a S term, bit1: mask(P) c term, bit2: state update
     int pos_a[3], pos_b[3], pos_c[3];   // TMA coordinate slot of {position, head, batch}
 };
 
@@ -346,10 +345,13 @@ struct Cfg {
     static_assert(TM_S + (REG_STATE ? 2 : 1) * DCT <= 512, "tensor memory budget");
 };
 
-template <typename T, int DA, int DCT>
+// APPLY: the instantiation that computes out = a S_init only -- no scores, no state update; b and c
+// are not read (a compile-time switch, so that the scan's own code is untouched by it).
+template <typename T, int DA, int DCT, bool APPLY = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
 mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
     using K = Cfg<T, DA, DCT>;
+    constexpr bool apply_only = APPLY;
     // which job this block belongs to (everything below is per job)
     int job = 0, job_block = 0;
     if (batch.interleave) {
@@ -417,7 +419,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
         *abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 2);   // released by both issuers
+            mbar_init(bar_empty + 8 * s, apply_only ? 1 : 2);   // released by both issuers
             mbar_init(bar_pfree + 8 * s, 1);
             mbar_init(bar_tfull + 8 * s, 1);
             mbar_init(bar_tfree + 8 * s, 128);
@@ -506,6 +508,11 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     if (!ok) break;
                     const int row = (int)(seg_begin + (int64_t)c * C);
                     const uint32_t st = stage0 + s * K::STAGE_BYTES;
+                    if constexpr (apply_only) {
+                        mbar_expect_tx(bar_full + 8 * s, K::A_BYTES);
+                        load_tile(st, &map_a, bar_full + 8 * s, 0, p.pos_a, row, K::A_BLKS);
+                        continue;
+                    }
                     mbar_expect_tx(bar_full + 8 * s, 2 * K::A_BYTES);
                     load_tile(st, &map_a, bar_full + 8 * s, 0, p.pos_a, row, K::A_BLKS);
                     load_tile(st + K::A_BYTES, &map_b, bar_full + 8 * s, 0, p.pos_b, row, K::A_BLKS);
@@ -566,22 +573,26 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         const uint32_t tO = tmem + K::TM_O + ob * DCT;
                         const uint32_t tP = tmem + K::TM_P + 128 * (ci & 1);
                         // O = a S: the a tile, the operand copy of the previous state, a free O
+                        // (apply only: the state operand is written once, before the first chunk)
                         ok = mbar_wait(bar_full + 8 * s, (ci >> 1) & 1, abort_flag) &&
-                             mbar_wait(bar_smready, ci & 1, abort_flag) &&
+                             ((apply_only && ci > 0) || mbar_wait(bar_smready, ci & 1, abort_flag)) &&
                              mbar_wait(bar_ofree + 8 * ob, (ouse & 1) ^ 1, abort_flag);
                         if (!ok) break;
                         tc_fence_after();
                         uint32_t acc = 0;
-                        if (p.terms & 1) {
 #pragma unroll
-                            for (int b = 0; b < K::A_BLKS; ++b)
+                        for (int b = 0; b < K::A_BLKS; ++b)
 #pragma unroll
-                                for (int k = 0; k < 4; ++k) {
-                                    const int krow = (b * K::EPB + k * K::KROWS);   // first state row
-                                    mma_ss<K::F16>(tO, a0 + (uint64_t)((b * K::BLK_BYTES + k * 32) >> 4),
-                                                   dSm + (uint64_t)((krow * 128) >> 4), ID_AS, acc);
-                                    acc = 1;
-                                }
+                            for (int k = 0; k < 4; ++k) {
+                                const int krow = (b * K::EPB + k * K::KROWS);   // first state row
+                                mma_ss<K::F16>(tO, a0 + (uint64_t)((b * K::BLK_BYTES + k * 32) >> 4),
+                                               dSm + (uint64_t)((krow * 128) >> 4), ID_AS, acc);
+                                acc = 1;
+                            }
+                        if constexpr (apply_only) {
+                            tc_commit(bar_ofull + 8 * ob);   // output workers
+                            tc_commit(bar_empty + 8 * s);    // the only release of the stage
+                            continue;
                         }
                         // the state operand in shared memory may now be replaced by the next state
                         tc_commit(bar_smfree);
@@ -590,18 +601,16 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                              mbar_wait(bar_fullc + 8 * s, (ci >> 1) & 1, abort_flag);
                         if (!ok) break;
                         tc_fence_after();
-                        if (p.terms & 2) {
 #pragma unroll
-                            for (int k = 0; k < C / K::KROWS; ++k) {
-                                mma_ts<K::F16>(tO, tP + k * 8, c0 + (uint64_t)((k * KSTEP_BYTES) >> 4), ID_PC, acc);
-                                acc = 1;
-                            }
+                        for (int k = 0; k < C / K::KROWS; ++k) {
+                            mma_ts<K::F16>(tO, tP + k * 8, c0 + (uint64_t)((k * KSTEP_BYTES) >> 4), ID_PC, acc);
+                            acc = 1;
                         }
                         tc_commit(bar_ofull + 8 * ob);       // output workers
                         tc_commit(bar_pfree + 8 * (ci & 1)); // this score buffer may be overwritten
                         tc_commit(bar_empty + 8 * s);        // one of the two releases of the stage
                     }
-                } else {
+                } else if (!apply_only) {
                     // ---- state issuer --------------------------------------------------------
                     auto issue_scores = [&](int ci) {
                         const int s = ci & 1;
@@ -646,13 +655,11 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                             (!K::RELOAD_B || mbar_test(bar_fullbmn + 8 * s, (ds >> 1) & 1))) {
                             const uint64_t bmn0 = dBmn0 + s * STAGE_UNITS, c0 = dCmn0 + s * STAGE_UNITS;
                             tc_fence_after();
-                            if (p.terms & 4) {
-                                const uint32_t tT = K::REG_STATE ? tS + s * DCT : tS;
+                            const uint32_t tT = K::REG_STATE ? tS + s * DCT : tS;
 #pragma unroll
-                                for (int k = 0; k < C / K::KROWS; ++k) {
-                                    const uint64_t off = (uint64_t)((k * KSTEP_BYTES) >> 4);
-                                    mma_ss<K::F16>(tT, bmn0 + off, c0 + off, ID_ST, (K::REG_STATE && k == 0) ? 0u : 1u);
-                                }
+                            for (int k = 0; k < C / K::KROWS; ++k) {
+                                const uint64_t off = (uint64_t)((k * KSTEP_BYTES) >> 4);
+                                mma_ss<K::F16>(tT, bmn0 + off, c0 + off, ID_ST, (K::REG_STATE && k == 0) ? 0u : 1u);
                             }
                             if constexpr (K::REG_STATE) tc_commit(bar_tfull + 8 * s);
                             else tc_commit(bar_sfull);
@@ -677,7 +684,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
         } else if (warp >= 11) {
             // ================= mask workers: causal mask on the scores, in place ================
             // (warps 11-14 cover the four 32-lane quarters of tensor memory: q = 3, 0, 1, 2)
-            if (!p.state_only) {
+            if (!p.state_only && !apply_only) {
                 const int q = warp & 3;
                 const uint32_t tlane = tmem + ((uint32_t)(32 * q) << 16);
                 uint32_t r[32];
@@ -956,7 +963,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     mbar_arrive(bar_smready2);
                 }
 
-                for (int ci = 0; ci + 1 < nchunk && ok; ++ci) {
+                for (int ci = 0; ci + 1 < nchunk && ok && !apply_only; ++ci) {
                     // ---- updated state -> shared-memory operand of the next chunk ---------------
                     // the new state is complete, and "a S" of this chunk has finished reading the
                     // old operand copy (which also keeps the two issuers within one chunk of each

@@ -35,7 +35,10 @@ __device__ __forceinline__ void step_store(__nv_bfloat16 *p, float x) { *p = __f
 
 // feature: 0 = inputs are features already, 1 = phi(x) = elu(x) + 1 applied to q and k here
 // (feature_maps/base.py:71-73)
-template <typename T>
+// UPDATE = false: the state is only read -- y = (Q . S) / (Q . z + eps) with k and v unused: a
+// step of cross attention over a fixed memory
+// (fast_transformers/recurrent/attention/cross_attention/linear_attention.py:66-69).
+template <typename T, bool UPDATE = true>
 __global__ void __launch_bounds__(kStepThreads)
 recurrent_step_kernel(const T *q, const T *k, const T *v, float *S, float *z, T *out, int H, int D,
                       int M, Strides2 qs, Strides2 ks, Strides2 vs, Strides2 os, int feature, float eps) {
@@ -56,13 +59,13 @@ recurrent_step_kernel(const T *q, const T *k, const T *v, float *S, float *z, T 
     // features, z += K, and the partial sums of Q . z
     float qz = 0.f;
     for (int d = t; d < D; d += kStepThreads) {
-        float a = step_load(qp + d), b = step_load(kp + d);
+        float a = step_load(qp + d), b = UPDATE ? step_load(kp + d) : 0.f;
         if (feature == 1) {
             a = a > 0.f ? a + 1.f : expf(a);   // elu(x) + 1
-            b = b > 0.f ? b + 1.f : expf(b);
+            if (UPDATE) b = b > 0.f ? b + 1.f : expf(b);
         }
         const float zn = zp[d] + b;
-        zp[d] = zn;
+        if (UPDATE) zp[d] = zn;
         sq[d] = a;
         sk[d] = b;
         qz += a * zn;
@@ -90,8 +93,9 @@ recurrent_step_kernel(const T *q, const T *k, const T *v, float *S, float *z, T 
         const int col4 = t % cg, rg = t / cg;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         if (rg < rg_count) {
-            const float4 vm = make_float4(step_load(vp + 4 * col4), step_load(vp + 4 * col4 + 1),
-                                          step_load(vp + 4 * col4 + 2), step_load(vp + 4 * col4 + 3));
+            const float4 vm = UPDATE ? make_float4(step_load(vp + 4 * col4), step_load(vp + 4 * col4 + 1),
+                                                   step_load(vp + 4 * col4 + 2), step_load(vp + 4 * col4 + 3))
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
             float4 *base = reinterpret_cast<float4 *>(Sp) + col4;
             int d = rg;
             for (; d + 3 * rg_count < D; d += 4 * rg_count) {
@@ -101,16 +105,20 @@ recurrent_step_kernel(const T *q, const T *k, const T *v, float *S, float *z, T 
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const float kd = sk[d + u * rg_count], qd = sq[d + u * rg_count];
-                    s[u].x += kd * vm.x; s[u].y += kd * vm.y; s[u].z += kd * vm.z; s[u].w += kd * vm.w;
-                    base[(int64_t)(d + u * rg_count) * cg] = s[u];
+                    if (UPDATE) {
+                        s[u].x += kd * vm.x; s[u].y += kd * vm.y; s[u].z += kd * vm.z; s[u].w += kd * vm.w;
+                        base[(int64_t)(d + u * rg_count) * cg] = s[u];
+                    }
                     acc.x += qd * s[u].x; acc.y += qd * s[u].y; acc.z += qd * s[u].z; acc.w += qd * s[u].w;
                 }
             }
             for (; d < D; d += rg_count) {
                 float4 s0 = base[(int64_t)d * cg];
                 const float kd = sk[d], qd = sq[d];
-                s0.x += kd * vm.x; s0.y += kd * vm.y; s0.z += kd * vm.z; s0.w += kd * vm.w;
-                base[(int64_t)d * cg] = s0;
+                if (UPDATE) {
+                    s0.x += kd * vm.x; s0.y += kd * vm.y; s0.z += kd * vm.z; s0.w += kd * vm.w;
+                    base[(int64_t)d * cg] = s0;
+                }
                 acc.x += qd * s0.x; acc.y += qd * s0.y; acc.z += qd * s0.z; acc.w += qd * s0.w;
             }
         }
@@ -137,11 +145,11 @@ recurrent_step_kernel(const T *q, const T *k, const T *v, float *S, float *z, T 
         const int col = t % mt, rg = t / mt;
         float acc = 0.f;
         if (rg < rg_count) {
-            const float vm = step_load(vp + m0 + col);
+            const float vm = UPDATE ? step_load(vp + m0 + col) : 0.f;
             for (int d = rg; d < D; d += rg_count) {
                 float *sp = Sp + (int64_t)d * M + m0 + col;
                 const float s = *sp + sk[d] * vm;
-                *sp = s;
+                if (UPDATE) *sp = s;
                 acc += sq[d] * s;
             }
         }

@@ -2,3 +2,4 @@
 linear self-attention step and the projection layer around it."""
 from .self_attention.attention_layer import RecurrentAttentionLayer  # noqa: F401
 from .self_attention.linear_attention import RecurrentLinearAttention  # noqa: F401
+from .cross_attention.linear_attention import RecurrentCrossLinearAttention  # noqa: F401

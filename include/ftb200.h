@@ -98,7 +98,8 @@ int ftb_last_cuda_error(void);
 #define FTB_KERNEL_NORMALISER 9   /* denominator Q . cumsum(K) and its gradients      */
 #define FTB_KERNEL_FEATURE_MAP 10 /* elu(x)+1 (x key-length mask) and its gradient    */
 #define FTB_KERNEL_RANK_EXCHANGE 11 /* push / receive of per-rank states over peer memory */
-#define FTB_KERNEL_KINDS 12
+#define FTB_KERNEL_APPLY_STATE 12  /* out = a . S for one fixed state per (batch, head) */
+#define FTB_KERNEL_KINDS 13
 uint64_t ftb_launch_count(void);
 /*
  * Device-side status word of the current device: 0, or the FTB_ERR_* code recorded by a kernel
@@ -246,6 +247,38 @@ int ftb_recurrent_linear_step(const void *q, const void *k, const void *v, float
                               const int64_t *q_strides, const int64_t *k_strides,
                               const int64_t *v_strides, const int64_t *out_strides, int dtype,
                               int feature_map, float eps, void *stream);
+
+/*
+ * One fixed state applied to every position:  out[n,h,l,:] = a[n,h,l,:] . S[n,h]  with S the
+ * (N,H,Da,Dc) fp32 state (or, state_is_transposed != 0, stored as (N,H,Dc,Da) and applied as its
+ * transpose).  With ftb_causal_state_sum this is the whole of NON-causal linear attention and of its
+ * gradients -- the reference writes them as torch.einsum calls
+ * (fast_transformers/attention/linear_attention.py:72-78: KV = einsum("nshd,nshm->nhmd", K, V),
+ * V' = einsum("nlhd,nhmd,nlh->nlhm", Q, KV, Z)):
+ *     S = state_sum(K, V);   out = apply(Q, S);
+ *     grad_Q = apply(G, S, transposed);   R = state_sum(Q, G);
+ *     grad_K = apply(V, R, transposed);   grad_V = apply(K, R).
+ * a, out: (N,H,L,Da) / (N,H,L,Dc) views, fp32 or bf16, last dimension contiguous, element strides of
+ * {batch, head, position}.  FTB_MODE_MMA takes the shapes the causal product takes in that mode
+ * (FTB_ERR_UNSUPPORTED otherwise, FTB_ERR_ALIGNMENT for rows that do not start on 16 bytes);
+ * FTB_MODE_FP32_SIMT takes any Da, Dc.  No scratch memory.
+ */
+int ftb_linear_apply_state(const void *a, const float *state, void *out, int64_t N, int64_t H, int64_t L,
+                           int64_t Da, int64_t Dc, const int64_t *a_strides, const int64_t *out_strides,
+                           int dtype, int mode, int state_is_transposed, void *stream);
+
+/*
+ * One step of linear CROSS attention over a fixed memory: y = (Q . S) / (Q . z + eps) with
+ * Q = phi(q); the state [S (N,H,D,M), z (N,H,D)] -- built once from the memory's keys and values with
+ * ftb_causal_state_sum and a sum of the key features -- is only read.  Replaces the arithmetic of
+ * RecurrentCrossLinearAttention.forward
+ * (fast_transformers/recurrent/attention/cross_attention/linear_attention.py:49-71).
+ * Arguments as for ftb_recurrent_linear_step, without k and v.
+ */
+int ftb_recurrent_cross_linear_step(const void *q, const float *S, const float *z, void *out, int64_t N,
+                                    int64_t H, int64_t D, int64_t M, const int64_t *q_strides,
+                                    const int64_t *out_strides, int dtype, int feature_map, float eps,
+                                    void *stream);
 
 /*
  * Exchange of per-rank states between the GPUs of ONE node without a library collective, for a

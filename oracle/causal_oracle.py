@@ -21,6 +21,8 @@ Functions (each cites the reference lines it restates):
 * ``reference_ext``                           -- the compiled reference extension itself.
 * ``layer_forward``                           -- ``CausalLinearAttention.forward``
   (``fast_transformers/attention/causal_linear_attention.py:71-104``) restated densely.
+* ``linear_layer_forward`` / ``linear_product`` -- the unmasked ``LinearAttention.forward``
+  (``fast_transformers/attention/linear_attention.py:55-80``) and its numerator.
 * ``favor_features`` / ``elu_features``       -- the two feature maps on the path
   (``feature_maps/base.py:71-73``, ``feature_maps/fourier_features.py:218-243``).
 """
@@ -295,6 +297,37 @@ def layer_forward(queries, keys, values, key_lengths=None, feature=elu_features,
     A = torch.einsum("nlhe,nshe->nhls", q, k) * torch.tril(torch.ones(L, L, dtype=dtype))
     out = torch.einsum("nhls,nshm->nlhm", A, v)
     return out * Z[:, :, :, None]
+
+
+def linear_layer_forward(queries, keys, values, key_lengths=None, feature=elu_features, eps=1e-6,
+                         dtype=torch.float64):
+    """``LinearAttention.forward`` (fast_transformers/attention/linear_attention.py:55-80), the
+    unmasked form: inputs (N, L, H, E), (N, S, H, E), (N, S, H, M); K is multiplied by the
+    key-length mask (:68); KV = sum_s K_s (x) v_s (:73); Z = 1 / (Q . sum_s K_s + eps) (:76);
+    result (N, L, H, M) = (Q . KV) Z (:79)."""
+    q = feature(queries.detach().to("cpu", dtype))
+    k = feature(keys.detach().to("cpu", dtype))
+    v = values.detach().to("cpu", dtype)
+    S = k.shape[1]
+    if key_lengths is not None:
+        mask = (torch.arange(S)[None, :] < key_lengths.cpu()[:, None]).to(dtype)
+        k = k * mask[:, :, None, None]
+    KV = torch.einsum("nshd,nshm->nhdm", k, v)
+    Z = 1.0 / (torch.einsum("nlhd,nhd->nlh", q, k.sum(dim=1)) + eps)
+    return torch.einsum("nlhd,nhdm,nlh->nlhm", q, KV, Z)
+
+
+def linear_product(Q, K, V, G=None, dtype=torch.float64):
+    """The unmasked product out = Q (K^T V) for (N, H, L, D), (N, H, S, D), (N, H, S, M) tensors
+    (the two einsums of linear_attention.py:73,79 without the normaliser) and, with ``G``, its
+    gradients by autograd.  Returns out or (out, gQ, gK, gV)."""
+    Q, K, V = (t.detach().to("cpu", dtype) for t in (Q, K, V))
+    if G is None:
+        return Q @ (K.transpose(-1, -2) @ V)
+    Q.requires_grad_(True), K.requires_grad_(True), V.requires_grad_(True)
+    out = Q @ (K.transpose(-1, -2) @ V)
+    (out * G.detach().to("cpu", dtype)).sum().backward()
+    return out.detach(), Q.grad, K.grad, V.grad
 
 
 def normaliser(Q, K, dtype=torch.float64):

@@ -235,8 +235,52 @@ def recurrent_encoder():
     print("recurrent_encoder.npz", os.path.getsize(os.path.join(HERE, "recurrent_encoder.npz")), "bytes")
 
 
+def linear():
+    """``linear.npz``: the reference's unmasked ``LinearAttention`` (inputs with keys longer than
+    queries and ragged key lengths, output, gradients of a weighted sum) and its
+    ``RecurrentCrossLinearAttention`` stepped over a few queries on the same memory (every output,
+    the state), with the check that the steps reproduce the batch form."""
+    import_reference_recurrent()
+    pkg_dir = os.path.join(build_ref.reference_root(), "fast_transformers")
+    m = types.ModuleType("fast_transformers.recurrent.attention.cross_attention")
+    m.__path__ = [os.path.join(pkg_dir, "recurrent/attention/cross_attention")]
+    sys.modules["fast_transformers.recurrent.attention.cross_attention"] = m
+    import fast_transformers.attention.linear_attention as la
+    import fast_transformers.recurrent.attention.cross_attention.linear_attention as rcla
+    import fast_transformers.masking as masking
+    torch.set_num_threads(1)
+    g = torch.Generator().manual_seed(808)
+    N, L, S, H, E, M = 3, 9, 14, 4, 16, 24
+    q = torch.randn(N, L, H, E, generator=g, requires_grad=True)
+    k = torch.randn(N, S, H, E, generator=g, requires_grad=True)
+    v = torch.randn(N, S, H, M, generator=g, requires_grad=True)
+    w = torch.randn(N, L, H, M, generator=g)
+    klen = torch.tensor([14, 5, 11])
+    att = la.LinearAttention(E).eval()
+    qlm = masking.LengthMask(torch.full((N,), L, dtype=torch.long))
+    klm = masking.LengthMask(klen, max_len=S)
+    y = att(q, k, v, masking.FullMask(L, S), qlm, klm)
+    (y * w).sum().backward()
+    blob = {"q": np_(q), "k": np_(k), "v": np_(v), "w": np_(w), "klen": np_(klen), "y": np_(y),
+            "gq": np_(q.grad), "gk": np_(k.grad), "gv": np_(v.grad)}
+    rec = rcla.RecurrentCrossLinearAttention(E).eval()
+    with torch.no_grad():
+        state, ys = None, []
+        for i in range(L):
+            yi, state = rec(q[:, i], k, v, klm, state)
+            ys.append(yi)
+    blob["step_y"] = np_(torch.stack(ys, 1))
+    blob["state_S"] = np_(state[0])      # (N, H, M, E) in the reference
+    blob["state_z"] = np_(state[1])
+    assert np.abs(blob["step_y"] - blob["y"]).max() < 1e-5
+    np.savez_compressed(os.path.join(HERE, "linear.npz"), **blob)
+    print("linear.npz", os.path.getsize(os.path.join(HERE, "linear.npz")), "bytes")
+
+
 if __name__ == "__main__":
-    if sys.argv[1:] == ["recurrent"]:
+    if sys.argv[1:] == ["linear"]:
+        linear()
+    elif sys.argv[1:] == ["recurrent"]:
         recurrent()
     elif sys.argv[1:] == ["recurrent_encoder"]:
         recurrent_encoder()
@@ -244,3 +288,4 @@ if __name__ == "__main__":
         main()
         recurrent()
         recurrent_encoder()
+        linear()

@@ -126,3 +126,15 @@ def test_recurrent_step_oracle_vs_reference(golden):
         assert orc.rel_err(state[1], T(g[tag + "_z"])) < 1e-6
     assert (orc.layer_forward(q, k, v) - T(g["batch_y"])).abs().max() < 1e-5
     assert (T(g["empty_y"]) - T(g["batch_y"])).abs().max() < 1e-5
+
+
+def test_unmasked_layer_restatement_matches_reference_golden(golden):
+    """The oracle's restatement of the unmasked LinearAttention against the reference's own
+    output (fixture generated from the unmodified reference module)."""
+    g = golden("linear")
+    q, k, v = (torch.from_numpy(g[n]) for n in "qkv")
+    klen = torch.from_numpy(g["klen"])
+    want = orc.linear_layer_forward(q, k, v, key_lengths=klen)
+    assert (want - torch.from_numpy(g["y"]).double()).abs().max() < 1e-5
+    # the recurrent cross-attention steps of the reference reproduce its batch form
+    assert np.abs(g["step_y"] - g["y"]).max() < 1e-5
