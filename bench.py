@@ -589,13 +589,22 @@ def sequence_parallel_record(args, dev, dist, rank, world, mode, lib):
 
     steps = max(args.steps, 10)
     graph_steps = 0
-    if exchange is not None and args.sp_graph:
-        graph_steps = next(d for d in range(min(10, steps), 0, -1) if steps % d == 0)
     valid, why = True, None
     try:
         step()
         if exchange is not None:
             exchange.check()
+        if exchange is not None and args.sp_graph:
+            # as many steps per graph as keep it under about 8 ms (longer graphs ran slower per
+            # step), the same number on every rank
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            torch.cuda.synchronize()
+            most = torch.tensor([max(1, min(10, int(8.0 / max(e0.elapsed_time(e1), 1e-3))))], device=dev)
+            dist.all_reduce(most, op=dist.ReduceOp.MIN)
+            graph_steps = next(d for d in range(int(most.item()), 0, -1) if steps % d == 0)
         tN = time_steps(step, steps, 3, dev, dist, graph_steps=graph_steps)
         if exchange is not None:
             exchange.check()        # a receive that gave up waiting leaves NaN and a status word
@@ -641,7 +650,8 @@ def sequence_parallel_record(args, dev, dist, rank, world, mode, lib):
         peak, _ = hbm_peak()
         rec = {"valid": True, "workload": workload_name(4, shape) + ", sequence split over %d ranks" % world,
                "mode": mode, "ms_per_step": tN, "value": shape["N"] * L / (tN * 1e-3) / 1e6, "unit": UNIT,
-               "steps": steps, "cuda_graph": bool(graph_steps), "positions_per_rank": Lr,
+               "steps": steps, "cuda_graph": bool(graph_steps), "steps_per_graph": graph_steps,
+               "positions_per_rank": Lr,
                "exchange": ("stores into the peers' buffers by this library's kernels (PeerExchange)"
                             if exchange is not None else "all_gather of the per-rank states (NCCL)"),
                "t1_ms": t1, "t1_how": "the same sequence on rank 0 alone, same process, CUDA graph of 2 steps",

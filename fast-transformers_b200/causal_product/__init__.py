@@ -114,6 +114,11 @@ def causal_dot_product_cuda(queries, keys, values, product, mode=None, initial_s
             raise RuntimeError("expected scalar type %s but found %s" % (queries.dtype, t.dtype))
     N, H, L, D = queries.shape
     M = values.shape[3]
+    if values.shape[:2] == (N, H) and values.shape[2] > L:
+        # The reference's layer hands over V with all S rows when L < S
+        # (causal_linear_attention.py:98-102); its kernels walk the L rows of Q and never look
+        # at the rest (tests/attention/test_causal_linear_attention.py:33-39).  Same here.
+        values = values[:, :, :L]
     if keys.shape != (N, H, L, D) or values.shape[:3] != (N, H, L) or \
             product.shape != (N, H, L, M):
         raise RuntimeError("shape mismatch between queries, keys, values and product")
@@ -172,6 +177,14 @@ def causal_dot_backward_cuda(queries, keys, values, grad_out, grad_queries, grad
     dt = _dtype_id(queries)
     N, H, L, D = queries.shape
     M = values.shape[3]
+    if values.shape[:2] == (N, H) and values.shape[2] > L:
+        # V longer than the queries (see the forward): rows past L take no part, their gradient
+        # is zero (the reference relies on its zero-initialised buffer for that)
+        values = values[:, :, :L]
+        if grad_values is not None and grad_values.shape[2] > L:
+            grad_values[:, :, L:].zero_()
+            grad_values = grad_values[:, :, :L]
+            wanted = [t for t in (grad_queries, grad_keys, grad_values) if t is not None]
     if grad_out.dtype != queries.dtype:
         grad_out = grad_out.to(queries.dtype)
     if grad_out.shape != (N, H, L, M):

@@ -327,6 +327,12 @@ struct Cfg {
     // the mask workers rearrange the tile in place once the score product has consumed it
     // (a state-only launch loads the MN-major image directly).
     static constexpr bool RELOAD_B = !F16;
+#ifndef FTB_B_BY_OUTPUT_WARPS
+#define FTB_B_BY_OUTPUT_WARPS 0
+#endif
+    // who rearranges b in place: the mask workers before they mask (0), or the output workers
+    // while the mask workers mask (1)
+    static constexpr bool B_BY_OUTPUT_WARPS = FTB_B_BY_OUTPUT_WARPS != 0;
     // state-only launches: the same ring memory as slots of b | c
     static constexpr int SO_BYTES = A_BYTES + C_BYTES;
     static constexpr int SO_STAGES = (STAGES * STAGE_BYTES) / SO_BYTES;
@@ -428,7 +434,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
             mbar_init(bar_ofull + 8 * s, 1);
             mbar_init(bar_ofree + 8 * s, 128);
             mbar_init(bar_fullc + 8 * s, 1);
-            // the 128 mask-worker threads that rearrange b in place
+            // the 128 threads that rearrange b in place
             mbar_init(bar_fullbmn + 8 * s, 128);
         }
         for (int s = 0; s < K::SO_STAGES; ++s) {
@@ -453,6 +459,39 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
+
+    // The score product reads b K-major (128-byte swizzle: 16-byte chunk c of row r sits at
+    // c ^ (r & 7)); the state update reads b MN-major, which for TF32 exists only in the
+    // 32-byte-atom swizzle (32-byte unit u of row r at u ^ (r & 3)).  Both keep a tile row in the
+    // same 128 bytes, so the second image is a permutation of the 8 chunks of every row, done in
+    // place once the score product has retired: a warp instruction covers four whole rows (no
+    // bank conflicts), reads them, then writes them back.  `t`: 0..127 within the four warps that
+    // share the work.
+    auto rearrange_b_in_place = [&](int ci, int t) {
+        uint8_t *bt = smem_gen + (ci & 1) * K::STAGE_BYTES + K::A_BYTES;
+        constexpr int NIT = K::A_BYTES / (128 * 16);   // 16-byte chunks per thread
+        static_assert(NIT % 4 == 0, "chunks are moved four at a time");
+        for (int it0 = 0; it0 < NIT; it0 += 4) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int idx = (it0 + j) * 128 + t;   // 16-byte chunk of the tile
+                v[j] = reinterpret_cast<const uint4 *>(bt + (size_t)(idx >> 3) * 128)[idx & 7];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int idx = (it0 + j) * 128 + t;
+                const int pk = idx & 7, row = (idx >> 3) & 127;
+                const int c = pk ^ (row & 7);          // logical chunk held here
+                const int pm = ((((c >> 1) ^ (row & 3)) << 1) | (c & 1));
+                reinterpret_cast<uint4 *>(bt + (size_t)(idx >> 3) * 128)[pm] = v[j];
+            }
+            __syncwarp();
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(bar_fullbmn + 8 * (ci & 1));
+    };
 
     if (nchunk > 0) {
         if (warp == 0) {
@@ -691,39 +730,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                 for (int ci = 0; ci < nchunk; ++ci) {
                     if (!mbar_wait(bar_pfull + 8 * (ci & 1), (ci >> 1) & 1, abort_flag)) break;
                     tc_fence_after();
-                    if constexpr (K::RELOAD_B) {
-                        // The score product has consumed the K-major image of b (128-byte
-                        // swizzle: 16-byte chunk c of row r sits at c ^ (r & 7)).  The state
-                        // update reads b MN-major, which for TF32 exists only in the 32-byte-atom
-                        // swizzle (32-byte unit u of row r at u ^ (r & 3)).  Both keep a tile row
-                        // in the same 128 bytes, so the second image is a permutation of the 8
-                        // chunks of every row, done here in place: a warp instruction covers four
-                        // whole rows (no bank conflicts), reads them, then writes them back.
-                        uint8_t *bt = smem_gen + (ci & 1) * K::STAGE_BYTES + K::A_BYTES;
-                        const int t = threadIdx.x - 352;
-                        constexpr int NIT = K::A_BYTES / (128 * 16);   // 16-byte chunks per thread
-                        static_assert(NIT % 4 == 0, "chunks are moved four at a time");
-                        for (int it0 = 0; it0 < NIT; it0 += 4) {
-                            uint4 v[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int idx = (it0 + j) * 128 + t;   // 16-byte chunk of the tile
-                                v[j] = reinterpret_cast<const uint4 *>(bt + (size_t)(idx >> 3) * 128)[idx & 7];
-                            }
-                            __syncwarp();
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int idx = (it0 + j) * 128 + t;
-                                const int pk = idx & 7, row = (idx >> 3) & 127;
-                                const int c = pk ^ (row & 7);          // logical chunk held here
-                                const int pm = ((((c >> 1) ^ (row & 3)) << 1) | (c & 1));
-                                reinterpret_cast<uint4 *>(bt + (size_t)(idx >> 3) * 128)[pm] = v[j];
-                            }
-                            __syncwarp();
-                        }
-                        fence_proxy_async_smem();
-                        mbar_arrive(bar_fullbmn + 8 * (ci & 1));
-                    }
+                    if constexpr (K::RELOAD_B && !K::B_BY_OUTPUT_WARPS) rearrange_b_in_place(ci, threadIdx.x - 352);
                     const uint32_t tP = tlane + K::TM_P + 128 * (ci & 1);
 #pragma unroll
                     for (int cb = 0; cb < 4; ++cb) {
@@ -785,6 +792,13 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     const int c = p.reverse ? nchunk - 1 - ci : ci;
                     const int64_t row0 = seg_begin + (int64_t)c * C;
                     const int ob = ci % K::NOBUF, ouse = ci / K::NOBUF;
+                    if constexpr (K::RELOAD_B && K::B_BY_OUTPUT_WARPS && !apply_only) {
+                        // these warps are idle between two stores: they make the MN-major image
+                        // of b while the mask workers mask the scores
+                        ok = mbar_wait(bar_pfull + 8 * (ci & 1), (ci >> 1) & 1, abort_flag);
+                        if (!ok) break;
+                        rearrange_b_in_place(ci, threadIdx.x - 192);
+                    }
                     ok = mbar_wait(bar_ofull + 8 * ob, ouse & 1, abort_flag);
                     if (!ok) break;
                     tc_fence_after();

@@ -259,3 +259,23 @@ def test_inputs_whose_last_dimension_is_not_contiguous(mode):
     want = (orc.dense_forward(Q, K, V),) + tuple(orc.dense_backward(Q, K, V, G))
     for name, a, b in zip(("out", "gQ", "gK", "gV"), (out, q.grad, k.grad, v.grad), want):
         assert orc.rel_err(a, b) < TOL[mode], name
+
+
+@pytest.mark.parametrize("mode", ["fp32", "mma"])
+def test_values_longer_than_queries_use_the_first_rows(mode):
+    """The reference's layer passes all S rows of V when L < S and its kernels read the first L
+    (tests/attention/test_causal_linear_attention.py:33-39); the gradient of the unread rows is 0."""
+    g = torch.Generator().manual_seed(12)
+    N, H, L, S, D = 1, 2, 200, 260, 64
+    Q, K, G = (torch.rand(N, H, L, D, generator=g) for _ in range(3))
+    V = torch.rand(N, H, S, D, generator=g)
+    Qd, Kd, Vd, Gd = dev(Q, K, V, G)
+    out = torch.empty(N, H, L, D, device="cuda")
+    causal_dot_product_cuda(Qd, Kd, Vd, out, mode)
+    gq, gk = torch.empty_like(Qd), torch.empty_like(Kd)
+    gv = torch.full_like(Vd, float("nan"))
+    causal_dot_backward_cuda(Qd, Kd, Vd, Gd, gq, gk, gv, mode)
+    want = (orc.dense_forward(Q, K, V[:, :, :L]),) + tuple(orc.dense_backward(Q, K, V[:, :, :L], G))
+    for name, a, b in zip(("out", "gQ", "gK", "gV"), (out, gq, gk, gv[:, :, :L]), want):
+        assert orc.rel_err(a, b) < TOL[mode], name
+    assert torch.all(gv[:, :, L:] == 0)
