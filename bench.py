@@ -833,6 +833,10 @@ def main():
     # ---- per-kernel device time (instrumented pass, after the timed region) --------------
     lib.ftb_timing_enable(1)
     for _ in range(args.steps):
+        if seq_parallel:
+            # the split step as it is (every launch is recorded, whichever thread makes it)
+            step()
+            continue
         # the backward pass runs on an autograd thread; call the native functions directly
         # so every launch is made (and recorded) by this thread
         from fast_transformers_b200.causal_product import (causal_dot_backward_cuda,
@@ -843,6 +847,7 @@ def main():
         causal_dot_product_cuda(Qd.data, Kd.data, Vd.data, o, mode, keep_workspace=kept)
         causal_dot_backward_cuda(Qd.data, Kd.data, Vd.data, Gd, gq, gk, gv, mode,
                                  forward_workspace=kept[0] if kept else None)
+    torch.cuda.synchronize()
     kinds = _native.timing_read()
     lib.ftb_timing_enable(0)
     peak_gbs, peak_src = hbm_peak()

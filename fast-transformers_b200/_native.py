@@ -28,7 +28,8 @@ EXPORTS = (
     "ftb_elu_feature_map", "ftb_elu_feature_map_backward",
     "ftb_exchange_bytes", "ftb_exchange_create", "ftb_exchange_open", "ftb_exchange_close",
     "ftb_exchange_destroy", "ftb_exchange_push", "ftb_exchange_receive",
-    "ftb_exchange_wait_limit_ms", "ftb_linear_apply_state", "ftb_recurrent_cross_linear_step",
+    "ftb_exchange_wait_limit_ms", "ftb_exchange_push_parts", "ftb_causal_state_parts",
+    "ftb_linear_apply_state", "ftb_recurrent_cross_linear_step",
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
                 "mma_bwd_qr", "mma_bwd_multi", "recurrent_step", "normaliser", "feature_map",
@@ -100,6 +101,10 @@ def lib():
     L.ftb_exchange_destroy.argtypes = [_vp]
     L.ftb_exchange_push.restype = _int
     L.ftb_exchange_push.argtypes = [_vp, _i64, ctypes.POINTER(_vp), _int, _int, _int, _vp]
+    L.ftb_exchange_push_parts.restype = _int
+    L.ftb_exchange_push_parts.argtypes = [_vp, _i64, _int, _i64, ctypes.POINTER(_vp), _int, _int, _int, _vp]
+    L.ftb_causal_state_parts.restype = _int
+    L.ftb_causal_state_parts.argtypes = [_i64] * 5 + [_int, _int]
     L.ftb_exchange_receive.restype = _int
     L.ftb_exchange_receive.argtypes = [_vp, _vp, _i64, _int, _int, _int, _vp]
     L.ftb_linear_apply_state.restype = _int

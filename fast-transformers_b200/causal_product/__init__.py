@@ -266,6 +266,31 @@ def causal_state_sum(x, y, mode=None, workspace=None, reverse=False):
     return state
 
 
+def causal_state_parts(x, y, workspace, mode=None):
+    """Partial sums of ``sum_l x_l (x) y_l`` left in ``workspace`` (a uint8 tensor of at least
+    ``workspace_bytes(..., want_state=True)`` bytes): returns the number of (D, M) float32 blocks per
+    (batch, head) pair that add up to the pair's state, or 0 when this shape and mode keep no raw
+    partial sums (nothing is launched then).  The workspace can be handed to the forward / backward
+    call like the one ``causal_state_sum`` fills."""
+    dev = _check_cuda(x, y)
+    dt = _dtype_id(x)
+    N, H, L, D = x.shape
+    M = y.shape[3]
+    L_ = _native.lib()
+    m = _mode_id(mode)
+    parts = L_.ftb_causal_state_parts(N, H, L, D, M, dt, m)
+    if parts == 0:
+        return 0
+    x, y = _rowmajor(x), _rowmajor(y)
+    with torch.cuda.device(dev):
+        st = L_.ftb_causal_state_sum(
+            _ptr(x), _ptr(y), None, N, H, L, D, M, _native.strides3(x), _native.strides3(y), dt, m, 0,
+            _ptr(workspace), workspace.numel() * workspace.element_size(),
+            ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    _native.check(st, "ftb_causal_state_sum")
+    return parts
+
+
 def _no_cpu(*args, **kwargs):
     raise RuntimeError("fast_transformers_b200 has no CPU implementation of causal_dot_product; "
                        "move the tensors to a CUDA (B200) device")

@@ -759,6 +759,15 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
     return rc;
 }
 
+int ftb_causal_state_parts(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M, int dtype, int mode) {
+    if (check_common(N, H, L, D, M, dtype, mode) != FTB_OK) return 0;
+    if (N <= 0 || H <= 0 || L <= 0 || D <= 0 || M <= 0) return 0;
+    Plan pl = choose_plan(mode, N * H, L);
+    if (pl.nseg == 1) return 1;
+    if (!sums_in_kernel(mode, pl)) return 0;   // the workspace then holds prefixes, not raw totals
+    return pl.nseg * state_sub(mode, pl, N * H);
+}
+
 int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, int64_t H,
                          int64_t L, int64_t D, int64_t M, const int64_t *xs, const int64_t *ys,
                          int dtype, int mode, int reverse, void *workspace, size_t workspace_bytes,
@@ -768,7 +777,23 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
     if (!xs || !ys) return FTB_ERR_INVALID;
     cudaStream_t st = (cudaStream_t)stream;
     if (N == 0 || H == 0 || D == 0 || M == 0) return FTB_OK;
-    if (!state) return FTB_ERR_INVALID;
+    if (!state) {
+        // partial sums only: ftb_causal_state_parts(...) blocks per (batch, head) at the start of
+        // `workspace`, for a caller that adds them up itself (ftb_exchange_push_parts)
+        if (L == 0 || !x || !y) return FTB_ERR_INVALID;
+        const int parts = ftb_causal_state_parts(N, H, L, D, M, dtype, mode);
+        if (parts == 0) return FTB_ERR_UNSUPPORTED;
+        size_t need = align256((size_t)N * H * parts * D * M * sizeof(float));
+        if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
+        Plan pl = choose_plan(mode, N * H, L);
+        if (pl.nseg > 1) {
+            const int sub = state_sub(mode, pl, N * H);
+            pl.seg_len /= sub;
+            pl.nseg *= sub;
+        }
+        return launch_state_sum(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, (float *)workspace,
+                                0, 0, st);
+    }
     if (L == 0) {
         FTB_CUDA(cudaMemsetAsync(state, 0, (size_t)N * H * D * M * 4, st));
         return FTB_OK;
@@ -1159,8 +1184,8 @@ int ftb_exchange_wait_limit_ms(int ms) {
     return (int)(before / 1000000LL);
 }
 
-int ftb_exchange_push(const float *state, int64_t elems, void *const *buffers, int rank, int world,
-                      int reverse, void *stream) {
+static int exchange_push(const float *state, int64_t elems, int64_t unit_elems, int parts_per_unit,
+                         void *const *buffers, int rank, int world, int reverse, void *stream) {
     int rc = exchange_check(world, elems);
     if (rc) return rc;
     if (!buffers || rank < 0 || rank >= world || (elems > 0 && !state)) return FTB_ERR_INVALID;
@@ -1179,10 +1204,23 @@ int ftb_exchange_push(const float *state, int64_t elems, void *const *buffers, i
     rc = device_status_ptr(&status);
     if (rc) return rc;
     LaunchScope scope(FTB_KERNEL_RANK_EXCHANGE, st);
-    xchg::push_kernel<<<grid, xchg::kThreads, 0, st>>>(state, elems, peers, rank, world, reverse ? 1 : 0,
-                                                       status, g_exchange_wait_ns.load());
+    xchg::push_kernel<<<grid, xchg::kThreads, 0, st>>>(state, elems, unit_elems, parts_per_unit, peers, rank,
+                                                       world, reverse ? 1 : 0, status, g_exchange_wait_ns.load());
     FTB_CUDA(cudaGetLastError());
     return FTB_OK;
+}
+
+int ftb_exchange_push(const float *state, int64_t elems, void *const *buffers, int rank, int world,
+                      int reverse, void *stream) {
+    return exchange_push(state, elems, elems, 1, buffers, rank, world, reverse, stream);
+}
+
+int ftb_exchange_push_parts(const float *parts, int64_t unit_elems, int parts_per_unit, int64_t units,
+                            void *const *buffers, int rank, int world, int reverse, void *stream) {
+    if (unit_elems < 0 || units < 0 || parts_per_unit < 1) return FTB_ERR_INVALID;
+    if (unit_elems % 4) return FTB_ERR_ALIGNMENT;
+    return exchange_push(parts, unit_elems * units, unit_elems, parts_per_unit, buffers, rank, world, reverse,
+                         stream);
 }
 
 int ftb_exchange_receive(void *buffer, float *out, int64_t elems, int rank, int world, int reverse,

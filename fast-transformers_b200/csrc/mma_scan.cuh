@@ -146,6 +146,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
 }
+// One thread of a converged warp (the hardware picks it).  Code under this predicate is known to
+// the compiler to run on a single thread, unlike code under `lane == 0`.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -283,6 +296,35 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 __device__ __forceinline__ void tmem_wait_st() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+// 64 columns of one lane quarter in one load (waits for the data).
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr)
+        : "memory");
+}
+// Zero `n` consecutive columns of this warp's lanes: one source register, named n times.
+__device__ __forceinline__ void tmem_st_zero16(uint32_t taddr) {
+    const uint32_t z = 0u;
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tmem_st_zero32(uint32_t taddr) {
+    const uint32_t z = 0u;
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tmem_st_zero64(uint32_t taddr) {
+    const uint32_t z = 0u;
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x64.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(z) : "memory");
+}
+// Zero `ncols` (a multiple of 16, at most 96) columns starting at `taddr`, in as few stores as possible.
+__device__ __forceinline__ void tmem_zero_columns(uint32_t taddr, int ncols) {
+    if (ncols >= 64) { tmem_st_zero64(taddr); taddr += 64; ncols -= 64; }
+    if (ncols >= 32) { tmem_st_zero32(taddr); taddr += 32; ncols -= 32; }
+    if (ncols >= 16) tmem_st_zero16(taddr);
+}
 
 // ---- descriptors ----------------------------------------------------------------------------
 // Shared-memory matrix descriptor (descriptor version 1).  layout 2 = 128-byte swizzle with
@@ -327,6 +369,12 @@ struct Cfg {
     // the mask workers rearrange the tile in place once the score product has consumed it
     // (a state-only launch loads the MN-major image directly).
     static constexpr bool RELOAD_B = !F16;
+#ifndef FTB_ELECT
+#define FTB_ELECT 0
+#endif
+#ifndef FTB_MASK_V2
+#define FTB_MASK_V2 0
+#endif
 #ifndef FTB_B_BY_OUTPUT_WARPS
 #define FTB_B_BY_OUTPUT_WARPS 0
 #endif
@@ -500,7 +548,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
             // bar_fullc[s] : c has landed (mask(P) c, state update)
             // bar_fullbmn[s]: the MN-major image of b is in b's slot (state update): rearranged in
             //                place by the mask workers (scan), or loaded as such (state only)
-            if (lane == 0) {
+            if (FTB_ELECT ? elect_one() : lane == 0) {
                 // State-only launches: an L2 prefetch ahead of the loads into shared memory
                 // (measured: ~8 % faster there; no gain for the scan, where it is not used).
                 auto prefetch_chunk = [&](int ci) {
@@ -566,7 +614,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
             //   warp 1  ("output" issuer): O = a S ; O += mask(P) c
             //   warp 10 ("state" issuer) : S += b^T c ; scores of the next chunk
             // They meet only through mbarriers; every barrier below has ONE waiting thread.
-            if (lane == 0) {
+            if (FTB_ELECT ? elect_one() : lane == 0) {
                 constexpr uint32_t ID_P = instr_desc(K::FMT, 0, 0, 128, 128);
                 constexpr uint32_t ID_AS = instr_desc(K::FMT, 0, 1, 128, DCT);
                 constexpr uint32_t ID_PC = instr_desc(K::FMT, 0, 1, 128, DCT);
@@ -732,6 +780,62 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     tc_fence_after();
                     if constexpr (K::RELOAD_B && !K::B_BY_OUTPUT_WARPS) rearrange_b_in_place(ci, threadIdx.x - 352);
                     const uint32_t tP = tlane + K::TM_P + 128 * (ci & 1);
+#if FTB_MASK_V2
+                    // Rows of this warp are 32q..32q+31.  Column blocks of 32: those on one side of
+                    // the diagonal are kept as they are, those on the other side are dropped
+                    // (zeroed), the diagonal block is masked element by element.
+                    const int nkeep = p.reverse ? 3 - q : q;      // whole blocks kept
+                    const int ndrop = 3 - nkeep;                  // whole blocks dropped
+                    if constexpr (!K::F16) {
+                        // TF32: the product reads the fp32 scores in place.  The dropped columns
+                        // are one range: zero them with the widest stores first (they do not
+                        // depend on the load below and overlap its latency), then the diagonal.
+                        tmem_zero_columns(tP + (p.reverse ? 0 : 32 * (q + 1)), 32 * ndrop);
+                        tmem_ld32(tP + 32 * q, r);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            const bool keep = p.reverse ? (e >= lane) : (e <= lane);
+                            r[e] = keep ? r[e] : 0u;
+                        }
+                        tmem_st32(tP + 32 * q, r);
+                    } else {
+                        // bf16: every kept block is rounded and packed in place (block cb: fp32
+                        // columns 32cb.., packed columns 16cb..), blocks in ascending order so that
+                        // a packed block never lands on scores that are still to be read; two
+                        // blocks per load where there are two.  The dropped range is zeroed last
+                        // (its packed columns overlap fp32 scores of kept blocks).
+                        auto pack = [&](const uint32_t *src, uint32_t *dst, bool diag) {
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) {
+                                float x0 = __uint_as_float(src[2 * e]), x1 = __uint_as_float(src[2 * e + 1]);
+                                if (diag) {
+                                    const bool k0 = p.reverse ? (2 * e >= lane) : (2 * e <= lane);
+                                    const bool k1 = p.reverse ? (2 * e + 1 >= lane) : (2 * e + 1 <= lane);
+                                    x0 = k0 ? x0 : 0.f;
+                                    x1 = k1 ? x1 : 0.f;
+                                }
+                                __nv_bfloat162 hh = __floats2bfloat162_rn(x0, x1);
+                                dst[e] = *reinterpret_cast<uint32_t *>(&hh);
+                            }
+                        };
+                        const int kb0 = p.reverse ? q : 0, kb1 = p.reverse ? 3 : q;   // kept blocks, diagonal included
+                        int cb = kb0;
+                        for (; cb + 1 <= kb1; cb += 2) {
+                            uint32_t w[64], h2[32];
+                            tmem_ld64(tP + 32 * cb, w);
+                            pack(w, h2, cb == q);
+                            pack(w + 32, h2 + 16, cb + 1 == q);
+                            tmem_st32(tP + 16 * cb, h2);
+                        }
+                        if (cb <= kb1) {
+                            uint32_t h[16];
+                            tmem_ld32(tP + 32 * cb, r);
+                            pack(r, h, cb == q);
+                            tmem_st16(tP + 16 * cb, h);
+                        }
+                        tmem_zero_columns(tP + (p.reverse ? 0 : 16 * (q + 1)), 16 * ndrop);
+                    }
+#else
 #pragma unroll
                     for (int cb = 0; cb < 4; ++cb) {
                         // rows of this warp are 32q..32q+31, columns of the block 32cb..32cb+31
@@ -774,6 +878,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                             tmem_st16(tP + 16 * cb, h);
                         }
                     }
+#endif
                     tmem_wait_st();
                     tc_fence_before();
                     mbar_arrive(bar_pready + 8 * (ci & 1));

@@ -13,8 +13,8 @@
 //   [flags: 2 x P u64]         flag[parity][src] = number of the last exchange src has delivered
 //   [slots: 2 x P x elems f32] slot[parity][src] = the state src delivered in that exchange
 //
-// push_kernel (rank r) stores its state into slot[e & 1][r] of every rank that needs it -- peer
-// stores over NVLink -- and then releases flag[e & 1][r] = e at system scope; receive_kernel waits
+// push_kernel (rank r) stores its state (given whole, or as partial sums that it adds up on the
+// way) into slot[e & 1][r] of every rank that needs it -- peer stores over NVLink -- and then releases flag[e & 1][r] = e at system scope; receive_kernel waits
 // (bounded) until the flags of the ranks it needs have reached e and adds their slots up in rank
 // order.  e comes from counters in the owner's control block, advanced by the kernels themselves,
 // so the pair can be captured in a CUDA graph and replayed.  There are two slots per source,
@@ -91,8 +91,8 @@ __device__ __forceinline__ bool wait_reaches(const unsigned long long *p, unsign
 // grid (blocks per target, targets); targets = the ranks after this one (before it when reverse).
 // A rank without targets launches one block, which only advances the counter.
 __global__ void __launch_bounds__(kThreads)
-push_kernel(const float *__restrict__ state, int64_t elems, Peers peers, int rank, int world, int reverse,
-            int *device_status, long long wait_ns) {
+push_kernel(const float *__restrict__ state, int64_t elems, int64_t unit_elems, int parts_per_unit,
+            Peers peers, int rank, int world, int reverse, int *device_status, long long wait_ns) {
     char *own = static_cast<char *>(peers.buf[rank]);
     volatile unsigned long long *ctl = reinterpret_cast<volatile unsigned long long *>(own);
     const unsigned long long epoch = ctl[0] + 1;   // no block writes ctl[0] before all have read it
@@ -119,9 +119,27 @@ push_kernel(const float *__restrict__ state, int64_t elems, Peers peers, int ran
     }
     __syncthreads();
     const bool deliver = !s_fail;
-    if (deliver)
+    if (deliver && parts_per_unit <= 1) {
         for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n4; i += (int64_t)gridDim.x * kThreads)
             dst[i] = src[i];
+    } else if (deliver) {
+        // the state arrives as `parts_per_unit` partial sums per unit of `unit_elems` floats (the
+        // per-segment totals of one (batch, head) pair): they are added up on the way, in a fixed order
+        const int64_t u4 = unit_elems / 4;
+        for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n4; i += (int64_t)gridDim.x * kThreads) {
+            const int64_t unit = i / u4, e = i - unit * u4;
+            const float4 *part = src + unit * parts_per_unit * u4 + e;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < parts_per_unit; ++k) {
+                const float4 v = part[(int64_t)k * u4];
+                acc.x += v.x;
+                acc.y += v.y;
+                acc.z += v.z;
+                acc.w += v.w;
+            }
+            dst[i] = acc;
+        }
+    }
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {

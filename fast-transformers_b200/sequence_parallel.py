@@ -58,6 +58,22 @@ class LocalOps(object):
         half = ws[total // 2:]
         return causal_state_sum(x, y, mode=self.mode, workspace=half, reverse=True), ws
 
+    def state_parts(self, x, y, reverse=False):
+        """Like ``state_sum`` but without adding the partial sums up: returns
+        ``(parts, blocks_per_pair, token)`` -- ``parts`` a float32 view of the workspace holding
+        ``blocks_per_pair`` (D, M) blocks per (batch, head) pair -- or None when this shape and mode
+        keep no raw partial sums.  ``PeerExchange.push_parts`` adds them up while it sends them."""
+        from .causal_product import causal_state_parts
+        total = self._bytes(x, y, reverse)
+        ws = torch.empty(max(total, 1), dtype=torch.uint8, device=x.device)
+        half = ws[total // 2:] if reverse else ws
+        n = causal_state_parts(x, y, half, mode=self.mode)
+        if n == 0:
+            return None
+        N, H, _, D = x.shape
+        count = N * H * n * D * y.shape[3]
+        return half[:4 * count].view(torch.float32), n, ws
+
     def forward(self, Q, K, V, initial_state, token):
         from .causal_product import causal_dot_product_cuda
         out = torch.empty(Q.shape[0], Q.shape[1], Q.shape[2], V.shape[3], device=Q.device,
@@ -74,6 +90,25 @@ class LocalOps(object):
                                  initial_grad_state=initial_grad_state, forward_workspace=use_fwd,
                                  workspace=bwd_token, workspace_has_grad_states=True)
         return gq, gk, gv
+
+    # The backward in two calls: grad_Q reads the forward states only, so it can run while the
+    # reverse states of the other ranks are still on their way.
+    def backward_queries(self, Q, K, V, G, initial_state, fwd_token, bwd_token):
+        from .causal_product import causal_dot_backward_cuda
+        gq = torch.empty_like(Q)
+        use_fwd = fwd_token if (fwd_token is not None and self.mode == "mma") else None
+        causal_dot_backward_cuda(Q, K, V, G, gq, None, None, self.mode, initial_state=initial_state,
+                                 forward_workspace=use_fwd, workspace=bwd_token,
+                                 workspace_has_grad_states=True)
+        return gq
+
+    def backward_keys_values(self, Q, K, V, G, initial_grad_state, bwd_token):
+        from .causal_product import causal_dot_backward_cuda
+        gk, gv = torch.empty_like(K), torch.empty_like(V)
+        causal_dot_backward_cuda(Q, K, V, G, None, gk, gv, self.mode,
+                                 initial_grad_state=initial_grad_state, workspace=bwd_token,
+                                 workspace_has_grad_states=True)
+        return gk, gv
 
 
 def exclusive_scan_over_ranks(local, group=None, reverse=False):
@@ -142,23 +177,56 @@ class PeerExchange(object):
                 self._bufs[r] = ptr.value
         dist.barrier(group=group)      # nobody pushes into a buffer that is not mapped everywhere
 
-    def exclusive_scan(self, local, reverse=False):
-        """Sum of ``local`` over the ranks before this one (after it when ``reverse``)."""
+    def _stream(self, device):
+        return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+    def push(self, local, reverse=False):
+        """Deliver this rank's state to the ranks after it (before it when ``reverse``)."""
         if self._own is None:
             raise RuntimeError("this exchange has been closed")
         if tuple(local.shape) != self.shape or local.dtype != torch.float32 or not local.is_cuda:
             raise RuntimeError("expected a float32 CUDA state of shape %r" % (self.shape,))
         local = local.contiguous()
-        out = torch.empty_like(local)
-        stream = ctypes.c_void_p(torch.cuda.current_stream(local.device).cuda_stream)
         with torch.cuda.device(local.device):
             self._native.check(self._lib.ftb_exchange_push(
                 ctypes.c_void_p(local.data_ptr()), self.elems, self._bufs, self.rank, self.world,
-                int(bool(reverse)), stream), "ftb_exchange_push")
+                int(bool(reverse)), self._stream(local.device)), "ftb_exchange_push")
+
+    def push_parts(self, parts, blocks_per_unit, reverse=False):
+        """The same for a state that exists only as partial sums: ``parts`` is a contiguous float32
+        tensor holding, for every unit (a (batch, head) pair: ``shape[0] * shape[1]`` of them),
+        ``blocks_per_unit`` blocks whose sum is the unit's state; they are added up on the way."""
+        if self._own is None:
+            raise RuntimeError("this exchange has been closed")
+        units = self.shape[0] * self.shape[1]
+        unit_elems = self.elems // max(units, 1)
+        if parts.dtype != torch.float32 or not parts.is_cuda or not parts.is_contiguous() or \
+                parts.numel() != self.elems * blocks_per_unit:
+            raise RuntimeError("parts does not hold %d blocks per unit of a %r state"
+                               % (blocks_per_unit, self.shape))
+        with torch.cuda.device(parts.device):
+            self._native.check(self._lib.ftb_exchange_push_parts(
+                ctypes.c_void_p(parts.data_ptr()), unit_elems, int(blocks_per_unit), units, self._bufs,
+                self.rank, self.world, int(bool(reverse)), self._stream(parts.device)),
+                "ftb_exchange_push_parts")
+
+    def receive(self, reverse=False):
+        """Sum of the states delivered by the ranks before this one (after it when ``reverse``);
+        zeros when there are none.  Waits (on the GPU, bounded) for the peers' pushes of the same
+        exchange; every rank must have issued its own push of that exchange before."""
+        if self._own is None:
+            raise RuntimeError("this exchange has been closed")
+        out = torch.empty(self.shape, dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
             self._native.check(self._lib.ftb_exchange_receive(
                 self._own, ctypes.c_void_p(out.data_ptr()), self.elems, self.rank, self.world,
-                int(bool(reverse)), stream), "ftb_exchange_receive")
+                int(bool(reverse)), self._stream(self.device)), "ftb_exchange_receive")
         return out
+
+    def exclusive_scan(self, local, reverse=False):
+        """Sum of ``local`` over the ranks before this one (after it when ``reverse``)."""
+        self.push(local, reverse)
+        return self.receive(reverse)
 
     def check(self):
         """Synchronise this device (all streams) and raise if a push or receive gave up waiting
@@ -182,12 +250,29 @@ class PeerExchange(object):
         self._own, self._peers = None, []
 
 
+def _split_ops(ops, exchange):
+    """The peer-memory exchange lets a rank push partial sums and overlap the wait for its peers
+    with work that does not need them; it is used when the local operations offer the pieces."""
+    return exchange is not None and all(hasattr(ops, n) for n in (
+        "state_parts", "backward_queries", "backward_keys_values")) and \
+        hasattr(exchange, "push_parts")
+
+
 class SequenceParallelCausalDotProduct(torch.autograd.Function):
     @staticmethod
     def forward(ctx, Q, K, V, group, ops, exchange):
-        T, token = ops.state_sum(K.detach(), V.detach(), reverse=False)
-        S_init = (exchange.exclusive_scan(T, reverse=False) if exchange is not None
-                  else exclusive_scan_over_ranks(T, group, reverse=False))
+        pushed = False
+        if _split_ops(ops, exchange):
+            got = ops.state_parts(K.detach(), V.detach(), reverse=False)
+            if got is not None:
+                parts, n, token = got
+                exchange.push_parts(parts, n, reverse=False)
+                S_init = exchange.receive(reverse=False)
+                pushed = True
+        if not pushed:
+            T, token = ops.state_sum(K.detach(), V.detach(), reverse=False)
+            S_init = (exchange.exclusive_scan(T, reverse=False) if exchange is not None
+                      else exclusive_scan_over_ranks(T, group, reverse=False))
         out = ops.forward(Q.detach(), K.detach(), V.detach(), S_init, token)
         ctx.save_for_backward(Q, K, V, S_init)
         ctx.group, ctx.ops, ctx.token, ctx.exchange = group, ops, token, exchange
@@ -196,12 +281,24 @@ class SequenceParallelCausalDotProduct(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         Q, K, V, S_init = ctx.saved_tensors
+        ops, exchange = ctx.ops, ctx.exchange
         G = grad_out if grad_out.dtype == Q.dtype else grad_out.to(Q.dtype)
-        U, bwd_token = ctx.ops.state_sum(Q.detach(), G, reverse=True)
-        R_init = (ctx.exchange.exclusive_scan(U, reverse=True) if ctx.exchange is not None
+        if _split_ops(ops, exchange):
+            got = ops.state_parts(Q.detach(), G, reverse=True)
+            if got is not None:
+                # push the reverse partial sums, compute grad_Q (it needs none of the peers'
+                # states) while they travel, then receive and finish
+                parts, n, bwd_token = got
+                exchange.push_parts(parts, n, reverse=True)
+                gq = ops.backward_queries(Q.detach(), K.detach(), V.detach(), G, S_init, ctx.token, bwd_token)
+                R_init = exchange.receive(reverse=True)
+                gk, gv = ops.backward_keys_values(Q.detach(), K.detach(), V.detach(), G, R_init, bwd_token)
+                return gq, gk, gv, None, None, None
+        U, bwd_token = ops.state_sum(Q.detach(), G, reverse=True)
+        R_init = (exchange.exclusive_scan(U, reverse=True) if exchange is not None
                   else exclusive_scan_over_ranks(U, ctx.group, reverse=True))
-        gq, gk, gv = ctx.ops.backward(Q.detach(), K.detach(), V.detach(), G, S_init, R_init,
-                                      ctx.token, bwd_token)
+        gq, gk, gv = ops.backward(Q.detach(), K.detach(), V.detach(), G, S_init, R_init,
+                                  ctx.token, bwd_token)
         return gq, gk, gv, None, None, None
 
 

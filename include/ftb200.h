@@ -181,7 +181,15 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
  * The per-segment states it leaves in `workspace` can be handed to the forward / backward entry
  * points (workspace_has_states / workspace_has_grad_states); pass reverse = 1 when they will seed
  * the backward's descending scans (x = Q, y = grad_out).
+ *
+ * state == NULL: only partial sums are produced -- ftb_causal_state_parts(...) blocks of (D,M) floats
+ * per (batch, head) pair, contiguous at the start of `workspace`, pair after pair -- for a caller
+ * that adds them up itself (ftb_exchange_push_parts does, on the way to the peers); the workspace
+ * can be handed on exactly as after a call with a state.  ftb_causal_state_parts returns 0 where
+ * the workspace would not hold raw partial sums (FTB_MODE_FP32_SIMT or very many segments); the
+ * call with state == NULL then returns FTB_ERR_UNSUPPORTED.
  */
+int ftb_causal_state_parts(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M, int dtype, int mode);
 int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, int64_t H,
                          int64_t L, int64_t D, int64_t M, const int64_t *x_strides,
                          const int64_t *y_strides, int dtype, int mode, int reverse,
@@ -296,6 +304,11 @@ int ftb_recurrent_cross_linear_step(const void *q, const float *S, const float *
  *                         after it (before it when reverse != 0) and then releases a per-slot
  *                         counter; `buffers` holds `world` pointers in rank order, this rank's own
  *                         buffer at [rank].
+ *   ftb_exchange_push_parts  the same for a state given as partial sums: `units` units (the (batch,
+ *                         head) pairs) of `unit_elems` floats each, every unit as `parts_per_unit`
+ *                         consecutive blocks of unit_elems floats whose sum is the unit's state
+ *                         (the layout ftb_causal_state_sum leaves with state == NULL); the blocks
+ *                         are added up in a fixed order while they are pushed.
  *   ftb_exchange_receive  waits until the ranks before this one (after it when reverse != 0) have
  *                         delivered, and writes the sum of their states to `out` (zeros when there
  *                         are none).  The wait is bounded (a second unless changed with
@@ -320,6 +333,8 @@ int ftb_exchange_destroy(void *buffer);
 int ftb_exchange_wait_limit_ms(int ms);
 int ftb_exchange_push(const float *state, int64_t elems, void *const *buffers, int rank, int world,
                       int reverse, void *stream);
+int ftb_exchange_push_parts(const float *parts, int64_t unit_elems, int parts_per_unit, int64_t units,
+                            void *const *buffers, int rank, int world, int reverse, void *stream);
 int ftb_exchange_receive(void *buffer, float *out, int64_t elems, int rank, int world, int reverse,
                          void *stream);
 
