@@ -41,6 +41,52 @@ class OracleOps(object):
                                     final_grad_state=initial_grad_state)
 
 
+class SplitOracleOps(OracleOps):
+    """The pieces the peer-memory path uses: partial sums (here three unequal slices of the
+    positions per (batch, head) pair) and the backward in two calls."""
+
+    def state_parts(self, x, y, reverse=False):
+        L = x.shape[2]
+        cuts = [0, L // 4, L // 2 + 1, L]
+        blocks = [(x[:, :, a:b].transpose(-1, -2) @ y[:, :, a:b]) for a, b in zip(cuts, cuts[1:])]
+        parts = torch.stack(blocks, dim=2).contiguous()      # (N, H, 3, D, M)
+        return parts.reshape(-1), 3, None
+
+    def backward_queries(self, Q, K, V, G, initial_state, fwd_token, bwd_token):
+        return self.backward(Q, K, V, G, initial_state, None, None, None)[0]
+
+    def backward_keys_values(self, Q, K, V, G, initial_grad_state, bwd_token):
+        return self.backward(Q, K, V, G, None, initial_grad_state, None, None)[1:]
+
+
+class GlooExchange(object):
+    """Stand-in for ``PeerExchange`` with the same push / receive split, over gloo."""
+
+    def __init__(self, shape):
+        self.shape, self.pending, self.log = tuple(shape), None, []
+
+    def push_parts(self, parts, blocks_per_unit, reverse=False):
+        N, H, D, M = self.shape
+        self.push(parts.view(N, H, blocks_per_unit, D, M).sum(dim=2), reverse)
+
+    def push(self, local, reverse=False):
+        assert self.pending is None, "two pushes without a receive in between"
+        self.pending = (local.contiguous(), reverse)
+        self.log.append("push")
+
+    def receive(self, reverse=False):
+        from fast_transformers_b200 import sequence_parallel as sp
+        local, rev = self.pending
+        assert rev == reverse
+        self.pending = None
+        self.log.append("receive")
+        return sp.exclusive_scan_over_ranks(local, reverse=reverse)
+
+    def exclusive_scan(self, local, reverse=False):
+        self.push(local, reverse)
+        return self.receive(reverse)
+
+
 def _worker(rank, world, port, case, errq):
     try:
         sys.path.insert(0, ROOT)
@@ -70,8 +116,16 @@ def _worker(rank, world, port, case, errq):
         want_g = orc.chunked_backward(Q, K, V, G, chunk=16)
 
         q, k, v = (sp.shard_sequence(t, rank, world).clone().requires_grad_(True) for t in (Q, K, V))
-        out = sp.sequence_parallel_causal_dot_product(q, k, v, ops=OracleOps())
-        out.backward(sp.shard_sequence(G, rank, world))
+        if case == "split_exchange":
+            # the path of the peer-memory exchange: partial sums pushed, grad_Q between the push
+            # and the receive of the reverse states
+            exchange = GlooExchange((N, H, D, M))
+            out = sp.sequence_parallel_causal_dot_product(q, k, v, ops=SplitOracleOps(), exchange=exchange)
+            out.backward(sp.shard_sequence(G, rank, world))
+            assert exchange.log == ["push", "receive", "push", "receive"] and exchange.pending is None
+        else:
+            out = sp.sequence_parallel_causal_dot_product(q, k, v, ops=OracleOps())
+            out.backward(sp.shard_sequence(G, rank, world))
         assert torch.allclose(out, sp.shard_sequence(want_out, rank, world), rtol=1e-12, atol=1e-12)
         for got, want in zip((q.grad, k.grad, v.grad), want_g):
             assert torch.allclose(got, sp.shard_sequence(want, rank, world), rtol=1e-12, atol=1e-12)
@@ -110,6 +164,10 @@ def _run(world, case):
 @pytest.mark.parametrize("world", [2, 3])
 def test_sequence_split_matches_single_rank(world):
     _run(world, "split")
+
+
+def test_split_exchange_path_matches_single_rank():
+    _run(3, "split_exchange")
 
 
 def test_rank_that_never_joins_is_an_error_not_a_hang():
