@@ -18,9 +18,10 @@
 // bits; the bf16 variant rounds this operand copy only -- the accumulated state stays fp32).
 //
 // Warp roles: warp 0 = TMA producer (+ TMEM allocation), warps 1 and 10 = single-thread MMA
-// issuers (outputs / scores and state), warps 2-5 = state workers (the loop-carried chain:
-// state update -> operand copy -> next a S), warps 6-9 = output workers (O rows -> global
-// memory), warps 11-14 = mask workers.  Every wait is bounded: on expiry the CTA records
+// issuers (outputs / scores and state; each elected with elect.sync), warps 2-5 = state workers
+// (the loop-carried chain: state update -> operand copy -> next a S), warps 6-9 = output workers
+// (O rows -> global memory; for TF32 they also make the MN-major image of b in place while the
+// mask workers mask), warps 11-14 = mask workers.  Every wait is bounded: on expiry the CTA records
 // FTB_ERR_TIMEOUT in a device status word, stops issuing work, releases its tensor memory and
 // returns.
 //
@@ -369,18 +370,6 @@ struct Cfg {
     // the mask workers rearrange the tile in place once the score product has consumed it
     // (a state-only launch loads the MN-major image directly).
     static constexpr bool RELOAD_B = !F16;
-#ifndef FTB_ELECT
-#define FTB_ELECT 0
-#endif
-#ifndef FTB_MASK_V2
-#define FTB_MASK_V2 0
-#endif
-#ifndef FTB_B_BY_OUTPUT_WARPS
-#define FTB_B_BY_OUTPUT_WARPS 0
-#endif
-    // who rearranges b in place: the mask workers before they mask (0), or the output workers
-    // while the mask workers mask (1)
-    static constexpr bool B_BY_OUTPUT_WARPS = FTB_B_BY_OUTPUT_WARPS != 0;
     // state-only launches: the same ring memory as slots of b | c
     static constexpr int SO_BYTES = A_BYTES + C_BYTES;
     static constexpr int SO_STAGES = (STAGES * STAGE_BYTES) / SO_BYTES;
@@ -548,7 +537,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
             // bar_fullc[s] : c has landed (mask(P) c, state update)
             // bar_fullbmn[s]: the MN-major image of b is in b's slot (state update): rearranged in
             //                place by the mask workers (scan), or loaded as such (state only)
-            if (FTB_ELECT ? elect_one() : lane == 0) {
+            if (elect_one()) {
                 // State-only launches: an L2 prefetch ahead of the loads into shared memory
                 // (measured: ~8 % faster there; no gain for the scan, where it is not used).
                 auto prefetch_chunk = [&](int ci) {
@@ -614,7 +603,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
             //   warp 1  ("output" issuer): O = a S ; O += mask(P) c
             //   warp 10 ("state" issuer) : S += b^T c ; scores of the next chunk
             // They meet only through mbarriers; every barrier below has ONE waiting thread.
-            if (FTB_ELECT ? elect_one() : lane == 0) {
+            if (elect_one()) {
                 constexpr uint32_t ID_P = instr_desc(K::FMT, 0, 0, 128, 128);
                 constexpr uint32_t ID_AS = instr_desc(K::FMT, 0, 1, 128, DCT);
                 constexpr uint32_t ID_PC = instr_desc(K::FMT, 0, 1, 128, DCT);
@@ -778,9 +767,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                 for (int ci = 0; ci < nchunk; ++ci) {
                     if (!mbar_wait(bar_pfull + 8 * (ci & 1), (ci >> 1) & 1, abort_flag)) break;
                     tc_fence_after();
-                    if constexpr (K::RELOAD_B && !K::B_BY_OUTPUT_WARPS) rearrange_b_in_place(ci, threadIdx.x - 352);
                     const uint32_t tP = tlane + K::TM_P + 128 * (ci & 1);
-#if FTB_MASK_V2
                     // Rows of this warp are 32q..32q+31.  Column blocks of 32: those on one side of
                     // the diagonal are kept as they are, those on the other side are dropped
                     // (zeroed), the diagonal block is masked element by element.
@@ -835,50 +822,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         }
                         tmem_zero_columns(tP + (p.reverse ? 0 : 16 * (q + 1)), 16 * ndrop);
                     }
-#else
-#pragma unroll
-                    for (int cb = 0; cb < 4; ++cb) {
-                        // rows of this warp are 32q..32q+31, columns of the block 32cb..32cb+31
-                        const bool all_keep = p.reverse ? (cb > q) : (cb < q);
-                        const bool all_drop = p.reverse ? (cb < q) : (cb > q);
-                        if constexpr (!K::F16) {
-                            if (all_keep) continue;
-                            if (all_drop) {
-#pragma unroll
-                                for (int e = 0; e < 32; ++e) r[e] = 0u;
-                            } else {
-                                tmem_ld32(tP + 32 * cb, r);
-#pragma unroll
-                                for (int e = 0; e < 32; ++e) {
-                                    const bool keep = p.reverse ? (e >= lane) : (e <= lane);
-                                    r[e] = keep ? r[e] : 0u;
-                                }
-                            }
-                            tmem_st32(tP + 32 * cb, r);
-                        } else {
-                            uint32_t h[16];
-                            if (all_drop) {
-#pragma unroll
-                                for (int e = 0; e < 16; ++e) h[e] = 0u;
-                            } else {
-                                tmem_ld32(tP + 32 * cb, r);
-#pragma unroll
-                                for (int e = 0; e < 16; ++e) {
-                                    float x0 = __uint_as_float(r[2 * e]), x1 = __uint_as_float(r[2 * e + 1]);
-                                    if (!all_keep) {
-                                        const bool k0 = p.reverse ? (2 * e >= lane) : (2 * e <= lane);
-                                        const bool k1 = p.reverse ? (2 * e + 1 >= lane) : (2 * e + 1 <= lane);
-                                        x0 = k0 ? x0 : 0.f;
-                                        x1 = k1 ? x1 : 0.f;
-                                    }
-                                    __nv_bfloat162 hh = __floats2bfloat162_rn(x0, x1);
-                                    h[e] = *reinterpret_cast<uint32_t *>(&hh);
-                                }
-                            }
-                            tmem_st16(tP + 16 * cb, h);
-                        }
-                    }
-#endif
                     tmem_wait_st();
                     tc_fence_before();
                     mbar_arrive(bar_pready + 8 * (ci & 1));
@@ -897,7 +840,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     const int c = p.reverse ? nchunk - 1 - ci : ci;
                     const int64_t row0 = seg_begin + (int64_t)c * C;
                     const int ob = ci % K::NOBUF, ouse = ci / K::NOBUF;
-                    if constexpr (K::RELOAD_B && K::B_BY_OUTPUT_WARPS && !apply_only) {
+                    if constexpr (K::RELOAD_B && !apply_only) {
                         // these warps are idle between two stores: they make the MN-major image
                         // of b while the mask workers mask the scores
                         ok = mbar_wait(bar_pfull + 8 * (ci & 1), (ci >> 1) & 1, abort_flag);
