@@ -33,7 +33,7 @@ EXPORTS = (
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
                 "mma_bwd_qr", "mma_bwd_multi", "recurrent_step", "normaliser", "feature_map",
-                "rank_exchange", "apply_state", "mma_state_bwd")
+                "rank_exchange", "apply_state")
 
 _lib = None
 _i64, _vp, _int, _sz = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t

@@ -252,9 +252,9 @@ def causal_state_sum(x, y, mode=None, workspace=None, reverse=False):
         nbytes = L_.ftb_causal_workspace_bytes(N, H, L, D, M, dt, m, 0, 1)
         if workspace is not None:
             # a caller-kept workspace: the per-segment states left in it can be handed to the
-            # forward (workspace_has_states) or backward (workspace_has_grad_states) call.  Only
-            # the totals area is written here, so half of a backward workspace is enough (the
-            # library checks the size it needs).
+            # forward (workspace_has_states) or backward (workspace_has_grad_states) call
+            if workspace.numel() * workspace.element_size() < nbytes:
+                raise RuntimeError("workspace tensor is too small")
             ws, nbytes = workspace, workspace.numel() * workspace.element_size()
         else:
             ws, nbytes = _workspace(nbytes, dev)

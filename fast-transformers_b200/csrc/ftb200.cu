@@ -186,8 +186,7 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
                        const int64_t *as, const int64_t *bs, const int64_t *cs, const int64_t *os,
                        int64_t N, int64_t H, int64_t L, int Da, int Dc, int dtype, Plan pl,
                        const float *states, const float *init, int sum_mode, int sub, float *state_out,
-                       int skip_lo, int skip_hi, int canon_is_DaDc, int reverse, int inclusive = 0,
-                       float *end_state_out = nullptr) {
+                       int skip_lo, int skip_hi, int canon_is_DaDc, int reverse) {
     const bool state_only = (a == nullptr);
     const bool apply_only = (b == nullptr);   // out = a S_init: only `a` is read
     const int DCT = dtype == FTB_F32 ? 64 : 128;
@@ -235,7 +234,6 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
     p.init = init; p.sum_mode = sum_mode; p.sub = sub < 1 ? 1 : sub;
     p.skip_lo = skip_lo; p.skip_hi = skip_hi;
     p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = state_only ? 1 : 0;
-    p.inclusive = inclusive; p.end_state_out = end_state_out;
     if (batch.b.njobs == 0) {
         batch.dtype = dtype;
         batch.kind = state_only ? FTB_KERNEL_MMA_STATE : (reverse ? FTB_KERNEL_MMA_BWD : FTB_KERNEL_MMA_FWD);
@@ -274,12 +272,11 @@ static int mma_launch(const void *a, const void *b, const void *c, void *out, co
                       const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H,
                       int64_t L, int Da, int Dc, int dtype, Plan pl, const float *states,
                       const float *init, int sum_mode, int sub, float *state_out, int skip_lo, int skip_hi,
-                      int canon_is_DaDc, int reverse, cudaStream_t st, bool after_own_launch = false,
-                      float *end_state_out = nullptr) {
+                      int canon_is_DaDc, int reverse, cudaStream_t st, bool after_own_launch = false) {
     MmaBatch batch;
     batch.after_own_launch = after_own_launch;
     int rc = mma_add_job(batch, a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, states, init,
-                         sum_mode, sub, state_out, skip_lo, skip_hi, canon_is_DaDc, reverse, 0, end_state_out);
+                         sum_mode, sub, state_out, skip_lo, skip_hi, canon_is_DaDc, reverse);
     if (rc) return rc;
     return mma_launch_batch(batch, st);
 }
@@ -314,12 +311,10 @@ struct SegStates {
 static int launch_scan(int mode, const void *a, const void *b, const void *c, void *out,
                        const int64_t *as, const int64_t *bs, const int64_t *cs, const int64_t *os,
                        int64_t N, int64_t H, int64_t L, int Da, int Dc, int dtype, Plan pl,
-                       SegStates ss, int canon_is_DaDc, int reverse, cudaStream_t st,
-                       float *end_state_out = nullptr) {
+                       SegStates ss, int canon_is_DaDc, int reverse, cudaStream_t st) {
     if (mode == FTB_MODE_MMA)
         return mma_launch(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, ss.states, ss.init,
-                          ss.sum_mode, ss.sub, nullptr, 0, 0, canon_is_DaDc, reverse, st, ss.fresh != 0,
-                          end_state_out);
+                          ss.sum_mode, ss.sub, nullptr, 0, 0, canon_is_DaDc, reverse, st, ss.fresh != 0);
     return simt_launch_scan(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl,
                             ss.states ? ss.states : ss.init, pl.nseg, canon_is_DaDc, reverse, st);
 }
@@ -572,25 +567,18 @@ int ftb_timing_read(float *ms_by_kind, int *launches_by_kind, int nkinds) {
     return rc;
 }
 
-// Layout of a forward workspace: [per-segment totals (or prefixes): totals_bytes][tensor-core mode:
-// the state at the END of every segment, one (D,M) block per (bh, seg): end_bytes].  The backward's
-// own workspace is two totals areas (forward states | reverse states).
-static size_t totals_bytes(int mode, Plan pl, int64_t N, int64_t H, int64_t D, int64_t M) {
-    return align256((size_t)N * H * pl.nseg * state_sub(mode, pl, N * H) * D * M * sizeof(float));
-}
-static size_t end_bytes(int mode, Plan pl, int64_t N, int64_t H, int64_t D, int64_t M) {
-    return mode == FTB_MODE_MMA ? align256((size_t)N * H * pl.nseg * D * M * sizeof(float)) : 0;
-}
-
 size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M,
                                   int dtype, int mode, int backward, int want_state) {
     (void)dtype;
     if (N <= 0 || H <= 0 || L <= 0 || D <= 0 || M <= 0) return 0;
-    Plan pl = choose_plan(mode, N * H, L);
-    const size_t one = totals_bytes(mode, pl, N, H, D, M);
-    if (backward) return 2 * one;
-    if (mode == FTB_MODE_MMA) return one + end_bytes(mode, pl, N, H, D, M);   // end states at a fixed offset
-    return (pl.nseg > 1 || want_state) ? one : 0;
+    {
+        Plan pl = choose_plan(mode, N * H, L);
+        size_t one = align256((size_t)N * H * pl.nseg * state_sub(mode, pl, N * H) * D * M *
+                              sizeof(float));
+        if (backward) return 2 * one;
+        return (pl.nseg > 1 || want_state) ? one : 0;
+    }
+    return 0;
 }
 
 int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *out, int64_t N,
@@ -627,13 +615,10 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
 
     Plan pl = choose_plan(mode, N * H, L);
     float *ws = (float *)workspace;
-    const size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, final_state != nullptr);
-    if (need && (!workspace || workspace_bytes < need)) return FTB_ERR_WORKSPACE;
-    // tensor-core mode: every scan block leaves the state at the end of its segment behind the
-    // totals; a backward call that is handed this workspace starts its descending scans from there
-    float *end_states = mode == FTB_MODE_MMA
-                            ? (float *)((char *)workspace + totals_bytes(mode, pl, N, H, D, M))
-                            : nullptr;
+    if (pl.nseg > 1 || final_state) {
+        size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, final_state != nullptr);
+        if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
+    }
     SegStates ss;
     if (workspace_has_states && mode == FTB_MODE_MMA && !final_state) {
         // ftb_causal_state_sum(k, v, ...) already left the per-segment states in `workspace`
@@ -644,7 +629,7 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
         if (rc) return rc;
     }
     return launch_scan(mode, q, k, v, out, qs, ks, vs, os, N, H, L, (int)D, (int)M, dtype, pl, ss,
-                       /*canon_is_DaDc=*/1, /*reverse=*/0, st, end_states);
+                       /*canon_is_DaDc=*/1, /*reverse=*/0, st);
 }
 
 int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const void *g, void *gq,
@@ -688,15 +673,10 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
     float *wsS = (float *)workspace;
     float *wsR = (float *)((char *)workspace + need / 2);
 
-    // Tensor-core mode with the forward call's workspace at hand: grad_Q walks its rows downwards
-    // from the segment-end states the forward scan left there, in step with grad_K and grad_V (one
-    // grid), so the tiles the three scans share come from HBM once.
-    const bool in_step = mode == FTB_MODE_MMA && forward_workspace != nullptr && want_q && want_kv;
-
     // forward states: taken from the forward call's workspace when the caller kept it
     SegStates sS{nullptr, initial_state, 0, 1}, sR{nullptr, initial_grad_state, 0, 1};
-    if (!want_q || in_step) {
-        // grad_Q is the only reader of the forward states (in step: of the segment-end states)
+    if (!want_q) {
+        // grad_Q is the only reader of the forward states
     } else if (forward_workspace && pl.nseg > 1) {
         sS = describe_states(mode, pl, (const float *)forward_workspace, initial_state, N * H);
     } else {
@@ -718,42 +698,6 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
         rc = prepare_states(mode, q, g, qs, gs, N, H, L, (int)D, (int)M, dtype, pl, wsR,
                             initial_grad_state, nullptr, 1, st, &sR);
         if (rc) return rc;
-    }
-
-    if (in_step) {
-        const float *end_states =
-            (const float *)((const char *)forward_workspace + totals_bytes(mode, pl, N, H, D, M));
-        MmaBatch sweep, scans;
-        if (r_with_grad_q) {   // (here: the reverse totals still have to be swept, in a grid of their own)
-            Plan fine = pl;
-            fine.seg_len = pl.seg_len / sR.sub;
-            fine.nseg = pl.nseg * sR.sub;
-            rc = mma_add_job(sweep, nullptr, q, g, nullptr, nullptr, qs, gs, nullptr, N, H, L, (int)D, (int)M,
-                             dtype, fine, nullptr, nullptr, 0, 1, wsR, 0, sR.sub, 1, 0);
-            if (rc) return rc;
-            sweep.kind = FTB_KERNEL_MMA_STATE_BWD;
-        }
-        // grad_Q_i = X_c g_i - sum_{j>i, j in chunk} (g_i . v_j) k_j, X_c the state after chunk c
-        rc = mma_add_job(scans, g, v, k, gq, gs, vs, ks, gqs, N, H, L, (int)M, (int)D, dtype, pl, end_states,
-                         nullptr, 0, 1, nullptr, 0, 0, 0, 1, /*inclusive=*/1);
-        if (rc) return rc;
-        if (gk) {
-            rc = mma_add_job(scans, v, g, q, gk, vs, gs, qs, gks, N, H, L, (int)M, (int)D, dtype, pl, sR.states,
-                             sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 0, 1);
-            if (rc) return rc;
-        }
-        if (gv) {
-            rc = mma_add_job(scans, k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl, sR.states,
-                             sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 1, 1);
-            if (rc) return rc;
-        }
-        scans.kind = FTB_KERNEL_MMA_BWD_MULTI;
-        if (r_with_grad_q) {
-            rc = mma_launch_batch(sweep, st);
-            if (rc) return rc;
-        }
-        scans.after_own_launch = r_with_grad_q || sR.fresh;   // a sweep of this call is directly in front
-        return mma_launch_batch(scans, st);
     }
 
     if (mode == FTB_MODE_MMA) {
@@ -858,9 +802,7 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
     Plan pl = choose_plan(mode, N * H, L);
     if (pl.nseg == 1)
         return launch_state_sum(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, state, 0, 0, st);
-    // (only the totals area of a forward workspace is written here, so half of a backward workspace
-    // is large enough as well)
-    size_t need = totals_bytes(mode, pl, N, H, D, M);
+    size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, 1);
     if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
     SegStates ss;
     return prepare_states(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, (float *)workspace,

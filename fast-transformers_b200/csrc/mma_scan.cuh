@@ -66,15 +66,6 @@ struct ScanParams {
     int canon_is_DaDc;    // canonical block is [DA][Dc] (1) or [Dc][DA] (0)
     int reverse;
     int state_only;
-    // A scan that walks its rows DOWNWARDS carrying the state that INCLUDES the current chunk:
-    //   out_c = a_c X_c - strictly_upper(a_c b_c^T) c_c ;   X_{c-1} = X_c - b_c^T c_c
-    // (requires reverse).  grad_Q in this form runs in step with grad_K and grad_V -- one grid, the
-    // same rows at the same time -- so that the tiles the three scans share are fetched from HBM once.
-    // The two minus signs are the negate-A bit of the instruction descriptors.
-    int inclusive;
-    // forward scans: where to leave the state after the segment's last chunk (per (bh, seg) block in
-    // canonical layout; nullptr = nowhere).  It is what `inclusive` scans of the backward start from.
-    float *end_state_out;
     int pos_a[3], pos_b[3], pos_c[3];   // TMA coordinate slot of {position, head, batch}
 };
 
@@ -615,9 +606,8 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
             if (elect_one()) {
                 constexpr uint32_t ID_P = instr_desc(K::FMT, 0, 0, 128, 128);
                 constexpr uint32_t ID_AS = instr_desc(K::FMT, 0, 1, 128, DCT);
-                constexpr uint32_t NEG_A = 1u << 13;   // instruction descriptor: negate the A operand
-                const uint32_t ID_PC = instr_desc(K::FMT, 0, 1, 128, DCT) | (p.inclusive ? NEG_A : 0u);
-                const uint32_t ID_ST = instr_desc(K::FMT, 1, 1, DA, DCT) | (p.inclusive ? NEG_A : 0u);
+                constexpr uint32_t ID_PC = instr_desc(K::FMT, 0, 1, 128, DCT);
+                constexpr uint32_t ID_ST = instr_desc(K::FMT, 1, 1, DA, DCT);
                 constexpr int KSTEP_BYTES = K::KROWS * 128;   // MN-major advance along K
                 const uint32_t tS = tmem + K::TM_S;
                 bool ok = true;
@@ -791,7 +781,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         tmem_ld32(tP + 32 * q, r);
 #pragma unroll
                         for (int e = 0; e < 32; ++e) {
-                            const bool keep = p.reverse ? (e >= lane + p.inclusive) : (e <= lane);
+                            const bool keep = p.reverse ? (e >= lane) : (e <= lane);
                             r[e] = keep ? r[e] : 0u;
                         }
                         tmem_st32(tP + 32 * q, r);
@@ -806,8 +796,8 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                             for (int e = 0; e < 16; ++e) {
                                 float x0 = __uint_as_float(src[2 * e]), x1 = __uint_as_float(src[2 * e + 1]);
                                 if (diag) {
-                                    const bool k0 = p.reverse ? (2 * e >= lane + p.inclusive) : (2 * e <= lane);
-                                    const bool k1 = p.reverse ? (2 * e + 1 >= lane + p.inclusive) : (2 * e + 1 <= lane);
+                                    const bool k0 = p.reverse ? (2 * e >= lane) : (2 * e <= lane);
+                                    const bool k1 = p.reverse ? (2 * e + 1 >= lane) : (2 * e + 1 <= lane);
                                     x0 = k0 ? x0 : 0.f;
                                     x1 = k1 ? x1 : 0.f;
                                 }
@@ -1077,42 +1067,6 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                     tc_fence_before();
                     mbar_arrive(bar_smready);
                     mbar_arrive(bar_smready2);
-                }
-                if (!apply_only && p.end_state_out != nullptr && ok) {
-                    // ---- the state after the segment's last chunk -> global memory -------------
-                    // (the increment of the last chunk is still in its accumulator: no later chunk
-                    // needed it)
-                    const int cl = nchunk - 1;
-                    const int64_t blk = (int64_t)DA * p.Dc;
-                    float *dst = p.end_state_out + ((int64_t)bh * p.nseg + seg) * blk;
-                    if constexpr (K::REG_STATE) ok = mbar_wait(bar_tfull + 8 * (cl & 1), (cl >> 1) & 1, abort_flag);
-                    else ok = mbar_wait(bar_sfull, cl & 1, abort_flag);
-                    if (ok) {
-                        tc_fence_after();
-#pragma unroll
-                        for (int cb = 0; cb < DCT / 32; ++cb) {
-                            if constexpr (K::REG_STATE) {
-                                tmem_ld32(tlane + K::TM_S + (cl & 1) * DCT + 32 * cb, r);
-#pragma unroll
-                                for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(stv[32 * cb + e] + __uint_as_float(r[e]));
-                            } else {
-                                tmem_ld32(tlane + K::TM_S + 32 * cb, r);
-                            }
-                            if (srow_ok) {
-                                const int dc0 = n0 + 32 * cb;
-                                if (p.canon_is_DaDc) {
-                                    float4 *d4 = reinterpret_cast<float4 *>(dst + (int64_t)srow * p.Dc + dc0);
-#pragma unroll
-                                    for (int e = 0; e < 8; ++e)
-                                        d4[e] = make_float4(__uint_as_float(r[4 * e]), __uint_as_float(r[4 * e + 1]),
-                                                            __uint_as_float(r[4 * e + 2]), __uint_as_float(r[4 * e + 3]));
-                                } else {
-#pragma unroll
-                                    for (int e = 0; e < 32; ++e) dst[(int64_t)(dc0 + e) * DA + srow] = __uint_as_float(r[e]);
-                                }
-                            }
-                        }
-                    }
                 }
             }
         }

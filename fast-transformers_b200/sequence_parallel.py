@@ -37,12 +37,9 @@ class LocalOps(object):
     per-segment states it computed on the way); ``forward`` / ``backward`` take the tokens back so
     K, V (and Q, grad_out) are swept once, not twice."""
 
-    def __init__(self, mode=None, overlap_grad_queries=False):
+    def __init__(self, mode=None):
         from .settings import get_mode
         self.mode = mode or get_mode()
-        # with a PeerExchange: compute grad_Q between the push and the receive of the reverse
-        # states (two backward calls) instead of all three gradients in one call afterwards
-        self.overlap_grad_queries = overlap_grad_queries
 
     def _bytes(self, Q, V, backward):
         from .causal_product import workspace_bytes
@@ -289,22 +286,13 @@ class SequenceParallelCausalDotProduct(torch.autograd.Function):
         if _split_ops(ops, exchange):
             got = ops.state_parts(Q.detach(), G, reverse=True)
             if got is not None:
+                # push the reverse partial sums, compute grad_Q (it needs none of the peers'
+                # states) while they travel, then receive and finish
                 parts, n, bwd_token = got
                 exchange.push_parts(parts, n, reverse=True)
-                if getattr(ops, "overlap_grad_queries", False):
-                    # grad_Q needs none of the peers' states: compute it while they travel
-                    gq = ops.backward_queries(Q.detach(), K.detach(), V.detach(), G, S_init, ctx.token,
-                                              bwd_token)
-                    R_init = exchange.receive(reverse=True)
-                    gk, gv = ops.backward_keys_values(Q.detach(), K.detach(), V.detach(), G, R_init,
-                                                      bwd_token)
-                else:
-                    # one call for the three gradients: with the forward's workspace at hand the
-                    # tensor-core kernels walk them in step and read shared tiles from HBM once,
-                    # which saves more than hiding the exchange behind grad_Q does
-                    R_init = exchange.receive(reverse=True)
-                    gq, gk, gv = ops.backward(Q.detach(), K.detach(), V.detach(), G, S_init, R_init,
-                                              ctx.token, bwd_token)
+                gq = ops.backward_queries(Q.detach(), K.detach(), V.detach(), G, S_init, ctx.token, bwd_token)
+                R_init = exchange.receive(reverse=True)
+                gk, gv = ops.backward_keys_values(Q.detach(), K.detach(), V.detach(), G, R_init, bwd_token)
                 return gq, gk, gv, None, None, None
         U, bwd_token = ops.state_sum(Q.detach(), G, reverse=True)
         R_init = (exchange.exclusive_scan(U, reverse=True) if exchange is not None

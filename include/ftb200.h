@@ -99,8 +99,7 @@ int ftb_last_cuda_error(void);
 #define FTB_KERNEL_FEATURE_MAP 10 /* elu(x)+1 (x key-length mask) and its gradient    */
 #define FTB_KERNEL_RANK_EXCHANGE 11 /* push / receive of per-rank states over peer memory */
 #define FTB_KERNEL_APPLY_STATE 12  /* out = a . S for one fixed state per (batch, head) */
-#define FTB_KERNEL_MMA_STATE_BWD 13 /* tcgen05 per-segment totals of (q, grad_out), a grid of its own */
-#define FTB_KERNEL_KINDS 14
+#define FTB_KERNEL_KINDS 13
 uint64_t ftb_launch_count(void);
 /*
  * Device-side status word of the current device: 0, or the FTB_ERR_* code recorded by a kernel
@@ -155,10 +154,7 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
  * forward_workspace  : optional; the workspace buffer the forward call on the same
  *                      q, k, v, shape, dtype, mode and initial_state used, if its contents are
  *                      still intact.  It holds the per-segment forward states, which the
- *                      backward then does not recompute (one pass over K and V saved), and in
- *                      FTB_MODE_MMA the state at the end of every segment, from which grad_Q is
- *                      then computed walking downwards in step with grad_K and grad_V (one grid;
- *                      the tiles the three share are read from HBM once).
+ *                      backward then does not recompute (one pass over K and V saved).
  *                      NULL = recompute.  The reference keeps nothing but Q, K, V either.
  * workspace_has_grad_states : non-zero when ftb_causal_state_sum(q, grad_out, ..., reverse = 1)
  *                      has just been run on the SECOND half of `workspace` (offset

@@ -174,11 +174,7 @@ def test_states_split_sequence_tf32():
         assert orc.rel_err(torch.cat([a, b], 2), c) < TOL
 
 
-def test_forward_workspace_reuse_against_recompute():
-    """With the forward's workspace the backward reads the forward states instead of sweeping K, V
-    again (grad_K, grad_V: the same arithmetic, bitwise equal) and computes grad_Q walking
-    downwards from the segment-end states, in step with the other two (a different order of the
-    same sums: equal to the ascending form within the tolerance, and to the oracle)."""
+def test_forward_workspace_reuse_is_bitwise_equal_to_recompute():
     Q, K, V, G = workloads.make_inputs(1)
     Qd, Kd, Vd, Gd = (t.cuda() for t in (Q, K, V, G))
     out = torch.empty_like(Vd)
@@ -188,38 +184,8 @@ def test_forward_workspace_reuse_against_recompute():
     b = [torch.empty_like(t) for t in (Qd, Kd, Vd)]
     causal_dot_backward_cuda(Qd, Kd, Vd, Gd, *a, "mma", forward_workspace=kept[0])
     causal_dot_backward_cuda(Qd, Kd, Vd, Gd, *b, "mma")
-    assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
-    want = orc.chunked_backward(Q, K, V, G)
-    assert orc.rel_err(a[0], want[0]) < TOL and orc.rel_err(b[0], want[0]) < TOL
-    assert orc.rel_err(a[0], b[0]) < TOL
-    # grad_Q alone with the forward's workspace: the ascending scan on the kept forward states
-    only_q = torch.empty_like(Qd)
-    causal_dot_backward_cuda(Qd, Kd, Vd, Gd, only_q, None, None, "mma", forward_workspace=kept[0])
-    assert torch.equal(only_q, b[0])
-
-
-@pytest.mark.parametrize("dtype,D,L,H", [(torch.float32, 64, 1000, 3), (torch.float32, 64, 5000, 2),
-                                         (torch.bfloat16, 128, 900, 2), (torch.bfloat16, 128, 4100, 1),
-                                         (torch.float32, 64, 128, 5)])
-def test_grad_queries_walked_downwards_from_segment_end_states(dtype, D, L, H):
-    """The in-step backward on ragged lengths, one and several segments, both operand types, with an
-    initial state and an initial reverse state."""
-    g = torch.Generator().manual_seed(L + D)
-    N = 1
-    Q, K, V, G = (torch.rand(N, H, L, D, generator=g).to(dtype) for _ in range(4))
-    S0, R0 = (torch.rand(N, H, D, D, generator=g) for _ in range(2))
-    Qd, Kd, Vd, Gd = (t.cuda() for t in (Q, K, V, G))
-    out = torch.empty_like(Vd)
-    kept = []
-    causal_dot_product_cuda(Qd, Kd, Vd, out, "mma", initial_state=S0.cuda(), keep_workspace=kept)
-    grads = [torch.full_like(t, float("nan")) for t in (Qd, Kd, Vd)]
-    causal_dot_backward_cuda(Qd, Kd, Vd, Gd, *grads, "mma", initial_state=S0.cuda(),
-                             initial_grad_state=R0.cuda(), forward_workspace=kept[0])
-    f = [t.float() for t in (Q, K, V, G)]
-    want = (orc.chunked_forward(*f[:3], initial_state=S0),) + tuple(
-        orc.chunked_backward(*f, initial_state=S0, final_grad_state=R0))
-    for name, a, b in zip(NAMES, [out] + grads, want):
-        assert orc.rel_err(a, b) < TOL, name
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
 
 
 @pytest.mark.parametrize("mode", ["mma", "fp32"])

@@ -44,7 +44,6 @@ class OracleOps(object):
 class SplitOracleOps(OracleOps):
     """The pieces the peer-memory path uses: partial sums (here three unequal slices of the
     positions per (batch, head) pair) and the backward in two calls."""
-    overlap_grad_queries = True
 
     def state_parts(self, x, y, reverse=False):
         L = x.shape[2]
@@ -117,13 +116,11 @@ def _worker(rank, world, port, case, errq):
         want_g = orc.chunked_backward(Q, K, V, G, chunk=16)
 
         q, k, v = (sp.shard_sequence(t, rank, world).clone().requires_grad_(True) for t in (Q, K, V))
-        if case in ("split_exchange", "split_exchange_joint"):
+        if case == "split_exchange":
             # the path of the peer-memory exchange: partial sums pushed, grad_Q between the push
             # and the receive of the reverse states
             exchange = GlooExchange((N, H, D, M))
-            ops = SplitOracleOps()
-            ops.overlap_grad_queries = case == "split_exchange"
-            out = sp.sequence_parallel_causal_dot_product(q, k, v, ops=ops, exchange=exchange)
+            out = sp.sequence_parallel_causal_dot_product(q, k, v, ops=SplitOracleOps(), exchange=exchange)
             out.backward(sp.shard_sequence(G, rank, world))
             assert exchange.log == ["push", "receive", "push", "receive"] and exchange.pending is None
         else:
@@ -169,9 +166,8 @@ def test_sequence_split_matches_single_rank(world):
     _run(world, "split")
 
 
-@pytest.mark.parametrize("case", ["split_exchange", "split_exchange_joint"])
-def test_split_exchange_path_matches_single_rank(case):
-    _run(3, case)
+def test_split_exchange_path_matches_single_rank():
+    _run(3, "split_exchange")
 
 
 def test_rank_that_never_joins_is_an_error_not_a_hang():
