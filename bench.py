@@ -49,9 +49,11 @@ def parse():
     ap.add_argument("--no-other-mode", action="store_true",
                     help="skip the few eager steps in the other arithmetic mode")
     ap.add_argument("--no-graph", action="store_true", help="time eager calls, not a CUDA graph")
-    ap.add_argument("--exchange", choices=["nccl", "peer"], default="nccl",
-                    help="config 4 on several GPUs: how the per-rank states travel (all_gather, "
-                         "or stores into the peers' buffers by this library's own kernels)")
+    ap.add_argument("--exchange", choices=["auto", "nccl", "peer"], default="auto",
+                    help="the sequence split on several GPUs: how the per-rank states travel (NCCL "
+                         "all_gather, or stores into the peers' buffers by this library's own kernels; "
+                         "auto = peer memory with the step in a CUDA graph, falling back to eager and "
+                         "then to NCCL if that fails; with --config 4 auto means nccl)")
     ap.add_argument("--sp-graph", action="store_true",
                     help="with --exchange peer: capture the sequence-parallel step in a CUDA graph")
     ap.add_argument("--graph-steps", type=int, default=0,
@@ -577,47 +579,70 @@ def sequence_parallel_record(args, dev, dist, rank, world, mode, lib):
     Q, K, V, G = (t.to(dev) for t in workloads.make_inputs(4, trial=rank, scale_L=Lr))
     Q.requires_grad_(True), K.requires_grad_(True), V.requires_grad_(True)
     ops = LocalOps(mode)
-    exchange = PeerExchange((shape["N"], shape["H"], shape["D"], shape["M"])) if args.exchange == "peer" else None
     last = {}
-
-    def step():
-        Q.grad = K.grad = V.grad = None
-        with ftb.mode(mode):
-            out = sequence_parallel_causal_dot_product(Q, K, V, ops=ops, exchange=exchange)
-            out.backward(G)
-        last["out"] = out.detach()   # (not `out`: it would keep the autograd graph of the step alive)
-
     steps = max(args.steps, 10)
-    graph_steps = 0
-    valid, why = True, None
-    try:
-        step()
-        if exchange is not None:
-            exchange.check()
-        if exchange is not None and args.sp_graph:
-            # as many steps per graph as keep it under about 8 ms (longer graphs ran slower per
-            # step), the same number on every rank
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
+
+    def attempt(use_peer, use_graph):
+        """Time the split step one way; returns (exchange, ms per step, steps per graph, error)."""
+        exchange = PeerExchange((shape["N"], shape["H"], shape["D"], shape["M"])) if use_peer else None
+
+        def step():
+            Q.grad = K.grad = V.grad = None
+            with ftb.mode(mode):
+                out = sequence_parallel_causal_dot_product(Q, K, V, ops=ops, exchange=exchange)
+                out.backward(G)
+            last["out"] = out.detach()   # (not `out`: it would keep the autograd graph of the step alive)
+
+        graph_steps, why, tN = 0, None, float("nan")
+        try:
             step()
-            e1.record()
-            torch.cuda.synchronize()
-            most = torch.tensor([max(1, min(10, int(8.0 / max(e0.elapsed_time(e1), 1e-3))))], device=dev)
-            dist.all_reduce(most, op=dist.ReduceOp.MIN)
-            graph_steps = next(d for d in range(int(most.item()), 0, -1) if steps % d == 0)
-        tN = time_steps(step, steps, 3, dev, dist, graph_steps=graph_steps)
-        if exchange is not None:
-            exchange.check()        # a receive that gave up waiting leaves NaN and a status word
-        else:
-            ftb.check_device_status(dev)
-    except Exception as e:          # reported, not hidden: the record is marked invalid
-        valid, why, tN = False, "%s: %s" % (type(e).__name__, e), float("nan")
-    flag = torch.tensor([0 if valid else 1], device=dev)
-    dist.all_reduce(flag)
-    if flag.item():
+            if exchange is not None:
+                exchange.check()
+            if use_graph:
+                # as many steps per graph as keep it under about 8 ms (longer graphs ran slower per
+                # step), the same number on every rank
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                step()
+                e1.record()
+                torch.cuda.synchronize()
+                most = torch.tensor([max(1, min(10, int(8.0 / max(e0.elapsed_time(e1), 1e-3))))], device=dev)
+                dist.all_reduce(most, op=dist.ReduceOp.MIN)
+                graph_steps = next(d for d in range(int(most.item()), 0, -1) if steps % d == 0)
+            tN = time_steps(step, steps, 3, dev, dist, graph_steps=graph_steps)
+            if exchange is not None:
+                exchange.check()        # a receive that gave up waiting leaves NaN and a status word
+            else:
+                ftb.check_device_status(dev)
+        except Exception as e:          # reported, not hidden
+            why = "%s: %s" % (type(e).__name__, e)
+        flag = torch.tensor([0 if why is None else 1], device=dev)
+        dist.all_reduce(flag)
+        if flag.item():
+            why = why or "another rank failed"
+        return exchange, tN, graph_steps, why
+
+    # --exchange auto (the default): the peer-memory exchange with the step captured in a CUDA graph;
+    # should that fail on this machine (a wait that ran out, a refused capture), the same step eager,
+    # then over NCCL's all_gather.  Every attempt is listed in the record.
+    if args.exchange == "peer":
+        plan = [(True, bool(args.sp_graph))]
+    elif args.exchange == "nccl":
+        plan = [(False, False)]
+    else:
+        plan = [(True, True), (True, False), (False, False)]
+    attempts, exchange, tN, graph_steps = [], None, float("nan"), 0
+    for use_peer, use_graph in plan:
+        exchange, tN, graph_steps, why = attempt(use_peer, use_graph)
+        attempts.append({"exchange": "peer" if use_peer else "nccl", "cuda_graph": use_graph,
+                         "ms_per_step": None if why else tN, "error": why})
+        if why is None:
+            break
         if exchange is not None:
             exchange.close()
-        return {"valid": False, "error": why or "another rank failed"}
+        exchange = None
+    if attempts[-1]["error"] is not None:
+        return {"valid": False, "attempts": attempts}
 
     # the whole sequence on rank 0: inputs and the split results of two heads
     heads = [0, 11]
@@ -654,6 +679,7 @@ def sequence_parallel_record(args, dev, dist, rank, world, mode, lib):
                "positions_per_rank": Lr,
                "exchange": ("stores into the peers' buffers by this library's kernels (PeerExchange)"
                             if exchange is not None else "all_gather of the per-rank states (NCCL)"),
+               "attempts": attempts,
                "t1_ms": t1, "t1_how": "the same sequence on rank 0 alone, same process, CUDA graph of 2 steps",
                "efficiency": t1 / (world * tN), "efficiency_formula": "t1_ms / (n_gpus * ms_per_step)",
                "frac_of_hbm_peak_per_gpu": alg / world / (tN * 1e-3) / 1e9 / peak,
