@@ -175,6 +175,7 @@ static int simt_launch_scan(const void *a, const void *b, const void *c, void *o
 struct MmaBatch {
     mma::ScanBatch b;
     int dtype = FTB_F32;
+    int da = 64;                     // width of the a / b rows (selects the instantiation)
     int kind = FTB_KERNEL_MMA_FWD;
     bool after_own_launch = false;   // see mma::launch_t
     bool apply = false;              // out = a S_init only (the APPLY instantiation)
@@ -189,7 +190,7 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
                        int skip_lo, int skip_hi, int canon_is_DaDc, int reverse) {
     const bool state_only = (a == nullptr);
     const bool apply_only = (b == nullptr);   // out = a S_init: only `a` is read
-    const int DCT = dtype == FTB_F32 ? 64 : 128;
+    const int DCT = (dtype == FTB_F32 || Da == 64) ? 64 : 128;
     // fp32 (TF32) operands read MN-major need the 32-byte-atom swizzle; bf16 uses one image
     const bool atom32 = dtype == FTB_F32;
     int64_t blocks = N * H * pl.nseg * (Dc / DCT);
@@ -236,6 +237,7 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
     p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = state_only ? 1 : 0;
     if (batch.b.njobs == 0) {
         batch.dtype = dtype;
+        batch.da = Da;
         batch.kind = state_only ? FTB_KERNEL_MMA_STATE : (reverse ? FTB_KERNEL_MMA_BWD : FTB_KERNEL_MMA_FWD);
     }
     batch.b.first_block[batch.b.njobs + 1] = batch.b.first_block[batch.b.njobs] + (int)blocks;
@@ -258,10 +260,14 @@ static int mma_launch_batch(MmaBatch &batch, cudaStream_t st) {
         batch.b.interleave = 0;
         if (batch.dtype == FTB_F32)
             e = mma::launch_t<float, 64, 64, true>(batch.b, st, false);
+        else if (batch.da == 64)
+            e = mma::launch_t<__nv_bfloat16, 64, 64, true>(batch.b, st, false);
         else
             e = mma::launch_t<__nv_bfloat16, 128, 128, true>(batch.b, st, false);
     } else if (batch.dtype == FTB_F32)
         e = mma::launch_t<float, 64, 64>(batch.b, st, batch.after_own_launch);
+    else if (batch.da == 64)
+        e = mma::launch_t<__nv_bfloat16, 64, 64>(batch.b, st, batch.after_own_launch);
     else
         e = mma::launch_t<__nv_bfloat16, 128, 128>(batch.b, st, batch.after_own_launch);
     if (e != cudaSuccess) return cuda_fail(e);

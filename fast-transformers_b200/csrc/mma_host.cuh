@@ -152,7 +152,7 @@ static Plan plan(int64_t BH, int64_t L, int ntile) {
 // Which (dtype, Da, Dc) combinations have a tensor-core kernel.
 static bool supported(int dtype, int64_t Da, int64_t Dc) {
     if (dtype == FTB_F32) return Da == 64 && Dc % 64 == 0 && Dc >= 64;
-    return Da == 128 && Dc % 128 == 0 && Dc >= 128;
+    return (Da == 128 && Dc % 128 == 0 && Dc >= 128) || (Da == 64 && Dc % 64 == 0 && Dc >= 64);
 }
 
 // Every grid is started with programmatic stream serialisation: its blocks may be placed while

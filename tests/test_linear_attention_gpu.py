@@ -39,7 +39,8 @@ def T(a):
     ("fp32", torch.float32, 64, 64, 300), ("fp32", torch.float32, 37, 90, 129),
     ("fp32", torch.bfloat16, 32, 48, 65), ("fp32", torch.float32, 256, 64, 500),
     ("mma", torch.float32, 64, 64, 1000), ("mma", torch.float32, 64, 64, 128),
-    ("mma", torch.float32, 64, 128, 333), ("mma", torch.bfloat16, 128, 128, 700)])
+    ("mma", torch.float32, 64, 128, 333), ("mma", torch.bfloat16, 128, 128, 700),
+    ("mma", torch.bfloat16, 64, 64, 450)])
 @pytest.mark.parametrize("transposed", [False, True])
 def test_apply_state_against_fp64(mode, dtype, Da, Dc, L, transposed):
     g = torch.Generator().manual_seed(Da + Dc + L)

@@ -85,6 +85,25 @@ def test_bf16_ragged(L):
     check(Q, K, V, G)
 
 
+@pytest.mark.parametrize("L", [77, 640, 2304])
+def test_bf16_head_dimension_64(L):
+    """bf16 tensors with D = M = 64 (the `<bf16, 64, 64>` instantiation: 64-lane state
+    accumulators, one 128-byte block per row)."""
+    g = torch.Generator().manual_seed(64 + L)
+    Q, K, V, G = (torch.randn(2, 3, L, 64, generator=g).to(torch.bfloat16) for _ in range(4))
+    check(Q, K, V, G)
+
+
+def test_bf16_head_dimension_64_many_heads_long():
+    g = torch.Generator().manual_seed(65)
+    H, L = 40, 4096
+    Q, K, V, G = (torch.rand(2, H, L, 64, generator=g).to(torch.bfloat16) for _ in range(4))
+    got = fwd_bwd(Q, K, V, G)
+    want = oracle(*(t[1:, 7:9] for t in (Q, K, V, G)))
+    for name, a, b in zip(NAMES, got, want):
+        assert orc.rel_err(a[1:, 7:9], b) < TOL, name
+
+
 def test_bf16_long_segments():
     """Enough (batch, head) pairs that a segment is a whole sequence of 10 chunks (config 4 runs
     228 chunks per segment): the barrier phases wrap several times.  Checked on four heads."""
