@@ -20,9 +20,12 @@ from torch.nn import Module
 
 from ..attention_registry import (AttentionRegistry, Callable, EventDispatcherInstance, Int,
                                   Optional)
-from ..causal_product import causal_dot_product, causal_normaliser
+from ..causal_product import (causal_dot_backward_cuda, causal_dot_product, causal_dot_product_cuda,
+                              causal_normaliser, causal_normaliser_backward_raw,
+                              causal_normaliser_raw)
 from ..events import EventDispatcher
-from ..feature_maps import elu_feature_map, elu_plus_one_native, is_default_elu_map
+from ..feature_maps import (elu_feature_map, elu_plus_one_backward_raw, elu_plus_one_forward_raw,
+                            elu_plus_one_native, is_default_elu_map)
 from ..settings import get_mode
 
 
@@ -31,6 +34,67 @@ def causal_linear(Q, K, V):
     write the (N, L, H, dim) storage directly through strides."""
     out = causal_dot_product(Q.permute(0, 2, 1, 3), K.permute(0, 2, 1, 3), V.permute(0, 2, 1, 3))
     return out.permute(0, 2, 1, 3)
+
+
+# The one-node form of the layer body (below) is used whenever it applies; tests switch it off to
+# compare it with the chain of separate autograd nodes.
+fused_node_enabled = True
+
+
+class _FusedElu1CausalLinear(torch.autograd.Function):
+    """The whole layer body for the default feature map as ONE autograd node:
+
+        Q = elu(q) + 1;  K = (elu(k) + 1) * key_mask;  den_l = Q_l . sum_{j<=l} K_j
+        y_l = (Q_l . sum_{j<=l} K_j^T V_j) / (den_l + eps)
+
+    (``causal_linear_attention.py:75-104``) on (N, L, H, .) tensors with L = S.  Built from the
+    same native passes as the unfused path; what changes is what is kept for the backward: the
+    raw queries and keys, V, the (N, H, L) denominator and the result -- not the feature tensors
+    Q and K (each as large as the input, otherwise saved twice: by the feature map and by the
+    product) nor the unnormalised product.  The backward recomputes Q and K (one native pass
+    each).  With y = out * Z, Z = 1 / (den + eps):
+
+        grad_out = grad_y * Z            grad_den = -Z * sum_m grad_y * y
+    """
+
+    @staticmethod
+    def forward(ctx, queries, keys, values, key_mask, eps, mode):
+        xq, xk = queries.contiguous(), keys.contiguous()
+        w = None if key_mask is None else key_mask.to(torch.float32).contiguous()
+        Q = elu_plus_one_forward_raw(xq, None)
+        K = elu_plus_one_forward_raw(xk, w)
+        Qp, Kp, Vp = Q.permute(0, 2, 1, 3), K.permute(0, 2, 1, 3), values.permute(0, 2, 1, 3)
+        den = causal_normaliser_raw(Qp, Kp)                          # (N, H, L) view of (N, L, H)
+        N, L, H, M = values.shape
+        y = torch.empty((N, L, H, M), device=values.device, dtype=values.dtype)
+        kept = []
+        causal_dot_product_cuda(Qp, Kp, Vp, y.permute(0, 2, 1, 3), mode, keep_workspace=kept)
+        Z = 1 / (den.permute(0, 2, 1) + eps)                         # (N, L, H)
+        y.mul_(Z[..., None])
+        ctx.save_for_backward(xq, xk, values, w, den, y)
+        ctx.eps, ctx.mode = eps, mode
+        ctx.forward_workspace = kept[0] if kept else None
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        xq, xk, values, w, den, y = ctx.saved_tensors
+        Q = elu_plus_one_forward_raw(xq, None)
+        K = elu_plus_one_forward_raw(xk, w)
+        Qp, Kp, Vp = Q.permute(0, 2, 1, 3), K.permute(0, 2, 1, 3), values.permute(0, 2, 1, 3)
+        Z = 1 / (den.permute(0, 2, 1) + ctx.eps)                     # (N, L, H)
+        gy = grad_y if grad_y.dtype == y.dtype else grad_y.to(y.dtype)
+        grad_den = -(Z * (gy * y).sum(-1))                           # (N, L, H)
+        grad_out = gy * Z[..., None]
+        gQ, gK, gV = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(values)
+        causal_dot_backward_cuda(Qp, Kp, Vp, grad_out.permute(0, 2, 1, 3), gQ.permute(0, 2, 1, 3),
+                                 gK.permute(0, 2, 1, 3), gV.permute(0, 2, 1, 3), ctx.mode,
+                                 forward_workspace=ctx.forward_workspace)
+        nq, nk = causal_normaliser_backward_raw(Qp, Kp, grad_den.permute(0, 2, 1))
+        gQ += nq.permute(0, 2, 1, 3)
+        gK += nk.permute(0, 2, 1, 3)
+        return (elu_plus_one_backward_raw(xq, gQ, None), elu_plus_one_backward_raw(xk, gK, w), gV,
+                None, None, None)
 
 
 class CausalLinearAttention(Module):
@@ -64,8 +128,19 @@ class CausalLinearAttention(Module):
         self.feature_map.new_feature_map(queries.device)
         if not attn_mask.lower_triangular:
             raise RuntimeError("CausalLinearAttention only supports full lower triangular masks")
-        if (is_default_elu_map(self.feature_map) and queries.is_cuda
-                and queries.dtype in (torch.float32, torch.bfloat16)):
+        native_map = (is_default_elu_map(self.feature_map) and queries.is_cuda
+                      and queries.dtype in (torch.float32, torch.bfloat16))
+        mode = get_mode()
+        if (fused_node_enabled and native_map and queries.shape[1] == keys.shape[1] == values.shape[1]
+                and keys.dtype == queries.dtype and values.dtype == queries.dtype
+                and queries.shape[3] in (16, 32, 64, 128)
+                and (mode == "mma" or values.shape[3] % 64 == 0)
+                and tuple(key_lengths.float_matrix.shape) == tuple(keys.shape[:2])):
+            # the common case (L = S, a width the streaming denominator kernels take): the whole
+            # body as one autograd node that keeps the raw inputs instead of the feature tensors
+            return _FusedElu1CausalLinear.apply(queries, keys, values, key_lengths.float_matrix,
+                                                self.eps, mode)
+        if native_map:
             # elu(x) + 1 and the key-length mask in one native pass each (and one each backward)
             Q = elu_plus_one_native(queries)
             K = elu_plus_one_native(keys, key_lengths.float_matrix)

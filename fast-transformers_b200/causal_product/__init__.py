@@ -356,6 +356,53 @@ def _strides_nhl(t):
     return (ctypes.c_int64 * 3)(s[0], s[1], s[2])
 
 
+def causal_normaliser_raw(Q, K):
+    """``den[n,h,l] = Q[n,h,l] . sum_{j<=l} K[n,h,j]`` for (N, H, L, D) views, no autograd; the
+    result has the memory order of ``Q[..., 0]``."""
+    dev = _check_cuda(Q, K)
+    if Q.shape != K.shape or Q.dtype != K.dtype:
+        raise RuntimeError("Q and K must have one shape and dtype")
+    dt = _dtype_id(Q)
+    N, H, L, D = Q.shape
+    q, k = _rowmajor(Q), _rowmajor(K)
+    den = torch.empty_like(Q[..., 0]) if D > 0 else torch.empty((N, H, L), device=dev, dtype=Q.dtype)
+    L_ = _native.lib()
+    with torch.cuda.device(dev):
+        nbytes = L_.ftb_causal_normaliser_workspace_bytes(N, H, L, D, 0)
+        ws, nbytes = _workspace(nbytes, dev)
+        st = L_.ftb_causal_normaliser(
+            _ptr(q), _ptr(k), _ptr(den), N, H, L, D, _native.strides3(q), _native.strides3(k),
+            _strides_nhl(den), dt, _ptr(ws), nbytes,
+            ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    _native.check(st, "ftb_causal_normaliser")
+    return den
+
+
+def causal_normaliser_backward_raw(Q, K, grad_den, need_q=True, need_k=True):
+    """Gradients of ``causal_normaliser_raw``: ``gQ_l = g_l * sum_{j<=l} K_j``,
+    ``gK_j = sum_{l>=j} g_l * Q_l`` (either may be skipped), in the memory order of Q and K."""
+    dev = Q.device
+    dt = _dtype_id(Q)
+    N, H, L, D = Q.shape
+    q, k = _rowmajor(Q), _rowmajor(K)
+    g = grad_den if grad_den.dtype == Q.dtype else grad_den.to(Q.dtype)
+    gq = _like(Q) if need_q else None
+    gk = _like(K) if need_k else None
+    if gq is None and gk is None:
+        return None, None
+    L_ = _native.lib()
+    with torch.cuda.device(dev):
+        nbytes = L_.ftb_causal_normaliser_workspace_bytes(N, H, L, D, 1)
+        ws, nbytes = _workspace(nbytes, dev)
+        st = L_.ftb_causal_normaliser_backward(
+            _ptr(q), _ptr(k), _ptr(g), _ptr(gq), _ptr(gk), N, H, L, D, _native.strides3(q),
+            _native.strides3(k), _strides_nhl(g), _native.strides3(gq if gq is not None else q),
+            _native.strides3(gk if gk is not None else k), dt, _ptr(ws), nbytes,
+            ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    _native.check(st, "ftb_causal_normaliser_backward")
+    return gq, gk
+
+
 class CausalNormaliser(torch.autograd.Function):
     """``den[n,h,l] = Q[n,h,l] . sum_{j<=l} K[n,h,j]`` for (N, H, L, D) views: the denominator of
     the attention layer, which the reference computes as
@@ -365,49 +412,15 @@ class CausalNormaliser(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, Q, K):
-        dev = _check_cuda(Q, K)
-        if Q.shape != K.shape or Q.dtype != K.dtype:
-            raise RuntimeError("Q and K must have one shape and dtype")
-        dt = _dtype_id(Q)
-        N, H, L, D = Q.shape
-        q, k = _rowmajor(Q.data), _rowmajor(K.data)
-        den = torch.empty_like(Q[..., 0]) if D > 0 else torch.empty((N, H, L), device=dev, dtype=Q.dtype)
-        L_ = _native.lib()
-        with torch.cuda.device(dev):
-            nbytes = L_.ftb_causal_normaliser_workspace_bytes(N, H, L, D, 0)
-            ws, nbytes = _workspace(nbytes, dev)
-            st = L_.ftb_causal_normaliser(
-                _ptr(q), _ptr(k), _ptr(den), N, H, L, D, _native.strides3(q), _native.strides3(k),
-                _strides_nhl(den), dt, _ptr(ws), nbytes,
-                ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
-        _native.check(st, "ftb_causal_normaliser")
+        den = causal_normaliser_raw(Q.data, K.data)
         ctx.save_for_backward(Q, K)
         return den
 
     @staticmethod
     def backward(ctx, grad_den):
         Q, K = ctx.saved_tensors
-        dev = Q.device
-        dt = _dtype_id(Q)
-        N, H, L, D = Q.shape
-        q, k = _rowmajor(Q.data), _rowmajor(K.data)
-        g = grad_den if grad_den.dtype == Q.dtype else grad_den.to(Q.dtype)
         need_q, need_k = ctx.needs_input_grad
-        gq = torch.empty_like(Q) if need_q else None
-        gk = torch.empty_like(K) if need_k else None
-        if gq is None and gk is None:
-            return None, None
-        L_ = _native.lib()
-        with torch.cuda.device(dev):
-            nbytes = L_.ftb_causal_normaliser_workspace_bytes(N, H, L, D, 1)
-            ws, nbytes = _workspace(nbytes, dev)
-            st = L_.ftb_causal_normaliser_backward(
-                _ptr(q), _ptr(k), _ptr(g), _ptr(gq), _ptr(gk), N, H, L, D, _native.strides3(q),
-                _native.strides3(k), _strides_nhl(g), _native.strides3(gq if gq is not None else q),
-                _native.strides3(gk if gk is not None else k), dt, _ptr(ws), nbytes,
-                ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
-        _native.check(st, "ftb_causal_normaliser_backward")
-        return gq, gk
+        return causal_normaliser_backward_raw(Q.data, K.data, grad_den, need_q, need_k)
 
 
 causal_normaliser = CausalNormaliser.apply

@@ -61,6 +61,41 @@ elu_feature_map = ActivationFunctionFeatureMap.factory(_elu_plus_one)
 _elu_plus_one.fused_id = "elu+1"
 
 
+def elu_plus_one_forward_raw(xc, w):
+    """``(elu(xc) + 1) * w`` in one native pass, no autograd: ``xc`` contiguous, float32 or
+    bfloat16 on CUDA; ``w`` None or a contiguous float32 tensor with one weight per leading row."""
+    import ctypes
+    from .. import _native
+    y = torch.empty_like(xc)
+    per = xc.numel() // w.numel() if w is not None and w.numel() else 1
+    with torch.cuda.device(xc.device):
+        st = _native.lib().ftb_elu_feature_map(
+            ctypes.c_void_p(xc.data_ptr()), ctypes.c_void_p(y.data_ptr()),
+            ctypes.c_void_p(w.data_ptr()) if w is not None else None, xc.numel(), per,
+            0 if xc.dtype == torch.float32 else 1,
+            ctypes.c_void_p(torch.cuda.current_stream(xc.device).cuda_stream))
+    _native.check(st, "ftb_elu_feature_map")
+    return y
+
+
+def elu_plus_one_backward_raw(xc, g, w):
+    """``g * w * (xc > 0 ? 1 : exp(xc))``: the gradient of ``elu_plus_one_forward_raw``."""
+    import ctypes
+    from .. import _native
+    g = g.contiguous()
+    gx = torch.empty_like(xc)
+    per = xc.numel() // w.numel() if w is not None and w.numel() else 1
+    with torch.cuda.device(xc.device):
+        st = _native.lib().ftb_elu_feature_map_backward(
+            ctypes.c_void_p(xc.data_ptr()), ctypes.c_void_p(g.data_ptr()),
+            ctypes.c_void_p(gx.data_ptr()),
+            ctypes.c_void_p(w.data_ptr()) if w is not None else None, xc.numel(), per,
+            0 if xc.dtype == torch.float32 else 1,
+            ctypes.c_void_p(torch.cuda.current_stream(xc.device).cuda_stream))
+    _native.check(st, "ftb_elu_feature_map_backward")
+    return gx
+
+
 class _EluPlusOneNative(torch.autograd.Function):
     """``(elu(x) + 1) * w`` with ``w`` one weight per leading-dimension row (or none) in one native
     pass, gradient ``g * w * (x > 0 ? 1 : exp(x))`` in another: the default feature map with the
@@ -69,39 +104,16 @@ class _EluPlusOneNative(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, weights):
-        import ctypes
-        from .. import _native
         xc = x.contiguous()
-        y = torch.empty_like(xc)
         w = None if weights is None else weights.to(torch.float32).contiguous()
-        per = xc.numel() // w.numel() if w is not None and w.numel() else 1
-        with torch.cuda.device(xc.device):
-            st = _native.lib().ftb_elu_feature_map(
-                ctypes.c_void_p(xc.data_ptr()), ctypes.c_void_p(y.data_ptr()),
-                ctypes.c_void_p(w.data_ptr()) if w is not None else None, xc.numel(), per,
-                0 if xc.dtype == torch.float32 else 1,
-                ctypes.c_void_p(torch.cuda.current_stream(xc.device).cuda_stream))
-        _native.check(st, "ftb_elu_feature_map")
+        y = elu_plus_one_forward_raw(xc, w)
         ctx.save_for_backward(xc, w)
-        ctx.per = per
         return y
 
     @staticmethod
     def backward(ctx, grad_y):
-        import ctypes
-        from .. import _native
         xc, w = ctx.saved_tensors
-        g = grad_y.contiguous()
-        gx = torch.empty_like(xc)
-        with torch.cuda.device(xc.device):
-            st = _native.lib().ftb_elu_feature_map_backward(
-                ctypes.c_void_p(xc.data_ptr()), ctypes.c_void_p(g.data_ptr()),
-                ctypes.c_void_p(gx.data_ptr()),
-                ctypes.c_void_p(w.data_ptr()) if w is not None else None, xc.numel(), ctx.per,
-                0 if xc.dtype == torch.float32 else 1,
-                ctypes.c_void_p(torch.cuda.current_stream(xc.device).cuda_stream))
-        _native.check(st, "ftb_elu_feature_map_backward")
-        return gx, None
+        return elu_plus_one_backward_raw(xc, grad_y, w), None
 
 
 def elu_plus_one_native(x, row_weights=None):

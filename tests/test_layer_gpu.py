@@ -170,3 +170,43 @@ def test_native_elu_feature_map_with_key_length_mask(dtype):
             want.backward(w.double())
             tol = 1e-6 if dtype == torch.float32 else 1e-2
             assert orc.rel_err(y, want) < tol and orc.rel_err(xd.grad, x64.grad) < tol
+
+
+@pytest.mark.parametrize("mode,dtype", [("fp32", torch.float32), ("mma", torch.float32), ("mma", torch.bfloat16)])
+def test_one_node_layer_equals_the_chain_of_nodes(mode, dtype):
+    """The layer body as one autograd node (raw inputs kept, feature tensors recomputed in the
+    backward) against the chain of separate nodes: same kernels, so the same output bit for bit
+    and gradients that differ only by the order of two additions; and against the fp64 oracle."""
+    import fast_transformers_b200 as ftb
+    from fast_transformers_b200.attention import causal_linear_attention as cla
+    g = torch.Generator().manual_seed(33)
+    N, L, H, E = 2, 700, 3, 64 if dtype == torch.float32 else 128
+    q, k, v, w = (torch.randn(N, L, H, E, generator=g).to(dtype) for _ in range(4))
+    klen = torch.tensor([700, 411])
+    masks = (TriangularCausalMask(L, device="cuda"), LengthMask(torch.full((N,), L, device="cuda")),
+             LengthMask(klen.cuda(), max_len=L))
+    att = CausalLinearAttention(E)
+    results = []
+    for fused in (True, False):
+        cla.fused_node_enabled = fused
+        try:
+            qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+            with ftb.mode(mode):
+                y = att(qd, kd, vd, *masks)
+                (y * w.cuda()).sum().backward()
+            results.append((y.detach(), qd.grad, kd.grad, vd.grad))
+        finally:
+            cla.fused_node_enabled = True
+    tol = 1e-5 if (mode == "fp32" and dtype == torch.float32) else 2e-2
+    assert torch.equal(results[0][0], results[1][0])
+    for a, b in zip(results[0][1:], results[1][1:]):
+        # (bf16: the two forms round their intermediate gradients to bf16 at different points)
+        assert orc.rel_err(a, b) < (1e-6 if dtype == torch.float32 else 5e-2)
+    want = orc.layer_forward(q.float(), k.float(), v.float(), key_lengths=klen)
+    assert orc.rel_err(results[0][0], want) < tol
+    # what the node keeps: the raw inputs, V, the mask, the denominator and the result
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    with ftb.mode(mode):
+        y = att(qd, kd, vd, *masks)
+    assert type(y.grad_fn).__name__ == "_FusedElu1CausalLinearBackward"
+    assert len(y.grad_fn.saved_tensors) == 6
