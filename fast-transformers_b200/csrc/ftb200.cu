@@ -73,6 +73,7 @@ struct LaunchScope {
 struct Plan {
     int64_t seg_len;
     int nseg;
+    int64_t dm = 0;   // D * M: elements of one state block (set by choose_plan)
 };
 
 constexpr int64_t kMinSegRows = 4 * CH;
@@ -129,10 +130,17 @@ static int launch_prefix(float *states, const float *init, float *total, const f
                          int64_t DM, int reverse, cudaStream_t st) {
     int64_t n = BH * DM;
     if (n <= 0) return FTB_OK;
-    int64_t blocks = (n + 255) / 256;
     LaunchScope scope(FTB_KERNEL_STATE_PREFIX, st);
-    state_prefix_kernel<<<(unsigned)blocks, 256, 0, st>>>(states, init, total, total_init, BH, nseg, DM,
-                                                             reverse);
+    auto aligned = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    if (DM % 4 == 0 && aligned(states) && aligned(init) && aligned(total) && aligned(total_init)) {
+        const int64_t n4 = n / 4;
+        state_prefix4_kernel<<<(unsigned)((n4 + 127) / 128), 128, 0, st>>>(
+            (float4 *)states, (const float4 *)init, (float4 *)total, (const float4 *)total_init, BH, nseg,
+            DM / 4, reverse);
+    } else {
+        state_prefix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(states, init, total, total_init, BH,
+                                                                        nseg, DM, reverse);
+    }
     FTB_CUDA(cudaGetLastError());
     return FTB_OK;
 }
@@ -287,12 +295,17 @@ static int mma_launch(const void *a, const void *b, const void *c, void *out, co
     return mma_launch_batch(batch, st);
 }
 
-static Plan choose_plan(int mode, int64_t BH, int64_t L) {
+static Plan choose_plan(int mode, int64_t BH, int64_t L, int64_t DM) {
+    Plan p;
     if (mode == FTB_MODE_MMA) {
         mma::Plan m = mma::plan(BH, L, 1);
-        return Plan{m.seg_len, m.nseg};
+        p.seg_len = m.seg_len;
+        p.nseg = m.nseg;
+    } else {
+        p = simt_plan(BH, L);
     }
-    return simt_plan(BH, L);
+    p.dm = DM;
+    return p;
 }
 
 static int launch_state_sum(int mode, const void *x, const void *y, const int64_t *xs,
@@ -325,8 +338,19 @@ static int launch_scan(int mode, const void *a, const void *b, const void *c, vo
                             ss.states ? ss.states : ss.init, pl.nseg, canon_is_DaDc, reverse, st);
 }
 
+// The tensor-core scan can add up raw segment totals itself (no prefix launch) -- worth it while
+// the sum is short or the segments are long: every state-worker thread of a block walks the
+// blocks in front of its segment row by row, batches of dependent loads that take ~13 us per grid
+// for 8 blocks of 64 KB (config 4's shape) and are invisible for 3 blocks of 16 KB (config 2).
+// Measured on config 4's recipe, one GPU, in-kernel sums against a prefix launch: 0.304 / 0.283 ms
+// at L = 16384, 0.512 / 0.498 ms at 32768, 0.934 / 0.931 ms at 65536, 3.63 / 3.81 ms at 262144
+// (there the prefix form also loses the sweep of (Q, grad_out) riding beside grad_Q).
+constexpr int64_t kSumInKernelMaxBytes = 128 * 1024;
+constexpr int64_t kSumInKernelAlwaysFromChunks = 64;   // segments this long amortise any sum
 static inline bool sums_in_kernel(int mode, Plan pl) {
-    return mode == FTB_MODE_MMA && pl.nseg <= mma::kSumInKernelMaxSegs;
+    if (mode != FTB_MODE_MMA || pl.nseg > mma::kSumInKernelMaxSegs) return false;
+    return (int64_t)(pl.nseg - 1) * pl.dm * 4 <= kSumInKernelMaxBytes ||
+           pl.seg_len / mma::C > kSumInKernelAlwaysFromChunks;
 }
 
 // The state-only launch reads (D+M)/(2D+2M) of what a scan reads, so on the scan's own segments it
@@ -578,7 +602,7 @@ size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, in
     (void)dtype;
     if (N <= 0 || H <= 0 || L <= 0 || D <= 0 || M <= 0) return 0;
     {
-        Plan pl = choose_plan(mode, N * H, L);
+        Plan pl = choose_plan(mode, N * H, L, (int64_t)D * M);
         size_t one = align256((size_t)N * H * pl.nseg * state_sub(mode, pl, N * H) * D * M *
                               sizeof(float));
         if (backward) return 2 * one;
@@ -619,7 +643,7 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
         return FTB_OK;
     }
 
-    Plan pl = choose_plan(mode, N * H, L);
+    Plan pl = choose_plan(mode, N * H, L, (int64_t)D * M);
     float *ws = (float *)workspace;
     if (pl.nseg > 1 || final_state) {
         size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, final_state != nullptr);
@@ -673,7 +697,7 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
     const bool want_q = gq != nullptr, want_kv = gk != nullptr || gv != nullptr;
     if (!want_q && !want_kv) return FTB_ERR_INVALID;
 
-    Plan pl = choose_plan(mode, N * H, L);
+    Plan pl = choose_plan(mode, N * H, L, (int64_t)D * M);
     size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 1, 0);
     if (need && (!workspace || workspace_bytes < need)) return FTB_ERR_WORKSPACE;
     float *wsS = (float *)workspace;
@@ -768,7 +792,7 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
 int ftb_causal_state_parts(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M, int dtype, int mode) {
     if (check_common(N, H, L, D, M, dtype, mode) != FTB_OK) return 0;
     if (N <= 0 || H <= 0 || L <= 0 || D <= 0 || M <= 0) return 0;
-    Plan pl = choose_plan(mode, N * H, L);
+    Plan pl = choose_plan(mode, N * H, L, (int64_t)D * M);
     if (pl.nseg == 1) return 1;
     if (!sums_in_kernel(mode, pl)) return 0;   // the workspace then holds prefixes, not raw totals
     return pl.nseg * state_sub(mode, pl, N * H);
@@ -791,7 +815,7 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
         if (parts == 0) return FTB_ERR_UNSUPPORTED;
         size_t need = align256((size_t)N * H * parts * D * M * sizeof(float));
         if (!workspace || workspace_bytes < need) return FTB_ERR_WORKSPACE;
-        Plan pl = choose_plan(mode, N * H, L);
+        Plan pl = choose_plan(mode, N * H, L, (int64_t)D * M);
         if (pl.nseg > 1) {
             const int sub = state_sub(mode, pl, N * H);
             pl.seg_len /= sub;
@@ -805,7 +829,7 @@ int ftb_causal_state_sum(const void *x, const void *y, float *state, int64_t N, 
         return FTB_OK;
     }
     if (!x || !y) return FTB_ERR_INVALID;
-    Plan pl = choose_plan(mode, N * H, L);
+    Plan pl = choose_plan(mode, N * H, L, (int64_t)D * M);
     if (pl.nseg == 1)
         return launch_state_sum(mode, x, y, xs, ys, N, H, L, (int)D, (int)M, dtype, pl, state, 0, 0, st);
     size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, 1);
@@ -1004,7 +1028,7 @@ int ftb_linear_apply_state(const void *a, const float *state, void *out, int64_t
         return FTB_OK;
     }
     if (mode == FTB_MODE_MMA) {
-        Plan pl = choose_plan(mode, N * H, L);
+        Plan pl = choose_plan(mode, N * H, L, (int64_t)Da * Dc);
         MmaBatch batch;
         int rc = mma_add_job(batch, a, nullptr, nullptr, out, as, nullptr, nullptr, os, N, H, L, (int)Da,
                              (int)Dc, dtype, pl, nullptr, state, 0, 1, nullptr, 0, 0,

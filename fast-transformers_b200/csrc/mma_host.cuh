@@ -118,7 +118,7 @@ static int sm_count() {
 // Segments are whole chunks; one CTA walks one segment.  The count is chosen to minimise
 // waves x (chunks per segment + a fixed per-CTA cost) over the device's SMs, with a small charge
 // per segment for its state traffic.
-constexpr int kSumInKernelMaxSegs = 16;  // up to here the scan kernel adds up raw totals itself
+constexpr int kSumInKernelMaxSegs = 16;  // the scan kernel adds up at most this many raw totals itself
 
 static Plan plan(int64_t BH, int64_t L, int ntile) {
     Plan p;
