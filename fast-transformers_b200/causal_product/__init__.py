@@ -11,7 +11,9 @@ with the reference's in-place signatures (``causal_product_cuda.cu:1471-1483``):
 Differences, all deliberate: there is no CPU entry (``dot["cpu"]`` is None and CPU tensors
 raise -- this package has no CPU path); kernels run on torch's current stream instead of
 the legacy default stream; outputs need not be zero on entry; bf16 tensors are accepted in
-addition to fp32 (bf16 in, bf16 out, fp32 state).
+addition to fp32 (bf16 in, bf16 out, fp32 state).  In ``"mma"`` mode a query / key width that is
+a multiple of 64 above 64 with M = 64 (the Favor map gives D = 256) is served by the library as
+a sum over 64-wide feature blocks (``ftb_causal_dot_product`` adds the blocks up in place).
 """
 import ctypes
 
@@ -89,19 +91,6 @@ def workspace_bytes(N, H, L, D, M, dtype, mode=None, backward=False, want_state=
         N, H, L, D, M, _DTYPES[dtype], _mode_id(mode), int(backward), int(want_state))
 
 
-def _feature_blocks(queries, values, mode, *states):
-    """Tensor-core mode, fp32, a key/query width that is a multiple of 64 above 64 (the Favor map
-    gives D = 256) with M = 64: the score q_i . k_j is a sum over 64-wide feature blocks, so the
-    product is the sum of the products of the blocks, each of which the D = M = 64 kernels take
-    (views into the rows; nothing is copied).  Returns the number of blocks, or 0."""
-    if (mode or get_mode()) != "mma" or queries.dtype != torch.float32:
-        return 0
-    D, M = queries.shape[3], values.shape[3]
-    if M != 64 or D <= 64 or D % 64 or any(s is not None for s in states):
-        return 0
-    return D // 64
-
-
 def causal_dot_product_cuda(queries, keys, values, product, mode=None, initial_state=None,
                             final_state=None, keep_workspace=None, workspace=None,
                             workspace_has_states=False):
@@ -122,16 +111,6 @@ def causal_dot_product_cuda(queries, keys, values, product, mode=None, initial_s
     if keys.shape != (N, H, L, D) or values.shape[:3] != (N, H, L) or \
             product.shape != (N, H, L, M):
         raise RuntimeError("shape mismatch between queries, keys, values and product")
-    nblk = _feature_blocks(queries, values, mode, initial_state, final_state, workspace)
-    if nblk:
-        part = torch.empty_like(product)
-        for b in range(nblk):
-            sl = slice(64 * b, 64 * b + 64)
-            causal_dot_product_cuda(queries[..., sl], keys[..., sl], values,
-                                    product if b == 0 else part, mode)
-            if b:
-                product += part
-        return
     if product.shape[3] > 1 and product.stride(3) != 1:
         raise RuntimeError("product must have a contiguous last dimension")
     q, k, v = _rowmajor(queries), _rowmajor(keys), _rowmajor(values)
@@ -189,22 +168,6 @@ def causal_dot_backward_cuda(queries, keys, values, grad_out, grad_queries, grad
         grad_out = grad_out.to(queries.dtype)
     if grad_out.shape != (N, H, L, M):
         raise RuntimeError("grad_out has the wrong shape")
-    nblk = _feature_blocks(queries, values, mode, initial_state, initial_grad_state,
-                           forward_workspace, workspace)
-    if nblk and len(wanted) < 3:
-        raise RuntimeError("feature-block products compute all three gradients at once")
-    if nblk:
-        # gradients of a sum of block products: grad_Q and grad_K block by block (written
-        # straight into the 64-wide column slices), grad_V summed over the blocks
-        part = torch.empty_like(grad_values)
-        for b in range(nblk):
-            sl = slice(64 * b, 64 * b + 64)
-            causal_dot_backward_cuda(queries[..., sl], keys[..., sl], values, grad_out,
-                                     grad_queries[..., sl], grad_keys[..., sl],
-                                     grad_values if b == 0 else part, mode)
-            if b:
-                grad_values += part
-        return
     q, k, v, g = (_rowmajor(t) for t in (queries, keys, values, grad_out))
     for t in wanted:
         if t.dtype != queries.dtype or (t.shape[3] > 1 and t.stride(3) != 1):
@@ -333,7 +296,7 @@ class CausalDotProduct(torch.autograd.Function):
         # the native function skips a gradient whose buffer is None (a constant V, for example
         # the column of ones behind the layer's normaliser, costs no grad_V scan)
         need = list(ctx.needs_input_grad[:3])
-        if not native or not any(need) or _feature_blocks(Q, V, ctx.mode, None, None, None, None):
+        if not native or not any(need):
             need = [True, True, True]
         # gradients in the memory order of their inputs (see forward)
         grad_Q = _like(Q) if need[0] else None

@@ -195,7 +195,7 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
                        const int64_t *as, const int64_t *bs, const int64_t *cs, const int64_t *os,
                        int64_t N, int64_t H, int64_t L, int Da, int Dc, int dtype, Plan pl,
                        const float *states, const float *init, int sum_mode, int sub, float *state_out,
-                       int skip_lo, int skip_hi, int canon_is_DaDc, int reverse) {
+                       int skip_lo, int skip_hi, int canon_is_DaDc, int reverse, int accumulate = 0) {
     const bool state_only = (a == nullptr);
     const bool apply_only = (b == nullptr);   // out = a S_init: only `a` is read
     const int DCT = (dtype == FTB_F32 || Da == 64) ? 64 : 128;
@@ -243,6 +243,7 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
     p.init = init; p.sum_mode = sum_mode; p.sub = sub < 1 ? 1 : sub;
     p.skip_lo = skip_lo; p.skip_hi = skip_hi;
     p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = state_only ? 1 : 0;
+    p.accumulate = accumulate;
     if (batch.b.njobs == 0) {
         batch.dtype = dtype;
         batch.da = Da;
@@ -286,11 +287,12 @@ static int mma_launch(const void *a, const void *b, const void *c, void *out, co
                       const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H,
                       int64_t L, int Da, int Dc, int dtype, Plan pl, const float *states,
                       const float *init, int sum_mode, int sub, float *state_out, int skip_lo, int skip_hi,
-                      int canon_is_DaDc, int reverse, cudaStream_t st, bool after_own_launch = false) {
+                      int canon_is_DaDc, int reverse, cudaStream_t st, bool after_own_launch = false,
+                      int accumulate = 0) {
     MmaBatch batch;
     batch.after_own_launch = after_own_launch;
     int rc = mma_add_job(batch, a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, states, init,
-                         sum_mode, sub, state_out, skip_lo, skip_hi, canon_is_DaDc, reverse);
+                         sum_mode, sub, state_out, skip_lo, skip_hi, canon_is_DaDc, reverse, accumulate);
     if (rc) return rc;
     return mma_launch_batch(batch, st);
 }
@@ -330,10 +332,11 @@ struct SegStates {
 static int launch_scan(int mode, const void *a, const void *b, const void *c, void *out,
                        const int64_t *as, const int64_t *bs, const int64_t *cs, const int64_t *os,
                        int64_t N, int64_t H, int64_t L, int Da, int Dc, int dtype, Plan pl,
-                       SegStates ss, int canon_is_DaDc, int reverse, cudaStream_t st) {
+                       SegStates ss, int canon_is_DaDc, int reverse, cudaStream_t st, int accumulate = 0) {
     if (mode == FTB_MODE_MMA)
         return mma_launch(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, ss.states, ss.init,
-                          ss.sum_mode, ss.sub, nullptr, 0, 0, canon_is_DaDc, reverse, st, ss.fresh != 0);
+                          ss.sum_mode, ss.sub, nullptr, 0, 0, canon_is_DaDc, reverse, st, ss.fresh != 0,
+                          accumulate);
     return simt_launch_scan(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl,
                             ss.states ? ss.states : ss.init, pl.nseg, canon_is_DaDc, reverse, st);
 }
@@ -415,13 +418,23 @@ static int prepare_states(int mode, const void *x, const void *y, const int64_t 
     return rc;
 }
 
+// Tensor-core mode, fp32, M = 64 and a query / key width that is a multiple of 64 above 64 (the
+// Favor map gives D = 256): the score q_i . k_j is a sum over 64-wide feature blocks, so the
+// product is the sum of the products of the blocks, each of which the <float, 64, 64> kernels take
+// through pointers into the rows; the blocks after the first ADD to out (to grad_V), grad_Q and
+// grad_K are written block by block.  Returns the number of blocks, or 0.
+static int wide_blocks(int mode, int dtype, int64_t D, int64_t M) {
+    if (mode != FTB_MODE_MMA || dtype != FTB_F32 || M != 64 || D <= 64 || D % 64) return 0;
+    return (int)(D / 64);
+}
+
 static int check_common(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M, int dtype, int mode) {
     if (N < 0 || H < 0 || L < 0 || D < 0 || M < 0) return FTB_ERR_INVALID;
     if (dtype != FTB_F32 && dtype != FTB_BF16) return FTB_ERR_INVALID;
     if (mode != FTB_MODE_FP32_SIMT && mode != FTB_MODE_MMA) return FTB_ERR_INVALID;
     if (mode == FTB_MODE_FP32_SIMT && (D > kSimtMaxDim || M > kSimtMaxDim)) return FTB_ERR_UNSUPPORTED;
     if (mode == FTB_MODE_MMA && D > 0 && M > 0 &&
-        !(mma::supported(dtype, D, M) && mma::supported(dtype, M, D)))
+        !(mma::supported(dtype, D, M) && mma::supported(dtype, M, D)) && !wide_blocks(mode, dtype, D, M))
         return FTB_ERR_UNSUPPORTED;
     return FTB_OK;
 }
@@ -599,26 +612,43 @@ int ftb_timing_read(float *ms_by_kind, int *launches_by_kind, int nkinds) {
 
 size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M,
                                   int dtype, int mode, int backward, int want_state) {
-    (void)dtype;
     if (N <= 0 || H <= 0 || L <= 0 || D <= 0 || M <= 0) return 0;
-    {
-        Plan pl = choose_plan(mode, N * H, L, (int64_t)D * M);
-        size_t one = align256((size_t)N * H * pl.nseg * state_sub(mode, pl, N * H) * D * M *
-                              sizeof(float));
-        if (backward) return 2 * one;
-        return (pl.nseg > 1 || want_state) ? one : 0;
+    if (const int nb = wide_blocks(mode, dtype, D, M)) {
+        // forward: one workspace per feature block, side by side (kept for the backward);
+        // backward: the blocks run one after the other and share one
+        const size_t one = ftb_causal_workspace_bytes(N, H, L, 64, M, dtype, mode, backward, want_state);
+        return backward ? one : (size_t)nb * one;
     }
-    return 0;
+    Plan pl = choose_plan(mode, N * H, L, (int64_t)D * M);
+    size_t one = align256((size_t)N * H * pl.nseg * state_sub(mode, pl, N * H) * D * M * sizeof(float));
+    if (backward) return 2 * one;
+    return (pl.nseg > 1 || want_state) ? one : 0;
 }
 
-int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *out, int64_t N,
-                           int64_t H, int64_t L, int64_t D, int64_t M, const int64_t *qs,
-                           const int64_t *ks, const int64_t *vs, const int64_t *os, int dtype,
-                           int mode, const float *initial_state, float *final_state,
-                           int workspace_has_states, void *workspace, size_t workspace_bytes,
-                           void *stream) {
+}  // extern "C"
+
+static int forward_impl(const void *q, const void *k, const void *v, void *out, int64_t N,
+                        int64_t H, int64_t L, int64_t D, int64_t M, const int64_t *qs,
+                        const int64_t *ks, const int64_t *vs, const int64_t *os, int dtype,
+                        int mode, const float *initial_state, float *final_state,
+                        int workspace_has_states, void *workspace, size_t workspace_bytes,
+                        void *stream, int accumulate) {
     int rc = check_common(N, H, L, D, M, dtype, mode);
     if (rc != FTB_OK) return rc;
+    if (const int nb = wide_blocks(mode, dtype, D, M)) {
+        if (initial_state || final_state || workspace_has_states) return FTB_ERR_UNSUPPORTED;
+        if (N == 0 || H == 0 || L == 0) return FTB_OK;
+        if (!q || !k || !v || !out || !qs || !ks || !vs || !os) return FTB_ERR_INVALID;
+        const size_t one = ftb_causal_workspace_bytes(N, H, L, 64, M, dtype, mode, 0, 0);
+        if (one && (!workspace || workspace_bytes < (size_t)nb * one)) return FTB_ERR_WORKSPACE;
+        for (int b = 0; b < nb; ++b) {
+            rc = forward_impl((const float *)q + 64 * b, (const float *)k + 64 * b, v, out, N, H, L, 64, M, qs,
+                              ks, vs, os, dtype, mode, nullptr, nullptr, 0,
+                              workspace ? (char *)workspace + (size_t)b * one : nullptr, one, stream, b > 0);
+            if (rc) return rc;
+        }
+        return FTB_OK;
+    }
     if (!qs || !ks || !vs || !os) return FTB_ERR_INVALID;
     const bool empty = (N == 0 || H == 0 || L == 0 || M == 0);
     if (!empty && (!q || !k || !v || !out) && D > 0) return FTB_ERR_INVALID;
@@ -659,7 +689,28 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
         if (rc) return rc;
     }
     return launch_scan(mode, q, k, v, out, qs, ks, vs, os, N, H, L, (int)D, (int)M, dtype, pl, ss,
-                       /*canon_is_DaDc=*/1, /*reverse=*/0, st);
+                       /*canon_is_DaDc=*/1, /*reverse=*/0, st, accumulate);
+}
+
+extern "C" {
+
+static int backward_impl(const void *q, const void *k, const void *v, const void *g, void *gq,
+                         void *gk, void *gv, int64_t N, int64_t H, int64_t L, int64_t D,
+                         int64_t M, const int64_t *qs, const int64_t *ks, const int64_t *vs,
+                         const int64_t *gs, const int64_t *gqs, const int64_t *gks,
+                         const int64_t *gvs, int dtype, int mode, const float *initial_state,
+                         const float *initial_grad_state, const void *forward_workspace,
+                         int workspace_has_grad_states, void *workspace, size_t workspace_bytes,
+                         void *stream, int accumulate_gv);
+
+int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *out, int64_t N,
+                           int64_t H, int64_t L, int64_t D, int64_t M, const int64_t *qs,
+                           const int64_t *ks, const int64_t *vs, const int64_t *os, int dtype,
+                           int mode, const float *initial_state, float *final_state,
+                           int workspace_has_states, void *workspace, size_t workspace_bytes,
+                           void *stream) {
+    return forward_impl(q, k, v, out, N, H, L, D, M, qs, ks, vs, os, dtype, mode, initial_state, final_state,
+                        workspace_has_states, workspace, workspace_bytes, stream, 0);
 }
 
 int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const void *g, void *gq,
@@ -670,9 +721,42 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
                             const float *initial_grad_state, const void *forward_workspace,
                             int workspace_has_grad_states, void *workspace, size_t workspace_bytes,
                             void *stream) {
+    return backward_impl(q, k, v, g, gq, gk, gv, N, H, L, D, M, qs, ks, vs, gs, gqs, gks, gvs, dtype, mode,
+                         initial_state, initial_grad_state, forward_workspace, workspace_has_grad_states,
+                         workspace, workspace_bytes, stream, 0);
+}
+
+
+
+static int backward_impl(const void *q, const void *k, const void *v, const void *g, void *gq,
+                         void *gk, void *gv, int64_t N, int64_t H, int64_t L, int64_t D,
+                         int64_t M, const int64_t *qs, const int64_t *ks, const int64_t *vs,
+                         const int64_t *gs, const int64_t *gqs, const int64_t *gks,
+                         const int64_t *gvs, int dtype, int mode, const float *initial_state,
+                         const float *initial_grad_state, const void *forward_workspace,
+                         int workspace_has_grad_states, void *workspace, size_t workspace_bytes,
+                         void *stream, int accumulate_gv) {
     int rc = check_common(N, H, L, D, M, dtype, mode);
     if (rc != FTB_OK) return rc;
     if (!qs || !ks || !vs || !gs || !gqs || !gks || !gvs) return FTB_ERR_INVALID;
+    if (const int nb = wide_blocks(mode, dtype, D, M)) {
+        if (initial_state || initial_grad_state || workspace_has_grad_states) return FTB_ERR_UNSUPPORTED;
+        if (N == 0 || H == 0 || L == 0) return FTB_OK;
+        if (!q || !k || !v || !g || (!gq && !gk && !gv)) return FTB_ERR_INVALID;
+        const size_t one = ftb_causal_workspace_bytes(N, H, L, 64, M, dtype, mode, 1, 0);
+        const size_t fone = ftb_causal_workspace_bytes(N, H, L, 64, M, dtype, mode, 0, 0);
+        if (one && (!workspace || workspace_bytes < one)) return FTB_ERR_WORKSPACE;
+        for (int b = 0; b < nb; ++b) {
+            // (the blocks run one after the other on the stream, so they share one backward workspace)
+            rc = backward_impl((const float *)q + 64 * b, (const float *)k + 64 * b, v, g,
+                               gq ? (float *)gq + 64 * b : nullptr, gk ? (float *)gk + 64 * b : nullptr, gv, N, H, L,
+                               64, M, qs, ks, vs, gs, gqs, gks, gvs, dtype, mode, nullptr, nullptr,
+                               forward_workspace ? (const char *)forward_workspace + (size_t)b * fone : nullptr, 0,
+                               workspace, one, stream, b > 0);
+            if (rc) return rc;
+        }
+        return FTB_OK;
+    }
     cudaStream_t st = (cudaStream_t)stream;
     if (N == 0 || H == 0 || L == 0) return FTB_OK;
     const size_t es = dtype == FTB_F32 ? 4 : 2;
@@ -761,7 +845,7 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
         }
         if (gv) {
             rc = mma_add_job(kv, k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl, sR.states,
-                             sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 1, 1);
+                             sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 1, 1, accumulate_gv);
             if (rc) return rc;
         }
         if (want_kv) kv.kind = (&kv == &first && want_q) || (gk && gv) ? FTB_KERNEL_MMA_BWD_MULTI

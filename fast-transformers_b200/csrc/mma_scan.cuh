@@ -66,6 +66,8 @@ struct ScanParams {
     int canon_is_DaDc;    // canonical block is [DA][Dc] (1) or [Dc][DA] (0)
     int reverse;
     int state_only;
+    int accumulate;       // fp32 scans: add the result to what `out` holds instead of replacing it (the
+                          // product over a wide feature dimension as a sum over 64-wide feature blocks)
     int pos_a[3], pos_b[3], pos_c[3];   // TMA coordinate slot of {position, head, batch}
 };
 
@@ -847,6 +849,50 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         ok = mbar_wait(bar_pfull + 8 * (ci & 1), (ci >> 1) & 1, abort_flag);
                         if (!ok) break;
                         rearrange_b_in_place(ci, threadIdx.x - 192);
+                    }
+                    if constexpr (!K::F16 && DCT == 64) {
+                        if (p.accumulate) {
+                            // accumulating scan: fetch what `out` holds for this chunk (the layout of
+                            // the stores below) before waiting for the accumulator, add, store
+                            float2 old[2][16];
+#pragma unroll
+                            for (int hf = 0; hf < 2; ++hf) {
+                                const int64_t ra = row0 + 32 * q + 16 * hf + (lane >> 2);
+                                const T *da = O + ra * p.so.l + n0 + 2 * (lane & 3);
+                                const T *db = da + 8 * p.so.l;
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    old[hf][2 * j] = ra < seg_end ? *reinterpret_cast<const float2 *>(da + 8 * j)
+                                                                  : make_float2(0.f, 0.f);
+                                    old[hf][2 * j + 1] = ra + 8 < seg_end ? *reinterpret_cast<const float2 *>(db + 8 * j)
+                                                                          : make_float2(0.f, 0.f);
+                                }
+                            }
+                            ok = mbar_wait(bar_ofull + 8 * ob, ouse & 1, abort_flag);
+                            if (!ok) break;
+                            tc_fence_after();
+#pragma unroll
+                            for (int hf = 0; hf < 2; ++hf) {
+                                tmem_ld16x256(tlane + ((uint32_t)(16 * hf) << 16) + K::TM_O + ob * DCT, r);
+                                const int64_t ra = row0 + 32 * q + 16 * hf + (lane >> 2);
+                                T *da = O + ra * p.so.l + n0 + 2 * (lane & 3);
+                                T *db = da + 8 * p.so.l;
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    if (ra < seg_end)
+                                        *reinterpret_cast<float2 *>(da + 8 * j) =
+                                            make_float2(old[hf][2 * j].x + __uint_as_float(r[4 * j]),
+                                                        old[hf][2 * j].y + __uint_as_float(r[4 * j + 1]));
+                                    if (ra + 8 < seg_end)
+                                        *reinterpret_cast<float2 *>(db + 8 * j) =
+                                            make_float2(old[hf][2 * j + 1].x + __uint_as_float(r[4 * j + 2]),
+                                                        old[hf][2 * j + 1].y + __uint_as_float(r[4 * j + 3]));
+                                }
+                            }
+                            tc_fence_before();
+                            mbar_arrive(bar_ofree + 8 * ob);
+                            continue;
+                        }
                     }
                     ok = mbar_wait(bar_ofull + 8 * ob, ouse & 1, abort_flag);
                     if (!ok) break;

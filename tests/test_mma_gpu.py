@@ -305,3 +305,34 @@ def test_kept_states_are_read_in_the_layout_they_were_written_in():
     causal_dot_product_cuda(Qd, Kd, Vd, out3, "mma", keep_workspace=kept)
     for name, a, b in zip(NAMES, [out3] + backward_with(kept[0]), want):
         assert orc.rel_err(a, b) < TOL, "(c) " + name
+
+
+def test_wide_feature_products_are_summed_in_place_by_the_library():
+    """D = 192 (three 64-wide feature blocks), M = 64, fp32, tensor-core mode: one native call per
+    direction; the library adds the blocks into `out` / `grad_V` itself (they hold NaN on entry: the
+    first block must replace, the others add), writes grad_Q / grad_K block by block, honours a
+    skipped gradient, and refuses states (which it does not carry per block)."""
+    g = torch.Generator().manual_seed(192)
+    N, H, L, D, M = 1, 3, 900, 192, 64
+    Q, K = (torch.rand(N, H, L, D, generator=g) * 0.5 for _ in range(2))
+    V, G = (torch.randn(N, H, L, M, generator=g) for _ in range(2))
+    Qd, Kd, Vd, Gd = (t.cuda() for t in (Q, K, V, G))
+    out = torch.full((N, H, L, M), float("nan"), device="cuda")
+    kept = []
+    n0 = _native.lib().ftb_launch_count()
+    causal_dot_product_cuda(Qd, Kd, Vd, out, "mma", keep_workspace=kept)
+    grads = [torch.full_like(t, float("nan")) for t in (Qd, Kd, Vd)]
+    causal_dot_backward_cuda(Qd, Kd, Vd, Gd, *grads, "mma", forward_workspace=kept[0])
+    assert _native.lib().ftb_launch_count() - n0 >= 6
+    want = oracle(Q, K, V, G)
+    for name, a, b in zip(NAMES, [out] + grads, want):
+        assert orc.rel_err(a, b) < TOL, name
+    only_v = torch.full_like(Vd, float("nan"))
+    causal_dot_backward_cuda(Qd, Kd, Vd, Gd, None, None, only_v, "mma")
+    assert torch.equal(only_v, grads[2])
+    only_q = torch.full_like(Qd, float("nan"))
+    causal_dot_backward_cuda(Qd, Kd, Vd, Gd, only_q, None, None, "mma")
+    assert orc.rel_err(only_q, want[1]) < TOL
+    with pytest.raises(_native.NativeError) as e:
+        causal_dot_product_cuda(Qd, Kd, Vd, out, "mma", initial_state=torch.zeros(N, H, D, M, device="cuda"))
+    assert e.value.status == _native.ERR_UNSUPPORTED
