@@ -883,12 +883,12 @@ def main():
     # Algorithmic bytes of one launch: every DISTINCT tensor the grid reads or writes, once
     # (elements per token-head; D-wide: Q, K, grad_Q, grad_K; M-wide: V, grad_out, out, grad_V).
     D, M = shape["D"], shape["M"]
-    with_qr = "mma_bwd_qr" in kinds
+    with_qr = "mma_bwd_qr" in kinds or "mma_bwd" in kinds    # grad_Q has a grid of its own
     per_launch_elems = {
         "simt_scan": (2 * D + 2 * M),               # three operand tensors in, one out (averaged
                                                     # over the four role permutations)
         "mma_fwd": (2 * D + 2 * M),                 # Q, K, V -> out
-        "mma_bwd": (2 * D + 2 * M),
+        "mma_bwd": (2 * D + 2 * M),                 # one gradient scan (grad_Q): three tensors in, one out
         "state_sum": (D + M),
         "mma_state": (D + M),                       # K, V (or Q, grad_out) -> totals
         # grad_Q scan (grad_out, V, K -> grad_Q) with the sweep of (Q, grad_out) beside it

@@ -800,7 +800,22 @@ static int backward_impl(const void *q, const void *k, const void *v, const void
     }
     // reverse states R = sum q (x) grad_out over the segments after each segment
     bool r_with_grad_q = false;   // tensor-core mode: the totals are swept in grad_Q's own launch
-    if (!want_kv) {
+    // grad_K and grad_V may walk WHOLE sequences (one segment per pair) although the forward and
+    // grad_Q use several: they then need no reverse totals at all -- no sweep of (q, grad_out) --
+    // and it costs nothing where the two scans of all pairs fill the device once either way
+    // (config 2: 128 blocks of 32 chunks instead of 256 blocks of 16 in 1.7 waves).
+    Plan pl_kv = pl;
+    if (mode == FTB_MODE_MMA && want_kv && gk && gv && pl.nseg > 1 && !workspace_has_grad_states) {
+        const int64_t sms = mma::sm_count(), chunks = (L + mma::C - 1) / mma::C, cps = pl.seg_len / mma::C;
+        const int64_t whole = (2 * N * H + sms - 1) / sms * (chunks + 1);
+        const int64_t split = (2 * N * H * pl.nseg + sms - 1) / sms * (cps + 1);
+        if (whole <= split) {
+            pl_kv.nseg = 1;
+            pl_kv.seg_len = chunks * mma::C;
+        }
+    }
+    const bool kv_whole = pl_kv.nseg != pl.nseg;
+    if (!want_kv || kv_whole) {
         // grad_K and grad_V are the only readers of the reverse states
     } else if (workspace_has_grad_states && mode == FTB_MODE_MMA) {
         // ftb_causal_state_sum(q, grad_out, ..., reverse=1, second half of `workspace`) ran before
@@ -828,7 +843,9 @@ static int backward_impl(const void *q, const void *k, const void *v, const void
             first.kind = FTB_KERNEL_MMA_BWD;
         }
         MmaBatch second;
-        MmaBatch &kv = r_with_grad_q ? second : first;
+        // (grad_K, grad_V on a plan of their own: a grid of their own, so that their blocks stay
+        // side by side; it reads nothing the grad_Q grid writes)
+        MmaBatch &kv = (r_with_grad_q || (kv_whole && want_q)) ? second : first;
         if (r_with_grad_q) {
             Plan fine = pl;
             fine.seg_len = pl.seg_len / sR.sub;
@@ -839,12 +856,12 @@ static int backward_impl(const void *q, const void *k, const void *v, const void
             first.kind = want_q ? FTB_KERNEL_MMA_BWD_QR : FTB_KERNEL_MMA_STATE;
         }
         if (gk) {
-            rc = mma_add_job(kv, v, g, q, gk, vs, gs, qs, gks, N, H, L, (int)M, (int)D, dtype, pl, sR.states,
+            rc = mma_add_job(kv, v, g, q, gk, vs, gs, qs, gks, N, H, L, (int)M, (int)D, dtype, pl_kv, sR.states,
                              sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 0, 1);
             if (rc) return rc;
         }
         if (gv) {
-            rc = mma_add_job(kv, k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl, sR.states,
+            rc = mma_add_job(kv, k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl_kv, sR.states,
                              sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 1, 1, accumulate_gv);
             if (rc) return rc;
         }
@@ -852,8 +869,8 @@ static int backward_impl(const void *q, const void *k, const void *v, const void
                                                                       : FTB_KERNEL_MMA_BWD;
         first.after_own_launch = sS.fresh || sR.fresh;   // a sweep of this call is directly in front
         rc = mma_launch_batch(first, st);
-        if (rc || !r_with_grad_q) return rc;
-        second.after_own_launch = true;   // directly behind {grad_Q scan + sweep}
+        if (rc || &kv == &first) return rc;
+        second.after_own_launch = true;   // directly behind this call's grad_Q grid
         return mma_launch_batch(second, st);
     }
 
