@@ -279,3 +279,69 @@ def test_values_longer_than_queries_use_the_first_rows(mode):
     for name, a, b in zip(("out", "gQ", "gK", "gV"), (out, gq, gk, gv[:, :, :L]), want):
         assert orc.rel_err(a, b) < TOL[mode], name
     assert torch.all(gv[:, :, L:] == 0)
+
+
+@pytest.mark.parametrize("mode", ["fp32", "mma"])
+def test_concurrent_calls_from_two_threads_on_two_streams(mode):
+    """The library is re-entrant: two host threads, each on a stream of its own, run forward and
+    backward at the same time (as the caller's thread and the autograd thread do); the results are
+    bitwise those of the same calls made one after the other."""
+    import threading
+    data = [dev(*workloads.make_inputs(1, trial=t)) for t in range(2)]
+
+    def work(i, box):
+        Q, K, V, G = data[i]
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            for _ in range(5):
+                out = torch.empty_like(V)
+                grads = [torch.empty_like(t) for t in (Q, K, V)]
+                causal_dot_product_cuda(Q, K, V, out, mode)
+                causal_dot_backward_cuda(Q, K, V, G, *grads, mode)
+            stream.synchronize()
+        box[i] = [out] + grads
+
+    serial, parallel = [None, None], [None, None]
+    for i in range(2):
+        work(i, serial)
+    threads = [threading.Thread(target=work, args=(i, parallel)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for a, b in zip(serial, parallel):
+        for x, y in zip(a, b):
+            assert torch.equal(x, y)
+
+
+def test_ordinary_launches_give_the_same_results_as_programmatic_ones():
+    """FTB200_NO_PDL=1 (ordinary launches instead of programmatic stream serialisation) in a child
+    process: same kernels, same arithmetic, bitwise the same results."""
+    import os
+    import subprocess
+    import sys
+    import tempfile
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import sys, torch; sys.path.insert(0, %r)\n"
+        "import fast_transformers_b200 as ftb\n"
+        "from fast_transformers_b200 import workloads\n"
+        "from fast_transformers_b200.causal_product import causal_dot_product\n"
+        "Q, K, V, G = (t.cuda() for t in workloads.make_inputs(1))\n"
+        "Q.requires_grad_(True); K.requires_grad_(True); V.requires_grad_(True)\n"
+        "with ftb.mode('mma'):\n"
+        "    out = causal_dot_product(Q, K, V); out.backward(G)\n"
+        "torch.cuda.synchronize(); ftb.check_device_status()\n"
+        "torch.save([out.detach().cpu(), Q.grad.cpu(), K.grad.cpu(), V.grad.cpu()], sys.argv[1])\n" % root)
+    results = []
+    with tempfile.TemporaryDirectory() as tmp:
+        for flag in ("0", "1"):
+            env = dict(os.environ)
+            env.pop("FTB200_NO_PDL", None)
+            if flag == "1":
+                env["FTB200_NO_PDL"] = "1"
+            path = os.path.join(tmp, "r%s.pt" % flag)
+            subprocess.run([sys.executable, "-c", code, path], check=True, env=env, timeout=300)
+            results.append(torch.load(path))
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
