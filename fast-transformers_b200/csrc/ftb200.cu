@@ -11,6 +11,7 @@
 #include <vector>
 
 #include "apply_state.cuh"
+#include "favor_map.cuh"
 #include "feature_map.cuh"
 #include "mma_host.cuh"
 #include "rank_exchange.cuh"
@@ -1102,6 +1103,48 @@ int ftb_recurrent_linear_step(const void *q, const void *k, const void *v, float
         recurrent_step_kernel<__nv_bfloat16><<<(unsigned)(N * H), kStepThreads, 0, st>>>(
             (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k, (const __nv_bfloat16 *)v, S, z,
             (__nv_bfloat16 *)out, (int)H, (int)D, (int)M, a, b, c, o, feature_map, eps);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Favor's positive random features, one pass on the tensor cores.
+// ---------------------------------------------------------------------------------------------
+int ftb_favor_feature_map(const float *x, const float *omega_t, float *out, int64_t rows, int64_t E,
+                          int64_t half, int64_t x_row_stride, int64_t out_row_stride, float softmax_temp,
+                          void *stream) {
+    if (rows < 0 || E <= 0 || half <= 0 || !(softmax_temp > 0.f)) return FTB_ERR_INVALID;
+    if (E != favor::kE || (half != 64 && half != 128)) return FTB_ERR_UNSUPPORTED;
+    if (rows == 0) return FTB_OK;
+    if (!x || !omega_t || !out) return FTB_ERR_INVALID;
+    if (rows > 0x7fffffffLL - favor::kRows) return FTB_ERR_UNSUPPORTED;
+    if (((uintptr_t)out & 7) || out_row_stride % 2 || out_row_stride < 2 * half) return FTB_ERR_ALIGNMENT;
+    CUtensorMap mx, mw;
+    favor::Params p;
+    const int64_t xs[3] = {0, 0, x_row_stride}, ws[3] = {0, 0, E};
+    int rc = mma::make_map(&mx, p.pos_x, x, 1, 1, rows, E, xs, FTB_F32);
+    if (rc) return rc;
+    rc = mma::make_map(&mw, p.pos_w, omega_t, 1, 1, half, E, ws, FTB_F32);
+    if (rc) return rc;
+    p.out = out;
+    p.rows = rows;
+    p.out_stride = out_row_stride;
+    p.scale = sqrtf(softmax_temp);
+    p.half_temp = 0.5f * softmax_temp;
+    p.log_term = 0.5f * logf((float)(2 * half));
+    const int64_t tiles = (rows + favor::kRows - 1) / favor::kRows;
+    const unsigned grid = (unsigned)std::min<int64_t>(tiles, 2 * (int64_t)mma::sm_count());
+    cudaStream_t st = (cudaStream_t)stream;
+    LaunchScope scope(FTB_KERNEL_FEATURE_MAP, st);
+    if (half == 64) {
+        FTB_CUDA(cudaFuncSetAttribute(favor::favor_map_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)favor::kSmem));
+        favor::favor_map_kernel<64><<<grid, favor::kThreads, favor::kSmem, st>>>(mx, mw, p);
+    } else {
+        FTB_CUDA(cudaFuncSetAttribute(favor::favor_map_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)favor::kSmem));
+        favor::favor_map_kernel<128><<<grid, favor::kThreads, favor::kSmem, st>>>(mx, mw, p);
+    }
     FTB_CUDA(cudaGetLastError());
     return FTB_OK;
 }

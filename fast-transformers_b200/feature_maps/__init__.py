@@ -213,6 +213,13 @@ class Favor(RandomFourierFeatures):
                           "{!r}.".format(x.shape))
 
     def forward(self, x):
+        from ..settings import get_mode
+        if (not self.stabilize and x.is_cuda and x.dtype == torch.float32 and get_mode() == "mma"
+                and x.shape[-1] == 64 and self.n_dims in (128, 256) and x.numel() > 0
+                and self.omega.device == x.device and self.omega.dtype == torch.float32):
+            # tensor-core mode: the whole map as one native pass (TF32 product, like that mode's
+            # attention kernels); the reference's formulation below stays the fp32-mode path
+            return _FavorNative.apply(x, self.omega, float(self.softmax_temp))
         x = x * sqrt(self.softmax_temp)
         norm_x_squared = torch.einsum("...d,...d->...", x, x).unsqueeze(-1)
         u = x.unsqueeze(-2).matmul(self.omega).squeeze(-2)
@@ -221,3 +228,47 @@ class Favor(RandomFourierFeatures):
             self._check_sequence_length(norm_x_squared)
             offset = offset + norm_x_squared.max(1, keepdim=True)[0]
         return torch.cat([torch.exp(u - offset), torch.exp(-u - offset)], dim=-1)
+
+
+def favor_features_raw(x, omega, softmax_temp):
+    """``[exp(u - off), exp(-u - off)]`` with ``u = x temp^(1/2) omega``, ``off = |x|^2 temp / 2 +
+    log(n) / 2`` (``fourier_features.py:218-243``) in one native pass: ``x`` (..., 64) float32 on
+    CUDA, ``omega`` (64, n/2) with n/2 = 64 or 128.  No autograd."""
+    import ctypes
+    from .. import _native
+    xc = x.contiguous()
+    half = omega.shape[1]
+    rows = xc.numel() // xc.shape[-1]
+    omega_t = omega.t().contiguous()
+    out = torch.empty(xc.shape[:-1] + (2 * half,), device=xc.device, dtype=torch.float32)
+    with torch.cuda.device(xc.device):
+        st = _native.lib().ftb_favor_feature_map(
+            ctypes.c_void_p(xc.data_ptr()), ctypes.c_void_p(omega_t.data_ptr()),
+            ctypes.c_void_p(out.data_ptr()), rows, xc.shape[-1], half, xc.shape[-1], 2 * half,
+            float(softmax_temp), ctypes.c_void_p(torch.cuda.current_stream(xc.device).cuda_stream))
+    _native.check(st, "ftb_favor_feature_map")
+    return out
+
+
+class _FavorNative(torch.autograd.Function):
+    """Favor's feature map with a native forward (one pass on the tensor cores).  The backward is
+    the chain rule on the saved input and OUTPUT -- with phi = [p, m]:
+    ``grad_u = g_p * p - g_m * m``, ``grad_off = -sum(g * phi)``,
+    ``grad_x = temp^(1/2) * (grad_u omega^T) + temp * grad_off * x`` -- as torch calls."""
+
+    @staticmethod
+    def forward(ctx, x, omega, softmax_temp):
+        phi = favor_features_raw(x, omega, softmax_temp)
+        ctx.save_for_backward(x, omega, phi)
+        ctx.softmax_temp = softmax_temp
+        return phi
+
+    @staticmethod
+    def backward(ctx, grad_phi):
+        x, omega, phi = ctx.saved_tensors
+        half = omega.shape[1]
+        gp = grad_phi * phi
+        grad_u = gp[..., :half] - gp[..., half:]
+        grad_off = -gp.sum(dim=-1, keepdim=True)
+        grad_x = sqrt(ctx.softmax_temp) * grad_u.matmul(omega.t()) + ctx.softmax_temp * grad_off * x
+        return grad_x, None, None

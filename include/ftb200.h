@@ -237,6 +237,21 @@ int ftb_elu_feature_map_backward(const void *x, const void *grad_y, void *grad_x
                                  int64_t elements_per_mask_entry, int dtype, void *stream);
 
 /*
+ * Favor's positive random features (fast_transformers/feature_maps/fourier_features.py:218-243,
+ * `stabilize` off), one pass on the tensor cores:
+ *     xs = x * softmax_temp^(1/2);  u = xs omega;  off = |xs|^2 / 2 + log(n) / 2
+ *     out = [exp(u - off), exp(-u - off)]                      n = 2 * half features per row
+ * x: `rows` rows of E = 64 fp32 values, x_row_stride elements apart (16-byte aligned rows);
+ * omega_t: the TRANSPOSE of the reference's `omega` buffer, (half, E) fp32 contiguous, half = 64 or
+ * 128; out: rows x n fp32, out_row_stride elements apart.  The product runs with TF32 operands
+ * (the features match fp64 to about 1e-3 relative): it belongs to the FTB_MODE_MMA tier; other
+ * shapes return FTB_ERR_UNSUPPORTED and the caller keeps the reference's torch formulation.
+ */
+int ftb_favor_feature_map(const float *x, const float *omega_t, float *out, int64_t rows, int64_t E,
+                          int64_t half, int64_t x_row_stride, int64_t out_row_stride, float softmax_temp,
+                          void *stream);
+
+/*
  * One step of the same attention as a recurrent model with a fixed-size state.  Replaces the
  * arithmetic of RecurrentLinearAttention.forward
  * (fast_transformers/recurrent/attention/self_attention/linear_attention.py:55-90), which the

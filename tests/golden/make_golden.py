@@ -277,8 +277,31 @@ def linear():
     print("linear.npz", os.path.getsize(os.path.join(HERE, "linear.npz")), "bytes")
 
 
+def favor_wide():
+    """``favor64.npz``: the reference's ``Favor`` on 64-wide inputs with 256 features (the shape of
+    configuration 5 and of the native feature-map kernel): omega, inputs, features, and the
+    gradient of a weighted sum with respect to the inputs."""
+    cp, cla, al, fm, masking, tr = import_reference()
+    from fast_transformers_b200 import workloads
+    torch.set_num_threads(1)
+    g = torch.Generator().manual_seed(909)
+    E, n_dims = 64, 256
+    f = fm.Favor(E, n_dims=n_dims)
+    omega = workloads.favor_omega(E, n_dims, g)
+    f.omega.copy_(omega)
+    x = (torch.randn(1, 19, 2, E, generator=g) * 0.5).requires_grad_(True)
+    w = torch.rand(1, 19, 2, n_dims, generator=g)
+    phi = f(x)
+    (phi * w).sum().backward()
+    np.savez_compressed(os.path.join(HERE, "favor64.npz"), omega=np_(omega), x=np_(x), w=np_(w),
+                        phi=np_(phi), gx=np_(x.grad))
+    print("favor64.npz", os.path.getsize(os.path.join(HERE, "favor64.npz")), "bytes")
+
+
 if __name__ == "__main__":
-    if sys.argv[1:] == ["linear"]:
+    if sys.argv[1:] == ["favor_wide"]:
+        favor_wide()
+    elif sys.argv[1:] == ["linear"]:
         linear()
     elif sys.argv[1:] == ["recurrent"]:
         recurrent()
@@ -289,3 +312,4 @@ if __name__ == "__main__":
         recurrent()
         recurrent_encoder()
         linear()
+        favor_wide()

@@ -210,3 +210,47 @@ def test_one_node_layer_equals_the_chain_of_nodes(mode, dtype):
         y = att(qd, kd, vd, *masks)
     assert type(y.grad_fn).__name__ == "_FusedElu1CausalLinearBackward"
     assert len(y.grad_fn.saved_tensors) == 6
+
+
+@pytest.mark.parametrize("n_dims,shape", [(256, (2, 300, 3, 64)), (128, (1, 129, 2, 64)), (256, (5, 64))])
+def test_native_favor_feature_map(golden, n_dims, shape):
+    """Favor's positive random features as one pass on the tensor cores (tensor-core mode) against
+    the fp64 restatement of the reference's formula, forward and gradient; in the fp32 mode the
+    reference's torch formulation runs and matches to fp32 accuracy."""
+    import fast_transformers_b200 as ftb
+    from fast_transformers_b200 import _native
+    torch.manual_seed(11)
+    fm = Favor(64, n_dims=n_dims, redraw=10 ** 9).cuda()
+    fm.new_feature_map("cuda")
+    x = (torch.randn(*shape) * 0.6)
+    w = torch.rand(*shape[:-1], n_dims)
+    omega = fm.omega.double().cpu()
+    xd = x.double().requires_grad_(True)
+    want = orc.favor_features(xd, omega)
+    (want * w.double()).sum().backward()
+    for mode, tol in (("mma", 2e-2), ("fp32", 1e-5)):
+        xg = x.cuda().requires_grad_(True)
+        n0 = _native.lib().ftb_launch_count()
+        with ftb.mode(mode):
+            phi = fm(xg)
+        launched = _native.lib().ftb_launch_count() - n0
+        assert launched == (1 if mode == "mma" else 0)
+        (phi * w.cuda()).sum().backward()
+        assert phi.shape == want.shape and torch.all(phi > 0)
+        assert orc.rel_err(phi, want) < tol, mode
+        assert orc.rel_err(xg.grad, xd.grad) < tol, mode
+
+
+def test_native_favor_feature_map_against_the_reference(golden):
+    """The reference's own Favor output and input gradient (fixture from the unmodified module,
+    64-wide inputs, 256 features) against the native pass."""
+    import fast_transformers_b200 as ftb
+    g = golden("favor64")
+    fm = Favor(64, n_dims=256, redraw=10 ** 9).cuda()
+    fm.omega.copy_(T(g["omega"]).cuda())
+    x = T(g["x"]).cuda().requires_grad_(True)
+    with ftb.mode("mma"):
+        phi = fm(x)
+    (phi * T(g["w"]).cuda()).sum().backward()
+    assert orc.rel_err(phi, T(g["phi"])) < 2e-2
+    assert orc.rel_err(x.grad, T(g["gx"])) < 2e-2
