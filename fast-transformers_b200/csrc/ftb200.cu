@@ -14,6 +14,7 @@
 #include "favor_map.cuh"
 #include "feature_map.cuh"
 #include "mma_host.cuh"
+#include "wide_scan.cuh"
 #include "rank_exchange.cuh"
 #include "recurrent_step.cuh"
 #include "simt_scan.cuh"
@@ -196,7 +197,8 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
                        const int64_t *as, const int64_t *bs, const int64_t *cs, const int64_t *os,
                        int64_t N, int64_t H, int64_t L, int Da, int Dc, int dtype, Plan pl,
                        const float *states, const float *init, int sum_mode, int sub, float *state_out,
-                       int skip_lo, int skip_hi, int canon_is_DaDc, int reverse, int accumulate = 0) {
+                       int skip_lo, int skip_hi, int canon_is_DaDc, int reverse, int accumulate = 0,
+                       int64_t state_blk = 0) {
     const bool state_only = (a == nullptr);
     const bool apply_only = (b == nullptr);   // out = a S_init: only `a` is read
     const int DCT = (dtype == FTB_F32 || Da == 64) ? 64 : 128;
@@ -245,6 +247,7 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
     p.skip_lo = skip_lo; p.skip_hi = skip_hi;
     p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = state_only ? 1 : 0;
     p.accumulate = accumulate;
+    p.state_blk = state_blk;
     if (batch.b.njobs == 0) {
         batch.dtype = dtype;
         batch.da = Da;
@@ -261,7 +264,8 @@ static int mma_launch_batch(MmaBatch &batch, cudaStream_t st) {
     // equal-sized scans are interleaved block by block (shared tiles meet in L2)
     bool equal = batch.b.njobs > 1;
     for (int j = 0; j < batch.b.njobs && equal; ++j)
-        equal = !batch.b.job[j].p.state_only &&
+        equal = batch.b.job[j].p.state_only == batch.b.job[0].p.state_only &&
+                (!batch.b.job[j].p.state_only || batch.b.job[j].p.state_blk != 0) &&
                 batch.b.first_block[j + 1] - batch.b.first_block[j] == batch.b.first_block[1];
     batch.b.interleave = equal ? 1 : 0;
     LaunchScope scope(batch.kind, st);
@@ -427,6 +431,24 @@ static int prepare_states(int mode, const void *x, const void *y, const int64_t 
 static int wide_blocks(int mode, int dtype, int64_t D, int64_t M) {
     if (mode != FTB_MODE_MMA || dtype != FTB_F32 || M != 64 || D <= 64 || D % 64) return 0;
     return (int)(D / 64);
+}
+
+// Segments of the wide form.  The scans that are wide on the a / b side walk all feature blocks of
+// a segment in one CTA, so the plan counts one CTA per (pair, segment); the scans that are wide on
+// the c side then run nb column tiles per segment side by side.  Whether the scans add up raw
+// totals themselves is decided on what ONE 64-row block needs (a 64 x M block per segment).
+struct WidePlan {
+    Plan pl;      // pl.dm = 64 * M
+    int sub;      // blocks per segment written by the state-only sweeps (state_sub)
+};
+static WidePlan wide_plan(int64_t BH, int64_t L, int nb, int64_t M) {
+    WidePlan w;
+    mma::Plan m = mma::plan(BH, L, 1);
+    w.pl.seg_len = m.seg_len;
+    w.pl.nseg = m.nseg;
+    w.pl.dm = 64 * M;
+    w.sub = state_sub(FTB_MODE_MMA, w.pl, BH * nb);
+    return w;
 }
 
 static int check_common(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M, int dtype, int mode) {
@@ -615,10 +637,11 @@ size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, in
                                   int dtype, int mode, int backward, int want_state) {
     if (N <= 0 || H <= 0 || L <= 0 || D <= 0 || M <= 0) return 0;
     if (const int nb = wide_blocks(mode, dtype, D, M)) {
-        // forward: one workspace per feature block, side by side (kept for the backward);
-        // backward: the blocks run one after the other and share one
-        const size_t one = ftb_causal_workspace_bytes(N, H, L, 64, M, dtype, mode, backward, want_state);
-        return backward ? one : (size_t)nb * one;
+        // per-segment states of the whole [D][M] width (a feature block is 64 of its rows)
+        const WidePlan w = wide_plan(N * H, L, nb, M);
+        const size_t one = align256((size_t)N * H * w.pl.nseg * w.sub * D * M * sizeof(float));
+        if (backward) return 2 * one;
+        return w.pl.nseg > 1 ? one : 0;
     }
     Plan pl = choose_plan(mode, N * H, L, (int64_t)D * M);
     size_t one = align256((size_t)N * H * pl.nseg * state_sub(mode, pl, N * H) * D * M * sizeof(float));
@@ -627,6 +650,173 @@ size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, in
 }
 
 }  // extern "C"
+
+// ---- wide feature dimension (D = 64 nb, M = 64, fp32, tensor cores) ------------------------------
+// The states of a (pair, segment) are kept as one [D][M] block; feature block b is its rows
+// 64 b .. 64 b + 63.  What is wide on the c / out side (grad_Q, grad_K: c = K or Q, D columns) is
+// ONE scan whose nb column tiles sit next to each other in the grid, so that the narrow operands
+// (grad_out and V) come from HBM once and from L2 for the other tiles.  What is wide on the a / b
+// side (out, grad_V) is a sum over the feature blocks: nb scans, the later ones adding to the
+// result.  The state-only sweeps of the nb blocks share one grid, block by block, for the same
+// reason (V, grad_out read once).
+
+// Per-segment totals of sum x_b (x) y for every feature block b into `ws`; on return `ss`
+// describes them for a scan over feature block 0 (block b: states + 64 b M).
+static int wide_states(const float *x, const float *y, const int64_t *xs, const int64_t *ys, int64_t N,
+                       int64_t H, int64_t L, int nb, int M, const WidePlan &w, float *ws, int reverse,
+                       cudaStream_t st, SegStates *ss) {
+    const int64_t DM = (int64_t)64 * nb * M;
+    *ss = SegStates{nullptr, nullptr, 0, 1};
+    if (w.pl.nseg == 1) return FTB_OK;
+    const bool in_kernel = sums_in_kernel(FTB_MODE_MMA, w.pl);
+    Plan fine = w.pl;
+    int skip_lo = 0, skip_hi = 0;
+    if (in_kernel) {
+        fine.seg_len = w.pl.seg_len / w.sub;
+        fine.nseg = w.pl.nseg * w.sub;
+        skip_lo = reverse ? 0 : (w.pl.nseg - 1) * w.sub;
+        skip_hi = skip_lo + w.sub;
+    }
+    MmaBatch sweep;
+    for (int b = 0; b < nb; ++b) {
+        if (sweep.b.njobs == mma::MAX_JOBS) {
+            int rc = mma_launch_batch(sweep, st);
+            if (rc) return rc;
+            sweep = MmaBatch();
+        }
+        int rc = mma_add_job(sweep, nullptr, x + 64 * b, y, nullptr, nullptr, xs, ys, nullptr, N, H, L, 64, M,
+                             FTB_F32, fine, nullptr, nullptr, 0, 1, ws + (int64_t)64 * b * M, skip_lo, skip_hi, 1, 0,
+                             0, DM);
+        if (rc) return rc;
+    }
+    int rc = mma_launch_batch(sweep, st);
+    if (rc) return rc;
+    if (in_kernel) {
+        *ss = SegStates{ws, nullptr, 1, w.sub, 1};
+        return FTB_OK;
+    }
+    rc = launch_prefix(ws, nullptr, nullptr, nullptr, N * H, w.pl.nseg, DM, reverse, st);
+    *ss = SegStates{ws, nullptr, 0, 1, 1};
+    return rc;
+}
+
+static SegStates wide_describe(const WidePlan &w, const float *ws) {
+    if (w.pl.nseg == 1) return SegStates{nullptr, nullptr, 0, 1};
+    if (sums_in_kernel(FTB_MODE_MMA, w.pl)) return SegStates{ws, nullptr, 1, w.sub};
+    return SegStates{ws, nullptr, 0, 1};
+}
+
+// One launch of the scan that sums over `cnt` (1 .. 4) feature blocks inside the tensor cores
+// (wide_scan.cuh): a, b are rows of 64 cnt floats, c and out rows of 64.
+static int wide_launch(const float *a, const float *b, const float *c, float *out, const int64_t *as,
+                       const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H, int64_t L,
+                       int cnt, const WidePlan &w, const float *states, int sum_mode, int sub, int64_t state_blk,
+                       int reverse, int accumulate, bool after_own_launch, int kind, cudaStream_t st) {
+    const int64_t blocks = N * H * w.pl.nseg;
+    if (blocks <= 0) return FTB_OK;
+    if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
+    CUtensorMap ma, mb, mc;
+    wide::Params p;
+    int rc = mma::make_map(&ma, p.pos_a, a, N, H, L, 64 * cnt, as, FTB_F32);
+    if (rc) return rc;
+    if ((rc = mma::make_map(&mb, p.pos_b, b, N, H, L, 64 * cnt, bs, FTB_F32))) return rc;
+    if ((rc = mma::make_map(&mc, p.pos_c, c, N, H, L, 64, cs, FTB_F32, true))) return rc;
+    if (((uintptr_t)out & 15) || (os[0] * 4) % 16 || (os[1] * 4) % 16 || (os[2] * 4) % 16) return FTB_ERR_ALIGNMENT;
+    p.out = out;
+    p.so = S3(os);
+    p.H = (int)H; p.L = L;
+    p.seg_len = w.pl.seg_len; p.nseg = w.pl.nseg; p.nb = cnt;
+    p.states = states; p.sum_mode = sum_mode; p.sub = sub < 1 ? 1 : sub; p.state_blk = state_blk;
+    p.reverse = reverse; p.accumulate = accumulate;
+    static const char *no_pdl = std::getenv("FTB200_NO_PDL");
+    p.wait_first = (no_pdl || after_own_launch) ? 0 : 1;
+    FTB_CUDA(cudaFuncSetAttribute(wide::wide_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)wide::kSmem));
+    LaunchScope scope(kind, st);
+    if (!no_pdl) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)blocks);
+        cfg.blockDim = dim3(mma::NTHREADS);
+        cfg.dynamicSmemBytes = wide::kSmem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, wide::wide_scan_kernel, ma, mb, mc, p) == cudaSuccess) return FTB_OK;
+        (void)cudaGetLastError();
+        p.wait_first = 0;
+    }
+    wide::wide_scan_kernel<<<(unsigned)blocks, mma::NTHREADS, wide::kSmem, st>>>(ma, mb, mc, p);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+
+static int wide_forward(const float *q, const float *k, const float *v, float *out, int64_t N, int64_t H,
+                        int64_t L, int nb, const int64_t *qs, const int64_t *ks, const int64_t *vs,
+                        const int64_t *os, float *ws, cudaStream_t st) {
+    const int M = 64;
+    const int64_t DM = (int64_t)64 * nb * M;
+    const WidePlan w = wide_plan(N * H, L, nb, M);
+    SegStates ss;
+    int rc = wide_states(k, v, ks, vs, N, H, L, nb, M, w, ws, 0, st, &ss);
+    if (rc) return rc;
+    for (int b0 = 0; b0 < nb; b0 += wide::MAXNB) {
+        // up to four feature blocks per launch; a later group adds to what the one before wrote
+        // and waits for that whole grid
+        const int cnt = nb - b0 < wide::MAXNB ? nb - b0 : wide::MAXNB;
+        rc = wide_launch(q + 64 * b0, k + 64 * b0, v, out, qs, ks, vs, os, N, H, L, cnt, w,
+                         ss.states ? ss.states + (int64_t)64 * b0 * M : nullptr, ss.sum_mode, ss.sub, DM, 0, b0 > 0,
+                         b0 == 0 && ss.fresh, FTB_KERNEL_MMA_FWD, st);
+        if (rc) return rc;
+    }
+    return FTB_OK;
+}
+
+static int wide_backward(const float *q, const float *k, const float *v, const float *g, float *gq, float *gk,
+                         float *gv, int64_t N, int64_t H, int64_t L, int nb, const int64_t *qs,
+                         const int64_t *ks, const int64_t *vs, const int64_t *gs, const int64_t *gqs,
+                         const int64_t *gks, const int64_t *gvs, const float *forward_workspace, float *workspace,
+                         size_t workspace_bytes, cudaStream_t st) {
+    const int M = 64, D = 64 * nb;
+    const int64_t DM = (int64_t)D * M;
+    const WidePlan w = wide_plan(N * H, L, nb, M);
+    float *wsS = workspace;
+    float *wsR = (float *)((char *)workspace + workspace_bytes / 2);
+    int rc;
+    SegStates sS{nullptr, nullptr, 0, 1}, sR{nullptr, nullptr, 0, 1};
+    if (gq) {
+        if (forward_workspace && w.pl.nseg > 1) sS = wide_describe(w, forward_workspace);
+        else if ((rc = wide_states(k, v, ks, vs, N, H, L, nb, M, w, wsS, 0, st, &sS))) return rc;
+    }
+    if ((gk || gv) && (rc = wide_states(q, g, qs, gs, N, H, L, nb, M, w, wsR, 1, st, &sR))) return rc;
+    // grad_Q and grad_K: one scan each over all D columns, in one grid with their blocks side by
+    // side (both read grad_out and V as their narrow operands)
+    MmaBatch first;
+    first.after_own_launch = sS.fresh || sR.fresh;
+    if (gq) {
+        rc = mma_add_job(first, g, v, k, gq, gs, vs, ks, gqs, N, H, L, M, D, FTB_F32, w.pl, sS.states, nullptr,
+                         sS.sum_mode, sS.sub, nullptr, 0, 0, 0, 0);
+        if (rc) return rc;
+    }
+    if (gk) {
+        rc = mma_add_job(first, v, g, q, gk, vs, gs, qs, gks, N, H, L, M, D, FTB_F32, w.pl, sR.states, nullptr,
+                         sR.sum_mode, sR.sub, nullptr, 0, 0, 0, 1);
+        if (rc) return rc;
+    }
+    first.kind = (gq && gk) ? FTB_KERNEL_MMA_BWD_MULTI : FTB_KERNEL_MMA_BWD;
+    if ((rc = mma_launch_batch(first, st))) return rc;
+    // grad_V: the sum over the feature blocks, up to four per launch
+    for (int b0 = 0; gv && b0 < nb; b0 += wide::MAXNB) {
+        const int cnt = nb - b0 < wide::MAXNB ? nb - b0 : wide::MAXNB;
+        rc = wide_launch(k + 64 * b0, q + 64 * b0, g, gv, ks, qs, gs, gvs, N, H, L, cnt, w,
+                         sR.states ? sR.states + (int64_t)64 * b0 * M : nullptr, sR.sum_mode, sR.sub, DM, 1, b0 > 0,
+                         b0 == 0 && (gq || gk || sR.fresh), FTB_KERNEL_MMA_BWD, st);
+        if (rc) return rc;
+    }
+    return FTB_OK;
+}
 
 static int forward_impl(const void *q, const void *k, const void *v, void *out, int64_t N,
                         int64_t H, int64_t L, int64_t D, int64_t M, const int64_t *qs,
@@ -640,15 +830,10 @@ static int forward_impl(const void *q, const void *k, const void *v, void *out, 
         if (initial_state || final_state || workspace_has_states) return FTB_ERR_UNSUPPORTED;
         if (N == 0 || H == 0 || L == 0) return FTB_OK;
         if (!q || !k || !v || !out || !qs || !ks || !vs || !os) return FTB_ERR_INVALID;
-        const size_t one = ftb_causal_workspace_bytes(N, H, L, 64, M, dtype, mode, 0, 0);
-        if (one && (!workspace || workspace_bytes < (size_t)nb * one)) return FTB_ERR_WORKSPACE;
-        for (int b = 0; b < nb; ++b) {
-            rc = forward_impl((const float *)q + 64 * b, (const float *)k + 64 * b, v, out, N, H, L, 64, M, qs,
-                              ks, vs, os, dtype, mode, nullptr, nullptr, 0,
-                              workspace ? (char *)workspace + (size_t)b * one : nullptr, one, stream, b > 0);
-            if (rc) return rc;
-        }
-        return FTB_OK;
+        const size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, 0);
+        if (need && (!workspace || workspace_bytes < need)) return FTB_ERR_WORKSPACE;
+        return wide_forward((const float *)q, (const float *)k, (const float *)v, (float *)out, N, H, L, nb,
+                            qs, ks, vs, os, (float *)workspace, (cudaStream_t)stream);
     }
     if (!qs || !ks || !vs || !os) return FTB_ERR_INVALID;
     const bool empty = (N == 0 || H == 0 || L == 0 || M == 0);
@@ -744,19 +929,11 @@ static int backward_impl(const void *q, const void *k, const void *v, const void
         if (initial_state || initial_grad_state || workspace_has_grad_states) return FTB_ERR_UNSUPPORTED;
         if (N == 0 || H == 0 || L == 0) return FTB_OK;
         if (!q || !k || !v || !g || (!gq && !gk && !gv)) return FTB_ERR_INVALID;
-        const size_t one = ftb_causal_workspace_bytes(N, H, L, 64, M, dtype, mode, 1, 0);
-        const size_t fone = ftb_causal_workspace_bytes(N, H, L, 64, M, dtype, mode, 0, 0);
-        if (one && (!workspace || workspace_bytes < one)) return FTB_ERR_WORKSPACE;
-        for (int b = 0; b < nb; ++b) {
-            // (the blocks run one after the other on the stream, so they share one backward workspace)
-            rc = backward_impl((const float *)q + 64 * b, (const float *)k + 64 * b, v, g,
-                               gq ? (float *)gq + 64 * b : nullptr, gk ? (float *)gk + 64 * b : nullptr, gv, N, H, L,
-                               64, M, qs, ks, vs, gs, gqs, gks, gvs, dtype, mode, nullptr, nullptr,
-                               forward_workspace ? (const char *)forward_workspace + (size_t)b * fone : nullptr, 0,
-                               workspace, one, stream, b > 0);
-            if (rc) return rc;
-        }
-        return FTB_OK;
+        const size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 1, 0);
+        if (need && (!workspace || workspace_bytes < need)) return FTB_ERR_WORKSPACE;
+        return wide_backward((const float *)q, (const float *)k, (const float *)v, (const float *)g,
+                             (float *)gq, (float *)gk, (float *)gv, N, H, L, nb, qs, ks, vs, gs, gqs, gks, gvs,
+                             (const float *)forward_workspace, (float *)workspace, need, (cudaStream_t)stream);
     }
     cudaStream_t st = (cudaStream_t)stream;
     if (N == 0 || H == 0 || L == 0) return FTB_OK;

@@ -68,14 +68,16 @@ struct ScanParams {
     int state_only;
     int accumulate;       // fp32 scans: add the result to what `out` holds instead of replacing it (the
                           // product over a wide feature dimension as a sum over 64-wide feature blocks)
+    int64_t state_blk;    // floats between consecutive (bh, seg) blocks of `states` / `state_out`; 0: DA * Dc
+                          // (a 64-row feature block of a wider [D][M] state sits inside a block of D * M)
     int pos_a[3], pos_b[3], pos_c[3];   // TMA coordinate slot of {position, head, batch}
 };
 
-// One launch carries up to three independent jobs (scans or state-only sweeps over the same
+// One launch carries up to five independent jobs (scans or state-only sweeps over the same
 // problem shape); job j owns the blocks [first_block[j], first_block[j+1]).  Independent scans
 // in one grid keep every SM busy while the last CTAs of the previous scan finish, and a short
 // state-only job rides on the SMs a 128-CTA scan leaves idle.
-constexpr int MAX_JOBS = 3;
+constexpr int MAX_JOBS = 5;
 struct ScanJob {
     CUtensorMap ma, mb, mbmn, mc;   // a, b (K-major image), b (MN-major image), c
     ScanParams p;
@@ -454,7 +456,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
         // segments): its totals are zero, and they are read like any other block.  (Done here,
         // before the roles: at the end of the kernel it kept the block's coordinates alive
         // through every loop and cost the bf16 scan a tenth of its speed.)
-        float *dst = p.state_out + ((int64_t)bh * p.nseg + seg) * ((int64_t)DA * p.Dc);
+        float *dst = p.state_out + ((int64_t)bh * p.nseg + seg) * (p.state_blk ? p.state_blk : (int64_t)DA * p.Dc);
         if (batch.wait_first) asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int e = threadIdx.x; e < DA * DCT; e += NTHREADS)
             dst[(int64_t)(e / DCT) * p.Dc + n0 + e % DCT] = 0.f;
@@ -995,7 +997,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                 ok = mbar_wait(bar_sfull, 0, abort_flag);
                 if (ok) {
                     tc_fence_after();
-                    float *dst = p.state_out + ((int64_t)bh * p.nseg + seg) * ((int64_t)DA * p.Dc);
+                    float *dst = p.state_out + ((int64_t)bh * p.nseg + seg) * (p.state_blk ? p.state_blk : (int64_t)DA * p.Dc);
 #pragma unroll
                     for (int cb = 0; cb < DCT / 32; ++cb) {
                         tmem_ld32(tlane + K::TM_S + 32 * cb, r);
@@ -1011,7 +1013,7 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
             } else {
                 // ---- initial state -> TMEM accumulator and shared-memory operand ---------------
                 {
-                    const int64_t blk = (int64_t)DA * p.Dc;
+                    const int64_t blk = p.state_blk ? p.state_blk : (int64_t)DA * p.Dc;
                     // blocks to add up: the per-bh initial state and either this segment's own
                     // block or the raw totals of every segment before (after) it
                     int s_lo = seg, s_hi = seg + 1, per_head = p.nseg;

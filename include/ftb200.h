@@ -29,8 +29,8 @@
  *     up to 512) or FTB_MODE_MMA (tcgen05 tensor cores: TF32 operands for fp32 I/O, bf16
  *     operands for bf16 I/O, fp32 accumulation and fp32 running state).  FTB_MODE_MMA takes
  *     D = M = 64 (fp32, bf16) and D = M = 128 (bf16); and, for fp32 with M = 64, any D that is a
- *     multiple of 64 (256 random features of a 64-wide query, say): the product is then computed
- *     as the sum over 64-wide feature blocks of D = 64 products, added up in place (no initial /
+ *     multiple of 64 (256 random features of a 64-wide query, say): the sum over the 64-wide
+ *     feature blocks is taken inside the tensor cores, up to four blocks per launch (no initial /
  *     final states or prepared workspaces for such shapes: FTB_ERR_UNSUPPORTED).
  *   - `stream` is a cudaStream_t passed as void*; work is enqueued, not synchronised.
  *     FTB_MODE_MMA grids are launched with programmatic stream serialisation: their blocks
