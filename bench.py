@@ -40,9 +40,10 @@ def parse():
     ap.add_argument("--recurrent", action="store_true",
                     help="time the recurrent step (decode) instead of the batch product: "
                          "N256 H16 D=M=128 fp32, one token per sequence and step")
-    ap.add_argument("--mode", default="mma", choices=["fp32", "mma"],
+    ap.add_argument("--mode", default="mma", choices=["fp32", "mma", "tf32x3"],
                     help="arithmetic of the kernels: tensor cores (TF32 operands for fp32 tensors, "
-                         "bf16 for bf16; <= 2e-2 vs fp64) or fp32 CUDA cores (<= 1e-5)")
+                         "bf16 for bf16; <= 2e-2 vs fp64), fp32 CUDA cores (<= 1e-5), or tensor cores "
+                         "with split TF32 operands, three products each (<= 1e-5; fp32, D = M = 64)")
     ap.add_argument("--L", type=int, default=None, help="override the sequence length")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -299,7 +300,7 @@ def run_encoder(args):
             "metric": METRIC, "value": world * tokens / (ms_step * 1e-3) / 1e6, "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": {"fp32": "f32", "mma": "tf32"}[mode],
+            "vs_baseline": None, "dtype": {"fp32": "f32", "mma": "tf32", "tf32x3": "tf32x3"}[mode],
             "data": "synthetic (seeded), random-init weights, dropout 0 (builder default 0.1)",
             "config": {"workload": "config3 causal-linear encoder fwd+bwd %d layers H%d d%d FFN%d "
                                    "X(%d,%d,%d) float32" % (cfg["n_layers"], H, D,
@@ -556,7 +557,7 @@ def product_record(cfg, mode, dev, steps, heads=None, trial=0):
         got = [t[:1, heads].detach() for t in (last["out"], Qd.grad, Kd.grad, Vd.grad)]
         rec["rel_err_vs_fp64"] = oracle_errors(Q, K, V, G, got, heads)
         rec["rel_err_heads"] = list(heads)
-        rec["tolerance_vs_fp64"] = 1e-5 if mode == "fp32" else 2e-2
+        rec["tolerance_vs_fp64"] = 2e-2 if mode == "mma" else 1e-5
     return rec
 
 
@@ -996,24 +997,28 @@ def main():
                       "(fast_transformers_b200.host_io.HostStepPipeline: copies and kernels of "
                       "neighbouring steps overlap)"}
 
-    # the other arithmetic mode on the same inputs, for reference (a few eager steps)
-    other = None
+    # the other arithmetic modes on the same inputs, for reference (a few eager steps each):
+    # `other_mode` is the fp32 CUDA-core tier (the tensor-core tier when that one is benchmarked),
+    # `other_modes` lists all of them
+    other, others = None, []
     if world == 1 and args.config in (1, 2) and Qd.dtype == torch.float32 and not args.no_other_mode:
-        om = "fp32" if mode == "mma" else "mma"
-        mode_saved, mode = mode, om
-        for _ in range(2):
-            step()
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(5):
-            step()
-        e1.record()
-        torch.cuda.synchronize()
+        mode_saved = mode
+        for om in [m for m in ("fp32", "tf32x3", "mma") if m != mode_saved]:
+            mode = om
+            for _ in range(2):
+                step()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(5):
+                step()
+            e1.record()
+            torch.cuda.synchronize()
+            oms = e0.elapsed_time(e1) / 5
+            others.append({"mode": om, "dtype": {"fp32": "f32", "mma": "tf32", "tf32x3": "tf32x3"}[om],
+                           "ms_per_step": oms, "value": tokens / (oms * 1e-3) / 1e6, "unit": UNIT,
+                           "cuda_graph": False, "tolerance_vs_fp64": 2e-2 if om == "mma" else 1e-5})
         mode = mode_saved
-        oms = e0.elapsed_time(e1) / 5
-        other = {"mode": om, "dtype": "f32" if om == "fp32" else "tf32", "ms_per_step": oms,
-                 "value": tokens / (oms * 1e-3) / 1e6, "unit": UNIT, "cuda_graph": False,
-                 "tolerance_vs_fp64": 1e-5 if om == "fp32" else 2e-2}
+        other = others[0]
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -1040,7 +1045,7 @@ def main():
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "strong" if args.config == 4 else "weak",
             "vs_baseline": None,
-            "dtype": {"fp32": "f32", "mma": "tf32" if esize == 4 else "bf16"}[mode],
+            "dtype": {"fp32": "f32", "mma": "tf32" if esize == 4 else "bf16", "tf32x3": "tf32x3"}[mode],
             "data": "synthetic (seeded)",
             "config": {"workload": name, "mode": mode, "io_dtype": str(Qd.dtype).replace("torch.", ""),
                        "global_batch": shape["N"] * (1 if seq_parallel else world), "cuda_graph": graph is not None,
@@ -1053,8 +1058,8 @@ def main():
                        "l2": "inputs+outputs per step (%.0f MB) exceed the 126 MB L2; no flush" %
                              (step_alg_bytes / 1e6)},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-            "gpu_launches": int(launches), "clocks": clocks, "other_mode": other,
-            "tolerance_vs_fp64": 1e-5 if mode == "fp32" else 2e-2,
+            "gpu_launches": int(launches), "clocks": clocks, "other_mode": other, "other_modes": others or None,
+            "tolerance_vs_fp64": 2e-2 if mode == "mma" else 1e-5,
         }
         if configs_rec is not None:
             line["configs"] = configs_rec

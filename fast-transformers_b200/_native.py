@@ -15,8 +15,8 @@ OK, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_WORKSPACE, ERR_CUDA, ERR_TIMEOUT, ERR_IN
     ERR_STATIC_LIMIT = range(8)
 STATIC_SCRATCH_BYTES = 16 * 1024 * 1024
 F32, BF16 = 0, 1
-MODE_FP32_SIMT, MODE_MMA = 0, 1
-MODE_IDS = {"fp32": MODE_FP32_SIMT, "mma": MODE_MMA}
+MODE_FP32_SIMT, MODE_MMA, MODE_MMA_X3 = 0, 1, 2
+MODE_IDS = {"fp32": MODE_FP32_SIMT, "mma": MODE_MMA, "tf32x3": MODE_MMA_X3}
 
 # every symbol include/ftb200.h declares
 EXPORTS = (

@@ -73,8 +73,18 @@ def _workspace(nbytes, device):
     return ws, nbytes
 
 
-def _mode_id(mode):
-    return _native.MODE_IDS[mode or get_mode()]
+def _mode_id(mode, split_ok=False):
+    """Native id of ``mode`` (default: the thread's setting).  ``"tf32x3"`` names an accuracy tier:
+    the split-operand tensor-core kernels where the caller says they apply (``split_ok``: the
+    causal product or its backward, fp32, D = M = 64, no states), the fp32 kernels elsewhere."""
+    name = mode or get_mode()
+    if name == "tf32x3" and not split_ok:
+        name = "fp32"
+    return _native.MODE_IDS[name]
+
+
+def _split_ok(t, D, M, *states):
+    return t.dtype == torch.float32 and D == 64 and M == 64 and all(s is None or s is False for s in states)
 
 
 def _state_ok(s, N, H, D, M, dev, name):
@@ -87,8 +97,9 @@ def _state_ok(s, N, H, D, M, dev, name):
 
 def workspace_bytes(N, H, L, D, M, dtype, mode=None, backward=False, want_state=False):
     """Scratch bytes of one forward (or backward) call; see ``ftb_causal_workspace_bytes``."""
+    split = dtype == torch.float32 and D == 64 and M == 64 and not want_state
     return _native.lib().ftb_causal_workspace_bytes(
-        N, H, L, D, M, _DTYPES[dtype], _mode_id(mode), int(backward), int(want_state))
+        N, H, L, D, M, _DTYPES[dtype], _mode_id(mode, split), int(backward), int(want_state))
 
 
 def causal_dot_product_cuda(queries, keys, values, product, mode=None, initial_state=None,
@@ -120,7 +131,9 @@ def causal_dot_product_cuda(queries, keys, values, product, mode=None, initial_s
                                     not final_state.is_contiguous()):
         raise RuntimeError("final_state must be a contiguous float32 (N, H, D, M) tensor")
     L_ = _native.lib()
-    m = _mode_id(mode)
+    m = _mode_id(mode, _split_ok(queries, D, M, initial_state, final_state, workspace_has_states))
+    if (mode or get_mode()) == "tf32x3" and m != _native.MODE_MMA_X3:
+        keep_workspace = None      # fp32-kernel states: not what a split-operand backward reads
     with torch.cuda.device(dev):
         nbytes = L_.ftb_causal_workspace_bytes(N, H, L, D, M, dt, m, 0, int(final_state is not None))
         if workspace is not None:
@@ -175,7 +188,7 @@ def causal_dot_backward_cuda(queries, keys, values, grad_out, grad_queries, grad
     initial_state = _state_ok(initial_state, N, H, D, M, dev, "initial_state")
     initial_grad_state = _state_ok(initial_grad_state, N, H, D, M, dev, "initial_grad_state")
     L_ = _native.lib()
-    m = _mode_id(mode)
+    m = _mode_id(mode, _split_ok(queries, D, M, initial_state, initial_grad_state, workspace_has_grad_states))
     with torch.cuda.device(dev):
         nbytes = L_.ftb_causal_workspace_bytes(N, H, L, D, M, dt, m, 1, 0)
         if workspace is not None:

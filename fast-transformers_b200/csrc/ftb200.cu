@@ -15,6 +15,7 @@
 #include "feature_map.cuh"
 #include "mma_host.cuh"
 #include "wide_scan.cuh"
+#include "x3_scan.cuh"
 #include "rank_exchange.cuh"
 #include "recurrent_step.cuh"
 #include "simt_scan.cuh"
@@ -433,6 +434,16 @@ static int wide_blocks(int mode, int dtype, int64_t D, int64_t M) {
     return (int)(D / 64);
 }
 
+// Segments of the split-operand tensor-core mode (fp32, D = M = 64): one CTA per (pair, segment).
+static Plan x3_plan(int64_t BH, int64_t L) {
+    Plan p;
+    mma::Plan m = mma::plan(BH, L, 1);
+    p.seg_len = m.seg_len;
+    p.nseg = m.nseg;
+    p.dm = 4096;
+    return p;
+}
+
 // Segments of the wide form.  The scans that are wide on the a / b side walk all feature blocks of
 // a segment in one CTA, so the plan counts one CTA per (pair, segment); the scans that are wide on
 // the c side then run nb column tiles per segment side by side.  Whether the scans add up raw
@@ -451,10 +462,14 @@ static WidePlan wide_plan(int64_t BH, int64_t L, int nb, int64_t M) {
     return w;
 }
 
-static int check_common(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M, int dtype, int mode) {
+static int check_common(int64_t N, int64_t H, int64_t L, int64_t D, int64_t M, int dtype, int mode,
+                        bool x3_ok = false) {
     if (N < 0 || H < 0 || L < 0 || D < 0 || M < 0) return FTB_ERR_INVALID;
     if (dtype != FTB_F32 && dtype != FTB_BF16) return FTB_ERR_INVALID;
-    if (mode != FTB_MODE_FP32_SIMT && mode != FTB_MODE_MMA) return FTB_ERR_INVALID;
+    if (mode != FTB_MODE_FP32_SIMT && mode != FTB_MODE_MMA && mode != FTB_MODE_MMA_X3) return FTB_ERR_INVALID;
+    // split-operand tensor-core mode: the product and its backward only, fp32, D = M = 64
+    if (mode == FTB_MODE_MMA_X3 && D > 0 && M > 0 && (!x3_ok || dtype != FTB_F32 || D != 64 || M != 64))
+        return FTB_ERR_UNSUPPORTED;
     if (mode == FTB_MODE_FP32_SIMT && (D > kSimtMaxDim || M > kSimtMaxDim)) return FTB_ERR_UNSUPPORTED;
     if (mode == FTB_MODE_MMA && D > 0 && M > 0 &&
         !(mma::supported(dtype, D, M) && mma::supported(dtype, M, D)) && !wide_blocks(mode, dtype, D, M))
@@ -643,6 +658,13 @@ size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, in
         if (backward) return 2 * one;
         return w.pl.nseg > 1 ? one : 0;
     }
+    if (mode == FTB_MODE_MMA_X3) {
+        if (check_common(N, H, L, D, M, dtype, mode, true) != FTB_OK) return 0;
+        const Plan pl = x3_plan(N * H, L);
+        const size_t one = align256((size_t)N * H * pl.nseg * 4096 * sizeof(float));
+        if (backward) return 2 * one;
+        return pl.nseg > 1 ? one : 0;
+    }
     Plan pl = choose_plan(mode, N * H, L, (int64_t)D * M);
     size_t one = align256((size_t)N * H * pl.nseg * state_sub(mode, pl, N * H) * D * M * sizeof(float));
     if (backward) return 2 * one;
@@ -650,6 +672,104 @@ size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, in
 }
 
 }  // extern "C"
+
+// ---- split-operand tensor-core mode (x3_scan.cuh): fp32, D = M = 64 ------------------------------
+// One scan (a, b, c) -> out, or, with a == nullptr, the state-only sweep of (b, c) -> state_out.
+static int x3_launch(const float *a, const float *b, const float *c, float *out, const int64_t *as,
+                     const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H, int64_t L,
+                     Plan pl, const float *states, int sum_mode, float *state_out, int skip_lo, int skip_hi,
+                     int canon_is_DaDc, int reverse, int kind, cudaStream_t st) {
+    const int64_t blocks = N * H * pl.nseg;
+    if (blocks <= 0) return FTB_OK;
+    if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
+    CUtensorMap ma, mb, mbmn, mc;
+    x3::Params p;
+    int rc;
+    if ((rc = mma::make_map(&mb, p.pos_b, b, N, H, L, 64, bs, FTB_F32))) return rc;
+    if ((rc = mma::make_map(&mbmn, p.pos_b, b, N, H, L, 64, bs, FTB_F32, true))) return rc;
+    if ((rc = mma::make_map(&mc, p.pos_c, c, N, H, L, 64, cs, FTB_F32, true))) return rc;
+    if (a) {
+        if ((rc = mma::make_map(&ma, p.pos_a, a, N, H, L, 64, as, FTB_F32))) return rc;
+        if (((uintptr_t)out & 15) || (os[0] * 4) % 16 || (os[1] * 4) % 16 || (os[2] * 4) % 16) return FTB_ERR_ALIGNMENT;
+    } else {
+        ma = mb;
+        for (int i = 0; i < 3; ++i) p.pos_a[i] = p.pos_b[i];
+    }
+    p.out = out;
+    p.so = a ? S3(os) : Strides3{0, 0, 0};
+    p.H = (int)H; p.L = L;
+    p.seg_len = pl.seg_len; p.nseg = pl.nseg;
+    p.states = states; p.sum_mode = sum_mode; p.state_out = state_out;
+    p.skip_lo = skip_lo; p.skip_hi = skip_hi;
+    p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = a ? 0 : 1;
+    FTB_CUDA(cudaFuncSetAttribute(x3::x3_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)x3::kSmem));
+    LaunchScope scope(kind, st);
+    x3::x3_scan_kernel<<<(unsigned)blocks, mma::NTHREADS, x3::kSmem, st>>>(ma, mb, mbmn, mc, p);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+
+// Per-segment totals of sum x (x) y into `ws`, as what the scans read.
+static int x3_states(const float *x, const float *y, const int64_t *xs, const int64_t *ys, int64_t N, int64_t H,
+                     int64_t L, Plan pl, float *ws, int reverse, cudaStream_t st, const float **states,
+                     int *sum_mode) {
+    *states = nullptr;
+    *sum_mode = 0;
+    if (pl.nseg == 1) return FTB_OK;
+    const bool in_kernel = pl.nseg <= mma::kSumInKernelMaxSegs;   // the scan adds up raw totals itself
+    int skip_lo = 0, skip_hi = 0;
+    if (in_kernel) {
+        skip_lo = reverse ? 0 : pl.nseg - 1;
+        skip_hi = skip_lo + 1;
+    }
+    int rc = x3_launch(nullptr, x, y, nullptr, nullptr, xs, ys, nullptr, N, H, L, pl, nullptr, 0, ws, skip_lo,
+                       skip_hi, 1, 0, FTB_KERNEL_MMA_STATE, st);
+    if (rc) return rc;
+    *states = ws;
+    *sum_mode = in_kernel ? 1 : 0;
+    if (in_kernel) return FTB_OK;
+    return launch_prefix(ws, nullptr, nullptr, nullptr, N * H, pl.nseg, 4096, reverse, st);
+}
+
+static int x3_forward(const float *q, const float *k, const float *v, float *out, int64_t N, int64_t H, int64_t L,
+                      const int64_t *qs, const int64_t *ks, const int64_t *vs, const int64_t *os, float *ws,
+                      cudaStream_t st) {
+    const Plan pl = x3_plan(N * H, L);
+    const float *states;
+    int sum_mode;
+    int rc = x3_states(k, v, ks, vs, N, H, L, pl, ws, 0, st, &states, &sum_mode);
+    if (rc) return rc;
+    return x3_launch(q, k, v, out, qs, ks, vs, os, N, H, L, pl, states, sum_mode, nullptr, 0, 0, 1, 0,
+                     FTB_KERNEL_MMA_FWD, st);
+}
+
+static int x3_backward(const float *q, const float *k, const float *v, const float *g, float *gq, float *gk,
+                       float *gv, int64_t N, int64_t H, int64_t L, const int64_t *qs, const int64_t *ks,
+                       const int64_t *vs, const int64_t *gs, const int64_t *gqs, const int64_t *gks,
+                       const int64_t *gvs, const float *forward_workspace, float *workspace, size_t workspace_bytes,
+                       cudaStream_t st) {
+    const Plan pl = x3_plan(N * H, L);
+    float *wsS = workspace, *wsR = (float *)((char *)workspace + workspace_bytes / 2);
+    const float *sS = nullptr, *sR = nullptr;
+    int mS = 0, mR = 0, rc;
+    if (gq) {
+        if (forward_workspace && pl.nseg > 1) {
+            sS = forward_workspace;
+            mS = pl.nseg <= mma::kSumInKernelMaxSegs ? 1 : 0;
+        } else if ((rc = x3_states(k, v, ks, vs, N, H, L, pl, wsS, 0, st, &sS, &mS))) return rc;
+    }
+    if ((gk || gv) && (rc = x3_states(q, g, qs, gs, N, H, L, pl, wsR, 1, st, &sR, &mR))) return rc;
+    if (gq && (rc = x3_launch(g, v, k, gq, gs, vs, ks, gqs, N, H, L, pl, sS, mS, nullptr, 0, 0, 0, 0,
+                              FTB_KERNEL_MMA_BWD, st)))
+        return rc;
+    if (gk && (rc = x3_launch(v, g, q, gk, vs, gs, qs, gks, N, H, L, pl, sR, mR, nullptr, 0, 0, 0, 1,
+                              FTB_KERNEL_MMA_BWD, st)))
+        return rc;
+    if (gv && (rc = x3_launch(k, q, g, gv, ks, qs, gs, gvs, N, H, L, pl, sR, mR, nullptr, 0, 0, 1, 1,
+                              FTB_KERNEL_MMA_BWD, st)))
+        return rc;
+    return FTB_OK;
+}
 
 // ---- wide feature dimension (D = 64 nb, M = 64, fp32, tensor cores) ------------------------------
 // The states of a (pair, segment) are kept as one [D][M] block; feature block b is its rows
@@ -824,8 +944,17 @@ static int forward_impl(const void *q, const void *k, const void *v, void *out, 
                         int mode, const float *initial_state, float *final_state,
                         int workspace_has_states, void *workspace, size_t workspace_bytes,
                         void *stream, int accumulate) {
-    int rc = check_common(N, H, L, D, M, dtype, mode);
+    int rc = check_common(N, H, L, D, M, dtype, mode, true);
     if (rc != FTB_OK) return rc;
+    if (mode == FTB_MODE_MMA_X3) {
+        if (initial_state || final_state || workspace_has_states) return FTB_ERR_UNSUPPORTED;
+        if (N == 0 || H == 0 || L == 0 || D == 0 || M == 0) return FTB_OK;
+        if (!q || !k || !v || !out || !qs || !ks || !vs || !os) return FTB_ERR_INVALID;
+        const size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, 0);
+        if (need && (!workspace || workspace_bytes < need)) return FTB_ERR_WORKSPACE;
+        return x3_forward((const float *)q, (const float *)k, (const float *)v, (float *)out, N, H, L, qs, ks, vs,
+                          os, (float *)workspace, (cudaStream_t)stream);
+    }
     if (const int nb = wide_blocks(mode, dtype, D, M)) {
         if (initial_state || final_state || workspace_has_states) return FTB_ERR_UNSUPPORTED;
         if (N == 0 || H == 0 || L == 0) return FTB_OK;
@@ -922,9 +1051,19 @@ static int backward_impl(const void *q, const void *k, const void *v, const void
                          const float *initial_grad_state, const void *forward_workspace,
                          int workspace_has_grad_states, void *workspace, size_t workspace_bytes,
                          void *stream, int accumulate_gv) {
-    int rc = check_common(N, H, L, D, M, dtype, mode);
+    int rc = check_common(N, H, L, D, M, dtype, mode, true);
     if (rc != FTB_OK) return rc;
     if (!qs || !ks || !vs || !gs || !gqs || !gks || !gvs) return FTB_ERR_INVALID;
+    if (mode == FTB_MODE_MMA_X3) {
+        if (initial_state || initial_grad_state || workspace_has_grad_states) return FTB_ERR_UNSUPPORTED;
+        if (N == 0 || H == 0 || L == 0 || D == 0 || M == 0) return FTB_OK;
+        if (!q || !k || !v || !g || (!gq && !gk && !gv)) return FTB_ERR_INVALID;
+        const size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 1, 0);
+        if (need && (!workspace || workspace_bytes < need)) return FTB_ERR_WORKSPACE;
+        return x3_backward((const float *)q, (const float *)k, (const float *)v, (const float *)g, (float *)gq,
+                           (float *)gk, (float *)gv, N, H, L, qs, ks, vs, gs, gqs, gks, gvs,
+                           (const float *)forward_workspace, (float *)workspace, need, (cudaStream_t)stream);
+    }
     if (const int nb = wide_blocks(mode, dtype, D, M)) {
         if (initial_state || initial_grad_state || workspace_has_grad_states) return FTB_ERR_UNSUPPORTED;
         if (N == 0 || H == 0 || L == 0) return FTB_OK;
@@ -1334,6 +1473,7 @@ int ftb_linear_apply_state(const void *a, const float *state, void *out, int64_t
                            int mode, int state_is_transposed, void *stream) {
     if (N < 0 || H < 0 || L < 0 || Da < 0 || Dc < 0) return FTB_ERR_INVALID;
     if (dtype != FTB_F32 && dtype != FTB_BF16) return FTB_ERR_INVALID;
+    if (mode == FTB_MODE_MMA_X3) return FTB_ERR_UNSUPPORTED;
     if (mode != FTB_MODE_FP32_SIMT && mode != FTB_MODE_MMA) return FTB_ERR_INVALID;
     if (!as || !os) return FTB_ERR_INVALID;
     if (mode == FTB_MODE_MMA && Da > 0 && Dc > 0 && !mma::supported(dtype, Da, Dc)) return FTB_ERR_UNSUPPORTED;

@@ -8,12 +8,17 @@ context manager, or the environment variable ``FTB200_MODE`` read at import.
   largest magnitude of the result).  Default.
 * ``"mma"``  -- tcgen05 tensor cores (TF32 operands for fp32 tensors, bf16 operands for bf16
   tensors), fp32 accumulation and fp32 running state; <= 2e-2 on the same metric.
+* ``"tf32x3"`` -- the accuracy of ``"fp32"`` on the tensor cores: every fp32 operand is split into
+  a TF32-exact high part and a low part and every product becomes three (fp32 accumulation);
+  <= 1e-5.  The split-operand kernels take the causal product and its backward for fp32 tensors
+  with 64-wide queries and values; every other shape, and every other operation, runs as in
+  ``"fp32"`` (the same accuracy tier).
 """
 import contextlib
 import os
 import threading
 
-_MODES = ("fp32", "mma")
+_MODES = ("fp32", "mma", "tf32x3")
 _default = os.environ.get("FTB200_MODE", "fp32").lower()
 if _default not in _MODES:
     raise ValueError("FTB200_MODE must be one of %r, got %r" % (_MODES, _default))

@@ -32,6 +32,11 @@
  *     multiple of 64 (256 random features of a 64-wide query, say): the sum over the 64-wide
  *     feature blocks is taken inside the tensor cores, up to four blocks per launch (no initial /
  *     final states or prepared workspaces for such shapes: FTB_ERR_UNSUPPORTED).
+ *     FTB_MODE_MMA_X3 (ftb_causal_dot_product, ftb_causal_dot_backward and the workspace query
+ *     only; fp32, D = M = 64; no states or prepared workspaces) also runs on the tensor cores
+ *     but keeps fp32 accuracy: every operand is split into a TF32-exact high part and a low part
+ *     and every product becomes three (hi hi + lo hi + hi lo, fp32 accumulation).  Its results
+ *     belong to the tier of FTB_MODE_FP32_SIMT (1e-5 against fp64) at several times its speed.
  *   - `stream` is a cudaStream_t passed as void*; work is enqueued, not synchronised.
  *     FTB_MODE_MMA grids are launched with programmatic stream serialisation: their blocks
  *     may be placed on SMs while the kernel in front of them in the stream drains, but the
@@ -72,6 +77,7 @@ extern "C" {
 
 #define FTB_MODE_FP32_SIMT 0
 #define FTB_MODE_MMA 1
+#define FTB_MODE_MMA_X3 2
 
 /* Library / ABI version (major*1000 + minor). */
 int ftb_version(void);

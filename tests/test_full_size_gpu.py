@@ -4,8 +4,8 @@ with the fp64 blocked recurrence (``oracle.chunked_forward`` / ``chunked_backwar
 of the reference's tests regrouped, ``tests/causal_product/test_causal_product_cpu.py:45-47,63-70``).
 
 Tolerances on ``max|x - x64| / max|x64|`` (the maximum taken over the sampled pairs):
-1e-5 for the ``"fp32"`` mode, 2e-2 for the ``"mma"`` mode (TF32 or bf16 operands, fp32
-accumulation and state).  The measured errors go to the file named by ``FTB200_PARITY_LOG`` (one
+1e-5 for the ``"fp32"`` mode and for ``"tf32x3"`` (split TF32 operands, three products each), 2e-2
+for the ``"mma"`` mode (TF32 or bf16 operands, fp32 accumulation and state).  The measured errors go to the file named by ``FTB200_PARITY_LOG`` (one
 JSON object per line) when that variable is set.
 """
 import json
@@ -22,7 +22,7 @@ import fast_transformers_b200 as ftb  # noqa: E402
 from fast_transformers_b200.causal_product import causal_dot_product  # noqa: E402
 
 NAMES = ("out", "gQ", "gK", "gV")
-TOL = {"fp32": 1e-5, "mma": 2e-2}
+TOL = {"fp32": 1e-5, "mma": 2e-2, "tf32x3": 1e-5}
 
 
 @pytest.fixture(scope="module", autouse=True)
@@ -66,7 +66,7 @@ def _check_pairs(config, mode, inputs, got, pairs, chunk=256):
     return errs
 
 
-@pytest.mark.parametrize("mode", ["mma", "fp32"])
+@pytest.mark.parametrize("mode", ["mma", "fp32", "tf32x3"])
 def test_config2_full_size_all_pairs(mode):
     """The benchmarked workload (N8 H8 L4096 D=M=64 fp32): every one of the 64 pairs, output and
     gradients."""
