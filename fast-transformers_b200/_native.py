@@ -30,6 +30,7 @@ EXPORTS = (
     "ftb_exchange_destroy", "ftb_exchange_push", "ftb_exchange_receive",
     "ftb_exchange_wait_limit_ms", "ftb_exchange_push_parts", "ftb_causal_state_parts",
     "ftb_linear_apply_state", "ftb_favor_feature_map", "ftb_recurrent_cross_linear_step",
+    "ftb_causal_dot_product_normalised",
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
                 "mma_bwd_qr", "mma_bwd_multi", "recurrent_step", "normaliser", "feature_map",
@@ -66,6 +67,9 @@ def lib():
     L.ftb_causal_dot_product.restype = _int
     L.ftb_causal_dot_product.argtypes = (
         [_vp] * 4 + [_i64] * 5 + [_i64p] * 4 + [_int, _int, _vp, _vp, _int, _vp, _sz, _vp])
+    L.ftb_causal_dot_product_normalised.restype = _int
+    L.ftb_causal_dot_product_normalised.argtypes = (
+        [_vp] * 5 + [_i64] * 5 + [_i64p] * 5 + [_int, _int, ctypes.c_float, _vp, _sz, _vp])
     L.ftb_causal_dot_backward.restype = _int
     L.ftb_causal_dot_backward.argtypes = (
         [_vp] * 7 + [_i64] * 5 + [_i64p] * 7 + [_int, _int, _vp, _vp, _vp, _int, _vp, _sz, _vp])

@@ -68,9 +68,14 @@ class _FusedElu1CausalLinear(torch.autograd.Function):
         N, L, H, M = values.shape
         y = torch.empty((N, L, H, M), device=values.device, dtype=values.dtype)
         kept = []
-        causal_dot_product_cuda(Qp, Kp, Vp, y.permute(0, 2, 1, 3), mode, keep_workspace=kept)
-        Z = 1 / (den.permute(0, 2, 1) + eps)                         # (N, L, H)
-        y.mul_(Z[..., None])
+        if mode == "mma" and den.dtype == torch.float32 and Q.shape[3] == M == 64:
+            # 1 / (den + eps) is applied by the scan as it stores its rows
+            causal_dot_product_cuda(Qp, Kp, Vp, y.permute(0, 2, 1, 3), mode, keep_workspace=kept,
+                                    row_den=den, eps=eps)
+        else:
+            causal_dot_product_cuda(Qp, Kp, Vp, y.permute(0, 2, 1, 3), mode, keep_workspace=kept)
+            Z = 1 / (den.permute(0, 2, 1) + eps)                     # (N, L, H)
+            y.mul_(Z[..., None])
         ctx.save_for_backward(xq, xk, values, w, den, y)
         ctx.eps, ctx.mode = eps, mode
         ctx.forward_workspace = kept[0] if kept else None

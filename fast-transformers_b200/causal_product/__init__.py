@@ -104,9 +104,12 @@ def workspace_bytes(N, H, L, D, M, dtype, mode=None, backward=False, want_state=
 
 def causal_dot_product_cuda(queries, keys, values, product, mode=None, initial_state=None,
                             final_state=None, keep_workspace=None, workspace=None,
-                            workspace_has_states=False):
+                            workspace_has_states=False, row_den=None, eps=0.0):
     """Fill ``product`` (N, H, L, M) in place -- the reference's native forward signature
-    (``causal_product_cuda.cu:1273-1276``), plus optional fp32 states (N, H, D, M)."""
+    (``causal_product_cuda.cu:1273-1276``), plus optional fp32 states (N, H, D, M).  With
+    ``row_den`` (fp32, (N, H, L), any strides) row i of the result is divided by
+    ``row_den[n, h, i] + eps`` as it is stored (``ftb_causal_dot_product_normalised``; ``"mma"``
+    mode, no states)."""
     dev = _check_cuda(queries, keys, values, product)
     dt = _dtype_id(queries)
     for t in (keys, values, product):
@@ -142,11 +145,23 @@ def causal_dot_product_cuda(queries, keys, values, product, mode=None, initial_s
             ws, nbytes = workspace, workspace.numel() * workspace.element_size()
         else:
             ws, nbytes = _workspace(nbytes, dev)
-        st = L_.ftb_causal_dot_product(
-            _ptr(q), _ptr(k), _ptr(v), _ptr(product), N, H, L, D, M,
-            _native.strides3(q), _native.strides3(k), _native.strides3(v),
-            _native.strides3(product), dt, m, _ptr(initial_state), _ptr(final_state),
-            int(bool(workspace_has_states)), _ptr(ws), nbytes, ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        if row_den is not None:
+            if initial_state is not None or final_state is not None or workspace_has_states:
+                raise RuntimeError("the normalised product takes no states")
+            if row_den.dtype != torch.float32 or row_den.shape != (N, H, L) or row_den.device != dev:
+                raise RuntimeError("row_den must be a float32 (N, H, L) tensor on the inputs' device")
+            dstr = (ctypes.c_int64 * 3)(*row_den.stride())
+            st = L_.ftb_causal_dot_product_normalised(
+                _ptr(q), _ptr(k), _ptr(v), _ptr(row_den), _ptr(product), N, H, L, D, M,
+                _native.strides3(q), _native.strides3(k), _native.strides3(v), dstr,
+                _native.strides3(product), dt, m, float(eps), _ptr(ws), nbytes, stream)
+        else:
+            st = L_.ftb_causal_dot_product(
+                _ptr(q), _ptr(k), _ptr(v), _ptr(product), N, H, L, D, M,
+                _native.strides3(q), _native.strides3(k), _native.strides3(v),
+                _native.strides3(product), dt, m, _ptr(initial_state), _ptr(final_state),
+                int(bool(workspace_has_states)), _ptr(ws), nbytes, stream)
     _native.check(st, "ftb_causal_dot_product")
     if keep_workspace is not None:
         # the per-segment forward states; the backward pass reuses them if handed back

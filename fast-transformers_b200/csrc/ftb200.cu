@@ -181,6 +181,13 @@ static int simt_launch_scan(const void *a, const void *b, const void *c, void *o
     return launch_scan_t<__nv_bfloat16, __nv_bfloat16>(p, blocks, smem, st);
 }
 
+// Per-row normaliser of a scan's output: row i is multiplied by 1 / (den[i] + eps) as it is stored.
+struct RowScale {
+    const float *den;
+    Strides3 s;      // element strides of {batch, head, position}
+    float eps;
+};
+
 // ---- tensor-core launches -------------------------------------------------------------------
 // A launch carries up to mma::MAX_JOBS independent jobs over one problem shape.
 struct MmaBatch {
@@ -198,8 +205,8 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
                        const int64_t *as, const int64_t *bs, const int64_t *cs, const int64_t *os,
                        int64_t N, int64_t H, int64_t L, int Da, int Dc, int dtype, Plan pl,
                        const float *states, const float *init, int sum_mode, int sub, float *state_out,
-                       int skip_lo, int skip_hi, int canon_is_DaDc, int reverse, int accumulate = 0,
-                       int64_t state_blk = 0) {
+                       int skip_lo, int skip_hi, int canon_is_DaDc, int reverse,
+                       const RowScale *scale = nullptr, int64_t state_blk = 0) {
     const bool state_only = (a == nullptr);
     const bool apply_only = (b == nullptr);   // out = a S_init: only `a` is read
     const int DCT = (dtype == FTB_F32 || Da == 64) ? 64 : 128;
@@ -247,7 +254,9 @@ static int mma_add_job(MmaBatch &batch, const void *a, const void *b, const void
     p.init = init; p.sum_mode = sum_mode; p.sub = sub < 1 ? 1 : sub;
     p.skip_lo = skip_lo; p.skip_hi = skip_hi;
     p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = state_only ? 1 : 0;
-    p.accumulate = accumulate;
+    p.row_den = scale ? scale->den : nullptr;
+    p.sden = scale ? scale->s : Strides3{0, 0, 0};
+    p.eps = scale ? scale->eps : 0.f;
     p.state_blk = state_blk;
     if (batch.b.njobs == 0) {
         batch.dtype = dtype;
@@ -294,11 +303,11 @@ static int mma_launch(const void *a, const void *b, const void *c, void *out, co
                       int64_t L, int Da, int Dc, int dtype, Plan pl, const float *states,
                       const float *init, int sum_mode, int sub, float *state_out, int skip_lo, int skip_hi,
                       int canon_is_DaDc, int reverse, cudaStream_t st, bool after_own_launch = false,
-                      int accumulate = 0) {
+                      const RowScale *scale = nullptr) {
     MmaBatch batch;
     batch.after_own_launch = after_own_launch;
     int rc = mma_add_job(batch, a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, states, init,
-                         sum_mode, sub, state_out, skip_lo, skip_hi, canon_is_DaDc, reverse, accumulate);
+                         sum_mode, sub, state_out, skip_lo, skip_hi, canon_is_DaDc, reverse, scale);
     if (rc) return rc;
     return mma_launch_batch(batch, st);
 }
@@ -338,11 +347,12 @@ struct SegStates {
 static int launch_scan(int mode, const void *a, const void *b, const void *c, void *out,
                        const int64_t *as, const int64_t *bs, const int64_t *cs, const int64_t *os,
                        int64_t N, int64_t H, int64_t L, int Da, int Dc, int dtype, Plan pl,
-                       SegStates ss, int canon_is_DaDc, int reverse, cudaStream_t st, int accumulate = 0) {
+                       SegStates ss, int canon_is_DaDc, int reverse, cudaStream_t st,
+                       const RowScale *scale = nullptr) {
     if (mode == FTB_MODE_MMA)
         return mma_launch(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl, ss.states, ss.init,
                           ss.sum_mode, ss.sub, nullptr, 0, 0, canon_is_DaDc, reverse, st, ss.fresh != 0,
-                          accumulate);
+                          scale);
     return simt_launch_scan(a, b, c, out, as, bs, cs, os, N, H, L, Da, Dc, dtype, pl,
                             ss.states ? ss.states : ss.init, pl.nseg, canon_is_DaDc, reverse, st);
 }
@@ -806,7 +816,7 @@ static int wide_states(const float *x, const float *y, const int64_t *xs, const 
         }
         int rc = mma_add_job(sweep, nullptr, x + 64 * b, y, nullptr, nullptr, xs, ys, nullptr, N, H, L, 64, M,
                              FTB_F32, fine, nullptr, nullptr, 0, 1, ws + (int64_t)64 * b * M, skip_lo, skip_hi, 1, 0,
-                             0, DM);
+                             nullptr, DM);
         if (rc) return rc;
     }
     int rc = mma_launch_batch(sweep, st);
@@ -943,8 +953,10 @@ static int forward_impl(const void *q, const void *k, const void *v, void *out, 
                         const int64_t *ks, const int64_t *vs, const int64_t *os, int dtype,
                         int mode, const float *initial_state, float *final_state,
                         int workspace_has_states, void *workspace, size_t workspace_bytes,
-                        void *stream, int accumulate) {
+                        void *stream, const RowScale *scale) {
     int rc = check_common(N, H, L, D, M, dtype, mode, true);
+    // the normaliser rides in the tensor-core scans' epilogue only
+    if (scale && (mode != FTB_MODE_MMA || wide_blocks(mode, dtype, D, M))) return FTB_ERR_UNSUPPORTED;
     if (rc != FTB_OK) return rc;
     if (mode == FTB_MODE_MMA_X3) {
         if (initial_state || final_state || workspace_has_states) return FTB_ERR_UNSUPPORTED;
@@ -1004,7 +1016,7 @@ static int forward_impl(const void *q, const void *k, const void *v, void *out, 
         if (rc) return rc;
     }
     return launch_scan(mode, q, k, v, out, qs, ks, vs, os, N, H, L, (int)D, (int)M, dtype, pl, ss,
-                       /*canon_is_DaDc=*/1, /*reverse=*/0, st, accumulate);
+                       /*canon_is_DaDc=*/1, /*reverse=*/0, st, scale);
 }
 
 extern "C" {
@@ -1016,7 +1028,7 @@ static int backward_impl(const void *q, const void *k, const void *v, const void
                          const int64_t *gvs, int dtype, int mode, const float *initial_state,
                          const float *initial_grad_state, const void *forward_workspace,
                          int workspace_has_grad_states, void *workspace, size_t workspace_bytes,
-                         void *stream, int accumulate_gv);
+                         void *stream);
 
 int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *out, int64_t N,
                            int64_t H, int64_t L, int64_t D, int64_t M, const int64_t *qs,
@@ -1025,7 +1037,18 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
                            int workspace_has_states, void *workspace, size_t workspace_bytes,
                            void *stream) {
     return forward_impl(q, k, v, out, N, H, L, D, M, qs, ks, vs, os, dtype, mode, initial_state, final_state,
-                        workspace_has_states, workspace, workspace_bytes, stream, 0);
+                        workspace_has_states, workspace, workspace_bytes, stream, nullptr);
+}
+
+int ftb_causal_dot_product_normalised(const void *q, const void *k, const void *v, const float *den, void *out,
+                                      int64_t N, int64_t H, int64_t L, int64_t D, int64_t M, const int64_t *qs,
+                                      const int64_t *ks, const int64_t *vs, const int64_t *dens,
+                                      const int64_t *os, int dtype, int mode, float eps, void *workspace,
+                                      size_t workspace_bytes, void *stream) {
+    if (!den || !dens) return FTB_ERR_INVALID;
+    RowScale sc{den, S3(dens), eps};
+    return forward_impl(q, k, v, out, N, H, L, D, M, qs, ks, vs, os, dtype, mode, nullptr, nullptr, 0, workspace,
+                        workspace_bytes, stream, &sc);
 }
 
 int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const void *g, void *gq,
@@ -1038,7 +1061,7 @@ int ftb_causal_dot_backward(const void *q, const void *k, const void *v, const v
                             void *stream) {
     return backward_impl(q, k, v, g, gq, gk, gv, N, H, L, D, M, qs, ks, vs, gs, gqs, gks, gvs, dtype, mode,
                          initial_state, initial_grad_state, forward_workspace, workspace_has_grad_states,
-                         workspace, workspace_bytes, stream, 0);
+                         workspace, workspace_bytes, stream);
 }
 
 
@@ -1050,7 +1073,7 @@ static int backward_impl(const void *q, const void *k, const void *v, const void
                          const int64_t *gvs, int dtype, int mode, const float *initial_state,
                          const float *initial_grad_state, const void *forward_workspace,
                          int workspace_has_grad_states, void *workspace, size_t workspace_bytes,
-                         void *stream, int accumulate_gv) {
+                         void *stream) {
     int rc = check_common(N, H, L, D, M, dtype, mode, true);
     if (rc != FTB_OK) return rc;
     if (!qs || !ks || !vs || !gs || !gqs || !gks || !gvs) return FTB_ERR_INVALID;
@@ -1179,7 +1202,7 @@ static int backward_impl(const void *q, const void *k, const void *v, const void
         }
         if (gv) {
             rc = mma_add_job(kv, k, q, g, gv, ks, qs, gs, gvs, N, H, L, (int)D, (int)M, dtype, pl_kv, sR.states,
-                             sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 1, 1, accumulate_gv);
+                             sR.init, sR.sum_mode, sR.sub, nullptr, 0, 0, 1, 1);
             if (rc) return rc;
         }
         if (want_kv) kv.kind = (&kv == &first && want_q) || (gk && gv) ? FTB_KERNEL_MMA_BWD_MULTI

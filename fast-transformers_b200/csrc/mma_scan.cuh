@@ -66,8 +66,9 @@ struct ScanParams {
     int canon_is_DaDc;    // canonical block is [DA][Dc] (1) or [Dc][DA] (0)
     int reverse;
     int state_only;
-    int accumulate;       // fp32 scans: add the result to what `out` holds instead of replacing it (the
-                          // product over a wide feature dimension as a sum over 64-wide feature blocks)
+    const float *row_den; // scans: out row i is multiplied by 1 / (row_den[i] + eps) on its way to memory
+    Strides3 sden;        // (the layer's normaliser, one fp32 value per (batch, head, position)); or nullptr
+    float eps;
     int64_t state_blk;    // floats between consecutive (bh, seg) blocks of `states` / `state_out`; 0: DA * Dc
                           // (a 64-row feature block of a wider [D][M] state sits inside a block of D * M)
     int pos_a[3], pos_b[3], pos_c[3];   // TMA coordinate slot of {position, head, batch}
@@ -841,6 +842,11 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                 uint32_t r[32];
                 bool ok = true;
                 T *O = reinterpret_cast<T *>(p.out) + (int64_t)bn * p.so.n + (int64_t)bhh * p.so.h;
+                const float *DEN = p.row_den ? p.row_den + (int64_t)bn * p.sden.n + (int64_t)bhh * p.sden.h : nullptr;
+                // 1 / (row_den + eps) of a row (1 without a normaliser or past the segment)
+                auto row_scale = [&](int64_t row) {
+                    return (DEN && row < seg_end) ? 1.f / (DEN[row * p.sden.l] + p.eps) : 1.f;
+                };
                 for (int ci = 0; ci < nchunk && ok; ++ci) {
                     const int c = p.reverse ? nchunk - 1 - ci : ci;
                     const int64_t row0 = seg_begin + (int64_t)c * C;
@@ -852,49 +858,17 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                         if (!ok) break;
                         rearrange_b_in_place(ci, threadIdx.x - 192);
                     }
+                    // (the row scales are fetched before the wait for the accumulator)
+                    float zs[(!K::F16 && DCT == 64) ? 4 : 1];
                     if constexpr (!K::F16 && DCT == 64) {
-                        if (p.accumulate) {
-                            // accumulating scan: fetch what `out` holds for this chunk (the layout of
-                            // the stores below) before waiting for the accumulator, add, store
-                            float2 old[2][16];
 #pragma unroll
-                            for (int hf = 0; hf < 2; ++hf) {
-                                const int64_t ra = row0 + 32 * q + 16 * hf + (lane >> 2);
-                                const T *da = O + ra * p.so.l + n0 + 2 * (lane & 3);
-                                const T *db = da + 8 * p.so.l;
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) {
-                                    old[hf][2 * j] = ra < seg_end ? *reinterpret_cast<const float2 *>(da + 8 * j)
-                                                                  : make_float2(0.f, 0.f);
-                                    old[hf][2 * j + 1] = ra + 8 < seg_end ? *reinterpret_cast<const float2 *>(db + 8 * j)
-                                                                          : make_float2(0.f, 0.f);
-                                }
-                            }
-                            ok = mbar_wait(bar_ofull + 8 * ob, ouse & 1, abort_flag);
-                            if (!ok) break;
-                            tc_fence_after();
-#pragma unroll
-                            for (int hf = 0; hf < 2; ++hf) {
-                                tmem_ld16x256(tlane + ((uint32_t)(16 * hf) << 16) + K::TM_O + ob * DCT, r);
-                                const int64_t ra = row0 + 32 * q + 16 * hf + (lane >> 2);
-                                T *da = O + ra * p.so.l + n0 + 2 * (lane & 3);
-                                T *db = da + 8 * p.so.l;
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) {
-                                    if (ra < seg_end)
-                                        *reinterpret_cast<float2 *>(da + 8 * j) =
-                                            make_float2(old[hf][2 * j].x + __uint_as_float(r[4 * j]),
-                                                        old[hf][2 * j].y + __uint_as_float(r[4 * j + 1]));
-                                    if (ra + 8 < seg_end)
-                                        *reinterpret_cast<float2 *>(db + 8 * j) =
-                                            make_float2(old[hf][2 * j + 1].x + __uint_as_float(r[4 * j + 2]),
-                                                        old[hf][2 * j + 1].y + __uint_as_float(r[4 * j + 3]));
-                                }
-                            }
-                            tc_fence_before();
-                            mbar_arrive(bar_ofree + 8 * ob);
-                            continue;
+                        for (int hf = 0; hf < 2; ++hf) {
+                            const int64_t ra = row0 + 32 * q + 16 * hf + (lane >> 2);
+                            zs[2 * hf] = row_scale(ra);
+                            zs[2 * hf + 1] = row_scale(ra + 8);
                         }
+                    } else {
+                        zs[0] = row_scale(row0 + i);
                     }
                     ok = mbar_wait(bar_ofull + 8 * ob, ouse & 1, abort_flag);
                     if (!ok) break;
@@ -910,6 +884,11 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
                             const int64_t ra = row0 + 32 * q + 16 * hf + (lane >> 2);
                             T *da = O + ra * p.so.l + n0 + 2 * (lane & 3);
                             T *db = da + 8 * p.so.l;
+                            if (DEN) {
+#pragma unroll
+                                for (int e = 0; e < 32; ++e)
+                                    r[e] = __float_as_uint(__uint_as_float(r[e]) * zs[2 * hf + ((e >> 1) & 1)]);
+                            }
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
                                 if (ra < seg_end)
@@ -924,6 +903,10 @@ mma_scan_kernel(const __grid_constant__ ScanBatch batch) {
 #pragma unroll
                     for (int cb = 0; cb < DCT / 32; ++cb) {
                         tmem_ld32(tlane + K::TM_O + ob * DCT + 32 * cb, r);
+                        if (DEN) {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * zs[0]);
+                        }
                         if (row < seg_end) {
                             if constexpr (K::F16) {
 #pragma unroll

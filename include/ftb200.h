@@ -151,6 +151,25 @@ int ftb_causal_dot_product(const void *q, const void *k, const void *v, void *ou
                            size_t workspace_bytes, void *stream);
 
 /*
+ * The forward product with the layer's normaliser applied on the way out:
+ *
+ *   out[n,h,i,:] = ( q_i . sum_{j<=i} k_j (x) v_j ) / (den[n,h,i] + eps)
+ *
+ * -- lines 95-104 of fast_transformers/attention/causal_linear_attention.py (Z = 1 / (Q . cumsum(K)
+ * + eps), V' = causal_linear(Q, K, V) * Z) without the product ever reaching memory unscaled.
+ * `den` holds one fp32 value per (batch, head, position) with element strides `den_strides`
+ * {batch, head, position} (what ftb_causal_normaliser wrote).  FTB_MODE_MMA with the shapes the
+ * 64- and 128-wide kernels take (no wide feature dimension); no states.  Everything else as
+ * ftb_causal_dot_product, the workspace included.
+ */
+int ftb_causal_dot_product_normalised(const void *q, const void *k, const void *v, const float *den,
+                                      void *out, int64_t N, int64_t H, int64_t L, int64_t D, int64_t M,
+                                      const int64_t *q_strides, const int64_t *k_strides,
+                                      const int64_t *v_strides, const int64_t *den_strides,
+                                      const int64_t *out_strides, int dtype, int mode, float eps,
+                                      void *workspace, size_t workspace_bytes, void *stream);
+
+/*
  * Backward: gq_i = S_i g_i ; gk_i = R_i v_i ; gv_i = R_i^T k_i with
  *           S_i = S_init + sum_{j<=i} k_j (x) v_j   and   R_i = R_init + sum_{j>=i} q_j (x) g_j.
  * Replaces causal_dot_backward(queries, keys, values, grad_out, grad_queries, grad_keys,

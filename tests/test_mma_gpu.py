@@ -343,3 +343,29 @@ def test_wide_feature_products_are_summed_by_the_library(D, L, H):
     with pytest.raises(_native.NativeError) as e:
         causal_dot_product_cuda(Qd, Kd, Vd, out, "mma", initial_state=torch.zeros(N, H, D, M, device="cuda"))
     assert e.value.status == _native.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 64), (torch.bfloat16, 128), (torch.bfloat16, 64)])
+def test_normaliser_applied_in_the_epilogue(dtype, D):
+    """``row_den``: row i of the product is divided by den[i] + eps as the scan stores it
+    (``ftb_causal_dot_product_normalised``), den given as an (N, H, L) view of (N, L, H) storage.
+    For fp32 the result is, bit for bit, the plain product times 1 / (den + eps)."""
+    g = torch.Generator().manual_seed(D)
+    N, H, L, eps = 2, 3, 1100, 1e-6
+    Q, K = (torch.rand(N, H, L, D, generator=g).to(dtype) for _ in range(2))
+    V = torch.randn(N, H, L, D, generator=g).to(dtype)
+    den = (torch.rand(N, L, H, generator=g) * 50 + 0.5).cuda().permute(0, 2, 1)
+    Qd, Kd, Vd = Q.cuda(), K.cuda(), V.cuda()
+    plain, scaled = torch.empty_like(Vd), torch.full_like(Vd, float("nan"))
+    causal_dot_product_cuda(Qd, Kd, Vd, plain, "mma")
+    causal_dot_product_cuda(Qd, Kd, Vd, scaled, "mma", row_den=den, eps=eps)
+    z = 1 / (den + eps)
+    if dtype == torch.float32:
+        assert torch.equal(scaled, plain * z[..., None])
+    want = orc.chunked_forward(Q.float(), K.float(), V.float()) * z.cpu().double()[..., None]
+    assert orc.rel_err(scaled, want) < TOL
+    with pytest.raises(_native.NativeError) as e:       # the fp32 kernels have no such epilogue
+        causal_dot_product_cuda(Qd.float(), Kd.float(), Vd.float(), plain.float(), "fp32", row_den=den, eps=eps)
+    assert e.value.status == _native.ERR_UNSUPPORTED
+    with pytest.raises(RuntimeError):
+        causal_dot_product_cuda(Qd, Kd, Vd, scaled, "mma", row_den=den.double(), eps=eps)
