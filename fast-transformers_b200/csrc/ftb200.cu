@@ -883,6 +883,53 @@ static int wide_launch(const float *a, const float *b, const float *c, float *ou
     return FTB_OK;
 }
 
+// One launch of the scan that is wide on the c / out side (wide_c_scan_kernel): a, b rows of 64
+// floats, c and out rows of 64 cnt (cnt = 2 .. 4).
+static int wide_c_launch(const float *a, const float *b, const float *c, float *out, const int64_t *as,
+                         const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H, int64_t L,
+                         int cnt, const WidePlan &w, const float *states, int sum_mode, int sub, int64_t state_blk,
+                         int reverse, bool after_own_launch, int kind, cudaStream_t st) {
+    const int64_t blocks = N * H * w.pl.nseg;
+    if (blocks <= 0) return FTB_OK;
+    if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
+    CUtensorMap ma, mb, mc;
+    wide::ParamsC p;
+    int rc = mma::make_map(&ma, p.pos_a, a, N, H, L, 64, as, FTB_F32);
+    if (rc) return rc;
+    if ((rc = mma::make_map(&mb, p.pos_b, b, N, H, L, 64, bs, FTB_F32))) return rc;
+    if ((rc = mma::make_map(&mc, p.pos_c, c, N, H, L, 64 * cnt, cs, FTB_F32, true))) return rc;
+    if (((uintptr_t)out & 15) || (os[0] * 4) % 16 || (os[1] * 4) % 16 || (os[2] * 4) % 16) return FTB_ERR_ALIGNMENT;
+    p.out = out;
+    p.so = S3(os);
+    p.H = (int)H; p.L = L;
+    p.seg_len = w.pl.seg_len; p.nseg = w.pl.nseg; p.nb = cnt;
+    p.states = states; p.sum_mode = sum_mode; p.sub = sub < 1 ? 1 : sub; p.state_blk = state_blk;
+    p.reverse = reverse;
+    static const char *no_pdl = std::getenv("FTB200_NO_PDL");
+    p.wait_first = (no_pdl || after_own_launch) ? 0 : 1;
+    FTB_CUDA(cudaFuncSetAttribute(wide::wide_c_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)wide::kSmem));
+    LaunchScope scope(kind, st);
+    if (!no_pdl) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)blocks);
+        cfg.blockDim = dim3(mma::NTHREADS);
+        cfg.dynamicSmemBytes = wide::kSmem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, wide::wide_c_scan_kernel, ma, mb, mc, p) == cudaSuccess) return FTB_OK;
+        (void)cudaGetLastError();
+        p.wait_first = 0;
+    }
+    wide::wide_c_scan_kernel<<<(unsigned)blocks, mma::NTHREADS, wide::kSmem, st>>>(ma, mb, mc, p);
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+
 static int wide_forward(const float *q, const float *k, const float *v, float *out, int64_t N, int64_t H,
                         int64_t L, int nb, const int64_t *qs, const int64_t *ks, const int64_t *vs,
                         const int64_t *os, float *ws, cudaStream_t st) {
@@ -921,28 +968,41 @@ static int wide_backward(const float *q, const float *k, const float *v, const f
         else if ((rc = wide_states(k, v, ks, vs, N, H, L, nb, M, w, wsS, 0, st, &sS))) return rc;
     }
     if ((gk || gv) && (rc = wide_states(q, g, qs, gs, N, H, L, nb, M, w, wsR, 1, st, &sR))) return rc;
-    // grad_Q and grad_K: one scan each over all D columns, in one grid with their blocks side by
-    // side (both read grad_out and V as their narrow operands)
-    MmaBatch first;
-    first.after_own_launch = sS.fresh || sR.fresh;
-    if (gq) {
-        rc = mma_add_job(first, g, v, k, gq, gs, vs, ks, gqs, N, H, L, M, D, FTB_F32, w.pl, sS.states, nullptr,
-                         sS.sum_mode, sS.sub, nullptr, 0, 0, 0, 0);
-        if (rc) return rc;
+    // grad_Q and grad_K: wide on the c / out side -- scores and mask once per chunk, the column
+    // blocks of K (Q) streamed, up to four per launch (a single left-over block: the 64-wide scan)
+    bool own = sS.fresh || sR.fresh;      // is the launch in front one of this call's?
+    for (int which = 0; which < 2; ++which) {
+        float *dst = which == 0 ? gq : gk;
+        if (!dst) continue;
+        const float *a = which == 0 ? g : v, *b = which == 0 ? v : g, *c = which == 0 ? k : q;
+        const int64_t *as = which == 0 ? gs : vs, *bs = which == 0 ? vs : gs, *cs = which == 0 ? ks : qs;
+        const int64_t *os = which == 0 ? gqs : gks;
+        const SegStates &ss = which == 0 ? sS : sR;
+        for (int b0 = 0; b0 < nb; b0 += wide::MAXNB) {
+            const int cnt = nb - b0 < wide::MAXNB ? nb - b0 : wide::MAXNB;
+            const float *st0 = ss.states ? ss.states + (int64_t)64 * b0 * M : nullptr;
+            if (cnt == 1) {
+                MmaBatch one;
+                one.after_own_launch = own;
+                rc = mma_add_job(one, a, b, c + 64 * b0, dst + 64 * b0, as, bs, cs, os, N, H, L, M, 64, FTB_F32, w.pl,
+                                 st0, nullptr, ss.sum_mode, ss.sub, nullptr, 0, 0, 0, which, nullptr, DM);
+                if (rc) return rc;
+                one.kind = FTB_KERNEL_MMA_BWD;
+                rc = mma_launch_batch(one, st);
+            } else {
+                rc = wide_c_launch(a, b, c + 64 * b0, dst + 64 * b0, as, bs, cs, os, N, H, L, cnt, w, st0, ss.sum_mode,
+                                   ss.sub, DM, which, own, FTB_KERNEL_MMA_BWD_MULTI, st);
+            }
+            if (rc) return rc;
+            own = true;
+        }
     }
-    if (gk) {
-        rc = mma_add_job(first, v, g, q, gk, vs, gs, qs, gks, N, H, L, M, D, FTB_F32, w.pl, sR.states, nullptr,
-                         sR.sum_mode, sR.sub, nullptr, 0, 0, 0, 1);
-        if (rc) return rc;
-    }
-    first.kind = (gq && gk) ? FTB_KERNEL_MMA_BWD_MULTI : FTB_KERNEL_MMA_BWD;
-    if ((rc = mma_launch_batch(first, st))) return rc;
     // grad_V: the sum over the feature blocks, up to four per launch
     for (int b0 = 0; gv && b0 < nb; b0 += wide::MAXNB) {
         const int cnt = nb - b0 < wide::MAXNB ? nb - b0 : wide::MAXNB;
         rc = wide_launch(k + 64 * b0, q + 64 * b0, g, gv, ks, qs, gs, gvs, N, H, L, cnt, w,
                          sR.states ? sR.states + (int64_t)64 * b0 * M : nullptr, sR.sum_mode, sR.sub, DM, 1, b0 > 0,
-                         b0 == 0 && (gq || gk || sR.fresh), FTB_KERNEL_MMA_BWD, st);
+                         b0 == 0 && own, FTB_KERNEL_MMA_BWD, st);
         if (rc) return rc;
     }
     return FTB_OK;

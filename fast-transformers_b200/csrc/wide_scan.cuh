@@ -452,5 +452,375 @@ wide_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same shape with the wide dimension on the c / out side: (a, b, c) = (grad_out, V, K) for
+// grad_Q, (V, grad_out, Q) walked downwards for grad_K -- a and b rows of 64, c and out rows of
+// 64 nb.  With the column blocks c_blk of c,
+//
+//   out_c,blk = a_c S_blk + mask(a_c b_c^T) c_c,blk ;   S_blk += b_c^T c_c,blk
+//
+// so the scores and their mask are made ONCE per chunk and a_c, b_c are loaded once; a step
+// (chunk, blk) loads one column block of c (32 KB) and writes one of out.  Shared memory: two
+// chunks of {a | b}, two c blocks, two operand images; tensor memory as above (P, two output
+// accumulators, the nb states in place).  The states are stored as [64 nb][64] blocks (the
+// forward's orientation), i.e. transposed to what this scan accumulates.
+struct ParamsC {
+    float *out;
+    Strides3 so;
+    int H;
+    int64_t L;
+    int64_t seg_len;
+    int nseg;
+    int nb;
+    const float *states;  // per (bh, seg) blocks of [64 nb][64] floats ([column of c][row of b]), or nullptr
+    int sum_mode;
+    int sub;
+    int64_t state_blk;
+    int reverse;
+    int wait_first;
+    int pos_a[3], pos_b[3], pos_c[3];
+};
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+wide_c_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ CUtensorMap map_c, const ParamsC p) {
+    if (!p.wait_first) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + kBarOff;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen + kBarOff + 384);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + kBarOff + 392);
+    const uint32_t bar_abfull = bars, bar_abempty = bars + 16, bar_fullbmn = bars + 32, bar_cfull = bars + 48,
+                   bar_cempty = bars + 64, bar_ofull = bars + 80, bar_ofree = bars + 96, bar_smready = bars + 112,
+                   bar_smready2 = bars + 128, bar_smfree = bars + 144, bar_pfull = bars + 160,
+                   bar_pready = bars + 168, bar_pfree = bars + 176, bar_sfull = bars + 184;   // [4]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = p.nb;
+    const int seg = (int)(blockIdx.x % (unsigned)p.nseg);
+    const int64_t bh = blockIdx.x / (unsigned)p.nseg;
+    const int bn = (int)(bh / p.H), bhh = (int)(bh % p.H);
+    const int64_t seg_begin = (int64_t)seg * p.seg_len;
+    const int64_t seg_end = min(p.L, seg_begin + p.seg_len);
+    int nchunk = (int)((seg_end - seg_begin + C - 1) / C);
+    if (nchunk < 0) nchunk = 0;
+    const int nstep = nchunk * nb;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar_abfull + 8 * s, 1);
+            mbar_init(bar_abempty + 8 * s, 2);    // both issuers
+            mbar_init(bar_fullbmn + 8 * s, 128);
+            mbar_init(bar_cfull + 8 * s, 1);
+            mbar_init(bar_cempty + 8 * s, 2);     // both issuers
+            mbar_init(bar_ofull + 8 * s, 1);
+            mbar_init(bar_ofree + 8 * s, 128);
+            mbar_init(bar_smready + 8 * s, 128);
+            mbar_init(bar_smready2 + 8 * s, 128);
+            mbar_init(bar_smfree + 8 * s, 1);
+        }
+        mbar_init(bar_pfull, 1);
+        mbar_init(bar_pready, 128);
+        mbar_init(bar_pfree, 1);
+        for (int b = 0; b < MAXNB; ++b) mbar_init(bar_sfull + 8 * b, 1);
+        fence_barrier_init();
+    }
+    if (warp == 0) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    if (p.wait_first) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
+
+    if (nchunk > 0) {
+        if (warp == 0) {
+            // ================= TMA producer =====================================================
+            if (elect_one()) {
+                bool ok = true;
+                for (int v = 0; v < nstep && ok; ++v) {
+                    const int ci = v / nb, blk = v - ci * nb;
+                    const int c = p.reverse ? nchunk - 1 - ci : ci;
+                    const int row = (int)(seg_begin + (int64_t)c * C);
+                    if (blk == 0) {
+                        const int sa = ci & 1;
+                        ok = mbar_wait(bar_abempty + 8 * sa, ((ci >> 1) & 1) ^ 1, abort_flag);
+                        if (!ok) break;
+                        const uint32_t st = base + sa * kStage;
+                        mbar_expect_tx(bar_abfull + 8 * sa, kStage);
+                        for (int b = 0; b < 2; ++b) {
+                            tma_load_4d(st + b * kBlk, &map_a, bar_abfull + 8 * sa, 32 * b, p.pos_a, row, bhh, bn);
+                            tma_load_4d(st + kTile + b * kBlk, &map_b, bar_abfull + 8 * sa, 32 * b, p.pos_b, row, bhh, bn);
+                        }
+                    }
+                    const int s = v & 1;
+                    ok = mbar_wait(bar_cempty + 8 * s, ((v >> 1) & 1) ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(bar_cfull + 8 * s, kTile);
+                    for (int b = 0; b < 2; ++b)
+                        tma_load_4d(base + kCOff + s * kTile + b * kBlk, &map_c, bar_cfull + 8 * s, 64 * blk + 32 * b,
+                                    p.pos_c, row, bhh, bn);
+                }
+            }
+        } else if (warp == 1 || warp == 10) {
+            // ================= MMA issuers ======================================================
+            if (elect_one()) {
+                constexpr uint32_t ID_P = instr_desc(2, 0, 0, 128, 128);
+                constexpr uint32_t ID_AS = instr_desc(2, 0, 1, 128, 64);
+                constexpr uint32_t ID_PC = instr_desc(2, 0, 1, 128, 64);
+                constexpr uint32_t ID_ST = instr_desc(2, 1, 1, 64, 64);
+                constexpr uint64_t STAGE_UNITS = (uint64_t)(kStage >> 4), TILE_UNITS = (uint64_t)(kTile >> 4),
+                                   IMG_UNITS = (uint64_t)(kImg >> 4);
+                const uint64_t dAk0 = smem_desc(base, 16, 1024);
+                const uint64_t dBk0 = smem_desc(base + kTile, 16, 1024);
+                const uint64_t dBmn0 = smem_desc(base + kTile, kBlk, 512, 1);
+                const uint64_t dCmn0 = smem_desc(base + kCOff, kBlk, 512, 1);
+                const uint64_t dSm0 = smem_desc(base + kImgOff, kImgBlk, 512, 1);
+                bool ok = true;
+                if (warp == 1) {
+                    // ---- output issuer: O_v = a S_blk + mask(P) c_blk ---------------------------
+                    for (int v = 0; v < nstep && ok; ++v) {
+                        const int ci = v / nb, blk = v - ci * nb;
+                        const int s = v & 1, sa = ci & 1;
+                        const uint32_t tO = tmem + TM_O + 64 * s;
+                        ok = (blk != 0 || mbar_wait(bar_abfull + 8 * sa, (ci >> 1) & 1, abort_flag)) &&
+                             mbar_wait(bar_smready + 8 * s, (v >> 1) & 1, abort_flag) &&
+                             mbar_wait(bar_ofree + 8 * s, ((v >> 1) & 1) ^ 1, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint64_t a0 = dAk0 + sa * STAGE_UNITS, sm0 = dSm0 + s * IMG_UNITS;
+#pragma unroll
+                        for (int b = 0; b < 2; ++b)
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                mma_ss<false>(tO, a0 + (uint64_t)((b * kBlk + k * 32) >> 4),
+                                              sm0 + (uint64_t)(((32 * b + 8 * k) * 128) >> 4), ID_AS, (b | k) ? 1u : 0u);
+                        tc_commit(bar_smfree + 8 * s);
+                        ok = (blk != 0 || mbar_wait(bar_pready, ci & 1, abort_flag)) &&
+                             mbar_wait(bar_cfull + 8 * s, (v >> 1) & 1, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint64_t c0 = dCmn0 + s * TILE_UNITS;
+#pragma unroll
+                        for (int k = 0; k < 16; ++k)
+                            mma_ts<false>(tO, tmem + TM_P + k * 8, c0 + (uint64_t)((k * 1024) >> 4), ID_PC, 1u);
+                        tc_commit(bar_ofull + 8 * s);
+                        tc_commit(bar_cempty + 8 * s);
+                        if (blk + 1 == nb) {
+                            tc_commit(bar_pfree);
+                            tc_commit(bar_abempty + 8 * sa);
+                        }
+                    }
+                } else {
+                    // ---- score / state issuer -------------------------------------------------------
+                    int sc = 0, ds = 0;     // next chunk to score, next step to update
+                    long long t0 = 0;
+                    uint32_t idle = 0;
+                    while (ds < nstep) {
+                        if (sc < nchunk && mbar_test(bar_abfull + 8 * (sc & 1), (sc >> 1) & 1) &&
+                            (sc == 0 || mbar_test(bar_pfree, (sc - 1) & 1))) {
+                            tc_fence_after();
+                            const uint64_t a0 = dAk0 + (sc & 1) * STAGE_UNITS, b0 = dBk0 + (sc & 1) * STAGE_UNITS;
+#pragma unroll
+                            for (int b = 0; b < 2; ++b)
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    const uint64_t off = (uint64_t)((b * kBlk + k * 32) >> 4);
+                                    mma_ss<false>(tmem + TM_P, a0 + off, b0 + off, ID_P, (b | k) ? 1u : 0u);
+                                }
+                            tc_commit(bar_pfull);
+                            ++sc;
+                            idle = 0;
+                            continue;
+                        }
+                        if (ds < sc * nb) {
+                            const int ci = ds / nb, blk = ds - ci * nb, s = ds & 1, sa = ci & 1;
+                            if (mbar_test(bar_fullbmn + 8 * sa, (ci >> 1) & 1) &&
+                                mbar_test(bar_cfull + 8 * s, (ds >> 1) & 1) &&
+                                mbar_test(bar_smready2 + 8 * s, (ds >> 1) & 1)) {
+                                tc_fence_after();
+                                const uint64_t bmn0 = dBmn0 + sa * STAGE_UNITS, c0 = dCmn0 + s * TILE_UNITS;
+#pragma unroll
+                                for (int k = 0; k < 16; ++k) {
+                                    const uint64_t off = (uint64_t)((k * 1024) >> 4);
+                                    mma_ss<false>(tmem + TM_S + 64 * blk, bmn0 + off, c0 + off, ID_ST, 1u);
+                                }
+                                tc_commit(bar_sfull + 8 * blk);
+                                tc_commit(bar_cempty + 8 * s);
+                                if (blk + 1 == nb) tc_commit(bar_abempty + 8 * sa);
+                                ++ds;
+                                idle = 0;
+                                continue;
+                            }
+                        }
+                        if (idle++ == 0) t0 = clock64();
+                        if ((idle & 63u) == 0u) {
+                            if (*abort_flag) break;
+                            if (clock64() - t0 > 4000000000LL) {
+                                *abort_flag = 1;
+                                atomicExch(&g_device_status, 5 /* FTB_ERR_TIMEOUT */);
+                                break;
+                            }
+                        }
+                    }
+                }
+            }
+        } else if (warp >= 11) {
+            // ================= mask workers: once per chunk, in place =============================
+            const int q = warp & 3;
+            const uint32_t tP = tmem + ((uint32_t)(32 * q) << 16) + TM_P;
+            uint32_t r[32];
+            for (int ci = 0; ci < nchunk; ++ci) {
+                if (!mbar_wait(bar_pfull, ci & 1, abort_flag)) break;
+                tc_fence_after();
+                const int nkeep = p.reverse ? 3 - q : q;
+                tmem_zero_columns(tP + (p.reverse ? 0 : 32 * (q + 1)), 32 * (3 - nkeep));
+                tmem_ld32(tP + 32 * q, r);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const bool keep = p.reverse ? (e >= lane) : (e <= lane);
+                    r[e] = keep ? r[e] : 0u;
+                }
+                tmem_st32(tP + 32 * q, r);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar_pready);
+            }
+        } else if (warp >= 6 && warp < 10) {
+            // ================= output workers ====================================================
+            const int q = warp & 3;
+            const int t = threadIdx.x - 192;
+            const uint32_t tlane = tmem + ((uint32_t)(32 * q) << 16);
+            uint32_t r[32];
+            bool ok = true;
+            float *O = p.out + (int64_t)bn * p.so.n + (int64_t)bhh * p.so.h;
+            for (int v = 0; v < nstep && ok; ++v) {
+                const int ci = v / nb, blk = v - ci * nb, s = v & 1;
+                if (blk == 0) {
+                    // MN-major image of b, in place, once the score product has read the tile
+                    ok = mbar_wait(bar_pfull, ci & 1, abort_flag);
+                    if (!ok) break;
+                    uint8_t *bt = gen + (ci & 1) * kStage + kTile;
+                    for (int it0 = 0; it0 < 16; it0 += 4) {
+                        uint4 vv[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int idx = (it0 + j) * 128 + t;
+                            vv[j] = reinterpret_cast<const uint4 *>(bt + (size_t)(idx >> 3) * 128)[idx & 7];
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int idx = (it0 + j) * 128 + t;
+                            const int pk = idx & 7, row = (idx >> 3) & 127;
+                            const int cc = pk ^ (row & 7);
+                            const int pm = ((((cc >> 1) ^ (row & 3)) << 1) | (cc & 1));
+                            reinterpret_cast<uint4 *>(bt + (size_t)(idx >> 3) * 128)[pm] = vv[j];
+                        }
+                        __syncwarp();
+                    }
+                    fence_proxy_async_smem();
+                    mbar_arrive(bar_fullbmn + 8 * (ci & 1));
+                }
+                const int c = p.reverse ? nchunk - 1 - ci : ci;
+                const int64_t row0 = seg_begin + (int64_t)c * C;
+                ok = mbar_wait(bar_ofull + 8 * s, (v >> 1) & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    tmem_ld16x256(tlane + ((uint32_t)(16 * hf) << 16) + TM_O + 64 * s, r);
+                    const int64_t ra = row0 + 32 * q + 16 * hf + (lane >> 2);
+                    float *da = O + ra * p.so.l + 64 * blk + 2 * (lane & 3);
+                    float *db = da + 8 * p.so.l;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (ra < seg_end) *reinterpret_cast<uint2 *>(da + 8 * j) = make_uint2(r[4 * j], r[4 * j + 1]);
+                        if (ra + 8 < seg_end) *reinterpret_cast<uint2 *>(db + 8 * j) = make_uint2(r[4 * j + 2], r[4 * j + 3]);
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(bar_ofree + 8 * s);
+            }
+        } else if (warp >= 2 && warp < 6) {
+            // ================= state workers ======================================================
+            const int q = warp & 3;
+            const uint32_t tlane = tmem + ((uint32_t)(32 * q) << 16);
+            const bool srow_ok = lane < 16;
+            const int srow = 16 * q + (lane & 15);      // row of b^T c = column of the stored block
+            uint32_t r[32];
+            bool ok = true;
+            {
+                int s_lo = seg, s_hi = seg + 1, per_head = p.nseg;
+                if (p.sum_mode) {
+                    per_head = p.nseg * p.sub;
+                    s_lo = p.reverse ? (seg + 1) * p.sub : 0;
+                    s_hi = p.reverse ? per_head : seg * p.sub;
+                }
+                if (!p.states) s_hi = s_lo;
+                if (s_hi > s_lo) asm volatile("griddepcontrol.wait;" ::: "memory");
+                for (int blk = 0; blk < nb; ++blk)
+#pragma unroll
+                    for (int cb = 0; cb < 2; ++cb) {
+                        float acc[32];
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+                        if (srow_ok)
+                            for (int sb = s_lo; sb < s_hi; ++sb) {
+                                const float *src = p.states + ((int64_t)bh * per_head + sb) * p.state_blk +
+                                                   (int64_t)(64 * blk + 32 * cb) * 64 + srow;
+#pragma unroll
+                                for (int e = 0; e < 32; ++e) acc[e] += src[e * 64];
+                            }
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(acc[e]);
+                        tmem_st32(tlane + TM_S + 64 * blk + 32 * cb, r);
+                    }
+                tmem_wait_st();
+            }
+            for (int v = 0; v < nstep && ok; ++v) {
+                const int ci = v / nb, blk = v - ci * nb, s = v & 1;
+                if (v >= 2) {
+                    const int v2 = v - 2, ci2 = v2 / nb, blk2 = v2 - ci2 * nb;
+                    ok = mbar_wait(bar_smfree + 8 * s, (v2 >> 1) & 1, abort_flag) &&
+                         mbar_wait(bar_sfull + 8 * blk2, ci2 & 1, abort_flag);
+                    if (!ok) break;
+                }
+                if (ci >= 1) {
+                    ok = mbar_wait(bar_sfull + 8 * blk, (ci - 1) & 1, abort_flag);
+                    if (!ok) break;
+                }
+                tc_fence_after();
+                uint8_t *img = gen + kImgOff + s * kImg;
+#pragma unroll
+                for (int cb = 0; cb < 2; ++cb) {
+                    tmem_ld32(tlane + TM_S + 64 * blk + 32 * cb, r);
+                    if (srow_ok) {
+                        uint8_t *rowp = img + cb * kImgBlk + srow * 128;
+#pragma unroll
+                        for (int ch = 0; ch < 8; ++ch)
+                            *reinterpret_cast<uint4 *>(rowp + (((ch >> 1) ^ (srow & 3)) * 32) + (ch & 1) * 16) =
+                                make_uint4(r[4 * ch], r[4 * ch + 1], r[4 * ch + 2], r[4 * ch + 3]);
+                    }
+                }
+                fence_proxy_async_smem();
+                tc_fence_before();
+                mbar_arrive(bar_smready + 8 * s);
+                mbar_arrive(bar_smready2 + 8 * s);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 }  // namespace wide
 }  // namespace ftb
