@@ -313,7 +313,8 @@ def test_wide_feature_products_are_summed_by_the_library(D, L, H):
     per direction.  out and grad_V (wide on the query / key side) are summed over the blocks inside
     the tensor cores, up to four blocks per launch (D = 320: a second launch adds the fifth); they
     hold NaN on entry, so the first launch must replace.  grad_Q and grad_K (wide on the output
-    side) are one scan each over D columns.  A skipped gradient is honoured; states are refused."""
+    side) stream up to four column blocks per launch past scores made once per chunk (D = 320: the
+    fifth block through the 64-wide scan).  A skipped gradient is honoured; states are refused."""
     g = torch.Generator().manual_seed(D + L)
     N, M = 1, 64
     Q, K = (torch.rand(N, H, L, D, generator=g) * 0.5 for _ in range(2))
