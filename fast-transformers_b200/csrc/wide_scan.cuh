@@ -66,6 +66,67 @@ struct Params {
     int pos_a[3], pos_b[3], pos_c[3];
 };
 
+// ---- pieces both kernels of this file share ------------------------------------------------------
+// MN-major image of a 128 x 64 fp32 tile, in place: 16-byte chunk c of row r moves from its place in
+// the 128-byte swizzle (c ^ (r & 7)) to its place in the 32-byte-atom swizzle.  `t`: 0..127 within
+// the four warps that share the tile; a warp instruction covers four whole rows.
+__device__ __forceinline__ void rearrange_tile_in_place(uint8_t *bt, int t) {
+    for (int it0 = 0; it0 < 16; it0 += 4) {
+        uint4 vv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int idx = (it0 + j) * 128 + t;
+            vv[j] = reinterpret_cast<const uint4 *>(bt + (size_t)(idx >> 3) * 128)[idx & 7];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int idx = (it0 + j) * 128 + t;
+            const int pk = idx & 7, row = (idx >> 3) & 127;
+            const int cc = pk ^ (row & 7);
+            const int pm = ((((cc >> 1) ^ (row & 3)) << 1) | (cc & 1));
+            reinterpret_cast<uint4 *>(bt + (size_t)(idx >> 3) * 128)[pm] = vv[j];
+        }
+        __syncwarp();
+    }
+    fence_proxy_async_smem();
+}
+
+// Causal mask on the 128 x 128 scores at `tP` (this warp's lane quarter q), in place: column blocks
+// of 32 on the far side of the diagonal are zeroed, the diagonal block element by element.
+__device__ __forceinline__ void mask_scores_in_place(uint32_t tP, int q, int lane, int reverse) {
+    uint32_t r[32];
+    const int nkeep = reverse ? 3 - q : q;
+    tmem_zero_columns(tP + (reverse ? 0 : 32 * (q + 1)), 32 * (3 - nkeep));
+    tmem_ld32(tP + 32 * q, r);
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+        const bool keep = reverse ? (e >= lane) : (e <= lane);
+        r[e] = keep ? r[e] : 0u;
+    }
+    tmem_st32(tP + 32 * q, r);
+    tmem_wait_st();
+}
+
+// The 64 x 64 state accumulator at `tS` (this warp's lane quarter) -> operand image `img` (read
+// MN-major by "a S"): 64-row accumulators keep their rows in 16 lanes per quarter.
+__device__ __forceinline__ void state_to_image(uint32_t tS, uint8_t *img, int lane, int q) {
+    uint32_t r[32];
+    const int srow = 16 * q + (lane & 15);
+#pragma unroll
+    for (int cb = 0; cb < 2; ++cb) {
+        tmem_ld32(tS + 32 * cb, r);
+        if (lane < 16) {
+            uint8_t *rowp = img + cb * kImgBlk + srow * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+                *reinterpret_cast<uint4 *>(rowp + (((ch >> 1) ^ (srow & 3)) * 32) + (ch & 1) * 16) =
+                    make_uint4(r[4 * ch], r[4 * ch + 1], r[4 * ch + 2], r[4 * ch + 3]);
+        }
+    }
+    fence_proxy_async_smem();
+}
+
 __global__ void __launch_bounds__(NTHREADS, 1)
 wide_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const Params p) {
@@ -269,20 +330,10 @@ wide_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             // ================= mask workers: once per chunk, in place =============================
             const int q = warp & 3;
             const uint32_t tP = tmem + ((uint32_t)(32 * q) << 16) + TM_P;
-            uint32_t r[32];
             for (int ci = 0; ci < nchunk; ++ci) {
                 if (!mbar_wait(bar_pfull, ci & 1, abort_flag)) break;
                 tc_fence_after();
-                const int nkeep = p.reverse ? 3 - q : q;
-                tmem_zero_columns(tP + (p.reverse ? 0 : 32 * (q + 1)), 32 * (3 - nkeep));
-                tmem_ld32(tP + 32 * q, r);
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const bool keep = p.reverse ? (e >= lane) : (e <= lane);
-                    r[e] = keep ? r[e] : 0u;
-                }
-                tmem_st32(tP + 32 * q, r);
-                tmem_wait_st();
+                mask_scores_in_place(tP, q, lane, p.reverse);
                 tc_fence_before();
                 mbar_arrive(bar_pready);
             }
@@ -343,26 +394,7 @@ wide_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 // 16-byte chunk c of row r moves from c ^ (r & 7) to the 32-byte-atom position
                 ok = mbar_wait(bar_sdone + 8 * s, (v >> 1) & 1, abort_flag);
                 if (!ok) break;
-                uint8_t *bt = gen + s * kStage + kTile;
-                for (int it0 = 0; it0 < 16; it0 += 4) {
-                    uint4 vv[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int idx = (it0 + j) * 128 + t;
-                        vv[j] = reinterpret_cast<const uint4 *>(bt + (size_t)(idx >> 3) * 128)[idx & 7];
-                    }
-                    __syncwarp();
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int idx = (it0 + j) * 128 + t;
-                        const int pk = idx & 7, row = (idx >> 3) & 127;
-                        const int cc = pk ^ (row & 7);
-                        const int pm = ((((cc >> 1) ^ (row & 3)) << 1) | (cc & 1));
-                        reinterpret_cast<uint4 *>(bt + (size_t)(idx >> 3) * 128)[pm] = vv[j];
-                    }
-                    __syncwarp();
-                }
-                fence_proxy_async_smem();
+                rearrange_tile_in_place(gen + s * kStage + kTile, t);
                 mbar_arrive(bar_fullbmn + 8 * s);
                 // the rows of the previous chunk (its accumulator completes a mask later than the
                 // score product of its last block: written here, it does not hold up the image)
@@ -425,19 +457,7 @@ wide_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (!ok) break;
                 }
                 tc_fence_after();
-                uint8_t *img = gen + kImgOff + s * kImg;
-#pragma unroll
-                for (int cb = 0; cb < 2; ++cb) {
-                    tmem_ld32(tlane + TM_S + 64 * blk + 32 * cb, r);
-                    if (srow_ok) {
-                        uint8_t *rowp = img + cb * kImgBlk + srow * 128;
-#pragma unroll
-                        for (int ch = 0; ch < 8; ++ch)
-                            *reinterpret_cast<uint4 *>(rowp + (((ch >> 1) ^ (srow & 3)) * 32) + (ch & 1) * 16) =
-                                make_uint4(r[4 * ch], r[4 * ch + 1], r[4 * ch + 2], r[4 * ch + 3]);
-                    }
-                }
-                fence_proxy_async_smem();
+                state_to_image(tlane + TM_S + 64 * blk, gen + kImgOff + s * kImg, lane, q);
                 tc_fence_before();
                 mbar_arrive(bar_smready + 8 * s);
                 mbar_arrive(bar_smready2 + 8 * s);
@@ -673,20 +693,10 @@ wide_c_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             // ================= mask workers: once per chunk, in place =============================
             const int q = warp & 3;
             const uint32_t tP = tmem + ((uint32_t)(32 * q) << 16) + TM_P;
-            uint32_t r[32];
             for (int ci = 0; ci < nchunk; ++ci) {
                 if (!mbar_wait(bar_pfull, ci & 1, abort_flag)) break;
                 tc_fence_after();
-                const int nkeep = p.reverse ? 3 - q : q;
-                tmem_zero_columns(tP + (p.reverse ? 0 : 32 * (q + 1)), 32 * (3 - nkeep));
-                tmem_ld32(tP + 32 * q, r);
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const bool keep = p.reverse ? (e >= lane) : (e <= lane);
-                    r[e] = keep ? r[e] : 0u;
-                }
-                tmem_st32(tP + 32 * q, r);
-                tmem_wait_st();
+                mask_scores_in_place(tP, q, lane, p.reverse);
                 tc_fence_before();
                 mbar_arrive(bar_pready);
             }
@@ -704,26 +714,7 @@ wide_c_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     // MN-major image of b, in place, once the score product has read the tile
                     ok = mbar_wait(bar_pfull, ci & 1, abort_flag);
                     if (!ok) break;
-                    uint8_t *bt = gen + (ci & 1) * kStage + kTile;
-                    for (int it0 = 0; it0 < 16; it0 += 4) {
-                        uint4 vv[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int idx = (it0 + j) * 128 + t;
-                            vv[j] = reinterpret_cast<const uint4 *>(bt + (size_t)(idx >> 3) * 128)[idx & 7];
-                        }
-                        __syncwarp();
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int idx = (it0 + j) * 128 + t;
-                            const int pk = idx & 7, row = (idx >> 3) & 127;
-                            const int cc = pk ^ (row & 7);
-                            const int pm = ((((cc >> 1) ^ (row & 3)) << 1) | (cc & 1));
-                            reinterpret_cast<uint4 *>(bt + (size_t)(idx >> 3) * 128)[pm] = vv[j];
-                        }
-                        __syncwarp();
-                    }
-                    fence_proxy_async_smem();
+                    rearrange_tile_in_place(gen + (ci & 1) * kStage + kTile, t);
                     mbar_arrive(bar_fullbmn + 8 * (ci & 1));
                 }
                 const int c = p.reverse ? nchunk - 1 - ci : ci;
@@ -795,19 +786,7 @@ wide_c_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     if (!ok) break;
                 }
                 tc_fence_after();
-                uint8_t *img = gen + kImgOff + s * kImg;
-#pragma unroll
-                for (int cb = 0; cb < 2; ++cb) {
-                    tmem_ld32(tlane + TM_S + 64 * blk + 32 * cb, r);
-                    if (srow_ok) {
-                        uint8_t *rowp = img + cb * kImgBlk + srow * 128;
-#pragma unroll
-                        for (int ch = 0; ch < 8; ++ch)
-                            *reinterpret_cast<uint4 *>(rowp + (((ch >> 1) ^ (srow & 3)) * 32) + (ch & 1) * 16) =
-                                make_uint4(r[4 * ch], r[4 * ch + 1], r[4 * ch + 2], r[4 * ch + 3]);
-                    }
-                }
-                fence_proxy_async_smem();
+                state_to_image(tlane + TM_S + 64 * blk, gen + kImgOff + s * kImg, lane, q);
                 tc_fence_before();
                 mbar_arrive(bar_smready + 8 * s);
                 mbar_arrive(bar_smready2 + 8 * s);
