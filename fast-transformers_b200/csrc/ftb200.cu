@@ -688,7 +688,7 @@ size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, in
 static int x3_launch(const float *a, const float *b, const float *c, float *out, const int64_t *as,
                      const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H, int64_t L,
                      Plan pl, const float *states, int sum_mode, float *state_out, int skip_lo, int skip_hi,
-                     int canon_is_DaDc, int reverse, int kind, cudaStream_t st) {
+                     int canon_is_DaDc, int reverse, bool after_own_launch, int kind, cudaStream_t st) {
     const int64_t blocks = N * H * pl.nseg;
     if (blocks <= 0) return FTB_OK;
     if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
@@ -712,8 +712,25 @@ static int x3_launch(const float *a, const float *b, const float *c, float *out,
     p.states = states; p.sum_mode = sum_mode; p.state_out = state_out;
     p.skip_lo = skip_lo; p.skip_hi = skip_hi;
     p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = a ? 0 : 1;
+    static const char *no_pdl = std::getenv("FTB200_NO_PDL");
+    p.wait_first = (no_pdl || after_own_launch) ? 0 : 1;
     FTB_CUDA(cudaFuncSetAttribute(x3::x3_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)x3::kSmem));
     LaunchScope scope(kind, st);
+    if (!no_pdl) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)blocks);
+        cfg.blockDim = dim3(mma::NTHREADS);
+        cfg.dynamicSmemBytes = x3::kSmem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, x3::x3_scan_kernel, ma, mb, mbmn, mc, p) == cudaSuccess) return FTB_OK;
+        (void)cudaGetLastError();
+        p.wait_first = 0;
+    }
     x3::x3_scan_kernel<<<(unsigned)blocks, mma::NTHREADS, x3::kSmem, st>>>(ma, mb, mbmn, mc, p);
     FTB_CUDA(cudaGetLastError());
     return FTB_OK;
@@ -721,8 +738,8 @@ static int x3_launch(const float *a, const float *b, const float *c, float *out,
 
 // Per-segment totals of sum x (x) y into `ws`, as what the scans read.
 static int x3_states(const float *x, const float *y, const int64_t *xs, const int64_t *ys, int64_t N, int64_t H,
-                     int64_t L, Plan pl, float *ws, int reverse, cudaStream_t st, const float **states,
-                     int *sum_mode) {
+                     int64_t L, Plan pl, float *ws, int reverse, bool after_own_launch, cudaStream_t st,
+                     const float **states, int *sum_mode) {
     *states = nullptr;
     *sum_mode = 0;
     if (pl.nseg == 1) return FTB_OK;
@@ -733,7 +750,7 @@ static int x3_states(const float *x, const float *y, const int64_t *xs, const in
         skip_hi = skip_lo + 1;
     }
     int rc = x3_launch(nullptr, x, y, nullptr, nullptr, xs, ys, nullptr, N, H, L, pl, nullptr, 0, ws, skip_lo,
-                       skip_hi, 1, 0, FTB_KERNEL_MMA_STATE, st);
+                       skip_hi, 1, 0, after_own_launch, FTB_KERNEL_MMA_STATE, st);
     if (rc) return rc;
     *states = ws;
     *sum_mode = in_kernel ? 1 : 0;
@@ -747,9 +764,12 @@ static int x3_forward(const float *q, const float *k, const float *v, float *out
     const Plan pl = x3_plan(N * H, L);
     const float *states;
     int sum_mode;
-    int rc = x3_states(k, v, ks, vs, N, H, L, pl, ws, 0, st, &states, &sum_mode);
+    int rc = x3_states(k, v, ks, vs, N, H, L, pl, ws, 0, false, st, &states, &sum_mode);
     if (rc) return rc;
-    return x3_launch(q, k, v, out, qs, ks, vs, os, N, H, L, pl, states, sum_mode, nullptr, 0, 0, 1, 0,
+    // (behind a sweep of this call the scan waits only for the totals; a prefix launch in between
+    // is not one of these kernels: then the scan waits for everything in front)
+    const bool own = states && sum_mode == 1;
+    return x3_launch(q, k, v, out, qs, ks, vs, os, N, H, L, pl, states, sum_mode, nullptr, 0, 0, 1, 0, own,
                      FTB_KERNEL_MMA_FWD, st);
 }
 
@@ -762,20 +782,35 @@ static int x3_backward(const float *q, const float *k, const float *v, const flo
     float *wsS = workspace, *wsR = (float *)((char *)workspace + workspace_bytes / 2);
     const float *sS = nullptr, *sR = nullptr;
     int mS = 0, mR = 0, rc;
+    bool own = false;      // is the launch in front one of this call's scan kernels?
     if (gq) {
         if (forward_workspace && pl.nseg > 1) {
             sS = forward_workspace;
             mS = pl.nseg <= mma::kSumInKernelMaxSegs ? 1 : 0;
-        } else if ((rc = x3_states(k, v, ks, vs, N, H, L, pl, wsS, 0, st, &sS, &mS))) return rc;
+        } else {
+            if ((rc = x3_states(k, v, ks, vs, N, H, L, pl, wsS, 0, false, st, &sS, &mS))) return rc;
+            own = sS && mS == 1;
+        }
     }
-    if ((gk || gv) && (rc = x3_states(q, g, qs, gs, N, H, L, pl, wsR, 1, st, &sR, &mR))) return rc;
-    if (gq && (rc = x3_launch(g, v, k, gq, gs, vs, ks, gqs, N, H, L, pl, sS, mS, nullptr, 0, 0, 0, 0,
-                              FTB_KERNEL_MMA_BWD, st)))
-        return rc;
-    if (gk && (rc = x3_launch(v, g, q, gk, vs, gs, qs, gks, N, H, L, pl, sR, mR, nullptr, 0, 0, 0, 1,
-                              FTB_KERNEL_MMA_BWD, st)))
-        return rc;
-    if (gv && (rc = x3_launch(k, q, g, gv, ks, qs, gs, gvs, N, H, L, pl, sR, mR, nullptr, 0, 0, 1, 1,
+    if (gk || gv) {
+        if ((rc = x3_states(q, g, qs, gs, N, H, L, pl, wsR, 1, own, st, &sR, &mR))) return rc;
+        own = sR ? mR == 1 : own;
+    }
+    // (a scan directly behind this call's own sweeps or scans waits only for the totals it reads:
+    // everything else it reads is the caller's input)
+    if (gq) {
+        if ((rc = x3_launch(g, v, k, gq, gs, vs, ks, gqs, N, H, L, pl, sS, mS, nullptr, 0, 0, 0, 0, own,
+                            FTB_KERNEL_MMA_BWD, st)))
+            return rc;
+        own = true;
+    }
+    if (gk) {
+        if ((rc = x3_launch(v, g, q, gk, vs, gs, qs, gks, N, H, L, pl, sR, mR, nullptr, 0, 0, 0, 1, own,
+                            FTB_KERNEL_MMA_BWD, st)))
+            return rc;
+        own = true;
+    }
+    if (gv && (rc = x3_launch(k, q, g, gv, ks, qs, gs, gvs, N, H, L, pl, sR, mR, nullptr, 0, 0, 1, 1, own,
                               FTB_KERNEL_MMA_BWD, st)))
         return rc;
     return FTB_OK;

@@ -59,6 +59,8 @@ struct Params {
     int canon_is_DaDc;    // stored blocks are [DA][Dc] (1) or [Dc][DA] (0)
     int reverse;
     int state_only;
+    int wait_first;       // programmatic launch: wait for the grid in front before any global access
+                          // (0: that grid is this call's own; only its totals are waited for)
     int pos_a[3], pos_b[3], pos_c[3];
 };
 
@@ -74,6 +76,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 x3_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_bmn, const __grid_constant__ CUtensorMap map_c,
                const Params p) {
+    if (!p.wait_first) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
@@ -96,6 +99,7 @@ x3_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (p.state_only && nchunk == 0 && !skipped) {
         // a segment without rows: its totals are zero, and they are read like any other block
         float *dst = p.state_out + ((int64_t)bh * p.nseg + seg) * 4096;
+        if (p.wait_first) asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int e = threadIdx.x; e < 4096; e += NTHREADS) dst[e] = 0.f;
     }
 
@@ -122,6 +126,10 @@ x3_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    if (p.wait_first) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
 
     // hi | lo of the tiles that landed: 16-byte pieces, shared by the 256 threads of warps 6-9 and
     // 11-14 (`t`: 0..255).  State-only launches have no a tile.
@@ -397,6 +405,8 @@ x3_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     s_hi = p.reverse ? p.nseg : seg;
                 }
                 if (!p.states) s_hi = s_lo;
+                // the totals come from the launch in front (a sweep of this call): wait for it here
+                if (s_hi > s_lo) asm volatile("griddepcontrol.wait;" ::: "memory");
                 if (srow_ok)
                     for (int sb = s_lo; sb < s_hi; ++sb) {
                         const float *src = p.states + ((int64_t)bh * p.nseg + sb) * 4096;
@@ -448,6 +458,8 @@ x3_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     if (warp == 0) tmem_dealloc(tmem, 512);
+    // no block of a programmatically launched grid ends before the grid in front of it has
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 }  // namespace x3

@@ -316,7 +316,8 @@ def test_concurrent_calls_from_two_threads_on_two_streams(mode):
 
 def test_ordinary_launches_give_the_same_results_as_programmatic_ones():
     """FTB200_NO_PDL=1 (ordinary launches instead of programmatic stream serialisation) in a child
-    process: same kernels, same arithmetic, bitwise the same results."""
+    process: same kernels, same arithmetic, bitwise the same results -- for the 64-wide scans and
+    for a wide feature dimension (three feature blocks)."""
     import os
     import subprocess
     import sys
@@ -331,8 +332,15 @@ def test_ordinary_launches_give_the_same_results_as_programmatic_ones():
         "Q.requires_grad_(True); K.requires_grad_(True); V.requires_grad_(True)\n"
         "with ftb.mode('mma'):\n"
         "    out = causal_dot_product(Q, K, V); out.backward(G)\n"
+        "res = [out.detach().cpu(), Q.grad.cpu(), K.grad.cpu(), V.grad.cpu()]\n"
+        "g = torch.Generator().manual_seed(3)\n"
+        "Q, K = (torch.rand(1, 5, 2000, 192, generator=g).cuda().requires_grad_(True) for _ in range(2))\n"
+        "V = torch.randn(1, 5, 2000, 64, generator=g).cuda().requires_grad_(True)\n"
+        "with ftb.mode('mma'):\n"
+        "    out = causal_dot_product(Q, K, V); out.backward(torch.ones_like(out))\n"
+        "res += [out.detach().cpu(), Q.grad.cpu(), K.grad.cpu(), V.grad.cpu()]\n"
         "torch.cuda.synchronize(); ftb.check_device_status()\n"
-        "torch.save([out.detach().cpu(), Q.grad.cpu(), K.grad.cpu(), V.grad.cpu()], sys.argv[1])\n" % root)
+        "torch.save(res, sys.argv[1])\n" % root)
     results = []
     with tempfile.TemporaryDirectory() as tmp:
         for flag in ("0", "1"):
