@@ -162,6 +162,18 @@ x3_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                     row, bhh, bn);
                         tma_load_4d(base + kC + b * kBlk, &map_c, bar_full, 32 * b, p.pos_c, row, bhh, bn);
                     }
+                    // With one stage the next chunk cannot land in shared memory yet; pull it towards
+                    // L2 meanwhile, so that its loads find it there (this kernel waits for latency, not
+                    // for HBM bandwidth).
+                    if (ci + 1 < nchunk) {
+                        const int cn = p.reverse ? nchunk - 2 - ci : ci + 1;
+                        const int rown = (int)(seg_begin + (int64_t)cn * C);
+                        for (int b = 0; b < 2; ++b) {
+                            if (!p.state_only) tma_prefetch_4d(&map_a, 32 * b, p.pos_a, rown, bhh, bn);
+                            tma_prefetch_4d(&map_b, 32 * b, p.pos_b, rown, bhh, bn);
+                            tma_prefetch_4d(&map_c, 32 * b, p.pos_c, rown, bhh, bn);
+                        }
+                    }
                 }
             }
         } else if (warp == 1 || warp == 10) {
