@@ -792,7 +792,21 @@ static int x3_backward(const float *q, const float *k, const float *v, const flo
             own = sS && mS == 1;
         }
     }
-    if (gk || gv) {
+    // grad_K and grad_V over WHOLE sequences where that takes fewer chunk times than a sweep of
+    // (q, grad_out) and two grids over the segments: no reverse totals then, and the two grids run
+    // side by side (the second is started programmatically while the first one runs; config 2:
+    // two grids of 64 blocks x 32 chunks at once instead of three grids of 128 x 16 in a row)
+    Plan pl_kv = pl;
+    if (gk && gv && pl.nseg > 1) {
+        const int64_t sms = mma::sm_count(), chunks = (L + mma::C - 1) / mma::C, cps = pl.seg_len / mma::C;
+        const int64_t whole = (2 * N * H + sms - 1) / sms * (chunks + 1);
+        const int64_t split = 3 * ((N * H * pl.nseg + sms - 1) / sms) * (cps + 1);
+        if (whole <= split) {
+            pl_kv.nseg = 1;
+            pl_kv.seg_len = chunks * mma::C;
+        }
+    }
+    if ((gk || gv) && pl_kv.nseg > 1) {
         if ((rc = x3_states(q, g, qs, gs, N, H, L, pl, wsR, 1, own, st, &sR, &mR))) return rc;
         own = sR ? mR == 1 : own;
     }
@@ -805,12 +819,12 @@ static int x3_backward(const float *q, const float *k, const float *v, const flo
         own = true;
     }
     if (gk) {
-        if ((rc = x3_launch(v, g, q, gk, vs, gs, qs, gks, N, H, L, pl, sR, mR, nullptr, 0, 0, 0, 1, own,
+        if ((rc = x3_launch(v, g, q, gk, vs, gs, qs, gks, N, H, L, pl_kv, sR, mR, nullptr, 0, 0, 0, 1, own,
                             FTB_KERNEL_MMA_BWD, st)))
             return rc;
         own = true;
     }
-    if (gv && (rc = x3_launch(k, q, g, gv, ks, qs, gs, gvs, N, H, L, pl, sR, mR, nullptr, 0, 0, 1, 1, own,
+    if (gv && (rc = x3_launch(k, q, g, gv, ks, qs, gs, gvs, N, H, L, pl_kv, sR, mR, nullptr, 0, 0, 1, 1, own,
                               FTB_KERNEL_MMA_BWD, st)))
         return rc;
     return FTB_OK;
