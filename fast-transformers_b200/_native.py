@@ -30,7 +30,7 @@ EXPORTS = (
     "ftb_exchange_destroy", "ftb_exchange_push", "ftb_exchange_receive",
     "ftb_exchange_wait_limit_ms", "ftb_exchange_push_parts", "ftb_causal_state_parts",
     "ftb_linear_apply_state", "ftb_favor_feature_map", "ftb_recurrent_cross_linear_step",
-    "ftb_causal_dot_product_normalised",
+    "ftb_causal_dot_product_normalised", "ftb_favor_feature_map_backward",
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
                 "mma_bwd_qr", "mma_bwd_multi", "recurrent_step", "normaliser", "feature_map",
@@ -116,6 +116,8 @@ def lib():
     L.ftb_recurrent_cross_linear_step.restype = _int
     L.ftb_recurrent_cross_linear_step.argtypes = (
         [_vp] * 4 + [_i64] * 4 + [_i64p] * 2 + [_int, _int, ctypes.c_float, _vp])
+    L.ftb_favor_feature_map_backward.restype = _int
+    L.ftb_favor_feature_map_backward.argtypes = [_vp] * 5 + [_i64] * 7 + [ctypes.c_float, _vp]
     L.ftb_favor_feature_map.restype = _int
     L.ftb_favor_feature_map.argtypes = [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.c_float, _vp]
     L.ftb_exchange_wait_limit_ms.restype = _int

@@ -1597,6 +1597,58 @@ int ftb_favor_feature_map(const float *x, const float *omega_t, float *out, int6
     return FTB_OK;
 }
 
+int ftb_favor_feature_map_backward(const float *grad_phi, const float *phi, const float *x, const float *omega,
+                                   float *grad_x, int64_t rows, int64_t E, int64_t half, int64_t grad_phi_row_stride,
+                                   int64_t phi_row_stride, int64_t x_row_stride, int64_t grad_x_row_stride,
+                                   float softmax_temp, void *stream) {
+    if (rows < 0 || E <= 0 || half <= 0 || !(softmax_temp > 0.f)) return FTB_ERR_INVALID;
+    if (E != favor::kE || (half != 64 && half != 128)) return FTB_ERR_UNSUPPORTED;
+    if (rows == 0) return FTB_OK;
+    if (!grad_phi || !phi || !x || !omega || !grad_x) return FTB_ERR_INVALID;
+    if (rows > 0x7fffffffLL - favor::kRows) return FTB_ERR_UNSUPPORTED;
+    if (((uintptr_t)grad_x & 7) || grad_x_row_stride % 2 || grad_x_row_stride < E) return FTB_ERR_ALIGNMENT;
+    CUtensorMap mg, mp, mx, mw;
+    favor::BwdParams p;
+    const int64_t gs[3] = {0, 0, grad_phi_row_stride}, ps[3] = {0, 0, phi_row_stride}, xs[3] = {0, 0, x_row_stride};
+    int rc = mma::make_map(&mg, p.pos_g, grad_phi, 1, 1, rows, 2 * half, gs, FTB_F32);
+    if (rc) return rc;
+    if ((rc = mma::make_map(&mp, p.pos_p, phi, 1, 1, rows, 2 * half, ps, FTB_F32))) return rc;
+    if ((rc = mma::make_map(&mx, p.pos_x, x, 1, 1, rows, E, xs, FTB_F32))) return rc;
+    {
+        // omega (E rows of `half` floats): boxes of 32 features x all 64 rows
+        mma::EncodeTiledFn enc = mma::encode_fn();
+        if (!enc) return FTB_ERR_CUDA;
+        if ((uintptr_t)omega & 15) return FTB_ERR_ALIGNMENT;
+        cuuint64_t gdim[2] = {(cuuint64_t)half, (cuuint64_t)E};
+        cuuint64_t gstr[1] = {(cuuint64_t)(half * 4)};
+        cuuint32_t box[2] = {32, (cuuint32_t)E}, estr[2] = {1, 1};
+        if (enc(&mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(omega), gdim, gstr, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return FTB_ERR_ALIGNMENT;
+    }
+    p.grad_x = grad_x;
+    p.rows = rows;
+    p.gx_stride = grad_x_row_stride;
+    p.scale = sqrtf(softmax_temp);
+    p.temp = softmax_temp;
+    const int64_t tiles = (rows + favor::kRows - 1) / favor::kRows;
+    const unsigned grid = (unsigned)std::min<int64_t>(tiles, (int64_t)mma::sm_count());
+    cudaStream_t st = (cudaStream_t)stream;
+    LaunchScope scope(FTB_KERNEL_FEATURE_MAP, st);
+    if (half == 64) {
+        FTB_CUDA(cudaFuncSetAttribute(favor::favor_map_backward_kernel<64>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)favor::kSmemBwd));
+        favor::favor_map_backward_kernel<64><<<grid, favor::kBwdThreads, favor::kSmemBwd, st>>>(mg, mp, mx, mw, p);
+    } else {
+        FTB_CUDA(cudaFuncSetAttribute(favor::favor_map_backward_kernel<128>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)favor::kSmemBwd));
+        favor::favor_map_backward_kernel<128><<<grid, favor::kBwdThreads, favor::kSmemBwd, st>>>(mg, mp, mx, mw, p);
+    }
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+
 // ---------------------------------------------------------------------------------------------
 // One fixed state applied to every position (the non-causal form), and a read-only step.
 // ---------------------------------------------------------------------------------------------

@@ -250,11 +250,31 @@ def favor_features_raw(x, omega, softmax_temp):
     return out
 
 
+def favor_features_backward_raw(grad_phi, phi, x, omega, softmax_temp):
+    """The input gradient of ``favor_features_raw`` in one native pass
+    (``ftb_favor_feature_map_backward``).  No autograd."""
+    import ctypes
+    from .. import _native
+    g, xc = grad_phi.contiguous(), x.contiguous()
+    half = omega.shape[1]
+    rows = xc.numel() // xc.shape[-1]
+    om = omega.contiguous()
+    grad_x = torch.empty_like(xc)
+    vp = ctypes.c_void_p
+    with torch.cuda.device(xc.device):
+        st = _native.lib().ftb_favor_feature_map_backward(
+            vp(g.data_ptr()), vp(phi.data_ptr()), vp(xc.data_ptr()), vp(om.data_ptr()), vp(grad_x.data_ptr()),
+            rows, xc.shape[-1], half, 2 * half, 2 * half, xc.shape[-1], xc.shape[-1], float(softmax_temp),
+            vp(torch.cuda.current_stream(xc.device).cuda_stream))
+    _native.check(st, "ftb_favor_feature_map_backward")
+    return grad_x
+
+
 class _FavorNative(torch.autograd.Function):
-    """Favor's feature map with a native forward (one pass on the tensor cores).  The backward is
-    the chain rule on the saved input and OUTPUT -- with phi = [p, m]:
+    """Favor's feature map, forward and backward one native pass each on the tensor cores.  The
+    backward is the chain rule on the saved input and OUTPUT -- with phi = [p, m]:
     ``grad_u = g_p * p - g_m * m``, ``grad_off = -sum(g * phi)``,
-    ``grad_x = temp^(1/2) * (grad_u omega^T) + temp * grad_off * x`` -- as torch calls."""
+    ``grad_x = temp^(1/2) * (grad_u omega^T) + temp * grad_off * x``."""
 
     @staticmethod
     def forward(ctx, x, omega, softmax_temp):
@@ -267,6 +287,8 @@ class _FavorNative(torch.autograd.Function):
     def backward(ctx, grad_phi):
         x, omega, phi = ctx.saved_tensors
         half = omega.shape[1]
+        if grad_phi.dtype == torch.float32 and grad_phi.is_cuda:
+            return favor_features_backward_raw(grad_phi, phi, x, omega, ctx.softmax_temp), None, None
         gp = grad_phi * phi
         grad_u = gp[..., :half] - gp[..., half:]
         grad_off = -gp.sum(dim=-1, keepdim=True)

@@ -277,6 +277,21 @@ int ftb_favor_feature_map(const float *x, const float *omega_t, float *out, int6
                           void *stream);
 
 /*
+ * The gradient of ftb_favor_feature_map's input, one pass: with phi = [p, m] the map's output and
+ * g = grad_phi,
+ *     grad_u = g_p p - g_m m;   grad_off = -sum(g phi)
+ *     grad_x = softmax_temp^(1/2) (grad_u omega^T) + softmax_temp grad_off x
+ * (what autograd derives from fourier_features.py:218-243).  grad_phi, phi: rows x n fp32 (row
+ * strides in elements, rows 16-byte aligned); x: rows x 64; omega: the reference's buffer as it
+ * is, (E, half) fp32 contiguous; grad_x: rows x 64.  Same shapes and tier as the forward.
+ */
+int ftb_favor_feature_map_backward(const float *grad_phi, const float *phi, const float *x,
+                                   const float *omega, float *grad_x, int64_t rows, int64_t E,
+                                   int64_t half, int64_t grad_phi_row_stride, int64_t phi_row_stride,
+                                   int64_t x_row_stride, int64_t grad_x_row_stride, float softmax_temp,
+                                   void *stream);
+
+/*
  * One step of the same attention as a recurrent model with a fixed-size state.  Replaces the
  * arithmetic of RecurrentLinearAttention.forward
  * (fast_transformers/recurrent/attention/self_attention/linear_attention.py:55-90), which the

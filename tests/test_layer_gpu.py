@@ -214,8 +214,8 @@ def test_one_node_layer_equals_the_chain_of_nodes(mode, dtype):
 
 @pytest.mark.parametrize("n_dims,shape", [(256, (2, 300, 3, 64)), (128, (1, 129, 2, 64)), (256, (5, 64))])
 def test_native_favor_feature_map(golden, n_dims, shape):
-    """Favor's positive random features as one pass on the tensor cores (tensor-core mode) against
-    the fp64 restatement of the reference's formula, forward and gradient; in the fp32 mode the
+    """Favor's positive random features, forward and backward one pass each on the tensor cores
+    (tensor-core mode), against the fp64 restatement of the reference's formula and its gradient; in the fp32 mode the
     reference's torch formulation runs and matches to fp32 accuracy."""
     import fast_transformers_b200 as ftb
     from fast_transformers_b200 import _native
@@ -235,7 +235,9 @@ def test_native_favor_feature_map(golden, n_dims, shape):
             phi = fm(xg)
         launched = _native.lib().ftb_launch_count() - n0
         assert launched == (1 if mode == "mma" else 0)
+        n0 = _native.lib().ftb_launch_count()
         (phi * w.cuda()).sum().backward()
+        assert _native.lib().ftb_launch_count() - n0 == (1 if mode == "mma" else 0)   # the native backward
         assert phi.shape == want.shape and torch.all(phi > 0)
         assert orc.rel_err(phi, want) < tol, mode
         assert orc.rel_err(xg.grad, xd.grad) < tol, mode
