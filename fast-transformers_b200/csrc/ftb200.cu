@@ -434,13 +434,13 @@ static int prepare_states(int mode, const void *x, const void *y, const int64_t 
     return rc;
 }
 
-// Tensor-core mode, fp32, M = 64 and a query / key width that is a multiple of 64 above 64 (the
-// Favor map gives D = 256): the score q_i . k_j is a sum over 64-wide feature blocks, so the
-// product is the sum of the products of the blocks, each of which the <float, 64, 64> kernels take
-// through pointers into the rows; the blocks after the first ADD to out (to grad_V), grad_Q and
-// grad_K are written block by block.  Returns the number of blocks, or 0.
+// Tensor-core mode, fp32, widths that are multiples of 64 with at least one of them above 64 (the
+// Favor map gives D = 256 for M = 64): served by the wide scans (wide_scan.cuh), which take the sum
+// over 64-wide feature blocks inside the tensor cores, one launch per 64 columns of the narrow side
+// and per group of four feature blocks.  Returns the number of feature blocks D / 64, or 0.
 static int wide_blocks(int mode, int dtype, int64_t D, int64_t M) {
-    if (mode != FTB_MODE_MMA || dtype != FTB_F32 || M != 64 || D <= 64 || D % 64) return 0;
+    if (mode != FTB_MODE_MMA || dtype != FTB_F32 || D < 64 || M < 64 || D % 64 || M % 64) return 0;
+    if (D == 64 && M == 64) return 0;
     return (int)(D / 64);
 }
 
@@ -467,8 +467,8 @@ static WidePlan wide_plan(int64_t BH, int64_t L, int nb, int64_t M) {
     mma::Plan m = mma::plan(BH, L, 1);
     w.pl.seg_len = m.seg_len;
     w.pl.nseg = m.nseg;
-    w.pl.dm = 64 * M;
-    w.sub = state_sub(FTB_MODE_MMA, w.pl, BH * nb);
+    w.pl.dm = 64 * 64;
+    w.sub = state_sub(FTB_MODE_MMA, w.pl, BH * nb * (M / 64));
     return w;
 }
 
@@ -890,12 +890,15 @@ static SegStates wide_describe(const WidePlan &w, const float *ws) {
 static int wide_launch(const float *a, const float *b, const float *c, float *out, const int64_t *as,
                        const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H, int64_t L,
                        int cnt, const WidePlan &w, const float *states, int sum_mode, int sub, int64_t state_blk,
-                       int reverse, int accumulate, bool after_own_launch, int kind, cudaStream_t st) {
+                       int64_t state_ld, int state_transposed, int reverse, int accumulate, bool after_own_launch,
+                       int kind, cudaStream_t st) {
     const int64_t blocks = N * H * w.pl.nseg;
     if (blocks <= 0) return FTB_OK;
     if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
     CUtensorMap ma, mb, mc;
     wide::Params p;
+    p.state_ld = state_ld;
+    p.state_transposed = state_transposed;
     int rc = mma::make_map(&ma, p.pos_a, a, N, H, L, 64 * cnt, as, FTB_F32);
     if (rc) return rc;
     if ((rc = mma::make_map(&mb, p.pos_b, b, N, H, L, 64 * cnt, bs, FTB_F32))) return rc;
@@ -979,33 +982,50 @@ static int wide_c_launch(const float *a, const float *b, const float *c, float *
     return FTB_OK;
 }
 
+// One scan that is wide on the a / b side, as launches of up to four feature blocks per 64 columns
+// of c / out: (a, b) rows of 64 na floats, c and out rows of 64 nc.  `states` as wide_states leaves
+// them ([64 na][64 nc] per block) -- or transposed ([64 nc][64 na]) for the scans whose a / b side
+// is the stored blocks' column side (grad_Q, grad_K).  `own`: whether the launch in front is one of
+// this call's (updated).
+static int wide_scan_ab(const float *a, const float *b, const float *c, float *out, const int64_t *as,
+                        const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H, int64_t L,
+                        int na, int nc, const WidePlan &w, const SegStates &ss, int64_t DM, int transposed,
+                        int reverse, int kind, bool *own, cudaStream_t st) {
+    const int64_t ld = transposed ? 64 * na : 64 * nc;     // row length of a stored block
+    for (int t = 0; t < nc; ++t)
+        for (int b0 = 0; b0 < na; b0 += wide::MAXNB) {
+            // a later group of feature blocks adds to what the one before wrote and waits for that
+            // whole grid; the first group of a column tile depends on nothing in front but totals
+            const int cnt = na - b0 < wide::MAXNB ? na - b0 : wide::MAXNB;
+            const float *st0 = nullptr;
+            if (ss.states)
+                st0 = transposed ? ss.states + (int64_t)64 * t * ld + 64 * b0 : ss.states + (int64_t)64 * b0 * ld + 64 * t;
+            int rc = wide_launch(a + 64 * b0, b + 64 * b0, c + 64 * t, out + 64 * t, as, bs, cs, os, N, H, L, cnt, w, st0,
+                                 ss.sum_mode, ss.sub, DM, ld, transposed, reverse, b0 > 0, b0 == 0 && *own, kind, st);
+            if (rc) return rc;
+            *own = true;
+        }
+    return FTB_OK;
+}
+
 static int wide_forward(const float *q, const float *k, const float *v, float *out, int64_t N, int64_t H,
-                        int64_t L, int nb, const int64_t *qs, const int64_t *ks, const int64_t *vs,
+                        int64_t L, int nb, int M, const int64_t *qs, const int64_t *ks, const int64_t *vs,
                         const int64_t *os, float *ws, cudaStream_t st) {
-    const int M = 64;
     const int64_t DM = (int64_t)64 * nb * M;
     const WidePlan w = wide_plan(N * H, L, nb, M);
     SegStates ss;
     int rc = wide_states(k, v, ks, vs, N, H, L, nb, M, w, ws, 0, st, &ss);
     if (rc) return rc;
-    for (int b0 = 0; b0 < nb; b0 += wide::MAXNB) {
-        // up to four feature blocks per launch; a later group adds to what the one before wrote
-        // and waits for that whole grid
-        const int cnt = nb - b0 < wide::MAXNB ? nb - b0 : wide::MAXNB;
-        rc = wide_launch(q + 64 * b0, k + 64 * b0, v, out, qs, ks, vs, os, N, H, L, cnt, w,
-                         ss.states ? ss.states + (int64_t)64 * b0 * M : nullptr, ss.sum_mode, ss.sub, DM, 0, b0 > 0,
-                         b0 == 0 && ss.fresh, FTB_KERNEL_MMA_FWD, st);
-        if (rc) return rc;
-    }
-    return FTB_OK;
+    bool own = ss.fresh != 0;
+    return wide_scan_ab(q, k, v, out, qs, ks, vs, os, N, H, L, nb, M / 64, w, ss, DM, 0, 0, FTB_KERNEL_MMA_FWD, &own, st);
 }
 
 static int wide_backward(const float *q, const float *k, const float *v, const float *g, float *gq, float *gk,
-                         float *gv, int64_t N, int64_t H, int64_t L, int nb, const int64_t *qs,
+                         float *gv, int64_t N, int64_t H, int64_t L, int nb, int M, const int64_t *qs,
                          const int64_t *ks, const int64_t *vs, const int64_t *gs, const int64_t *gqs,
                          const int64_t *gks, const int64_t *gvs, const float *forward_workspace, float *workspace,
                          size_t workspace_bytes, cudaStream_t st) {
-    const int M = 64, D = 64 * nb;
+    const int D = 64 * nb, mt = M / 64;
     const int64_t DM = (int64_t)D * M;
     const WidePlan w = wide_plan(N * H, L, nb, M);
     float *wsS = workspace;
@@ -1017,9 +1037,9 @@ static int wide_backward(const float *q, const float *k, const float *v, const f
         else if ((rc = wide_states(k, v, ks, vs, N, H, L, nb, M, w, wsS, 0, st, &sS))) return rc;
     }
     if ((gk || gv) && (rc = wide_states(q, g, qs, gs, N, H, L, nb, M, w, wsR, 1, st, &sR))) return rc;
-    // grad_Q and grad_K: wide on the c / out side -- scores and mask once per chunk, the column
-    // blocks of K (Q) streamed, up to four per launch (a single left-over block: the 64-wide scan)
     bool own = sS.fresh || sR.fresh;      // is the launch in front one of this call's?
+    // grad_Q: (grad_out, V, K) and grad_K: (V, grad_out, Q) walked downwards.  Their a / b side is
+    // the value side (64 mt wide), their c / out side the feature side (D wide).
     for (int which = 0; which < 2; ++which) {
         float *dst = which == 0 ? gq : gk;
         if (!dst) continue;
@@ -1027,6 +1047,17 @@ static int wide_backward(const float *q, const float *k, const float *v, const f
         const int64_t *as = which == 0 ? gs : vs, *bs = which == 0 ? vs : gs, *cs = which == 0 ? ks : qs;
         const int64_t *os = which == 0 ? gqs : gks;
         const SegStates &ss = which == 0 ? sS : sR;
+        if (mt > 1) {
+            // wide on both sides: the sum over the value blocks inside the tensor cores, one launch
+            // per 64 feature columns (the stored [D][M] blocks read transposed)
+            rc = wide_scan_ab(a, b, c, dst, as, bs, cs, os, N, H, L, mt, nb, w, ss, DM, 1, which, FTB_KERNEL_MMA_BWD,
+                              &own, st);
+            if (rc) return rc;
+            continue;
+        }
+        // 64 value columns: wide on the c / out side only -- scores and mask once per chunk, the
+        // column blocks of K (Q) streamed, up to four per launch (a single left-over block: the
+        // 64-wide scan)
         for (int b0 = 0; b0 < nb; b0 += wide::MAXNB) {
             const int cnt = nb - b0 < wide::MAXNB ? nb - b0 : wide::MAXNB;
             const float *st0 = ss.states ? ss.states + (int64_t)64 * b0 * M : nullptr;
@@ -1046,14 +1077,9 @@ static int wide_backward(const float *q, const float *k, const float *v, const f
             own = true;
         }
     }
-    // grad_V: the sum over the feature blocks, up to four per launch
-    for (int b0 = 0; gv && b0 < nb; b0 += wide::MAXNB) {
-        const int cnt = nb - b0 < wide::MAXNB ? nb - b0 : wide::MAXNB;
-        rc = wide_launch(k + 64 * b0, q + 64 * b0, g, gv, ks, qs, gs, gvs, N, H, L, cnt, w,
-                         sR.states ? sR.states + (int64_t)64 * b0 * M : nullptr, sR.sum_mode, sR.sub, DM, 1, b0 > 0,
-                         b0 == 0 && own, FTB_KERNEL_MMA_BWD, st);
-        if (rc) return rc;
-    }
+    // grad_V: (K, Q, grad_out) walked downwards: the sum over the feature blocks
+    if (gv)
+        return wide_scan_ab(k, q, g, gv, ks, qs, gs, gvs, N, H, L, nb, mt, w, sR, DM, 0, 1, FTB_KERNEL_MMA_BWD, &own, st);
     return FTB_OK;
 }
 
@@ -1082,7 +1108,7 @@ static int forward_impl(const void *q, const void *k, const void *v, void *out, 
         if (!q || !k || !v || !out || !qs || !ks || !vs || !os) return FTB_ERR_INVALID;
         const size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 0, 0);
         if (need && (!workspace || workspace_bytes < need)) return FTB_ERR_WORKSPACE;
-        return wide_forward((const float *)q, (const float *)k, (const float *)v, (float *)out, N, H, L, nb,
+        return wide_forward((const float *)q, (const float *)k, (const float *)v, (float *)out, N, H, L, nb, (int)M,
                             qs, ks, vs, os, (float *)workspace, (cudaStream_t)stream);
     }
     if (!qs || !ks || !vs || !os) return FTB_ERR_INVALID;
@@ -1203,7 +1229,7 @@ static int backward_impl(const void *q, const void *k, const void *v, const void
         const size_t need = ftb_causal_workspace_bytes(N, H, L, D, M, dtype, mode, 1, 0);
         if (need && (!workspace || workspace_bytes < need)) return FTB_ERR_WORKSPACE;
         return wide_backward((const float *)q, (const float *)k, (const float *)v, (const float *)g,
-                             (float *)gq, (float *)gk, (float *)gv, N, H, L, nb, qs, ks, vs, gs, gqs, gks, gvs,
+                             (float *)gq, (float *)gk, (float *)gv, N, H, L, nb, (int)M, qs, ks, vs, gs, gqs, gks, gvs,
                              (const float *)forward_workspace, (float *)workspace, need, (cudaStream_t)stream);
     }
     cudaStream_t st = (cudaStream_t)stream;

@@ -56,10 +56,13 @@ struct Params {
     int64_t seg_len;      // multiple of C
     int nseg;
     int nb;               // feature blocks (2 .. MAXNB)
-    const float *states;  // per (bh, seg) blocks of [64 nb][64] floats, or nullptr
+    const float *states;  // per (bh, seg) blocks [64 nb rows of a / b][columns of c] (see state_ld,
+                          // state_transposed), or nullptr
     int sum_mode;         // as mma::ScanParams
     int sub;
     int64_t state_blk;    // floats between consecutive (bh, seg) blocks
+    int64_t state_ld;     // floats between consecutive rows of a stored block (its full width)
+    int state_transposed; // the stored block holds [column of c][row of a / b] instead
     int reverse;
     int accumulate;       // add to what `out` holds
     int wait_first;       // programmatic launch: wait for the grid in front before any global access
@@ -427,12 +430,19 @@ wide_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         for (int e = 0; e < 32; ++e) acc[e] = 0.f;
                         if (srow_ok)
                             for (int sb = s_lo; sb < s_hi; ++sb) {
-                                const float4 *s4 = reinterpret_cast<const float4 *>(
-                                    p.states + ((int64_t)bh * per_head + sb) * p.state_blk + (int64_t)(64 * blk + srow) * 64 + 32 * cb);
+                                const float *src = p.states + ((int64_t)bh * per_head + sb) * p.state_blk;
+                                if (p.state_transposed) {
+                                    src += (int64_t)(32 * cb) * p.state_ld + 64 * blk + srow;
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) {
-                                    const float4 x = s4[e];
-                                    acc[4 * e] += x.x; acc[4 * e + 1] += x.y; acc[4 * e + 2] += x.z; acc[4 * e + 3] += x.w;
+                                    for (int e = 0; e < 32; ++e) acc[e] += src[e * p.state_ld];
+                                } else {
+                                    const float4 *s4 = reinterpret_cast<const float4 *>(
+                                        src + (int64_t)(64 * blk + srow) * p.state_ld + 32 * cb);
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e) {
+                                        const float4 x = s4[e];
+                                        acc[4 * e] += x.x; acc[4 * e + 1] += x.y; acc[4 * e + 2] += x.z; acc[4 * e + 3] += x.w;
+                                    }
                                 }
                             }
 #pragma unroll

@@ -28,10 +28,10 @@
  *   - `mode` selects the arithmetic: FTB_MODE_FP32_SIMT (fp32 FMA on CUDA cores, any D, M
  *     up to 512) or FTB_MODE_MMA (tcgen05 tensor cores: TF32 operands for fp32 I/O, bf16
  *     operands for bf16 I/O, fp32 accumulation and fp32 running state).  FTB_MODE_MMA takes
- *     D = M = 64 (fp32, bf16) and D = M = 128 (bf16); and, for fp32 with M = 64, any D that is a
- *     multiple of 64 (256 random features of a 64-wide query, say): the sum over the 64-wide
- *     feature blocks is taken inside the tensor cores, up to four blocks per launch (no initial /
- *     final states or prepared workspaces for such shapes: FTB_ERR_UNSUPPORTED).
+ *     D = M = 64 (fp32, bf16) and D = M = 128 (bf16); and, for fp32, any D and M that are multiples
+ *     of 64 (256 random features of a 64-wide query, say, or 128-wide heads): the sums over 64-wide
+ *     feature blocks are then taken inside the tensor cores, up to four blocks per launch (no
+ *     initial / final states or prepared workspaces for such shapes: FTB_ERR_UNSUPPORTED).
  *     FTB_MODE_MMA_X3 (ftb_causal_dot_product, ftb_causal_dot_backward and the workspace query
  *     only; fp32, D = M = 64; no states or prepared workspaces) also runs on the tensor cores
  *     but keeps fp32 accuracy: every operand is split into a TF32-exact high part and a low part

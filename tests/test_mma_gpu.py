@@ -370,3 +370,35 @@ def test_normaliser_applied_in_the_epilogue(dtype, D):
     assert e.value.status == _native.ERR_UNSUPPORTED
     with pytest.raises(RuntimeError):
         causal_dot_product_cuda(Qd, Kd, Vd, scaled, "mma", row_den=den.double(), eps=eps)
+
+
+@pytest.mark.parametrize("D,M,L,H", [(64, 128, 700, 3), (128, 128, 1500, 2), (192, 128, 900, 2), (128, 192, 640, 3),
+                                     (320, 128, 400, 1), (64, 320, 300, 2)])
+def test_fp32_widths_that_are_multiples_of_64(D, M, L, H):
+    """fp32 tensors in tensor-core mode with any query / value widths that are multiples of 64: the
+    sums over 64-wide feature blocks (of the queries for out and grad_V, of the values for grad_Q and
+    grad_K) are taken inside the tensor cores, one launch per 64 columns of the other side and per
+    group of four blocks.  Outputs hold NaN on entry; with and without the forward's workspace."""
+    g = torch.Generator().manual_seed(D * 7 + M)
+    N = 2
+    Q, K = (torch.rand(N, H, L, D, generator=g) * 0.5 for _ in range(2))
+    V, G = (torch.randn(N, H, L, M, generator=g) for _ in range(2))
+    Qd, Kd, Vd, Gd = (t.cuda() for t in (Q, K, V, G))
+    out = torch.full((N, H, L, M), float("nan"), device="cuda")
+    kept = []
+    causal_dot_product_cuda(Qd, Kd, Vd, out, "mma", keep_workspace=kept)
+    grads = [torch.full_like(t, float("nan")) for t in (Qd, Kd, Vd)]
+    causal_dot_backward_cuda(Qd, Kd, Vd, Gd, *grads, "mma", forward_workspace=kept[0])
+    want = oracle(Q, K, V, G)
+    for name, a, b in zip(NAMES, [out] + grads, want):
+        assert orc.rel_err(a, b) < TOL, name
+    again = [torch.full_like(t, float("nan")) for t in (Qd, Kd, Vd)]
+    causal_dot_backward_cuda(Qd, Kd, Vd, Gd, *again, "mma")
+    for a, b in zip(grads, again):
+        assert torch.equal(a, b)
+    # through autograd as well
+    q, k, v = (t.clone().requires_grad_(True) for t in (Qd, Kd, Vd))
+    with ftb.mode("mma"):
+        causal_dot_product(q, k, v).backward(Gd)
+    for a, b in zip(grads, (q.grad, k.grad, v.grad)):
+        assert torch.equal(a, b)
