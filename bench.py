@@ -79,33 +79,55 @@ def workload_name(cfg, shape):
 # clocks
 # ------------------------------------------------------------------------------------------
 class ClockSampler:
+    """nvidia-smi polled every 100 ms in a child process while the timed region runs.  A region of a
+    few milliseconds is over before the first sample arrives: `keep_loaded` then repeats the same
+    work, untimed, until a few samples have been taken under that load."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.proc = None
+        self.proc, self.lines = None, []
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
                  "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, bufsize=1)
         except OSError:
             self.proc = None
+            return
+        import threading
+        self.reader = threading.Thread(target=self._read, daemon=True)
+        self.reader.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line)
+
+    def samples(self):
+        return sum(1 for line in list(self.lines) if len(line.split(",")) >= 7)
+
+    def keep_loaded(self, work, want=3, budget_s=2.0):
+        """Run `work()` (the timed region's own launches, untimed now) until `want` samples exist."""
+        if self.proc is None:
+            return
+        t0 = time.time()
+        while self.samples() < want and time.time() - t0 < budget_s:
+            work()
+            torch.cuda.synchronize()
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-            out, _ = self.proc.communicate()
+        self.reader.join(timeout=5)
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
+        for line in list(self.lines):
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -384,6 +406,7 @@ def run_recurrent(args):
         graph.replay()
     e1.record()
     torch.cuda.synchronize()
+    sampler.keep_loaded(graph.replay)
     clocks = sampler.stop()
     ms_step = e0.elapsed_time(e1) / (args.steps * per_graph)
     launches = args.steps * per_graph
@@ -843,6 +866,10 @@ def main():
     launches = (launches_per_step * args.steps if graph is not None
                 else lib.ftb_launch_count() - launches0)
     barrier()
+    if sampler and not seq_parallel:
+        # (the timed region is a few milliseconds: the same launches go on, untimed, until the
+        # clock samples have been taken under their load)
+        sampler.keep_loaded((lambda: graph.replay()) if graph is not None else step)
     clocks = sampler.stop() if sampler else None
     # no kernel of the timed region gave up a bounded wait (a timed-out exchange leaves NaN
     # behind and a status word; the number would be meaningless)
