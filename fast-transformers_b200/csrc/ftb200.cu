@@ -454,6 +454,18 @@ static Plan x3_plan(int64_t BH, int64_t L) {
     return p;
 }
 
+// The state-only sweep of the split-operand mode runs on `sub` times finer segments where that
+// fills more SMs (a function of the shape alone: forward and backward agree on the layout).
+static int x3_sub(Plan pl, int64_t BH) {
+    if (pl.nseg < 2 || pl.nseg > mma::kSumInKernelMaxSegs) return 1;
+    const int64_t cps = pl.seg_len / mma::C;
+    for (int sub = 4; sub >= 2; --sub)
+        if (cps % sub == 0 && BH * (pl.nseg - 1) * sub <= (int64_t)mma::sm_count() * 13 / 12 &&
+            pl.nseg * sub <= mma::kSumInKernelMaxSegs)
+            return sub;
+    return 1;
+}
+
 // Segments of the wide form.  The scans that are wide on the a / b side walk all feature blocks of
 // a segment in one CTA, so the plan counts one CTA per (pair, segment); the scans that are wide on
 // the c side then run nb column tiles per segment side by side.  Whether the scans add up raw
@@ -671,7 +683,7 @@ size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, in
     if (mode == FTB_MODE_MMA_X3) {
         if (check_common(N, H, L, D, M, dtype, mode, true) != FTB_OK) return 0;
         const Plan pl = x3_plan(N * H, L);
-        const size_t one = align256((size_t)N * H * pl.nseg * 4096 * sizeof(float));
+        const size_t one = align256((size_t)N * H * pl.nseg * x3_sub(pl, N * H) * 4096 * sizeof(float));
         if (backward) return 2 * one;
         return pl.nseg > 1 ? one : 0;
     }
@@ -687,7 +699,7 @@ size_t ftb_causal_workspace_bytes(int64_t N, int64_t H, int64_t L, int64_t D, in
 // One scan (a, b, c) -> out, or, with a == nullptr, the state-only sweep of (b, c) -> state_out.
 static int x3_launch(const float *a, const float *b, const float *c, float *out, const int64_t *as,
                      const int64_t *bs, const int64_t *cs, const int64_t *os, int64_t N, int64_t H, int64_t L,
-                     Plan pl, const float *states, int sum_mode, float *state_out, int skip_lo, int skip_hi,
+                     Plan pl, const float *states, int sum_mode, int sub, float *state_out, int skip_lo, int skip_hi,
                      int canon_is_DaDc, int reverse, bool after_own_launch, int kind, cudaStream_t st) {
     const int64_t blocks = N * H * pl.nseg;
     if (blocks <= 0) return FTB_OK;
@@ -709,7 +721,7 @@ static int x3_launch(const float *a, const float *b, const float *c, float *out,
     p.so = a ? S3(os) : Strides3{0, 0, 0};
     p.H = (int)H; p.L = L;
     p.seg_len = pl.seg_len; p.nseg = pl.nseg;
-    p.states = states; p.sum_mode = sum_mode; p.state_out = state_out;
+    p.states = states; p.sum_mode = sum_mode; p.sub = sub < 1 ? 1 : sub; p.state_out = state_out;
     p.skip_lo = skip_lo; p.skip_hi = skip_hi;
     p.canon_is_DaDc = canon_is_DaDc; p.reverse = reverse; p.state_only = a ? 0 : 1;
     static const char *no_pdl = std::getenv("FTB200_NO_PDL");
@@ -736,25 +748,39 @@ static int x3_launch(const float *a, const float *b, const float *c, float *out,
     return FTB_OK;
 }
 
+// Where a split-operand scan finds its segment-start states.
+struct X3States {
+    const float *states = nullptr;
+    int sum_mode = 0;     // 1: raw totals, `sub` blocks per segment, added up by the scan
+    int sub = 1;
+};
+
+static X3States x3_describe(Plan pl, int64_t BH, const float *ws) {
+    X3States s;
+    if (pl.nseg == 1) return s;
+    s.states = ws;
+    s.sum_mode = pl.nseg <= mma::kSumInKernelMaxSegs ? 1 : 0;
+    s.sub = s.sum_mode ? x3_sub(pl, BH) : 1;
+    return s;
+}
+
 // Per-segment totals of sum x (x) y into `ws`, as what the scans read.
 static int x3_states(const float *x, const float *y, const int64_t *xs, const int64_t *ys, int64_t N, int64_t H,
                      int64_t L, Plan pl, float *ws, int reverse, bool after_own_launch, cudaStream_t st,
-                     const float **states, int *sum_mode) {
-    *states = nullptr;
-    *sum_mode = 0;
+                     X3States *out) {
+    *out = x3_describe(pl, N * H, ws);
     if (pl.nseg == 1) return FTB_OK;
-    const bool in_kernel = pl.nseg <= mma::kSumInKernelMaxSegs;   // the scan adds up raw totals itself
+    Plan fine = pl;
     int skip_lo = 0, skip_hi = 0;
-    if (in_kernel) {
-        skip_lo = reverse ? 0 : pl.nseg - 1;
-        skip_hi = skip_lo + 1;
+    if (out->sum_mode) {     // the scan adds up raw totals itself: the segment nobody reads from is skipped
+        fine.seg_len = pl.seg_len / out->sub;
+        fine.nseg = pl.nseg * out->sub;
+        skip_lo = reverse ? 0 : (pl.nseg - 1) * out->sub;
+        skip_hi = skip_lo + out->sub;
     }
-    int rc = x3_launch(nullptr, x, y, nullptr, nullptr, xs, ys, nullptr, N, H, L, pl, nullptr, 0, ws, skip_lo,
+    int rc = x3_launch(nullptr, x, y, nullptr, nullptr, xs, ys, nullptr, N, H, L, fine, nullptr, 0, 1, ws, skip_lo,
                        skip_hi, 1, 0, after_own_launch, FTB_KERNEL_MMA_STATE, st);
-    if (rc) return rc;
-    *states = ws;
-    *sum_mode = in_kernel ? 1 : 0;
-    if (in_kernel) return FTB_OK;
+    if (rc || out->sum_mode) return rc;
     return launch_prefix(ws, nullptr, nullptr, nullptr, N * H, pl.nseg, 4096, reverse, st);
 }
 
@@ -762,15 +788,14 @@ static int x3_forward(const float *q, const float *k, const float *v, float *out
                       const int64_t *qs, const int64_t *ks, const int64_t *vs, const int64_t *os, float *ws,
                       cudaStream_t st) {
     const Plan pl = x3_plan(N * H, L);
-    const float *states;
-    int sum_mode;
-    int rc = x3_states(k, v, ks, vs, N, H, L, pl, ws, 0, false, st, &states, &sum_mode);
+    X3States ss;
+    int rc = x3_states(k, v, ks, vs, N, H, L, pl, ws, 0, false, st, &ss);
     if (rc) return rc;
     // (behind a sweep of this call the scan waits only for the totals; a prefix launch in between
     // is not one of these kernels: then the scan waits for everything in front)
-    const bool own = states && sum_mode == 1;
-    return x3_launch(q, k, v, out, qs, ks, vs, os, N, H, L, pl, states, sum_mode, nullptr, 0, 0, 1, 0, own,
-                     FTB_KERNEL_MMA_FWD, st);
+    const bool own = ss.states && ss.sum_mode == 1;
+    return x3_launch(q, k, v, out, qs, ks, vs, os, N, H, L, pl, ss.states, ss.sum_mode, ss.sub, nullptr, 0, 0, 1, 0,
+                     own, FTB_KERNEL_MMA_FWD, st);
 }
 
 static int x3_backward(const float *q, const float *k, const float *v, const float *g, float *gq, float *gk,
@@ -780,16 +805,15 @@ static int x3_backward(const float *q, const float *k, const float *v, const flo
                        cudaStream_t st) {
     const Plan pl = x3_plan(N * H, L);
     float *wsS = workspace, *wsR = (float *)((char *)workspace + workspace_bytes / 2);
-    const float *sS = nullptr, *sR = nullptr;
-    int mS = 0, mR = 0, rc;
+    X3States sS, sR;
+    int rc;
     bool own = false;      // is the launch in front one of this call's scan kernels?
     if (gq) {
         if (forward_workspace && pl.nseg > 1) {
-            sS = forward_workspace;
-            mS = pl.nseg <= mma::kSumInKernelMaxSegs ? 1 : 0;
+            sS = x3_describe(pl, N * H, forward_workspace);
         } else {
-            if ((rc = x3_states(k, v, ks, vs, N, H, L, pl, wsS, 0, false, st, &sS, &mS))) return rc;
-            own = sS && mS == 1;
+            if ((rc = x3_states(k, v, ks, vs, N, H, L, pl, wsS, 0, false, st, &sS))) return rc;
+            own = sS.states && sS.sum_mode == 1;
         }
     }
     // grad_K and grad_V over WHOLE sequences where that takes fewer chunk times than a sweep of
@@ -807,25 +831,25 @@ static int x3_backward(const float *q, const float *k, const float *v, const flo
         }
     }
     if ((gk || gv) && pl_kv.nseg > 1) {
-        if ((rc = x3_states(q, g, qs, gs, N, H, L, pl, wsR, 1, own, st, &sR, &mR))) return rc;
-        own = sR ? mR == 1 : own;
+        if ((rc = x3_states(q, g, qs, gs, N, H, L, pl, wsR, 1, own, st, &sR))) return rc;
+        own = sR.states ? sR.sum_mode == 1 : own;
     }
     // (a scan directly behind this call's own sweeps or scans waits only for the totals it reads:
     // everything else it reads is the caller's input)
     if (gq) {
-        if ((rc = x3_launch(g, v, k, gq, gs, vs, ks, gqs, N, H, L, pl, sS, mS, nullptr, 0, 0, 0, 0, own,
-                            FTB_KERNEL_MMA_BWD, st)))
+        if ((rc = x3_launch(g, v, k, gq, gs, vs, ks, gqs, N, H, L, pl, sS.states, sS.sum_mode, sS.sub, nullptr, 0, 0, 0,
+                            0, own, FTB_KERNEL_MMA_BWD, st)))
             return rc;
         own = true;
     }
     if (gk) {
-        if ((rc = x3_launch(v, g, q, gk, vs, gs, qs, gks, N, H, L, pl_kv, sR, mR, nullptr, 0, 0, 0, 1, own,
-                            FTB_KERNEL_MMA_BWD, st)))
+        if ((rc = x3_launch(v, g, q, gk, vs, gs, qs, gks, N, H, L, pl_kv, sR.states, sR.sum_mode, sR.sub, nullptr, 0, 0,
+                            0, 1, own, FTB_KERNEL_MMA_BWD, st)))
             return rc;
         own = true;
     }
-    if (gv && (rc = x3_launch(k, q, g, gv, ks, qs, gs, gvs, N, H, L, pl_kv, sR, mR, nullptr, 0, 0, 1, 1, own,
-                              FTB_KERNEL_MMA_BWD, st)))
+    if (gv && (rc = x3_launch(k, q, g, gv, ks, qs, gs, gvs, N, H, L, pl_kv, sR.states, sR.sum_mode, sR.sub, nullptr, 0,
+                              0, 1, 1, own, FTB_KERNEL_MMA_BWD, st)))
         return rc;
     return FTB_OK;
 }

@@ -54,6 +54,8 @@ struct Params {
     int nseg;
     const float *states;  // per (bh, seg) [64][64] blocks, or nullptr
     int sum_mode;         // 0: the block of a segment is its start state; 1: raw totals, summed here
+    int sub;              // sum_mode 1: `states` holds `sub` blocks per segment of this launch (the
+                          // sweep ran on `sub` times finer segments, to fill more SMs)
     float *state_out;     // state-only: per (bh, seg) totals
     int skip_lo, skip_hi; // state-only: segments whose totals nobody reads
     int canon_is_DaDc;    // stored blocks are [DA][Dc] (1) or [Dc][DA] (0)
@@ -411,17 +413,18 @@ x3_scan_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int e = 0; e < 64; ++e) stv[e] = 0.f;
             if (!p.state_only) {
                 // ---- segment-start state ------------------------------------------------------------
-                int s_lo = seg, s_hi = seg + 1;
+                int s_lo = seg, s_hi = seg + 1, per_head = p.nseg;
                 if (p.sum_mode) {
-                    s_lo = p.reverse ? seg + 1 : 0;
-                    s_hi = p.reverse ? p.nseg : seg;
+                    per_head = p.nseg * p.sub;
+                    s_lo = p.reverse ? (seg + 1) * p.sub : 0;
+                    s_hi = p.reverse ? per_head : seg * p.sub;
                 }
                 if (!p.states) s_hi = s_lo;
                 // the totals come from the launch in front (a sweep of this call): wait for it here
                 if (s_hi > s_lo) asm volatile("griddepcontrol.wait;" ::: "memory");
                 if (srow_ok)
                     for (int sb = s_lo; sb < s_hi; ++sb) {
-                        const float *src = p.states + ((int64_t)bh * p.nseg + sb) * 4096;
+                        const float *src = p.states + ((int64_t)bh * per_head + sb) * 4096;
                         if (p.canon_is_DaDc) {
                             const float4 *s4 = reinterpret_cast<const float4 *>(src + srow * 64);
 #pragma unroll
