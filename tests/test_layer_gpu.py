@@ -256,3 +256,27 @@ def test_native_favor_feature_map_against_the_reference(golden):
     (phi * T(g["w"]).cuda()).sum().backward()
     assert orc.rel_err(phi, T(g["phi"])) < 2e-2
     assert orc.rel_err(x.grad, T(g["gx"])) < 2e-2
+
+
+def test_layer_with_128_wide_fp32_heads_in_tensor_core_mode():
+    """fp32 tensors with 128-wide heads in tensor-core mode (the product through the wide scans,
+    the denominator through the streaming kernels): the fp64 layer output, and gradients that agree
+    with the fp32 mode's."""
+    import fast_transformers_b200 as ftb
+    g = torch.Generator().manual_seed(128)
+    N, L, H, E = 2, 520, 2, 128
+    q, k, v, w = (torch.randn(N, L, H, E, generator=g) for _ in range(4))
+    klen = torch.tensor([520, 301])
+    masks = (TriangularCausalMask(L, device="cuda"), LengthMask(torch.full((N,), L, device="cuda")),
+             LengthMask(klen.cuda(), max_len=L))
+    att = CausalLinearAttention(E)
+    res = {}
+    for mode in ("mma", "fp32"):
+        qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+        with ftb.mode(mode):
+            y = att(qd, kd, vd, *masks)
+            (y * w.cuda()).sum().backward()
+        res[mode] = (y.detach(), qd.grad, kd.grad, vd.grad)
+    assert orc.rel_err(res["mma"][0], orc.layer_forward(q, k, v, key_lengths=klen)) < 2e-2
+    for a, b in zip(res["mma"], res["fp32"]):
+        assert orc.rel_err(a, b.double()) < 2e-2
