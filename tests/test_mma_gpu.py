@@ -307,14 +307,17 @@ def test_kept_states_are_read_in_the_layout_they_were_written_in():
         assert orc.rel_err(a, b) < TOL, "(c) " + name
 
 
-@pytest.mark.parametrize("D,L,H", [(192, 900, 3), (128, 1300, 2), (256, 2500, 5), (320, 700, 2), (256, 128, 1)])
+@pytest.mark.parametrize("D,L,H", [(192, 900, 3), (128, 1300, 2), (256, 2500, 5), (320, 700, 2), (256, 128, 1),
+                                   (128, 40000, 1)])
 def test_wide_feature_products_are_summed_by_the_library(D, L, H):
     """D = 64 nb (two to five 64-wide feature blocks), M = 64, fp32, tensor-core mode: one native call
     per direction.  out and grad_V (wide on the query / key side) are summed over the blocks inside
     the tensor cores, up to four blocks per launch (D = 320: a second launch adds the fifth); they
     hold NaN on entry, so the first launch must replace.  grad_Q and grad_K (wide on the output
     side) stream up to four column blocks per launch past scores made once per chunk (D = 320: the
-    fifth block through the 64-wide scan).  A skipped gradient is honoured; states are refused."""
+    fifth block through the 64-wide scan).  One long sequence alone is cut into more segments than a
+    scan adds up itself (a prefix launch turns the totals into start states).  A skipped gradient is
+    honoured; states are refused."""
     g = torch.Generator().manual_seed(D + L)
     N, M = 1, 64
     Q, K = (torch.rand(N, H, L, D, generator=g) * 0.5 for _ in range(2))
