@@ -212,6 +212,15 @@ class Favor(RandomFourierFeatures):
                           "and the heads are flipped. The shape of the input is "
                           "{!r}.".format(x.shape))
 
+    def _omega_transposed(self):
+        """omega^T as the native forward reads it, made once per draw of omega (the buffer is
+        redrawn in place, which bumps its version counter)."""
+        key = (self.omega.data_ptr(), self.omega._version)
+        if getattr(self, "_omega_t_key", None) != key:
+            self._omega_t = self.omega.detach().t().contiguous()
+            self._omega_t_key = key
+        return self._omega_t
+
     def forward(self, x):
         from ..settings import get_mode
         if (not self.stabilize and x.is_cuda and x.dtype == torch.float32 and get_mode() == "mma"
@@ -219,7 +228,7 @@ class Favor(RandomFourierFeatures):
                 and self.omega.device == x.device and self.omega.dtype == torch.float32):
             # tensor-core mode: the whole map as one native pass (TF32 product, like that mode's
             # attention kernels); the reference's formulation below stays the fp32-mode path
-            return _FavorNative.apply(x, self.omega, float(self.softmax_temp))
+            return _FavorNative.apply(x, self.omega, float(self.softmax_temp), self._omega_transposed())
         x = x * sqrt(self.softmax_temp)
         norm_x_squared = torch.einsum("...d,...d->...", x, x).unsqueeze(-1)
         u = x.unsqueeze(-2).matmul(self.omega).squeeze(-2)
@@ -230,7 +239,7 @@ class Favor(RandomFourierFeatures):
         return torch.cat([torch.exp(u - offset), torch.exp(-u - offset)], dim=-1)
 
 
-def favor_features_raw(x, omega, softmax_temp):
+def favor_features_raw(x, omega, softmax_temp, omega_t=None):
     """``[exp(u - off), exp(-u - off)]`` with ``u = x temp^(1/2) omega``, ``off = |x|^2 temp / 2 +
     log(n) / 2`` (``fourier_features.py:218-243``) in one native pass: ``x`` (..., 64) float32 on
     CUDA, ``omega`` (64, n/2) with n/2 = 64 or 128.  No autograd."""
@@ -239,7 +248,8 @@ def favor_features_raw(x, omega, softmax_temp):
     xc = x.contiguous()
     half = omega.shape[1]
     rows = xc.numel() // xc.shape[-1]
-    omega_t = omega.t().contiguous()
+    if omega_t is None:
+        omega_t = omega.t().contiguous()
     out = torch.empty(xc.shape[:-1] + (2 * half,), device=xc.device, dtype=torch.float32)
     with torch.cuda.device(xc.device):
         st = _native.lib().ftb_favor_feature_map(
@@ -277,8 +287,8 @@ class _FavorNative(torch.autograd.Function):
     ``grad_x = temp^(1/2) * (grad_u omega^T) + temp * grad_off * x``."""
 
     @staticmethod
-    def forward(ctx, x, omega, softmax_temp):
-        phi = favor_features_raw(x, omega, softmax_temp)
+    def forward(ctx, x, omega, softmax_temp, omega_t=None):
+        phi = favor_features_raw(x, omega, softmax_temp, omega_t)
         ctx.save_for_backward(x, omega, phi)
         ctx.softmax_temp = softmax_temp
         return phi
@@ -288,9 +298,9 @@ class _FavorNative(torch.autograd.Function):
         x, omega, phi = ctx.saved_tensors
         half = omega.shape[1]
         if grad_phi.dtype == torch.float32 and grad_phi.is_cuda:
-            return favor_features_backward_raw(grad_phi, phi, x, omega, ctx.softmax_temp), None, None
+            return favor_features_backward_raw(grad_phi, phi, x, omega, ctx.softmax_temp), None, None, None
         gp = grad_phi * phi
         grad_u = gp[..., :half] - gp[..., half:]
         grad_off = -gp.sum(dim=-1, keepdim=True)
         grad_x = sqrt(ctx.softmax_temp) * grad_u.matmul(omega.t()) + ctx.softmax_temp * grad_off * x
-        return grad_x, None, None
+        return grad_x, None, None, None
