@@ -39,6 +39,16 @@ def test_workspace_query_is_a_pure_function(native_lib):
     b = native_lib.ftb_causal_workspace_bytes(8, 8, 4096, 64, 64, 0, 0, 1, 0)
     assert a == b and a > 0 and a % 256 == 0
     assert native_lib.ftb_causal_workspace_bytes(0, 8, 4096, 64, 64, 0, 0, 0, 0) == 0
+    ws = native_lib.ftb_causal_workspace_bytes
+    # tensor-core mode, wide fp32 shapes: whole [D][M] state blocks, forward one set, backward two
+    fwd, bwd = ws(4, 12, 16384, 256, 64, 0, _native.MODE_MMA, 0, 0), ws(4, 12, 16384, 256, 64, 0, _native.MODE_MMA, 1, 0)
+    assert fwd > 0 and fwd % (256 * 64 * 4) == 0 and bwd == 2 * fwd
+    assert ws(2, 2, 4096, 128, 128, 0, _native.MODE_MMA, 1, 0) % (128 * 128 * 4) == 0
+    # the split-operand mode: fp32 D = M = 64 only (0: nothing to allocate for a shape it refuses)
+    x3 = ws(8, 8, 4096, 64, 64, 0, _native.MODE_MMA_X3, 1, 0)
+    assert x3 > 0 and x3 % (2 * 64 * 64 * 4) == 0
+    assert ws(8, 8, 4096, 32, 32, 0, _native.MODE_MMA_X3, 1, 0) == 0
+    assert ws(8, 8, 4096, 64, 64, 1, _native.MODE_MMA_X3, 1, 0) == 0
 
 
 def test_cpu_tensors_are_rejected_loudly():
@@ -50,11 +60,16 @@ def test_cpu_tensors_are_rejected_loudly():
 
 
 def test_mode_setting():
-    assert ftb.get_mode() in ("fp32", "mma")
+    assert ftb.get_mode() in ("fp32", "mma", "tf32x3")
     before = ftb.get_mode()
     with ftb.mode("mma"):
         assert ftb.get_mode() == "mma"
     assert ftb.get_mode() == before
+    with ftb.mode("tf32x3"):
+        assert ftb.get_mode() == "tf32x3"
+        # the tier's name resolves to the split-operand kernels only where the caller says they apply
+        from fast_transformers_b200.causal_product import _mode_id
+        assert _mode_id(None, True) == _native.MODE_MMA_X3 and _mode_id(None) == _native.MODE_FP32_SIMT
     with pytest.raises(ValueError):
         ftb.set_mode("fp16")
 
