@@ -98,6 +98,21 @@ def make_inputs(config, trial=0, scale_L=None, scale_N=None, scale_H=None):
 
 
 # algorithmic work per token-head (each tensor touched once; multiply-add = 2 flop)
+WIDE_GOLDEN_SHAPES = ((128, 128), (256, 64), (64, 192))     # (D, M) of tests/golden/product_wide.npz
+WIDE_GOLDEN_ROWS = slice(3, None, 8)                        # the rows that fixture keeps
+
+
+def wide_golden_inputs(D, M, L=200):
+    """Inputs behind ``tests/golden/product_wide.npz`` for one (D, M): one (batch, head) pair of
+    ``L`` positions from numpy's legacy generator (stable across versions), so that the fixture
+    holds the reference's outputs only.  Returns Q, K (1, 1, L, D) and V, grad_out (1, 1, L, M)."""
+    import numpy as np
+    r = np.random.RandomState(1000 * D + M)
+    Q, K = (torch.from_numpy(r.rand(1, 1, L, D).astype(np.float32) * 0.5) for _ in range(2))
+    V, G = (torch.from_numpy(r.randn(1, 1, L, M).astype(np.float32)) for _ in range(2))
+    return Q, K, V, G
+
+
 def algorithmic_bytes(D, M, elem_bytes):
     return (6 * D + 5 * M) * elem_bytes
 

@@ -298,9 +298,31 @@ def favor_wide():
     print("favor64.npz", os.path.getsize(os.path.join(HERE, "favor64.npz")), "bytes")
 
 
+def product_wide():
+    """``product_wide.npz``: the reference's product and gradients for query / value widths that are
+    multiples of 64 above 64 (every eighth row from row 3 on, plus checksums of the whole tensors);
+    the inputs are ``fast_transformers_b200.workloads.wide_golden_inputs``."""
+    cp, cla, al, fm, masking, tr = import_reference()
+    from fast_transformers_b200 import workloads
+    torch.set_num_threads(1)
+    blob = {}
+    for D, M in workloads.WIDE_GOLDEN_SHAPES:
+        Q, K, V, G = workloads.wide_golden_inputs(D, M)
+        Qr, Kr, Vr = (t.clone().requires_grad_(True) for t in (Q, K, V))
+        out = cp.causal_dot_product(Qr, Kr, Vr)
+        out.backward(G)
+        for name, t in (("out", out), ("gQ", Qr.grad), ("gK", Kr.grad), ("gV", Vr.grad)):
+            blob["%s_%d_%d" % (name, D, M)] = np_(t[:, :, workloads.WIDE_GOLDEN_ROWS])
+            blob["sum_%s_%d_%d" % (name, D, M)] = np.array(t.double().sum().item())
+    np.savez_compressed(os.path.join(HERE, "product_wide.npz"), **blob)
+    print("product_wide.npz", os.path.getsize(os.path.join(HERE, "product_wide.npz")), "bytes")
+
+
 if __name__ == "__main__":
     if sys.argv[1:] == ["favor_wide"]:
         favor_wide()
+    elif sys.argv[1:] == ["product_wide"]:
+        product_wide()
     elif sys.argv[1:] == ["linear"]:
         linear()
     elif sys.argv[1:] == ["recurrent"]:
@@ -313,3 +335,4 @@ if __name__ == "__main__":
         recurrent_encoder()
         linear()
         favor_wide()
+        product_wide()

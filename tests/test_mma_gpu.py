@@ -405,3 +405,21 @@ def test_fp32_widths_that_are_multiples_of_64(D, M, L, H):
         causal_dot_product(q, k, v).backward(Gd)
     for a, b in zip(grads, (q.grad, k.grad, v.grad)):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("D,M", workloads.WIDE_GOLDEN_SHAPES)
+def test_wide_shapes_against_the_reference(golden, D, M):
+    """The reference's own outputs and gradients for widths that are multiples of 64 above 64
+    (fixture from its unmodified CPU kernel; sampled rows): tensor-core mode within 2e-2, fp32 mode
+    within 1e-5."""
+    g = golden("product_wide")
+    Q, K, V, G = workloads.wide_golden_inputs(D, M)
+    rows = workloads.WIDE_GOLDEN_ROWS
+    for mode, tol in (("mma", TOL), ("fp32", 1e-5)):
+        q, k, v = (t.cuda().requires_grad_(True) for t in (Q, K, V))
+        with ftb.mode(mode):
+            out = causal_dot_product(q, k, v)
+            out.backward(G.cuda())
+        for name, a in zip(NAMES, (out, q.grad, k.grad, v.grad)):
+            ref = torch.from_numpy(g["%s_%d_%d" % (name, D, M)])
+            assert orc.rel_err(a.detach().cpu()[:, :, rows], ref) < tol, (mode, name)

@@ -138,3 +138,20 @@ def test_unmasked_layer_restatement_matches_reference_golden(golden):
     assert (want - torch.from_numpy(g["y"]).double()).abs().max() < 1e-5
     # the recurrent cross-attention steps of the reference reproduce its batch form
     assert np.abs(g["step_y"] - g["y"]).max() < 1e-5
+
+
+@pytest.mark.parametrize("D,M", workloads.WIDE_GOLDEN_SHAPES)
+def test_wide_shapes_oracle_vs_reference(golden, D, M):
+    """Query / value widths that are multiples of 64 above 64 (the shapes the wide tensor-core scans
+    take): the sequential C port reproduces the reference's kernel bit for bit, the fp64 blocked
+    form agrees with it to fp32 accuracy, on the sampled rows and on the checksums."""
+    g = golden("product_wide")
+    Q, K, V, G = workloads.wide_golden_inputs(D, M)
+    rows = workloads.WIDE_GOLDEN_ROWS
+    port = (orc.c_forward(Q, K, V),) + tuple(orc.c_backward(Q, K, V, G))
+    f64 = (orc.chunked_forward(Q, K, V, chunk=64),) + tuple(orc.chunked_backward(Q, K, V, G, chunk=64))
+    for name, c, x in zip(("out", "gQ", "gK", "gV"), port, f64):
+        ref = T(g["%s_%d_%d" % (name, D, M)])
+        assert torch.equal(c[:, :, rows], ref), name
+        assert orc.rel_err(ref, x[:, :, rows]) < 2e-6, name
+        np.testing.assert_allclose(x.sum().item(), g["sum_%s_%d_%d" % (name, D, M)], rtol=1e-5, atol=1e-3)
