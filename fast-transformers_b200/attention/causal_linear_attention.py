@@ -95,9 +95,9 @@ class _FusedElu1CausalLinear(torch.autograd.Function):
         causal_dot_backward_cuda(Qp, Kp, Vp, grad_out.permute(0, 2, 1, 3), gQ.permute(0, 2, 1, 3),
                                  gK.permute(0, 2, 1, 3), gV.permute(0, 2, 1, 3), ctx.mode,
                                  forward_workspace=ctx.forward_workspace)
-        nq, nk = causal_normaliser_backward_raw(Qp, Kp, grad_den.permute(0, 2, 1))
-        gQ += nq.permute(0, 2, 1, 3)
-        gK += nk.permute(0, 2, 1, 3)
+        # the denominator's gradients join the product's in place
+        causal_normaliser_backward_raw(Qp, Kp, grad_den.permute(0, 2, 1),
+                                       add_to=(gQ.permute(0, 2, 1, 3), gK.permute(0, 2, 1, 3)))
         return (elu_plus_one_backward_raw(xq, gQ, None), elu_plus_one_backward_raw(xk, gK, w), gV,
                 None, None, None)
 

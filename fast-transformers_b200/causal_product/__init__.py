@@ -369,23 +369,32 @@ def causal_normaliser_raw(Q, K):
     return den
 
 
-def causal_normaliser_backward_raw(Q, K, grad_den, need_q=True, need_k=True):
+def causal_normaliser_backward_raw(Q, K, grad_den, need_q=True, need_k=True, add_to=None):
     """Gradients of ``causal_normaliser_raw``: ``gQ_l = g_l * sum_{j<=l} K_j``,
-    ``gK_j = sum_{l>=j} g_l * Q_l`` (either may be skipped), in the memory order of Q and K."""
+    ``gK_j = sum_{l>=j} g_l * Q_l`` (either may be skipped), in the memory order of Q and K.
+    ``add_to=(gQ, gK)``: the gradients are ADDED to these tensors (row-contiguous, of Q's and K's
+    shape and dtype; ``None`` skips one) instead of returned in new ones."""
     dev = Q.device
     dt = _dtype_id(Q)
     N, H, L, D = Q.shape
     q, k = _rowmajor(Q), _rowmajor(K)
     g = grad_den if grad_den.dtype == Q.dtype else grad_den.to(Q.dtype)
-    gq = _like(Q) if need_q else None
-    gk = _like(K) if need_k else None
+    if add_to is not None:
+        gq, gk = add_to
+        for t, like in ((gq, Q), (gk, K)):
+            if t is not None and (t.shape != like.shape or t.dtype != like.dtype or t.stride(3) != 1):
+                raise RuntimeError("add_to tensors must match Q / K in shape and dtype and be row-contiguous")
+    else:
+        gq = _like(Q) if need_q else None
+        gk = _like(K) if need_k else None
     if gq is None and gk is None:
         return None, None
     L_ = _native.lib()
+    fn = L_.ftb_causal_normaliser_backward_add if add_to is not None else L_.ftb_causal_normaliser_backward
     with torch.cuda.device(dev):
         nbytes = L_.ftb_causal_normaliser_workspace_bytes(N, H, L, D, 1)
         ws, nbytes = _workspace(nbytes, dev)
-        st = L_.ftb_causal_normaliser_backward(
+        st = fn(
             _ptr(q), _ptr(k), _ptr(g), _ptr(gq), _ptr(gk), N, H, L, D, _native.strides3(q),
             _native.strides3(k), _strides_nhl(g), _native.strides3(gq if gq is not None else q),
             _native.strides3(gk if gk is not None else k), dt, _ptr(ws), nbytes,

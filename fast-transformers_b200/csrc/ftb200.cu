@@ -1062,11 +1062,33 @@ int ftb_causal_normaliser(const void *q, const void *k, void *den, int64_t N, in
                             : norm_launch<__nv_bfloat16>(p, N * H, dtype, st);
 }
 
+static int normaliser_backward(const void *q, const void *k, const void *grad_den, void *gq, void *gk,
+                               int64_t N, int64_t H, int64_t L, int64_t D, const int64_t *qs,
+                               const int64_t *ks, const int64_t *gdens, const int64_t *gqs, const int64_t *gks,
+                               int dtype, void *workspace, size_t workspace_bytes, void *stream, int accumulate);
+
 int ftb_causal_normaliser_backward(const void *q, const void *k, const void *grad_den, void *gq,
                                    void *gk, int64_t N, int64_t H, int64_t L, int64_t D,
                                    const int64_t *qs, const int64_t *ks, const int64_t *gdens,
                                    const int64_t *gqs, const int64_t *gks, int dtype, void *workspace,
                                    size_t workspace_bytes, void *stream) {
+    return normaliser_backward(q, k, grad_den, gq, gk, N, H, L, D, qs, ks, gdens, gqs, gks, dtype, workspace,
+                               workspace_bytes, stream, 0);
+}
+
+int ftb_causal_normaliser_backward_add(const void *q, const void *k, const void *grad_den, void *gq,
+                                       void *gk, int64_t N, int64_t H, int64_t L, int64_t D,
+                                       const int64_t *qs, const int64_t *ks, const int64_t *gdens,
+                                       const int64_t *gqs, const int64_t *gks, int dtype, void *workspace,
+                                       size_t workspace_bytes, void *stream) {
+    return normaliser_backward(q, k, grad_den, gq, gk, N, H, L, D, qs, ks, gdens, gqs, gks, dtype, workspace,
+                               workspace_bytes, stream, 1);
+}
+
+static int normaliser_backward(const void *q, const void *k, const void *grad_den, void *gq, void *gk,
+                               int64_t N, int64_t H, int64_t L, int64_t D, const int64_t *qs,
+                               const int64_t *ks, const int64_t *gdens, const int64_t *gqs, const int64_t *gks,
+                               int dtype, void *workspace, size_t workspace_bytes, void *stream, int accumulate) {
     int rc = norm_check(N, H, L, D, dtype);
     if (rc) return rc;
     if (!qs || !ks || !gdens || !gqs || !gks) return FTB_ERR_INVALID;
@@ -1080,6 +1102,7 @@ int ftb_causal_normaliser_backward(const void *q, const void *k, const void *gra
     p.qs = Strides3n{qs[0], qs[1], qs[2]}; p.ks = Strides3n{ks[0], ks[1], ks[2]};
     p.gs = Strides3n{gdens[0], gdens[1], gdens[2]};
     p.H = (int)H; p.D = (int)D; p.L = L;
+    p.accumulate = accumulate;
     if (gq) {   // gQ_l = g_l * sum_{j<=l} K_j
         p.out = gq; p.os = Strides3n{gqs[0], gqs[1], gqs[2]};
         p.totals = (float *)workspace; p.mode = NORM_BWD_Q;

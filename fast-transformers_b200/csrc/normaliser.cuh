@@ -40,6 +40,7 @@ struct NormParams {
     float *totals;              // (N*H, nseg, D) fp32: per-segment sums of K rows (FWD, BWD_Q)
                                 // or of g * Q rows (BWD_K)
     int mode;
+    int accumulate;             // backward modes: add to what `out` holds instead of replacing it
 };
 
 // ---- per-segment totals ---------------------------------------------------------------------
@@ -161,7 +162,8 @@ norm_scan_kernel(const NormParams p) {
         } else {
             for (int e = t; e < rows * D; e += kNormThreads) {
                 const int r = e / D, d = e % D;
-                const float v = p.mode == NORM_BWD_Q ? sG[r] * sX[r * PD + d] : sX[r * PD + d];
+                float v = p.mode == NORM_BWD_Q ? sG[r] * sX[r * PD + d] : sX[r * PD + d];
+                if (p.accumulate) v += step_load(op + (row0 + r) * p.os.l + d);
                 step_store(op + (row0 + r) * p.os.l + d, v);
             }
         }
@@ -274,9 +276,13 @@ norm_stream_kernel(const NormParams p, int64_t ngroups) {
                 for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(gmask, acc, o);
                 if (gl == u) keep = acc;
             } else if (ok) {
-                const float4 v = mode == NORM_BWD_Q
-                                     ? make_float4(gx[u] * run.x, gx[u] * run.y, gx[u] * run.z, gx[u] * run.w)
-                                     : run;
+                float4 v = mode == NORM_BWD_Q
+                               ? make_float4(gx[u] * run.x, gx[u] * run.y, gx[u] * run.z, gx[u] * run.w)
+                               : run;
+                if (p.accumulate) {
+                    const float4 o = norm_load4(op + row[u] * p.os.l + d);
+                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
                 norm_store4(op + row[u] * p.os.l + d, v);
             }
         }

@@ -249,6 +249,17 @@ int ftb_causal_normaliser_backward(const void *q, const void *k, const void *gra
                                    size_t workspace_bytes, void *stream);
 
 /*
+ * The same, ADDED to what grad_q / grad_k hold (the layer's backward: the product's gradients are
+ * there already, the denominator's join them without a pass of their own).
+ */
+int ftb_causal_normaliser_backward_add(const void *q, const void *k, const void *grad_den,
+                                       void *grad_q, void *grad_k, int64_t N, int64_t H, int64_t L,
+                                       int64_t D, const int64_t *q_strides, const int64_t *k_strides,
+                                       const int64_t *grad_den_strides, const int64_t *grad_q_strides,
+                                       const int64_t *grad_k_strides, int dtype, void *workspace,
+                                       size_t workspace_bytes, void *stream);
+
+/*
  * The default feature map phi(x) = elu(x) + 1 (fast_transformers/feature_maps/base.py:71-73) with
  * the layer's key-length mask (fast_transformers/attention/causal_linear_attention.py:83) folded
  * in, and its gradient grad_x = grad_y * w * (x > 0 ? 1 : exp(x)).  x, y (grad_y, grad_x):

@@ -147,6 +147,26 @@ def test_native_normaliser_partial_gradients_and_limits():
     assert causal_normaliser(torch.rand(0, 2, 5, 4, device="cuda"), torch.rand(0, 2, 5, 4, device="cuda")).shape == (0, 2, 5)
 
 
+@pytest.mark.parametrize("D,L", [(64, 3000), (128, 700), (40, 333)])
+def test_native_normaliser_gradients_added_in_place(D, L):
+    """``add_to``: the denominator's gradients are added to tensors that hold other gradients already
+    (``ftb_causal_normaliser_backward_add``; the streaming kernels for D = 64 and 128, the tile kernel
+    for D = 40), in (N, L, H, D) storage; one of the two may be skipped."""
+    from fast_transformers_b200.causal_product import causal_normaliser_backward_raw
+    g = torch.Generator().manual_seed(D)
+    N, H = 2, 3
+    Q, K = (torch.rand(N, L, H, D, generator=g).cuda().permute(0, 2, 1, 3) for _ in range(2))
+    gden = torch.randn(N, L, H, generator=g).cuda().permute(0, 2, 1)
+    base_q, base_k = (torch.randn(N, L, H, D, generator=g).cuda().permute(0, 2, 1, 3) for _ in range(2))
+    nq, nk = causal_normaliser_backward_raw(Q, K, gden)
+    aq, ak = base_q.clone(memory_format=torch.preserve_format), base_k.clone(memory_format=torch.preserve_format)
+    causal_normaliser_backward_raw(Q, K, gden, add_to=(aq, ak))
+    assert torch.equal(aq, base_q + nq) and torch.equal(ak, base_k + nk)
+    only_k = base_k.clone(memory_format=torch.preserve_format)
+    causal_normaliser_backward_raw(Q, K, gden, add_to=(None, only_k))
+    assert torch.equal(only_k, ak)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_native_elu_feature_map_with_key_length_mask(dtype):
     """(elu(x) + 1) * mask and its gradient in one pass each, against torch in fp64
