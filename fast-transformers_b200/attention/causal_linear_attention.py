@@ -41,6 +41,31 @@ def causal_linear(Q, K, V):
 fused_node_enabled = True
 
 
+def _division_backward(gy, y, den, eps):
+    """``grad_out = grad_y * Z`` and ``grad_den = -Z * sum_m grad_y * y`` for ``Z = 1 / (den + eps)``;
+    ``gy``, ``y`` (N, L, H, M), ``den`` the (N, H, L) view of (N, L, H) storage.  One native pass for
+    contiguous fp32 rows of 16, 32, 64 or 128 values, the torch formulation otherwise."""
+    N, L, H, M = y.shape
+    den_nlh = den.permute(0, 2, 1)
+    if (y.dtype == torch.float32 and den.dtype == torch.float32 and M in (16, 32, 64, 128)
+            and y.is_contiguous() and den_nlh.is_contiguous() and y.numel() > 0):
+        import ctypes
+        from .. import _native
+        gy = gy.contiguous()
+        grad_out = torch.empty_like(y)
+        grad_den = torch.empty((N, L, H), device=y.device, dtype=torch.float32)
+        vp = ctypes.c_void_p
+        with torch.cuda.device(y.device):
+            st = _native.lib().ftb_normalised_output_grads(
+                vp(gy.data_ptr()), vp(y.data_ptr()), vp(den_nlh.data_ptr()), vp(grad_out.data_ptr()),
+                vp(grad_den.data_ptr()), N * L * H, M, float(eps),
+                vp(torch.cuda.current_stream(y.device).cuda_stream))
+        _native.check(st, "ftb_normalised_output_grads")
+        return grad_out, grad_den
+    Z = 1 / (den_nlh + eps)
+    return gy * Z[..., None], -(Z * (gy * y).sum(-1))
+
+
 class _FusedElu1CausalLinear(torch.autograd.Function):
     """The whole layer body for the default feature map as ONE autograd node:
 
@@ -87,10 +112,8 @@ class _FusedElu1CausalLinear(torch.autograd.Function):
         Q = elu_plus_one_forward_raw(xq, None)
         K = elu_plus_one_forward_raw(xk, w)
         Qp, Kp, Vp = Q.permute(0, 2, 1, 3), K.permute(0, 2, 1, 3), values.permute(0, 2, 1, 3)
-        Z = 1 / (den.permute(0, 2, 1) + ctx.eps)                     # (N, L, H)
         gy = grad_y if grad_y.dtype == y.dtype else grad_y.to(y.dtype)
-        grad_den = -(Z * (gy * y).sum(-1))                           # (N, L, H)
-        grad_out = gy * Z[..., None]
+        grad_out, grad_den = _division_backward(gy, y, den, ctx.eps)   # (N, L, H, M), (N, L, H)
         gQ, gK, gV = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(values)
         causal_dot_backward_cuda(Qp, Kp, Vp, grad_out.permute(0, 2, 1, 3), gQ.permute(0, 2, 1, 3),
                                  gK.permute(0, 2, 1, 3), gV.permute(0, 2, 1, 3), ctx.mode,

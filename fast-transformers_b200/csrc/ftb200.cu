@@ -1119,6 +1119,28 @@ static int normaliser_backward(const void *q, const void *k, const void *grad_de
     return rc;
 }
 
+int ftb_normalised_output_grads(const float *grad_y, const float *y, const float *den, float *grad_out,
+                                float *grad_den, int64_t rows, int64_t M, float eps, void *stream) {
+    if (rows < 0 || M <= 0) return FTB_ERR_INVALID;
+    if (M != 16 && M != 32 && M != 64 && M != 128) return FTB_ERR_UNSUPPORTED;
+    if (rows == 0) return FTB_OK;
+    if (!grad_y || !y || !den || !grad_out || !grad_den) return FTB_ERR_INVALID;
+    if ((((uintptr_t)grad_y | (uintptr_t)y | (uintptr_t)grad_out) & 15) != 0) return FTB_ERR_ALIGNMENT;
+    const int lpr = (int)(M / 4);
+    const int64_t blocks = (rows * lpr + 255) / 256;
+    if (blocks > 0x7fffffffLL) return FTB_ERR_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    LaunchScope scope(FTB_KERNEL_NORMALISER, st);
+    switch (lpr) {
+        case 4: normalised_grads_kernel<4><<<(unsigned)blocks, 256, 0, st>>>(grad_y, y, den, grad_out, grad_den, rows, eps); break;
+        case 8: normalised_grads_kernel<8><<<(unsigned)blocks, 256, 0, st>>>(grad_y, y, den, grad_out, grad_den, rows, eps); break;
+        case 16: normalised_grads_kernel<16><<<(unsigned)blocks, 256, 0, st>>>(grad_y, y, den, grad_out, grad_den, rows, eps); break;
+        default: normalised_grads_kernel<32><<<(unsigned)blocks, 256, 0, st>>>(grad_y, y, den, grad_out, grad_den, rows, eps); break;
+    }
+    FTB_CUDA(cudaGetLastError());
+    return FTB_OK;
+}
+
 // ---------------------------------------------------------------------------------------------
 // phi(x) = elu(x) + 1 with the key-length mask folded in, and its gradient.
 // ---------------------------------------------------------------------------------------------

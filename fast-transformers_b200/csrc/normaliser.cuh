@@ -292,4 +292,28 @@ norm_stream_kernel(const NormParams p, int64_t ngroups) {
     if (TOTALS) *reinterpret_cast<float4 *>(tot + (int64_t)seg * p.D) = run;
 }
 
+// ---- the layer's division, backward -----------------------------------------------------------
+// With y = out * Z, Z = 1 / (den + eps) per row (fast_transformers/attention/
+// causal_linear_attention.py:95-104):  grad_out = grad_y * Z,  grad_den = -Z * sum_m grad_y * y.
+// One pass over grad_y and y (rows of M = 4 * LPR fp32 values, contiguous), LPR lanes per row.
+template <int LPR>
+__global__ void __launch_bounds__(256)
+normalised_grads_kernel(const float *__restrict__ grad_y, const float *__restrict__ y,
+                        const float *__restrict__ den, float *__restrict__ grad_out,
+                        float *__restrict__ grad_den, int64_t rows, float eps) {
+    const int lane = threadIdx.x & 31, gl = lane % LPR;
+    const unsigned gmask = LPR == 32 ? 0xffffffffu : (((1u << LPR) - 1u) << (lane / LPR * LPR));
+    const int64_t row = ((int64_t)blockIdx.x * 256 + threadIdx.x) / LPR;
+    if (row >= rows) return;
+    const int64_t off = row * (4 * LPR) + 4 * gl;
+    const float4 g = *reinterpret_cast<const float4 *>(grad_y + off);
+    const float4 v = *reinterpret_cast<const float4 *>(y + off);
+    const float z = 1.f / (den[row] + eps);
+    float s = g.x * v.x + g.y * v.y + g.z * v.z + g.w * v.w;
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(gmask, s, o);
+    *reinterpret_cast<float4 *>(grad_out + off) = make_float4(g.x * z, g.y * z, g.z * z, g.w * z);
+    if (gl == 0) grad_den[row] = -z * s;
+}
+
 }  // namespace ftb

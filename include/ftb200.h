@@ -260,6 +260,16 @@ int ftb_causal_normaliser_backward_add(const void *q, const void *k, const void 
                                        size_t workspace_bytes, void *stream);
 
 /*
+ * The layer's division, backward: with y = out * Z, Z = 1 / (den + eps) per row
+ * (fast_transformers/attention/causal_linear_attention.py:95-104),
+ *     grad_out = grad_y * Z        grad_den = -Z * sum_m grad_y * y
+ * in one pass.  grad_y, y, grad_out: `rows` contiguous rows of M fp32 values (M = 16, 32, 64 or 128;
+ * 16-byte aligned); den, grad_den: one fp32 value per row.
+ */
+int ftb_normalised_output_grads(const float *grad_y, const float *y, const float *den, float *grad_out,
+                                float *grad_den, int64_t rows, int64_t M, float eps, void *stream);
+
+/*
  * The default feature map phi(x) = elu(x) + 1 (fast_transformers/feature_maps/base.py:71-73) with
  * the layer's key-length mask (fast_transformers/attention/causal_linear_attention.py:83) folded
  * in, and its gradient grad_x = grad_y * w * (x > 0 ? 1 : exp(x)).  x, y (grad_y, grad_x):

@@ -147,6 +147,24 @@ def test_native_normaliser_partial_gradients_and_limits():
     assert causal_normaliser(torch.rand(0, 2, 5, 4, device="cuda"), torch.rand(0, 2, 5, 4, device="cuda")).shape == (0, 2, 5)
 
 
+@pytest.mark.parametrize("M", [16, 64, 128, 24])
+def test_division_backward_in_one_pass(M):
+    """``grad_out = grad_y Z`` and ``grad_den = -Z sum(grad_y y)`` for ``Z = 1 / (den + eps)`` from one
+    native pass (``ftb_normalised_output_grads``; M = 24 takes the torch formulation)."""
+    from fast_transformers_b200 import _native
+    from fast_transformers_b200.attention.causal_linear_attention import _division_backward
+    g = torch.Generator().manual_seed(M)
+    N, L, H, eps = 2, 333, 3, 1e-6
+    gy, y = (torch.randn(N, L, H, M, generator=g).cuda() for _ in range(2))
+    den = (torch.rand(N, L, H, generator=g) * 20 + 0.1).cuda().permute(0, 2, 1)      # (N, H, L) view
+    n0 = _native.lib().ftb_launch_count()
+    grad_out, grad_den = _division_backward(gy, y, den, eps)
+    assert _native.lib().ftb_launch_count() - n0 == (1 if M != 24 else 0)
+    Z = 1 / (den.permute(0, 2, 1).double() + eps)
+    assert orc.rel_err(grad_out, gy.double() * Z[..., None]) < 1e-6
+    assert orc.rel_err(grad_den, -(Z * (gy.double() * y.double()).sum(-1))) < 1e-6
+
+
 @pytest.mark.parametrize("D,L", [(64, 3000), (128, 700), (40, 333)])
 def test_native_normaliser_gradients_added_in_place(D, L):
     """``add_to``: the denominator's gradients are added to tensors that hold other gradients already
