@@ -4,14 +4,14 @@
 // mma_launch_batch, launch_prefix, LaunchScope, FTB_CUDA, WidePlan, wide_plan).
 #pragma once
 
-// ---- wide feature dimension (D = 64 nb, M = 64, fp32, tensor cores) ------------------------------
+// ---- wide widths (D = 64 nb, M = 64 mt, fp32, tensor cores) ------------------------------------
 // The states of a (pair, segment) are kept as one [D][M] block; feature block b is its rows
-// 64 b .. 64 b + 63.  What is wide on the c / out side (grad_Q, grad_K: c = K or Q, D columns) is
-// ONE scan whose nb column tiles sit next to each other in the grid, so that the narrow operands
-// (grad_out and V) come from HBM once and from L2 for the other tiles.  What is wide on the a / b
-// side (out, grad_V) is a sum over the feature blocks: nb scans, the later ones adding to the
-// result.  The state-only sweeps of the nb blocks share one grid, block by block, for the same
-// reason (V, grad_out read once).
+// 64 b .. 64 b + 63.  A scan that is wide on its a / b side (out and grad_V always; grad_Q and
+// grad_K when M > 64) takes the sum over the 64-wide blocks of that side inside the tensor cores
+// (wide_scan_kernel), up to four blocks per launch and one launch per 64 columns of its c side.
+// With M = 64, grad_Q and grad_K are wide on the c / out side only: scores and mask once per chunk,
+// the column blocks of K (Q) streamed (wide_c_scan_kernel).  The state-only sweeps of the feature
+// blocks share one grid, block by block, so that V (grad_out) is read once there as well.
 
 // Per-segment totals of sum x_b (x) y for every feature block b into `ws`; on return `ss`
 // describes them for a scan over feature block 0 (block b: states + 64 b M).
