@@ -11,9 +11,11 @@ with the reference's in-place signatures (``causal_product_cuda.cu:1471-1483``):
 Differences, all deliberate: there is no CPU entry (``dot["cpu"]`` is None and CPU tensors
 raise -- this package has no CPU path); kernels run on torch's current stream instead of
 the legacy default stream; outputs need not be zero on entry; bf16 tensors are accepted in
-addition to fp32 (bf16 in, bf16 out, fp32 state).  In ``"mma"`` mode a query / key width that is
-a multiple of 64 above 64 with M = 64 (the Favor map gives D = 256) is served by the library as
-a sum over 64-wide feature blocks (``ftb_causal_dot_product`` adds the blocks up in place).
+addition to fp32 (bf16 in, bf16 out, fp32 state).  In ``"mma"`` mode fp32 tensors may have any
+query / value widths that are multiples of 64 (the Favor map gives D = 256; 128-wide heads): the
+library takes the sums over 64-wide feature blocks inside the tensor cores.  The mode
+``"tf32x3"`` names the accuracy tier of ``"fp32"`` on the tensor cores (split operands; fp32 tensors
+with D = M = 64, everything else runs as ``"fp32"``).
 """
 import ctypes
 
