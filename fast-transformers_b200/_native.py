@@ -32,6 +32,7 @@ EXPORTS = (
     "ftb_linear_apply_state", "ftb_favor_feature_map", "ftb_recurrent_cross_linear_step",
     "ftb_causal_dot_product_normalised", "ftb_favor_feature_map_backward",
     "ftb_causal_normaliser_backward_add", "ftb_normalised_output_grads",
+    "ftb_causal_normaliser_backward_elu",
 )
 KERNEL_KINDS = ("state_sum", "state_prefix", "simt_scan", "mma_fwd", "mma_bwd", "mma_state",
                 "mma_bwd_qr", "mma_bwd_multi", "recurrent_step", "normaliser", "feature_map",
@@ -90,6 +91,9 @@ def lib():
     L.ftb_causal_normaliser_backward.restype = _int
     L.ftb_causal_normaliser_backward.argtypes = (
         [_vp] * 5 + [_i64] * 4 + [_i64p] * 5 + [_int, _vp, _sz, _vp])
+    L.ftb_causal_normaliser_backward_elu.restype = _int
+    L.ftb_causal_normaliser_backward_elu.argtypes = (
+        [_vp] * 8 + [_i64] * 4 + [_i64p] * 7 + [_int, _vp, _sz, _vp])
     L.ftb_normalised_output_grads.restype = _int
     L.ftb_normalised_output_grads.argtypes = [_vp] * 5 + [_i64, _i64, ctypes.c_float, _vp]
     L.ftb_causal_normaliser_backward_add.restype = _int

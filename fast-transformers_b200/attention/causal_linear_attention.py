@@ -21,6 +21,7 @@ from torch.nn import Module
 from ..attention_registry import (AttentionRegistry, Callable, EventDispatcherInstance, Int,
                                   Optional)
 from ..causal_product import (causal_dot_backward_cuda, causal_dot_product, causal_dot_product_cuda,
+                              causal_normaliser_backward_elu_raw,
                               causal_normaliser, causal_normaliser_backward_raw,
                               causal_normaliser_raw)
 from ..events import EventDispatcher
@@ -118,7 +119,12 @@ class _FusedElu1CausalLinear(torch.autograd.Function):
         causal_dot_backward_cuda(Qp, Kp, Vp, grad_out.permute(0, 2, 1, 3), gQ.permute(0, 2, 1, 3),
                                  gK.permute(0, 2, 1, 3), gV.permute(0, 2, 1, 3), ctx.mode,
                                  forward_workspace=ctx.forward_workspace)
-        # the denominator's gradients join the product's in place
+        # the denominator's gradients join the product's in place, and the sum goes through the
+        # feature map's derivative on its way back to memory
+        if causal_normaliser_backward_elu_raw(Qp, Kp, grad_den.permute(0, 2, 1), gQ.permute(0, 2, 1, 3),
+                                              gK.permute(0, 2, 1, 3), xq.permute(0, 2, 1, 3),
+                                              xk.permute(0, 2, 1, 3), w):
+            return gQ, gK, gV, None, None, None
         causal_normaliser_backward_raw(Qp, Kp, grad_den.permute(0, 2, 1),
                                        add_to=(gQ.permute(0, 2, 1, 3), gK.permute(0, 2, 1, 3)))
         return (elu_plus_one_backward_raw(xq, gQ, None), elu_plus_one_backward_raw(xk, gK, w), gV,

@@ -405,6 +405,37 @@ def causal_normaliser_backward_raw(Q, K, grad_den, need_q=True, need_k=True, add
     return gq, gk
 
 
+def causal_normaliser_backward_elu_raw(Q, K, grad_den, grad_q, grad_k, xq, xk, key_weights=None):
+    """In place: ``grad_q <- (grad_q + n_q) phi'(xq)``, ``grad_k <- (grad_k + n_k) w phi'(xk)`` with
+    ``n_q``, ``n_k`` the denominator's gradients (``causal_normaliser_backward_raw``),
+    ``phi(x) = elu(x) + 1`` and ``w`` the (N, L) key weights -- the tail of the layer's backward in two
+    launches (``ftb_causal_normaliser_backward_elu``).  All tensors (N, H, L, D) views with a
+    contiguous last dimension; returns False, with nothing changed, for shapes the kernels do not
+    take."""
+    dev = Q.device
+    dt = _dtype_id(Q)
+    N, H, L, D = Q.shape
+    ok = D in (16, 32, 64, 128)
+    for t in (Q, K, grad_q, grad_k, xq, xk):
+        ok = ok and t.shape == Q.shape and t.dtype == Q.dtype and t.stride(3) == 1 and \
+            all(s % 4 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0
+    if not ok:
+        return False
+    g = grad_den if grad_den.dtype == Q.dtype else grad_den.to(Q.dtype)
+    w = None if key_weights is None else key_weights.to(torch.float32).contiguous()
+    L_ = _native.lib()
+    with torch.cuda.device(dev):
+        nbytes = L_.ftb_causal_normaliser_workspace_bytes(N, H, L, D, 1)
+        ws, nbytes = _workspace(nbytes, dev)
+        st = L_.ftb_causal_normaliser_backward_elu(
+            _ptr(Q), _ptr(K), _ptr(g), _ptr(grad_q), _ptr(grad_k), _ptr(xq), _ptr(xk), _ptr(w), N, H, L, D,
+            _native.strides3(Q), _native.strides3(K), _strides_nhl(g), _native.strides3(grad_q),
+            _native.strides3(grad_k), _native.strides3(xq), _native.strides3(xk), dt, _ptr(ws), nbytes,
+            ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    _native.check(st, "ftb_causal_normaliser_backward_elu")
+    return True
+
+
 class CausalNormaliser(torch.autograd.Function):
     """``den[n,h,l] = Q[n,h,l] . sum_{j<=l} K[n,h,j]`` for (N, H, L, D) views: the denominator of
     the attention layer, which the reference computes as

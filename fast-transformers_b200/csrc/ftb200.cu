@@ -1062,10 +1062,17 @@ int ftb_causal_normaliser(const void *q, const void *k, void *den, int64_t N, in
                             : norm_launch<__nv_bfloat16>(p, N * H, dtype, st);
 }
 
+// (elu: raw inputs and the key mask of the layer's feature map, or nullptr; see NormParams::elu_x)
+struct NormElu {
+    const void *xq, *xk;
+    const int64_t *xqs, *xks;
+    const float *key_mask;
+};
 static int normaliser_backward(const void *q, const void *k, const void *grad_den, void *gq, void *gk,
                                int64_t N, int64_t H, int64_t L, int64_t D, const int64_t *qs,
                                const int64_t *ks, const int64_t *gdens, const int64_t *gqs, const int64_t *gks,
-                               int dtype, void *workspace, size_t workspace_bytes, void *stream, int accumulate);
+                               int dtype, void *workspace, size_t workspace_bytes, void *stream, int accumulate,
+                               const NormElu *elu = nullptr);
 
 int ftb_causal_normaliser_backward(const void *q, const void *k, const void *grad_den, void *gq,
                                    void *gk, int64_t N, int64_t H, int64_t L, int64_t D,
@@ -1085,10 +1092,23 @@ int ftb_causal_normaliser_backward_add(const void *q, const void *k, const void 
                                workspace_bytes, stream, 1);
 }
 
+int ftb_causal_normaliser_backward_elu(const void *q, const void *k, const void *grad_den, void *gq,
+                                       void *gk, const void *xq, const void *xk, const float *key_mask,
+                                       int64_t N, int64_t H, int64_t L, int64_t D, const int64_t *qs,
+                                       const int64_t *ks, const int64_t *gdens, const int64_t *gqs,
+                                       const int64_t *gks, const int64_t *xqs, const int64_t *xks, int dtype,
+                                       void *workspace, size_t workspace_bytes, void *stream) {
+    if ((gq && (!xq || !xqs)) || (gk && (!xk || !xks))) return FTB_ERR_INVALID;
+    NormElu elu{xq, xk, xqs, xks, key_mask};
+    return normaliser_backward(q, k, grad_den, gq, gk, N, H, L, D, qs, ks, gdens, gqs, gks, dtype, workspace,
+                               workspace_bytes, stream, 1, &elu);
+}
+
 static int normaliser_backward(const void *q, const void *k, const void *grad_den, void *gq, void *gk,
                                int64_t N, int64_t H, int64_t L, int64_t D, const int64_t *qs,
                                const int64_t *ks, const int64_t *gdens, const int64_t *gqs, const int64_t *gks,
-                               int dtype, void *workspace, size_t workspace_bytes, void *stream, int accumulate) {
+                               int dtype, void *workspace, size_t workspace_bytes, void *stream, int accumulate,
+                               const NormElu *elu) {
     int rc = norm_check(N, H, L, D, dtype);
     if (rc) return rc;
     if (!qs || !ks || !gdens || !gqs || !gks) return FTB_ERR_INVALID;
@@ -1103,8 +1123,22 @@ static int normaliser_backward(const void *q, const void *k, const void *grad_de
     p.gs = Strides3n{gdens[0], gdens[1], gdens[2]};
     p.H = (int)H; p.D = (int)D; p.L = L;
     p.accumulate = accumulate;
+    auto with_elu = [&](const void *x, const int64_t *xs, const float *mask) -> int {
+        p.elu_x = nullptr;
+        p.elu_mask = nullptr;
+        if (!elu) return FTB_OK;
+        p.elu_x = x;
+        p.xs = Strides3n{xs[0], xs[1], xs[2]};
+        p.elu_mask = mask;
+        // only the streaming kernels take the feature map's factor
+        const uintptr_t a = dtype == FTB_F32 ? 15 : 7;
+        if (!norm_fast_ok(p, dtype, true) || ((uintptr_t)x & a) || xs[0] % 4 || xs[1] % 4 || xs[2] % 4)
+            return FTB_ERR_UNSUPPORTED;
+        return FTB_OK;
+    };
     if (gq) {   // gQ_l = g_l * sum_{j<=l} K_j
         p.out = gq; p.os = Strides3n{gqs[0], gqs[1], gqs[2]};
+        if ((rc = with_elu(elu ? elu->xq : nullptr, elu ? elu->xqs : nullptr, nullptr))) return rc;
         p.totals = (float *)workspace; p.mode = NORM_BWD_Q;
         rc = dtype == FTB_F32 ? norm_launch<float>(p, N * H, dtype, st)
                               : norm_launch<__nv_bfloat16>(p, N * H, dtype, st);
@@ -1112,6 +1146,8 @@ static int normaliser_backward(const void *q, const void *k, const void *grad_de
     }
     if (gk) {   // gK_j = sum_{l>=j} g_l * Q_l
         p.out = gk; p.os = Strides3n{gks[0], gks[1], gks[2]};
+        if ((rc = with_elu(elu ? elu->xk : nullptr, elu ? elu->xks : nullptr, elu ? elu->key_mask : nullptr)))
+            return rc;
         p.totals = (float *)((char *)workspace + need / 2); p.mode = NORM_BWD_K;
         rc = dtype == FTB_F32 ? norm_launch<float>(p, N * H, dtype, st)
                               : norm_launch<__nv_bfloat16>(p, N * H, dtype, st);

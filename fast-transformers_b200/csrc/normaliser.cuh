@@ -41,6 +41,9 @@ struct NormParams {
                                 // or of g * Q rows (BWD_K)
     int mode;
     int accumulate;             // backward modes: add to what `out` holds instead of replacing it
+    const void *elu_x;          // streaming backward kernels with `accumulate`: the sum is then taken
+    Strides3n xs;               // through phi(x) = elu(x) + 1 of this raw input (same shape as out) and
+    const float *elu_mask;      // a per-(batch, position) weight: out = (out + n) * w * phi'(x)
 };
 
 // ---- per-segment totals ---------------------------------------------------------------------
@@ -282,6 +285,15 @@ norm_stream_kernel(const NormParams p, int64_t ngroups) {
                 if (p.accumulate) {
                     const float4 o = norm_load4(op + row[u] * p.os.l + d);
                     v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                    if (p.elu_x) {
+                        const float4 xv = norm_load4(reinterpret_cast<const T *>(p.elu_x) + n * p.xs.n + h * p.xs.h +
+                                                     row[u] * p.xs.l + d);
+                        const float w = p.elu_mask ? p.elu_mask[n * p.L + row[u]] : 1.f;
+                        v.x *= w * (xv.x > 0.f ? 1.f : expf(xv.x));
+                        v.y *= w * (xv.y > 0.f ? 1.f : expf(xv.y));
+                        v.z *= w * (xv.z > 0.f ? 1.f : expf(xv.z));
+                        v.w *= w * (xv.w > 0.f ? 1.f : expf(xv.w));
+                    }
                 }
                 norm_store4(op + row[u] * p.os.l + d, v);
             }

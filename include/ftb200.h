@@ -260,6 +260,24 @@ int ftb_causal_normaliser_backward_add(const void *q, const void *k, const void 
                                        size_t workspace_bytes, void *stream);
 
 /*
+ * The same, with the layer's default feature map phi(x) = elu(x) + 1 (and the key-length weights
+ * w, one fp32 value per (batch, position), or NULL) taken along: with xq, xk the raw inputs of the
+ * map (same shapes as grad_q, grad_k; element strides {batch, head, position}),
+ *     grad_q <- (grad_q + n_q) * phi'(xq)        grad_k <- (grad_k + n_k) * w * phi'(xk)
+ * i.e. what fast_transformers/feature_maps/base.py:71-73 and attention/causal_linear_attention.py:83
+ * contribute to the backward, without a pass of their own.  D = 16, 32, 64 or 128 with 16-byte
+ * aligned rows (other shapes: FTB_ERR_UNSUPPORTED, nothing is changed).
+ */
+int ftb_causal_normaliser_backward_elu(const void *q, const void *k, const void *grad_den,
+                                       void *grad_q, void *grad_k, const void *xq, const void *xk,
+                                       const float *key_weights, int64_t N, int64_t H, int64_t L,
+                                       int64_t D, const int64_t *q_strides, const int64_t *k_strides,
+                                       const int64_t *grad_den_strides, const int64_t *grad_q_strides,
+                                       const int64_t *grad_k_strides, const int64_t *xq_strides,
+                                       const int64_t *xk_strides, int dtype, void *workspace,
+                                       size_t workspace_bytes, void *stream);
+
+/*
  * The layer's division, backward: with y = out * Z, Z = 1 / (den + eps) per row
  * (fast_transformers/attention/causal_linear_attention.py:95-104),
  *     grad_out = grad_y * Z        grad_den = -Z * sum_m grad_y * y

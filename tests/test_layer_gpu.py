@@ -147,6 +147,37 @@ def test_native_normaliser_partial_gradients_and_limits():
     assert causal_normaliser(torch.rand(0, 2, 5, 4, device="cuda"), torch.rand(0, 2, 5, 4, device="cuda")).shape == (0, 2, 5)
 
 
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 64), (torch.float32, 16), (torch.bfloat16, 128)])
+def test_normaliser_gradients_through_the_feature_map_in_place(dtype, D):
+    """``ftb_causal_normaliser_backward_elu``: (grad + n) * w * phi'(x) in place equals the
+    accumulating normaliser backward followed by the feature map's backward pass."""
+    from fast_transformers_b200.causal_product import (causal_normaliser_backward_elu_raw,
+                                                       causal_normaliser_backward_raw)
+    from fast_transformers_b200.feature_maps import elu_plus_one_backward_raw, elu_plus_one_forward_raw
+    g = torch.Generator().manual_seed(D)
+    N, L, H = 2, 700, 3
+    xq, xk = (torch.randn(N, L, H, D, generator=g).to(dtype).cuda() for _ in range(2))
+    w = (torch.arange(L)[None, :] < torch.tensor([L, 400])[:, None]).float().cuda()
+    Q, K = elu_plus_one_forward_raw(xq, None), elu_plus_one_forward_raw(xk, w)
+    gden = torch.randn(N, L, H, generator=g).cuda().permute(0, 2, 1)
+    base = [torch.randn(N, L, H, D, generator=g).to(dtype).cuda() for _ in range(2)]
+    P = lambda t: t.permute(0, 2, 1, 3)     # noqa: E731
+    want = [b.clone() for b in base]
+    causal_normaliser_backward_raw(P(Q), P(K), gden, add_to=(P(want[0]), P(want[1])))
+    want = [elu_plus_one_backward_raw(xq, want[0], None), elu_plus_one_backward_raw(xk, want[1], w)]
+    got = [b.clone() for b in base]
+    assert causal_normaliser_backward_elu_raw(P(Q), P(K), gden, P(got[0]), P(got[1]), P(xq), P(xk), w)
+    tol = 1e-6 if dtype == torch.float32 else 2e-2
+    for a, b in zip(got, want):
+        assert orc.rel_err(a, b.double()) < tol
+    # a width the streaming kernels do not take: refused, nothing changed
+    odd = [torch.randn(1, 5, 2, 24, device="cuda") for _ in range(6)]
+    keep = odd[2].clone()
+    assert not causal_normaliser_backward_elu_raw(P(odd[0]), P(odd[1]), torch.randn(1, 2, 5, device="cuda"),
+                                                  P(odd[2]), P(odd[3]), P(odd[4]), P(odd[5]))
+    assert torch.equal(odd[2], keep)
+
+
 @pytest.mark.parametrize("M", [16, 64, 128, 24])
 def test_division_backward_in_one_pass(M):
     """``grad_out = grad_y Z`` and ``grad_den = -Z sum(grad_y y)`` for ``Z = 1 / (den + eps)`` from one
